@@ -1,0 +1,25 @@
+"""Limits of one running engine, with the reference's names, defaults and checks
+(crates/core/src/lib.rs:146-187)."""
+from __future__ import annotations
+
+from dataclasses import dataclass
+
+from ..errors import InvalidRequest
+
+
+@dataclass
+class RuntimeConfig:
+    max_seq_len: int = 4096      # prompt + generated tokens of one request
+    page_size: int = 16          # tokens per cache page; a power of two, at most 256
+    prefill_budget: int = 512    # tokens of one step (decoded tokens and prompt portions)
+    max_running: int = 32        # requests that hold cache pages at the same time
+    max_waiting: int = 256       # requests queued before admission
+    prefix_cache: bool = False   # accepted for the reference's flag; sharing is not built
+
+    def validate(self) -> None:
+        limits = (self.max_seq_len, self.page_size, self.prefill_budget, self.max_running,
+                  self.max_waiting)
+        if any((not isinstance(v, int)) or v <= 0 for v in limits):
+            raise InvalidRequest("runtime limits must be positive")
+        if self.page_size & (self.page_size - 1) or self.page_size > 256:
+            raise InvalidRequest("page_size must be a power of two <= 256")

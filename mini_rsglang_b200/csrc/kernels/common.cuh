@@ -1,0 +1,50 @@
+// Shared helpers of the engine's CUDA kernels (sm_100a).
+#pragma once
+#include <cuda_bf16.h>
+#include <cuda_runtime.h>
+#include <math_constants.h>
+#include <stdint.h>
+
+typedef __nv_bfloat16 bf16;
+
+template <typename T> __device__ __forceinline__ float to_float(T x);
+template <> __device__ __forceinline__ float to_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ float to_float<bf16>(bf16 x) { return __bfloat162float(x); }
+
+template <typename T> __device__ __forceinline__ T from_float(float x);
+template <> __device__ __forceinline__ float from_float<float>(float x) { return x; }
+template <> __device__ __forceinline__ bf16 from_float<bf16>(float x) { return __float2bfloat16_rn(x); }
+
+__device__ __forceinline__ float warp_sum(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x += __shfl_xor_sync(0xffffffffu, x, o);
+    return x;
+}
+__device__ __forceinline__ float warp_max(float x) {
+#pragma unroll
+    for (int o = 16; o > 0; o >>= 1) x = fmaxf(x, __shfl_xor_sync(0xffffffffu, x, o));
+    return x;
+}
+
+// Sum over a block of up to 1024 threads; every thread gets the result.  `scratch` has 33 floats.
+__device__ __forceinline__ float block_sum(float x, float* scratch) {
+    const int lane = threadIdx.x & 31, warp = threadIdx.x >> 5, warps = (blockDim.x + 31) >> 5;
+    x = warp_sum(x);
+    __syncthreads();  // scratch may still be read from an earlier call
+    if (lane == 0) scratch[warp] = x;
+    __syncthreads();
+    if (warp == 0) {
+        float y = lane < warps ? scratch[lane] : 0.0f;
+        y = warp_sum(y);
+        if (lane == 0) scratch[32] = y;
+    }
+    __syncthreads();
+    return scratch[32];
+}
+
+// Every launcher returns the CUDA error code of its launch (0 = success).
+#define MRS_RETURN_LAUNCH_STATUS() return (int)cudaGetLastError()
+#define MRS_EXPORT extern "C" __attribute__((visibility("default")))
+
+// Status codes of the launchers' own argument checks (negative, so they cannot be CUDA codes).
+#define MRS_BAD_ARGUMENT (-2)

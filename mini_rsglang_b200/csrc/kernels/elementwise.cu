@@ -1,0 +1,235 @@
+// Embedding, residual-add + RMSNorm, per-head norm + rotary + cache write, SiLU-multiply.
+// Every kernel exists for float32 and bfloat16 activations; statistics, angles and the
+// residual stream are float32 in both.
+#include "common.cuh"
+
+// ---------------------------------------------------------------------------------------------
+// Embedding: residual[t, :] = float(table[ids[t], :])      (reference: ops.cu:15-18)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
+                             float* __restrict__ residual, int width) {
+    const int t = blockIdx.x;
+    const T* row = table + (size_t)ids[t] * width;
+    float* out = residual + (size_t)t * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) out[i] = to_float(row[i]);
+}
+
+MRS_EXPORT int mrs_embed(int is_bf16, const void* table, const int* ids, float* residual,
+                         int tokens, int width, void* stream) {
+    if (tokens <= 0) return 0;
+    const int threads = width >= 1024 ? 256 : 128;
+    if (is_bf16)
+        embed_kernel<bf16><<<tokens, threads, 0, (cudaStream_t)stream>>>((const bf16*)table, ids, residual, width);
+    else
+        embed_kernel<float><<<tokens, threads, 0, (cudaStream_t)stream>>>((const float*)table, ids, residual, width);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Residual add + RMSNorm                                   (reference: ops.cu:62-78)
+//   v = residual[src] (+ delta[src]);  if write_back: residual[src] = v
+//   out[r] = T(v * rsqrt(mean(v^2) + eps) * weight)
+// `rows` (optional) picks the source rows, so the last norm runs only where logits are wanted.
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                   const float* __restrict__ weight, float eps, T* __restrict__ out,
+                                   const int* __restrict__ rows, int width, int write_back) {
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* res = residual + src * width;
+    const T* del = delta ? delta + src * width : nullptr;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = res[i];
+        if (del) v += to_float(del[i]);
+        if (write_back && del) res[i] = v;
+        sum += v * v;
+    }
+    const float scale = rsqrtf(block_sum(sum, scratch) / (float)width + eps);
+    T* o = out + (size_t)r * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        float v = res[i];
+        if (del && !write_back) v += to_float(del[i]);
+        o[i] = from_float<T>(v * scale * weight[i]);
+    }
+}
+
+MRS_EXPORT int mrs_add_rmsnorm(int is_bf16, float* residual, const void* delta, const float* weight,
+                               float eps, void* out, const int* rows, int n_rows, int width,
+                               int write_back, void* stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (is_bf16)
+        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+            residual, (const bf16*)delta, weight, eps, (bf16*)out, rows, width, write_back);
+    else
+        add_rmsnorm_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+            residual, (const float*)delta, weight, eps, (float*)out, rows, width, write_back);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// Plain RMSNorm of activations of type T (no residual): out = T(x * rsqrt(mean(x^2)+eps) * w).
+template <typename T>
+__global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ weight, float eps,
+                               T* __restrict__ out, int width) {
+    __shared__ float scratch[33];
+    const T* row = x + (size_t)blockIdx.x * width;
+    float sum = 0.0f;
+    for (int i = threadIdx.x; i < width; i += blockDim.x) {
+        const float v = to_float(row[i]);
+        sum += v * v;
+    }
+    const float scale = rsqrtf(block_sum(sum, scratch) / (float)width + eps);
+    T* o = out + (size_t)blockIdx.x * width;
+    for (int i = threadIdx.x; i < width; i += blockDim.x)
+        o[i] = from_float<T>(to_float(row[i]) * scale * weight[i]);
+}
+
+MRS_EXPORT int mrs_rmsnorm(int is_bf16, const void* x, const float* weight, float eps, void* out,
+                           int n_rows, int width, void* stream) {
+    if (n_rows <= 0) return 0;
+    const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    if (is_bf16)
+        rmsnorm_kernel<bf16><<<n_rows, threads, 0, (cudaStream_t)stream>>>((const bf16*)x, weight, eps, (bf16*)out, width);
+    else
+        rmsnorm_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>((const float*)x, weight, eps, (float*)out, width);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------------------------
+// Per-head RMSNorm of q and k, rotary position encoding of q and k, and the write of k and v
+// into the paged cache, in one pass over the fused projection output.
+//   (reference: split_columns ops.cu:29-32, rms 66-78, rope 79-90, scatter 95-98)
+// qkv: [tokens, (nq + 2 nkv) * d]; q_out: [tokens, nq * d];
+// caches: [pages, nkv, page_size, d]; slots[t] = page * page_size + offset (or < 0: no write).
+// One warp per (token, head).  Norm weights and the frequency table are optional.
+// ---------------------------------------------------------------------------------------------
+#define MRS_MAX_HEAD_DIM 256
+
+template <typename T>
+__global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, T* __restrict__ q_out,
+                                          T* __restrict__ k_cache, T* __restrict__ v_cache,
+                                          const int* __restrict__ positions, const int* __restrict__ slots,
+                                          const float* __restrict__ q_norm, const float* __restrict__ k_norm,
+                                          float eps, const float* __restrict__ inv_freq,
+                                          int tokens, int nq, int nkv, int d, int page_size, int write_kv) {
+    __shared__ float stage[4][MRS_MAX_HEAD_DIM];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int heads = nq + 2 * nkv;
+    const long long unit = (long long)blockIdx.x * 4 + warp;
+    if (unit >= (long long)tokens * heads) return;
+    const int t = (int)(unit / heads), h = (int)(unit % heads);
+    const int kind = h < nq ? 0 : (h < nq + nkv ? 1 : 2);   // 0 q, 1 k, 2 v
+    if (kind != 0 && !write_kv) return;
+    const T* src = qkv + (size_t)t * heads * d + (size_t)h * d;
+    float x[MRS_MAX_HEAD_DIM / 32];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < MRS_MAX_HEAD_DIM / 32; ++i) {
+        const int e = lane + 32 * i;
+        x[i] = e < d ? to_float(src[e]) : 0.0f;
+        sum += x[i] * x[i];
+    }
+    const float* norm = kind == 0 ? q_norm : (kind == 1 ? k_norm : nullptr);
+    if (norm) {
+        const float scale = rsqrtf(warp_sum(sum) / (float)d + eps);
+#pragma unroll
+        for (int i = 0; i < MRS_MAX_HEAD_DIM / 32; ++i) {
+            const int e = lane + 32 * i;
+            if (e < d) x[i] = x[i] * scale * norm[e];
+        }
+    }
+    if (kind != 2 && inv_freq) {
+        const int half = d >> 1;
+        const float pos = (float)positions[t];
+#pragma unroll
+        for (int i = 0; i < MRS_MAX_HEAD_DIM / 32; ++i) {
+            const int e = lane + 32 * i;
+            if (e < d) stage[warp][e] = x[i];
+        }
+        __syncwarp();
+#pragma unroll
+        for (int i = 0; i < MRS_MAX_HEAD_DIM / 32; ++i) {
+            const int e = lane + 32 * i;
+            if (e < d) {
+                const int j = e < half ? e : e - half;
+                float s, c;
+                sincosf(pos * inv_freq[j], &s, &c);
+                const float partner = stage[warp][e < half ? e + half : e - half];
+                x[i] = e < half ? x[i] * c - partner * s : x[i] * c + partner * s;
+            }
+        }
+    }
+    T* dst;
+    if (kind == 0) {
+        dst = q_out + (size_t)t * nq * d + (size_t)h * d;
+    } else {
+        const int slot = slots[t];
+        if (slot < 0) return;
+        const int page = slot / page_size, off = slot % page_size;
+        const int g = kind == 1 ? h - nq : h - nq - nkv;
+        T* base = kind == 1 ? k_cache : v_cache;
+        dst = base + (((size_t)page * nkv + g) * page_size + off) * d;
+    }
+#pragma unroll
+    for (int i = 0; i < MRS_MAX_HEAD_DIM / 32; ++i) {
+        const int e = lane + 32 * i;
+        if (e < d) dst[e] = from_float<T>(x[i]);
+    }
+}
+
+MRS_EXPORT int mrs_qk_norm_rope_store(int is_bf16, const void* qkv, void* q_out, void* k_cache, void* v_cache,
+                                      const int* positions, const int* slots, const float* q_norm,
+                                      const float* k_norm, float eps, const float* inv_freq, int tokens,
+                                      int nq, int nkv, int d, int page_size, int write_kv, void* stream) {
+    if (tokens <= 0) return 0;
+    if (d <= 0 || d > MRS_MAX_HEAD_DIM || (d & 1)) return MRS_BAD_ARGUMENT;
+    const long long units = (long long)tokens * (nq + 2 * nkv);
+    const unsigned blocks = (unsigned)((units + 3) / 4);
+    if (is_bf16)
+        qk_norm_rope_store_kernel<bf16><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+            (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots, q_norm, k_norm,
+            eps, inv_freq, tokens, nq, nkv, d, page_size, write_kv);
+    else
+        qk_norm_rope_store_kernel<float><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+            (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slots, q_norm, k_norm,
+            eps, inv_freq, tokens, nq, nkv, d, page_size, write_kv);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------------------------
+// SiLU-multiply over the fused gate/up projection: out[t, i] = silu(gu[t, i]) * gu[t, I + i]
+//   (reference: ops.cu:91-94)
+// ---------------------------------------------------------------------------------------------
+template <typename T>
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter) {
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / inter;
+        const int c = (int)(i % inter);
+        const float g = to_float(gate_up[t * 2 * inter + c]);
+        const float u = to_float(gate_up[t * 2 * inter + inter + c]);
+        out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
+    }
+}
+
+MRS_EXPORT int mrs_silu_mul(int is_bf16, const void* gate_up, void* out, int tokens, int inter, void* stream) {
+    const long long total = (long long)tokens * inter;
+    if (total <= 0) return 0;
+    const int threads = 256;
+    long long want = (total + threads - 1) / threads;
+    const unsigned blocks = (unsigned)(want > 148 * 16 ? 148 * 16 : want);
+    if (is_bf16)
+        silu_mul_kernel<bf16><<<blocks, threads, 0, (cudaStream_t)stream>>>((const bf16*)gate_up, (bf16*)out, total, inter);
+    else
+        silu_mul_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>((const float*)gate_up, (float*)out, total, inter);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+MRS_EXPORT const char* mrs_error_string(int code) {
+    if (code == MRS_BAD_ARGUMENT) return "kernel launcher refused its arguments (size outside what the kernel supports)";
+    return cudaGetErrorString((cudaError_t)code);
+}

@@ -1,0 +1,216 @@
+"""Python face of the engine's CUDA kernels.
+
+Every function checks its tensors (device, dtype, contiguity, sizes) on the host and then
+calls one `extern "C"` launcher of the in-tree kernel library with raw pointers and the
+current CUDA stream.  There is no other implementation behind these names: without a GPU,
+or without the compiled library, they raise `BackendError`."""
+from __future__ import annotations
+
+import ctypes
+import math
+
+import torch
+
+from .csrc.build import kernel_library
+from .errors import BackendError, InvalidRequest
+
+_c_int, _c_vp, _c_float = ctypes.c_int, ctypes.c_void_p, ctypes.c_float
+
+_SIGNATURES = {
+    "mrs_embed": [_c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_add_rmsnorm": [_c_int, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_rmsnorm": [_c_int, _c_vp, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_qk_norm_rope_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp,
+                               _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_silu_mul": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_attention_simt": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
+                           _c_int, _c_int, _c_float, _c_int, _c_vp],
+    "mrs_gemm_f32": [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_argmax": [_c_vp, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_sample": [_c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp],
+}
+
+_lib = None
+launch_count = 0   # launches of the engine's own kernels since import (read by the benchmark)
+
+
+def library() -> ctypes.CDLL:
+    global _lib
+    if _lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        lib = kernel_library()
+        for name, argtypes in _SIGNATURES.items():
+            fn = getattr(lib, name)
+            fn.argtypes = argtypes
+            fn.restype = _c_int
+        lib.mrs_error_string.argtypes = [_c_int]
+        lib.mrs_error_string.restype = ctypes.c_char_p
+        _lib = lib
+    return _lib
+
+
+def _stream() -> int:
+    return torch.cuda.current_stream().cuda_stream
+
+
+def _check(code: int, what: str) -> None:
+    global launch_count
+    launch_count += 1
+    if code != 0:
+        raise BackendError(f"{what}: {library().mrs_error_string(code).decode()} (code {code})")
+
+
+def _ptr(t: torch.Tensor | None) -> int | None:
+    return None if t is None else t.data_ptr()
+
+
+def _need(t: torch.Tensor, dtype, what: str, shape: tuple | None = None) -> None:
+    if not t.is_cuda:
+        raise BackendError(f"{what}: tensor is not on a CUDA device")
+    if dtype is not None and t.dtype != dtype:
+        raise InvalidRequest(f"{what}: dtype {t.dtype}, expected {dtype}")
+    if not t.is_contiguous():
+        raise InvalidRequest(f"{what}: tensor is not contiguous")
+    if shape is not None and tuple(t.shape) != tuple(shape):
+        raise InvalidRequest(f"{what}: shape {tuple(t.shape)}, expected {tuple(shape)}")
+
+
+def _is_bf16(dtype: torch.dtype) -> int:
+    if dtype is torch.bfloat16:
+        return 1
+    if dtype is torch.float32:
+        return 0
+    raise InvalidRequest(f"activations must be bfloat16 or float32, got {dtype}")
+
+
+def embed(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> None:
+    """residual[t, :] = float32(table[ids[t], :])."""
+    tokens, width = residual.shape
+    _need(table, None, "embed table")
+    _need(ids, torch.int32, "embed ids", (tokens,))
+    _need(residual, torch.float32, "embed output")
+    if table.shape[1] != width:
+        raise InvalidRequest("embed: width mismatch")
+    _check(library().mrs_embed(_is_bf16(table.dtype), table.data_ptr(), ids.data_ptr(), residual.data_ptr(),
+                               tokens, width, _stream()), "embed")
+
+
+def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,
+                out: torch.Tensor, rows: torch.Tensor | None = None, write_back: bool = True) -> None:
+    """v = residual (+ delta); residual = v when write_back; out = norm(v) * weight.
+    With `rows`, out[i] comes from source row rows[i]."""
+    n_rows, width = out.shape
+    _need(residual, torch.float32, "add_rmsnorm residual")
+    _need(weight, torch.float32, "add_rmsnorm weight", (width,))
+    _need(out, None, "add_rmsnorm out")
+    if residual.shape[1] != width:
+        raise InvalidRequest("add_rmsnorm: width mismatch")
+    if delta is not None:
+        _need(delta, out.dtype, "add_rmsnorm delta", tuple(residual.shape))
+    if rows is not None:
+        _need(rows, torch.int32, "add_rmsnorm rows", (n_rows,))
+    elif residual.shape[0] != n_rows:
+        raise InvalidRequest("add_rmsnorm: row count mismatch")
+    _check(library().mrs_add_rmsnorm(_is_bf16(out.dtype), residual.data_ptr(), _ptr(delta), weight.data_ptr(),
+                                     float(eps), out.data_ptr(), _ptr(rows), n_rows, width, int(write_back),
+                                     _stream()), "add_rmsnorm")
+
+
+def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor) -> None:
+    width = x.shape[-1]
+    _need(x, out.dtype, "rmsnorm input", tuple(out.shape))
+    _need(weight, torch.float32, "rmsnorm weight", (width,))
+    _need(out, None, "rmsnorm out")
+    _check(library().mrs_rmsnorm(_is_bf16(x.dtype), x.data_ptr(), weight.data_ptr(), float(eps), out.data_ptr(),
+                                 x.numel() // width, width, _stream()), "rmsnorm")
+
+
+def qk_norm_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
+                       v_cache: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor | None,
+                       q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
+                       inv_freq: torch.Tensor | None, nq: int, nkv: int, d: int, page_size: int) -> None:
+    """Per-head norm of q and k, rotary of q and k, q to `q_out`, k and v into the paged cache
+    ([pages, nkv, page_size, d]) at `slots`.  Without caches only q is produced."""
+    tokens = qkv.shape[0]
+    write_kv = k_cache is not None
+    _need(qkv, None, "qkv", (tokens, (nq + 2 * nkv) * d))
+    _need(q_out, qkv.dtype, "q_out", (tokens, nq * d))
+    _need(positions, torch.int32, "positions", (tokens,))
+    if write_kv:
+        _need(k_cache, qkv.dtype, "k cache")
+        _need(v_cache, qkv.dtype, "v cache", tuple(k_cache.shape))
+        if tuple(k_cache.shape[1:]) != (nkv, page_size, d):
+            raise InvalidRequest(f"cache shape {tuple(k_cache.shape)} does not match heads/page/head_dim")
+        _need(slots, torch.int32, "slots", (tokens,))
+    for w, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+        if w is not None:
+            _need(w, torch.float32, name, (d,))
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq", (d // 2,))
+    _check(library().mrs_qk_norm_rope_store(_is_bf16(qkv.dtype), qkv.data_ptr(), q_out.data_ptr(), _ptr(k_cache),
+                                            _ptr(v_cache), positions.data_ptr(), _ptr(slots), _ptr(q_norm),
+                                            _ptr(k_norm), float(eps), _ptr(inv_freq), tokens, nq, nkv, d,
+                                            page_size, int(write_kv), _stream()), "qk_norm_rope_store")
+
+
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+    tokens, inter = out.shape
+    _need(gate_up, out.dtype, "gate_up", (tokens, 2 * inter))
+    _need(out, None, "silu_mul out")
+    _check(library().mrs_silu_mul(_is_bf16(out.dtype), gate_up.data_ptr(), out.data_ptr(), tokens, inter, _stream()),
+           "silu_mul")
+
+
+def attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
+                   seq_of_token: torch.Tensor, block_table: torch.Tensor, out: torch.Tensor, nq: int, nkv: int,
+                   d: int, window: int = 0, scale: float | None = None) -> None:
+    """Causal paged attention; one warp per (token, head); any sizes; float32 or bfloat16."""
+    tokens = q.shape[0]
+    _need(q, None, "q", (tokens, nq * d))
+    _need(k_cache, q.dtype, "k cache")
+    _need(v_cache, q.dtype, "v cache", tuple(k_cache.shape))
+    _need(out, q.dtype, "attention out", (tokens, nq * d))
+    _need(positions, torch.int32, "positions", (tokens,))
+    _need(seq_of_token, torch.int32, "seq_of_token", (tokens,))
+    _need(block_table, torch.int32, "block_table")
+    page_size = k_cache.shape[2]
+    if tuple(k_cache.shape[1:]) != (nkv, page_size, d):
+        raise InvalidRequest("attention: cache shape does not match heads/head_dim")
+    _check(library().mrs_attention_simt(_is_bf16(q.dtype), q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(),
+                                        positions.data_ptr(), seq_of_token.data_ptr(), block_table.data_ptr(),
+                                        out.data_ptr(), tokens, nq, nkv, d, page_size, block_table.shape[1],
+                                        float(scale if scale is not None else 1.0 / math.sqrt(d)), int(window),
+                                        _stream()), "attention_simt")
+
+
+def gemm_f32(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] . weight[N, K]^T in true float32 (CUDA-core FMA)."""
+    m, k = x.shape
+    n = weight.shape[0]
+    _need(x, torch.float32, "gemm input")
+    _need(weight, torch.float32, "gemm weight", (n, k))
+    _need(out, torch.float32, "gemm out", (m, n))
+    _check(library().mrs_gemm_f32(x.data_ptr(), weight.data_ptr(), out.data_ptr(), m, n, k, _stream()), "gemm_f32")
+
+
+def argmax(logits: torch.Tensor, out: torch.Tensor) -> None:
+    rows, vocab = logits.shape
+    _need(logits, torch.float32, "logits")
+    _need(out, torch.int32, "argmax out", (rows,))
+    _check(library().mrs_argmax(logits.data_ptr(), out.data_ptr(), rows, vocab, _stream()), "argmax")
+
+
+def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor, top_p: torch.Tensor,
+           seed: torch.Tensor, draw_index: torch.Tensor, out: torch.Tensor) -> None:
+    rows, vocab = logits.shape
+    _need(logits, torch.float32, "logits")
+    _need(temperature, torch.float32, "temperature", (rows,))
+    _need(top_k, torch.int32, "top_k", (rows,))
+    _need(top_p, torch.float32, "top_p", (rows,))
+    _need(seed, torch.int64, "seed", (rows,))
+    _need(draw_index, torch.int32, "draw_index", (rows,))
+    _need(out, torch.int32, "sample out", (rows,))
+    _check(library().mrs_sample(logits.data_ptr(), rows, vocab, temperature.data_ptr(), top_k.data_ptr(),
+                                top_p.data_ptr(), seed.data_ptr(), draw_index.data_ptr(), out.data_ptr(),
+                                _stream()), "sample")

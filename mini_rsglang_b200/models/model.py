@@ -1,0 +1,63 @@
+"""A model built from a `ModelSpec`: parts with their tensors bound, run in the order the
+spec gives."""
+from __future__ import annotations
+
+import torch
+
+from ..parts.base import Runtime
+from .spec import ModelSpec
+
+
+class Model:
+    def __init__(self, spec: ModelSpec, tensors: dict[str, torch.Tensor], runtime: Runtime):
+        self.spec = spec
+        self.runtime = runtime
+        self.embedding, self.blocks, self.final_norm, self.head = spec.build_parts()
+        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+            part.bind(tensors, runtime)
+        # cache entry that each run of the order reads; runs that borrow a cache write nothing
+        self.cache_entry = [e.cache_of if e.cache_of is not None else i for i, e in enumerate(spec.run_order)]
+        self.writes_cache = [e.cache_of is None for e in spec.run_order]
+
+    def kv_needs(self):
+        return [self.blocks[e.layer].mixer.cache_need() if e.cache_of is None else None for e in self.spec.run_order]
+
+    def state_needs(self):
+        return [self.blocks[e.layer].mixer.state_need() if e.cache_of is None else None for e in self.spec.run_order]
+
+    def weight_bytes(self) -> int:
+        seen, total = set(), 0
+        for part in (self.embedding, *self.blocks, self.final_norm, self.head):
+            for t in _tensors_of(part):
+                if t.data_ptr() not in seen:
+                    seen.add(t.data_ptr())
+                    total += t.numel() * t.element_size()
+        return total
+
+    def forward(self, ctx, storage) -> torch.Tensor | None:
+        """Runs the step's tokens through every layer; float32 logits [wanted, vocab], or None
+        when no logits are wanted (the head is then skipped, as in the reference,
+        crates/engine/src/lib.rs:132-135)."""
+        stream = self.embedding.forward(ctx)
+        pending = None
+        for index, entry in enumerate(self.spec.run_order):
+            pending = self.blocks[entry.layer].forward(stream, pending, ctx, storage.entries[self.cache_entry[index]],
+                                                       self.writes_cache[index])
+        if ctx.want_rows is None:
+            return None
+        hidden = self.final_norm.add_norm(stream, pending, rows=ctx.want_rows, write_back=False)
+        return self.head.forward(hidden)
+
+
+def _tensors_of(part, seen=None):
+    out = []
+    seen = seen if seen is not None else set()
+    if id(part) in seen:
+        return out
+    seen.add(id(part))
+    for value in vars(part).values():
+        if isinstance(value, torch.Tensor):
+            out.append(value)
+        elif hasattr(value, "bind") and hasattr(value, "weight_specs"):
+            out += _tensors_of(value, seen)
+    return out

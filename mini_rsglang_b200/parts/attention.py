@@ -1,0 +1,83 @@
+"""Grouped-query attention over the paged cache, with optional per-head q/k norms and a
+position encoding (reference: crates/models/src/qwen3.rs:178-202).
+
+One projection gives q, k and v (the three matrices are concatenated by rows when bound);
+one kernel applies the head norms and the rotation and writes k and v into the cache pages;
+attention reads the cache through the request's block table; one projection brings the
+heads back to the model width."""
+from __future__ import annotations
+
+import torch
+
+from .. import kernels
+from ..errors import InvalidRequest
+from ..weights.spec import WeightSpec
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec
+from .linear import linear
+
+
+def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) -> None:
+    """Attention of this step's queries over their requests' cached keys and values."""
+    kernels.attention_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, ctx.block_tables[cache.group],
+                           out, nq, nkv, d, window)
+
+
+@MIXERS.register("gqa_attention")
+class GroupedQueryAttention(Mixer):
+    def __init__(self, prefix: str, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
+                 position: PartSpec, q_norm: PartSpec | None = None, k_norm: PartSpec | None = None,
+                 window: int = 0):
+        super().__init__(prefix)
+        if num_heads % num_kv_heads:
+            raise InvalidRequest("query heads must be a multiple of key/value heads")
+        if head_dim % 2 or head_dim > 256:
+            raise InvalidRequest(f"head_dim {head_dim} must be even and at most 256")
+        self.width, self.nq, self.nkv, self.d = int(width), int(num_heads), int(num_kv_heads), int(head_dim)
+        self.window = int(window)
+        self.position = POSITION_ENCODINGS.build(position, prefix)
+        self.q_norm = NORMS.build(q_norm, f"{prefix}.q_norm") if q_norm else None
+        self.k_norm = NORMS.build(k_norm, f"{prefix}.k_norm") if k_norm else None
+        for norm in (self.q_norm, self.k_norm):
+            if norm is not None and norm.width != self.d:
+                raise InvalidRequest("a head norm must have the head's width")
+        self.qkv = self.o = None
+
+    def weight_specs(self):
+        specs = [WeightSpec(self.name("q_proj.weight"), (self.nq * self.d, self.width)),
+                 WeightSpec(self.name("k_proj.weight"), (self.nkv * self.d, self.width)),
+                 WeightSpec(self.name("v_proj.weight"), (self.nkv * self.d, self.width)),
+                 WeightSpec(self.name("o_proj.weight"), (self.width, self.nq * self.d))]
+        for norm in (self.q_norm, self.k_norm):
+            if norm is not None:
+                specs += norm.weight_specs()
+        return specs
+
+    def cache_need(self):
+        return KVNeed(self.nkv, self.d, "window" if self.window else "full", self.window)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.qkv = torch.cat([tensors[self.name("q_proj.weight")], tensors[self.name("k_proj.weight")],
+                              tensors[self.name("v_proj.weight")]], dim=0).contiguous()
+        self.o = tensors[self.name("o_proj.weight")].contiguous()
+        self.position.bind(tensors, runtime)
+        for norm in (self.q_norm, self.k_norm):
+            if norm is not None:
+                norm.bind(tensors, runtime)
+        if (self.q_norm and self.k_norm and self.q_norm.eps != self.k_norm.eps):
+            raise InvalidRequest("q and k head norms must share one eps")
+
+    def forward(self, h, ctx, cache, write_cache=True):
+        tokens = h.shape[0]
+        qkv = linear(h, self.qkv)
+        q = torch.empty((tokens, self.nq * self.d), dtype=h.dtype, device=h.device)
+        eps = self.q_norm.eps if self.q_norm else (self.k_norm.eps if self.k_norm else 0.0)
+        group = cache.group
+        kernels.qk_norm_rope_store(
+            qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
+            ctx.slots[group] if write_cache else None,
+            self.q_norm.weight if self.q_norm else None, self.k_norm.weight if self.k_norm else None, eps,
+            self.position.tables()["inv_freq"], self.nq, self.nkv, self.d, cache.k.shape[2])
+        out = torch.empty_like(q)
+        paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
+        return linear(out, self.o)

@@ -1,0 +1,171 @@
+"""What a model is put together from, and the registries that name the kinds of each part.
+
+A model is data (`models/spec.py`): for every layer a block kind, two norms, a mixer and a
+feed-forward, each a `PartSpec` (kind + parameters), and a run order.  The classes behind
+the kinds are registered here.  A part gets its sizes and constants as parameters, declares
+the tensors it wants (`weight_specs`), what it needs of the cache (`cache_need`,
+`state_need`), takes its tensors (`bind`) and computes (`forward`).  No part knows which
+model it is in: a new architecture is new specs, and new parts only where it computes
+something new.
+
+Interfaces (all tensors on the device; `ctx` is an `engine.context.StepContext`):
+  Norm.forward(x) -> y                             x, y [rows, width] of the engine's dtype
+  Norm.add_norm(residual, delta, rows, write_back) -> y
+      residual float32 [T, width] (+ delta of the engine's dtype), normalised; the sum is
+      written back unless told otherwise; `rows` picks source rows
+  PositionEncoding.tables() -> dict                what the mixer's kernel needs (inv_freq)
+  Mixer.forward(h, ctx, cache, write_cache) -> y   h, y [T, width]; `cache` is the entry of
+      `CacheStorage` that this run of the layer reads (and writes when `write_cache`)
+  FeedForward.forward(h, ctx) -> y
+  Block.forward(stream, pending, ctx, cache, write_cache) -> pending
+      `stream` is the float32 residual stream [T, width], updated in place; `pending` is a
+      branch output not yet added (the next norm adds it), or None
+"""
+from __future__ import annotations
+
+from dataclasses import dataclass, field
+from typing import Any, Callable
+
+import torch
+
+from ..errors import InvalidRequest
+from ..weights.spec import WeightSpec
+
+
+@dataclass(frozen=True)
+class PartSpec:
+    """A part as data: the registered kind and its parameters."""
+
+    kind: str
+    params: dict = field(default_factory=dict)
+
+
+@dataclass(frozen=True)
+class KVNeed:
+    """A mixer that keeps keys and values in pages: all of them, or a window."""
+
+    kv_heads: int
+    head_dim: int
+    kind: str = "full"       # "full" | "window"
+    window: int = 0
+
+
+@dataclass(frozen=True)
+class StateNeed:
+    """A mixer that keeps a state of fixed size per request, in the request's state slot."""
+
+    shape: tuple[int, ...]
+    dtype: torch.dtype = torch.float32
+
+
+@dataclass
+class Runtime:
+    """Where and in which precision a model runs."""
+
+    device: torch.device
+    dtype: torch.dtype           # torch.bfloat16 (serving) or torch.float32 (the 32-bit path)
+    page_size: int = 16
+
+    @property
+    def is_bf16(self) -> bool:
+        return self.dtype is torch.bfloat16
+
+
+class Part:
+    """Base of every part.  `prefix` is the root of its tensor names in the checkpoint."""
+
+    def __init__(self, prefix: str = ""):
+        self.prefix = prefix
+        self.runtime: Runtime | None = None
+
+    def name(self, leaf: str) -> str:
+        return f"{self.prefix}.{leaf}" if self.prefix else leaf
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return []
+
+    def bind(self, tensors: dict[str, torch.Tensor], runtime: Runtime) -> None:
+        """Take the tensors named by `weight_specs` (already on the device, in their held dtype)."""
+        self.runtime = runtime
+
+
+class Norm(Part):
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        raise NotImplementedError
+
+    def add_norm(self, residual: torch.Tensor, delta: torch.Tensor | None, rows: torch.Tensor | None = None,
+                 write_back: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class PositionEncoding(Part):
+    def tables(self) -> dict[str, Any]:
+        raise NotImplementedError
+
+
+class Mixer(Part):
+    def cache_need(self) -> KVNeed | None:
+        return None
+
+    def state_need(self) -> StateNeed | None:
+        return None
+
+    def forward(self, h: torch.Tensor, ctx, cache, write_cache: bool = True) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class FeedForward(Part):
+    def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Block(Part):
+    def __init__(self, prefix: str, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
+        super().__init__(prefix)
+        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+
+    def children(self) -> list[Part]:
+        return [self.norm1, self.mixer, self.norm2, self.feed_forward]
+
+    def weight_specs(self) -> list[WeightSpec]:
+        return [s for child in self.children() for s in child.weight_specs()]
+
+    def bind(self, tensors, runtime) -> None:
+        super().bind(tensors, runtime)
+        for child in self.children():
+            child.bind(tensors, runtime)
+
+    def forward(self, stream, pending, ctx, cache, write_cache: bool = True):
+        raise NotImplementedError
+
+
+class Registry:
+    """Name -> class for one kind of part."""
+
+    def __init__(self, what: str):
+        self.what = what
+        self.entries: dict[str, Callable] = {}
+
+    def register(self, kind: str, cls: Callable | None = None, replace: bool = False):
+        def put(c):
+            if kind in self.entries and not replace and self.entries[kind] is not c:
+                raise InvalidRequest(f"{self.what} kind {kind!r} is registered already")
+            self.entries[kind] = c
+            return c
+
+        return put if cls is None else put(cls)
+
+    def get(self, kind: str) -> Callable:
+        if kind not in self.entries:
+            raise InvalidRequest(f"unknown {self.what} kind {kind!r}; registered: {sorted(self.entries)}")
+        return self.entries[kind]
+
+    def build(self, spec: PartSpec, prefix: str, **extra):
+        return self.get(spec.kind)(prefix=prefix, **spec.params, **extra)
+
+
+NORMS = Registry("norm")
+POSITION_ENCODINGS = Registry("position encoding")
+MIXERS = Registry("mixer")
+FEED_FORWARDS = Registry("feed-forward")
+BLOCKS = Registry("block")
