@@ -6,8 +6,21 @@ from parts, a paged cache manager, one step function for mixed batches, a contin
 scheduler, samplers, a command line, and hand-written CUDA kernels."""
 from .config import ModelConfig, Qwen3Config, RuntimeConfig
 from .errors import BackendError, CapacityError, EngineError, EngineStopped, InvalidRequest
+from .sampling.params import SamplingParams
+
+
+def __getattr__(name):
+    """The engine classes import torch-side modules; they are loaded at first use."""
+    if name in ("EngineHandle", "GenerateRequest", "TokenIds", "Token", "Finished", "Error", "GenerationResult",
+                "ModelRunner", "SequenceStep", "Scheduler"):
+        from . import engine
+
+        return getattr(engine, name)
+    raise AttributeError(name)
+
 
 __version__ = "0.1.0"
 
 __all__ = ["ModelConfig", "Qwen3Config", "RuntimeConfig", "BackendError", "CapacityError", "EngineError",
-           "EngineStopped", "InvalidRequest", "__version__"]
+           "EngineStopped", "InvalidRequest", "SamplingParams", "EngineHandle", "GenerateRequest", "TokenIds",
+           "__version__"]

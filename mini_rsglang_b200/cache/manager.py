@@ -148,6 +148,9 @@ class CacheManager:
 
     def table(self, request: int, group: int = 0) -> np.ndarray:
         """Logical page -> physical page of a request in a group (-1: given back)."""
+        need = -(-max(int(self.lib.mrs_cache_length(self.handle, request)), 0) // self.page_size)
+        if need > self._scratch.size:
+            self._scratch = np.empty(2 * need, dtype=np.int32)
         n = self.lib.mrs_cache_table(self.handle, request, group, self._scratch.ctypes.data, self._scratch.size)
         if n < 0:
             self._raise(n, f"block table of request {request}")

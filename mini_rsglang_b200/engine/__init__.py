@@ -1,3 +1,7 @@
+from .handle import (EngineHandle, Error, Finished, GenerateRequest, GenerationResult, GenerationStream, Token,
+                     TokenIds)
 from .runner import ModelRunner, SequenceStep
+from .scheduler import Scheduler
 
-__all__ = ["ModelRunner", "SequenceStep"]
+__all__ = ["EngineHandle", "Error", "Finished", "GenerateRequest", "GenerationResult", "GenerationStream", "Token",
+           "TokenIds", "ModelRunner", "SequenceStep", "Scheduler"]

@@ -1,0 +1,245 @@
+"""The engine in process: cuttings with the tiny configurations' own page sizes, page reuse with
+weights that make a wrong key show, long decoding, first tokens, generation through the entry
+point and the command line."""
+import json
+import os
+import subprocess
+import sys
+
+import pytest
+import torch
+from conftest import ROOT, TINY
+
+import plain_qwen3 as P
+import trace_tools as T
+from mini_rsglang_b200 import RuntimeConfig, SamplingParams
+from mini_rsglang_b200.engine import EngineHandle, GenerateRequest, ModelRunner, SequenceStep, Token, TokenIds, Finished
+
+pytestmark = pytest.mark.gpu
+
+
+def runner_for(folder, name, dtype, pages=64, max_seq_len=1024, running=4):
+    limits = RuntimeConfig(max_seq_len=max_seq_len, page_size=TINY[name][1], max_running=running)
+    return ModelRunner.load(folder, dtype=dtype, limits=limits, num_pages=pages)
+
+
+def plain(folder, tokens):
+    return P.logits_of_sequence(P.PlainConfig.load(folder), P.load_plain_weights(folder), tokens)
+
+
+def feed(runner, request, tokens, cuts, want_all=True):
+    """Feeds `tokens` of one request in portions of the given sizes; returns logits of every position."""
+    out, pos = [], 0
+    runner.cache.open(request)
+    for n in cuts:
+        runner.cache.extend(request, pos + n)
+        out.append(runner.step([SequenceStep(request, tokens[pos:pos + n], pos, list(range(n)))]).double().cpu())
+        pos += n
+    assert pos == len(tokens)
+    return torch.cat(out)
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "C"])
+def test_first_tokens_of_a_sequence(model_folders, name, dtype):
+    """Positions 0, 1, 2: one key, the first page, no rotation at position 0."""
+    runner = runner_for(model_folders[name], name, dtype)
+    tokens = [5, 9, 2]
+    want = plain(model_folders[name], tokens)
+    T.check_rows(feed(runner, 1, tokens, [3]), want, dtype, "first tokens whole")
+    T.check_rows(feed(runner, 2, tokens, [1, 1, 1]), want, dtype, "first tokens one by one")
+    one = feed(runner, 3, tokens[:1], [1])
+    T.check_rows(one, want[:1], dtype, "a prompt of one token")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_page_edges_with_the_configurations_own_page_size(model_folders, name, dtype):
+    """Cuts that end exactly at, one before and one after a page's edge."""
+    page = TINY[name][1]
+    runner = runner_for(model_folders[name], name, dtype)
+    vocab = TINY[name][0]["vocab_size"]
+    tokens = [(7 * i + 3) % vocab for i in range(4 * page + 3)]
+    want = plain(model_folders[name], tokens)
+    cuts = [page - 1, 1, 1, page, page + 1, page - 2]
+    cuts.append(len(tokens) - sum(cuts))
+    T.check_rows(feed(runner, 1, tokens, cuts), want, dtype, f"{name} page edges")
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_long_decoding(model_folders, dtype):
+    """A short prompt, then 300 tokens one by one: rounding must not build up, pages keep coming."""
+    name = "B"
+    runner = runner_for(model_folders[name], name, dtype)
+    vocab = TINY[name][0]["vocab_size"]
+    tokens = [(11 * i + 5) % vocab for i in range(310)]
+    want = plain(model_folders[name], tokens)
+    got = feed(runner, 1, tokens, [10] + [1] * 300)
+    T.check_rows(got, want, dtype, "long decoding")
+
+
+def sharpen(folder, out, factor):
+    """The same model with q and k head-norm weights scaled: attention gets peaked, so a key
+    read from the wrong place moves the logits by far more than rounding."""
+    from safetensors.torch import load_file
+    from mini_rsglang_b200.weights import write_safetensors
+    tensors = load_file(os.path.join(folder, "model.safetensors"))
+    for name in tensors:
+        if name.endswith("q_norm.weight") or name.endswith("k_norm.weight"):
+            tensors[name] = (tensors[name].float() * factor).to(tensors[name].dtype)
+    os.makedirs(out, exist_ok=True)
+    write_safetensors(os.path.join(out, "model.safetensors"), tensors)
+    with open(os.path.join(folder, "config.json")) as f, open(os.path.join(out, "config.json"), "w") as g:
+        g.write(f.read())
+    return out
+
+
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_reused_pages_with_peaked_attention_in_float32(model_folders, tmp_path, name):
+    """Requests come and go in a pool that holds two of them, so every page is written by several
+    requests in turn and block tables are out of order; with peaked attention a stale or
+    misplaced key would change the logits at once."""
+    # factor 3: scores grow ninefold; float32 rounding of a score of that size stays below the gate
+    folder = sharpen(model_folders[name], str(tmp_path / "sharp"), 3.0)
+    cfg, weights = P.PlainConfig.load(folder), P.load_plain_weights(folder)
+    page = TINY[name][1]
+    reqs = T.requests_for(cfg.vocab_size, [50, 33, 61, 18, 47, 29, 55], seed=3)
+    pool_pages = 2 * (-(-61 // page)) + 1
+    limits = RuntimeConfig(max_seq_len=512, page_size=page, max_running=4)
+    runner = ModelRunner.load(folder, dtype="float32", limits=limits, num_pages=pool_pages)
+    cache = runner.cache
+    queue, live, fed = list(reqs), {}, {}
+    ids = {r: i + 1 for i, r in enumerate(reqs)}
+    seen_tables = []
+    import random
+    rng = random.Random(4)
+    while queue or live:
+        while queue and len(live) < 3:
+            need = -(-len(reqs[queue[0]]) // page)
+            held = sum(-(-len(reqs[r]) // page) for r in live)
+            if held + need > pool_pages:
+                break
+            live[queue.pop(0)] = 0
+            cache.open(ids[list(live)[-1]])
+        batch, places = [], []
+        for r in list(live):
+            p, tokens = live[r], reqs[r]
+            n = min(rng.choice([1, 2, 3, 7, 12]), len(tokens) - p)
+            cache.extend(ids[r], p + n)
+            batch.append(SequenceStep(ids[r], tokens[p:p + n], p, [n - 1]))
+            places.append((r, p + n - 1))
+            live[r] = p + n
+        got = runner.step(batch).double().cpu()
+        want = torch.stack([P.logits_of_sequence(cfg, weights, reqs[r][:p + 1])[-1] for r, p in places])
+        T.check_rows(got, want, "float32", f"{name} reuse")
+        for r in list(live):
+            if live[r] == len(reqs[r]):
+                seen_tables.append(list(cache.table(ids[r])))
+                cache.close(ids[r])
+                del live[r]
+        cache.check_integrity()
+    assert any(t != sorted(t) or t[0] != 0 for t in seen_tables[1:]), "block tables never left the natural order"
+    used = [p for t in seen_tables for p in t]
+    assert len(used) > pool_pages                       # pages were used again
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B"])
+def test_greedy_generation_through_the_entry_point(model_folders, name, dtype):
+    folder = model_folders[name]
+    cfg, weights = P.PlainConfig.load(folder), P.load_plain_weights(folder)
+    limits = RuntimeConfig(max_seq_len=256, page_size=TINY[name][1], prefill_budget=8, max_running=3)
+    engine = EngineHandle.load(folder, 0, config=limits, dtype=dtype, num_pages=40)
+    prompts = [[3, 1, 4, 1, 5], [9, 2, 6, 5, 3, 5, 8, 9, 7], [2, 7, 1, 8, 2, 8, 1, 8, 2, 8, 4, 5, 9], [6]]
+    steps = 8
+    results = engine.generate_many(prompts, SamplingParams(max_tokens=steps, ignore_eos=True))
+    for prompt, result in zip(prompts, results):
+        assert result.finish_reason == "length" and result.prompt_tokens == len(prompt)
+        # follow the engine's tokens; at every step they must be the plain arg-max unless the two
+        # best plain logits are closer than the path's rounding
+        tokens = list(prompt)
+        for token in result.token_ids:
+            logits = P.logits_of_sequence(cfg, weights, tokens)[-1]
+            best = P.greedy(logits)
+            if token != best:
+                gap = (logits[best] - logits[token]).item()
+                allowed = 2e-5 if dtype == "float32" else 0.02 * logits.abs().max().item()
+                assert gap <= allowed, f"token {token} instead of {best}, gap {gap}"
+            tokens.append(token)
+    assert engine.runner.cache.free_pages() == 40
+    metrics = engine.metrics()
+    assert metrics["completed"] == 4 and metrics["generated_tokens"] == 4 * steps and metrics["mixed_batches"] > 0
+    engine.shutdown()
+
+
+def test_streams_events_stop_reason_and_seeded_sampling(model_folders):
+    folder = model_folders["B"]
+    limits = RuntimeConfig(max_seq_len=128, page_size=16, prefill_budget=8, max_running=4)
+    engine = EngineHandle.load(folder, 0, config=limits, dtype="bfloat16", num_pages=32)
+    # temperature 0.7, seeded: the same seed gives the same tokens whatever else runs beside it
+    params = SamplingParams(temperature=0.7, seed=1234, max_tokens=6, ignore_eos=True)
+    alone = engine.generate_many([[5, 6, 7, 8]], params)[0].token_ids
+    beside = engine.generate_many([[1, 2, 3], [5, 6, 7, 8], [9] * 20],
+                                  [SamplingParams(max_tokens=9, ignore_eos=True), params,
+                                   SamplingParams(temperature=1.0, seed=5, max_tokens=3, ignore_eos=True)])
+    assert beside[1].token_ids == alone
+    other_seed = engine.generate_many([[5, 6, 7, 8]], SamplingParams(temperature=0.7, seed=99, max_tokens=6, ignore_eos=True))
+    assert other_seed[0].token_ids != alone
+    # events of one stream, and an end-of-sequence token stops it
+    stream = engine.generate(GenerateRequest(TokenIds([5, 6, 7, 8]), SamplingParams(max_tokens=4, ignore_eos=True)))
+    events = list(stream)
+    assert [type(e) for e in events] == [Token] * 4 + [Finished] and events[-1].reason == "length"
+    first = events[0].token_id
+    engine.scheduler = type(engine.scheduler)(engine.runner.cache, limits, [first], 384)
+    stopped = engine.generate_many([[5, 6, 7, 8]], SamplingParams(max_tokens=4))[0]
+    assert stopped.finish_reason == "stop" and stopped.token_ids == [first]
+    engine.shutdown()
+    from mini_rsglang_b200 import EngineStopped
+    with pytest.raises(EngineStopped):
+        engine.generate(GenerateRequest(TokenIds([1]), SamplingParams()))
+
+
+def test_refusals_of_the_entry_point_and_the_step_function(model_folders):
+    from mini_rsglang_b200 import CapacityError, InvalidRequest
+    folder = model_folders["A"]
+    limits = RuntimeConfig(max_seq_len=64, page_size=4, prefill_budget=8, max_running=2, max_waiting=2)
+    engine = EngineHandle.load(folder, 0, config=limits, dtype="float32", num_pages=8)
+    with pytest.raises(InvalidRequest):
+        engine.generate(GenerateRequest(TokenIds([]), SamplingParams()))
+    with pytest.raises(InvalidRequest):
+        engine.generate(GenerateRequest(TokenIds([256]), SamplingParams(max_tokens=2)))
+    with pytest.raises(InvalidRequest, match="context limit"):
+        engine.generate(GenerateRequest(TokenIds([1] * 60), SamplingParams(max_tokens=8)))
+    with pytest.raises(CapacityError):
+        engine.generate(GenerateRequest(TokenIds([1] * 30), SamplingParams(max_tokens=8)))   # 10 pages > 8
+    runner = engine.runner
+    runner.cache.open(77)
+    runner.cache.extend(77, 4)
+    with pytest.raises(InvalidRequest, match="appears twice"):
+        runner.step([SequenceStep(77, [1, 2], 0), SequenceStep(77, [3], 2)])
+    with pytest.raises(InvalidRequest, match="coverage"):
+        runner.step([SequenceStep(77, [1] * 6, 0)])
+    with pytest.raises(InvalidRequest, match="out of range"):
+        runner.step([SequenceStep(77, [999], 0)])
+    with pytest.raises(InvalidRequest):
+        runner.step([])
+    runner.cache.close(77)
+    with pytest.raises(InvalidRequest, match="max_position_embeddings"):
+        EngineHandle.load(folder, 0, config=RuntimeConfig(max_seq_len=4096), dtype="float32", num_pages=8)
+
+
+def test_command_line_generates_what_the_entry_point_generates(model_folders, tmp_path):
+    folder = model_folders["A"]
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "mini-rsglang"), "--model", folder, "--dtype", "float32",
+           "--page-size", "4", "--max-seq-len", "128", "--num-pages", "32", "generate", "--token-ids", "3,1,4,1,5",
+           "--max-tokens", "5", "--ignore-eos", "--json"]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr
+    events = [json.loads(line) for line in proc.stdout.splitlines() if line.startswith("{")]
+    tokens = [e["Token"]["token_id"] for e in events if "Token" in e]
+    done = events[-1]["Finished"]
+    assert done["reason"] == "length" and done["prompt_tokens"] == 5 and done["completion_tokens"] == 5
+    cfg, weights = P.PlainConfig.load(folder), P.load_plain_weights(folder)
+    assert tokens == P.generate_greedy(cfg, weights, [3, 1, 4, 1, 5], 5)
+    bad = subprocess.run(cmd[:-6] + ["--token-ids", "3,x", "--max-tokens", "5"], capture_output=True, text=True, timeout=300)
+    assert bad.returncode != 0 and "comma-separated integers" in bad.stderr
