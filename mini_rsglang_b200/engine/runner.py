@@ -91,6 +91,7 @@ class ModelRunner:
         self._host = None       # pinned int32 staging buffer
         self._dev = None
         self.steps = 0
+        self.h2d_bytes = 0      # bytes of batch metadata copied to the device so far
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -202,6 +203,7 @@ class ModelRunner:
                 slots_view[row:row + counts[i]] = t[p // S].astype(np.int64) * S + p % S
                 row += counts[i]
         dev[:cursor].copy_(host[:cursor], non_blocking=True)
+        self.h2d_bytes += 4 * cursor
 
         def dview(name, shape=None):
             start, n = layout[name]
