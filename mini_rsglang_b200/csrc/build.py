@@ -165,3 +165,10 @@ def specialised_kernel_library(source: str, defines: dict[str, int], extra_flags
         return _build(name, [os.path.join(folder, source)], [nvcc], flags, link, folder)
 
     return _load(name, builder)
+
+
+# Head sizes whose attention is compiled ahead of time by the build check; any other multiple of
+# 16 up to 256 is compiled when a model first needs it.
+PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
+SPECIALISED_BUILDS = tuple((lambda d=d: specialised_kernel_library("attention_mma.cu", {"MRS_HEAD_DIM": d}))
+                           for d in PREBUILT_HEAD_DIMS)

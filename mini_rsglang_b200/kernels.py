@@ -11,7 +11,7 @@ import math
 
 import torch
 
-from .csrc.build import kernel_library
+from .csrc.build import kernel_library, specialised_kernel_library
 from .errors import BackendError, InvalidRequest
 
 _c_int, _c_vp, _c_float = ctypes.c_int, ctypes.c_void_p, ctypes.c_float
@@ -214,3 +214,93 @@ def sample(logits: torch.Tensor, temperature: torch.Tensor, top_k: torch.Tensor,
     _check(library().mrs_sample(logits.data_ptr(), rows, vocab, temperature.data_ptr(), top_k.data_ptr(),
                                 top_p.data_ptr(), seed.data_ptr(), draw_index.data_ptr(), out.data_ptr(),
                                 _stream()), "sample")
+
+
+# ------------------------------------------------------------------------------------------------
+# tensor-core attention, one library per head size
+# ------------------------------------------------------------------------------------------------
+_attention_libs: dict[int, ctypes.CDLL] = {}
+_scratch: dict[torch.device, torch.Tensor] = {}
+
+MMA_ROWS_WIDE, MMA_ROWS_NARROW = 64, 16
+
+
+def attention_mma_supported(d: int, group: int) -> bool:
+    return d % 16 == 0 and 16 <= d <= 256 and group <= MMA_ROWS_WIDE
+
+
+def attention_mma_library(d: int) -> ctypes.CDLL:
+    """The tensor-core attention compiled for head size `d` (built at first use)."""
+    if d not in _attention_libs:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        lib = specialised_kernel_library("attention_mma.cu", {"MRS_HEAD_DIM": d})
+        lib.mrs_attention_mma_rows_mode.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_int, _c_int, _c_int,
+                                                    _c_float, _c_int, _c_vp]
+        lib.mrs_attention_mma_rows_mode.restype = _c_int
+        lib.mrs_attention_mma_keys_mode.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int,
+                                                    _c_int, _c_float, _c_int, _c_int, _c_vp]
+        lib.mrs_attention_mma_keys_mode.restype = _c_int
+        lib.mrs_attention_mma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
+        lib.mrs_attention_mma_scratch_floats.restype = ctypes.c_longlong
+        _attention_libs[d] = lib
+    return _attention_libs[d]
+
+
+def attention_scratch(device: torch.device, floats: int) -> torch.Tensor:
+    """Scratch memory for split attention, kept and grown per device."""
+    have = _scratch.get(device)
+    if have is None or have.numel() < floats:
+        have = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        _scratch[device] = have
+    return have
+
+
+def _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d):
+    tokens = q.shape[0]
+    _need(q, torch.bfloat16, "q", (tokens, nq * d))
+    _need(k_cache, torch.bfloat16, "k cache")
+    _need(v_cache, torch.bfloat16, "v cache", tuple(k_cache.shape))
+    _need(out, torch.bfloat16, "attention out", (tokens, nq * d))
+    _need(positions, torch.int32, "positions", (tokens,))
+    _need(block_table, torch.int32, "block_table")
+    _need(tiles, torch.int32, "tiles")
+    if tiles.dim() != 2 or tiles.shape[1] != 4:
+        raise InvalidRequest("attention tiles must be [n, 4] (sequence, first token, tokens, 0)")
+    if tuple(k_cache.shape[1:]) != (nkv, k_cache.shape[2], d):
+        raise InvalidRequest("attention: cache shape does not match heads/head_dim")
+
+
+def attention_mma_rows(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int,
+                       window: int = 0, scale: float | None = None) -> None:
+    """Tiles of up to 64 // (nq // nkv) tokens of one request each."""
+    _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
+    lib = attention_mma_library(d)
+    _check(lib.mrs_attention_mma_rows_mode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
+                                           block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(),
+                                           tiles.shape[0], out.data_ptr(), nq, nkv, k_cache.shape[2],
+                                           float(scale if scale is not None else 1.0 / math.sqrt(d)), int(window),
+                                           _stream()), "attention_mma_rows")
+
+
+def attention_mma_keys(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int,
+                       window: int = 0, splits: int = 1, scale: float | None = None,
+                       scratch: torch.Tensor | None = None) -> None:
+    """Tiles of up to 16 // (nq // nkv) tokens each; `splits` CTAs share the keys of a tile."""
+    global launch_count
+    _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
+    lib = attention_mma_library(d)
+    if splits > 1:
+        need = lib.mrs_attention_mma_scratch_floats(tiles.shape[0], nkv, splits)
+        if scratch is None:
+            scratch = attention_scratch(q.device, need)
+        _need(scratch, torch.float32, "attention scratch")
+        if scratch.numel() < need:
+            raise InvalidRequest(f"attention scratch holds {scratch.numel()} floats, {need} are needed")
+        launch_count += 1          # the combine kernel
+    _check(lib.mrs_attention_mma_keys_mode(q.data_ptr(), k_cache.data_ptr(), v_cache.data_ptr(), positions.data_ptr(),
+                                           block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(),
+                                           tiles.shape[0], out.data_ptr(), _ptr(scratch) if splits > 1 else None,
+                                           nq, nkv, k_cache.shape[2],
+                                           float(scale if scale is not None else 1.0 / math.sqrt(d)), int(window),
+                                           int(splits), _stream()), "attention_mma_keys")

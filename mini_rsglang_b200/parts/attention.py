@@ -16,10 +16,58 @@ from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec
 from .linear import linear
 
 
+SM_COUNT = 148
+
+
+def plan_attention_tiles(ctx, group: int):
+    """Cuts the step's sequences into tiles for the tensor-core kernels: sequences with few
+    query rows (decoded tokens, short portions) go to the keys mode in tiles of 16 // group
+    tokens, the others to the rows mode in tiles of 64 // group tokens.  Returns
+    (narrow tiles, wide tiles, splits) with the tile lists on the device, or None when a list
+    would be empty.  The plan is kept in the context for the other layers of the step."""
+    plans = ctx.__dict__.setdefault("_attention_plans", {})
+    if group in plans:
+        return plans[group]
+    narrow_tokens = kernels.MMA_ROWS_NARROW // group
+    wide_tokens = kernels.MMA_ROWS_WIDE // group
+    narrow, wide = [], []
+    longest_narrow = 0
+    for i in range(ctx.num_sequences):
+        first, n = ctx.host_q_start[i], ctx.host_q_start[i + 1] - ctx.host_q_start[i]
+        if narrow_tokens >= 1 and n <= narrow_tokens:
+            narrow.append((i, first, n, 0))
+            longest_narrow = max(longest_narrow, ctx.host_start_pos[i] + n)
+        else:
+            for start in range(0, n, wide_tokens):
+                wide.append((i, first + start, min(wide_tokens, n - start), 0))
+    device = ctx.positions.device
+    both = torch.tensor(narrow + wide, dtype=torch.int32).view(-1, 4).to(device, non_blocking=True)
+    plans[group] = (both[:len(narrow)] if narrow else None, both[len(narrow):] if wide else None, longest_narrow)
+    return plans[group]
+
+
+def choose_splits(tiles: int, nkv: int, longest_context: int) -> int:
+    """CTAs per tile in the keys mode: enough to fill the GPU twice, at least 256 keys each."""
+    blocks = -(-longest_context // 64)
+    want = -(-2 * SM_COUNT // max(tiles * nkv, 1))
+    return max(1, min(want, blocks // 4))
+
+
 def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) -> None:
-    """Attention of this step's queries over their requests' cached keys and values."""
-    kernels.attention_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, ctx.block_tables[cache.group],
-                           out, nq, nkv, d, window)
+    """Attention of this step's queries over their requests' cached keys and values: on the
+    tensor cores when the activations are bfloat16 and the head size is a multiple of 16,
+    else (the 32-bit path, odd head sizes, very wide groups) the CUDA-core kernel."""
+    table = ctx.block_tables[cache.group]
+    group = nq // nkv
+    if q.dtype is not torch.bfloat16 or not kernels.attention_mma_supported(d, group):
+        kernels.attention_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, table, out, nq, nkv, d, window)
+        return
+    narrow, wide, longest = plan_attention_tiles(ctx, group)
+    if narrow is not None:
+        kernels.attention_mma_keys(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window,
+                                   choose_splits(narrow.shape[0], nkv, longest))
+    if wide is not None:
+        kernels.attention_mma_rows(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
 
 
 @MIXERS.register("gqa_attention")

@@ -112,11 +112,12 @@ def linear(ar: Arith, x: torch.Tensor, weight: torch.Tensor, round_out: bool = T
 
 
 def rope_inverse_frequencies(head_dim: int, theta: float) -> torch.Tensor:
-    """f_j = 1 / f32(theta^(2j/d)) for j in [0, d/2) (crates/kernels/src/lib.rs:612-614)."""
+    """f_j = 1f32 / f32(theta^(2j/d)) for j in [0, d/2): the power in float64, narrowed to
+    float32, the reciprocal in float32 (crates/kernels/src/lib.rs:612-614)."""
     out = []
     for j in range(head_dim // 2):
-        power = torch.tensor(float(theta) ** (2 * j / head_dim), dtype=torch.float64)
-        out.append(1.0 / power.to(torch.float32).to(torch.float64))
+        power = torch.tensor(float(theta) ** (2 * j / head_dim), dtype=torch.float64).to(torch.float32)
+        out.append((torch.tensor(1.0, dtype=torch.float32) / power).to(torch.float64))
     return torch.stack(out)
 
 

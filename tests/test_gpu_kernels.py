@@ -1,0 +1,376 @@
+"""Each kernel alone against a plain float32/float64 PyTorch statement of the same operation,
+at sizes other than the engine's tiny configurations (widths and vocabularies that are no power
+of two, head sizes in steps of 16, odd numbers of heads and groups)."""
+import math
+import random
+
+import pytest
+import torch
+
+from mini_rsglang_b200 import BackendError, InvalidRequest, kernels
+from mini_rsglang_b200.parts.position import RotaryPosition
+from mini_rsglang_b200.sampling import Sampler, SamplingParams, uniform_from_counter
+import plain_qwen3 as P
+
+pytestmark = pytest.mark.gpu
+DEV = "cuda:0"
+DTYPES = [torch.float32, torch.bfloat16]
+
+
+def close(got, want, dtype, what=""):
+    got, want = got.double().cpu(), want.double().cpu()
+    if dtype is torch.float32:
+        tol = 2e-5 * max(1.0, want.abs().max().item())
+    else:
+        tol = 2 ** -7 * max(1.0, want.abs().max().item())     # one bfloat16 rounding of the result, with room
+    err = (got - want).abs().max().item()
+    assert err <= tol, f"{what}: max error {err:.3e} > {tol:.3e}"
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_embed(dtype):
+    table = torch.randn(301, 72, device=DEV).to(dtype)
+    ids = torch.tensor([0, 300, 5, 5, 17], dtype=torch.int32, device=DEV)
+    out = torch.empty(5, 72, device=DEV)
+    kernels.embed(table, ids, out)
+    assert torch.equal(out, table.float()[ids.long()])
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("width", [72, 1000, 4096])
+def test_add_rmsnorm(dtype, width):
+    rows = 7
+    residual = torch.randn(rows, width, device=DEV)
+    delta = torch.randn(rows, width, device=DEV).to(dtype)
+    weight = 1 + 0.1 * torch.randn(width, device=DEV)
+    eps = 1e-5
+    total = residual.double() + delta.double()
+    want = total * torch.rsqrt(total.pow(2).mean(-1, keepdim=True) + eps) * weight.double()
+    work = residual.clone()
+    out = torch.empty(rows, width, device=DEV, dtype=dtype)
+    kernels.add_rmsnorm(work, delta, weight, eps, out)
+    close(out, want, dtype, "add_rmsnorm")
+    close(work, total, torch.float32, "residual written back")
+    # picked rows, nothing written back, a row asked for twice
+    pick = torch.tensor([6, 0, 6], dtype=torch.int32, device=DEV)
+    work = residual.clone()
+    out = torch.empty(3, width, device=DEV, dtype=dtype)
+    kernels.add_rmsnorm(work, delta, weight, eps, out, rows=pick, write_back=False)
+    close(out, want[pick.long()], dtype, "picked rows")
+    assert torch.equal(work, residual)
+    # no delta
+    out = torch.empty(rows, width, device=DEV, dtype=dtype)
+    kernels.add_rmsnorm(residual.clone(), None, weight, eps, out)
+    x = residual.double()
+    close(out, x * torch.rsqrt(x.pow(2).mean(-1, keepdim=True) + eps) * weight.double(), dtype, "no delta")
+    # plain norm of activations
+    x = torch.randn(rows, width, device=DEV).to(dtype)
+    out = torch.empty_like(x)
+    kernels.rmsnorm(x, weight, eps, out)
+    xd = x.double()
+    close(out, xd * torch.rsqrt(xd.pow(2).mean(-1, keepdim=True) + eps) * weight.double(), dtype, "rmsnorm")
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+def test_silu_mul(dtype):
+    gate_up = torch.randn(5, 2 * 136, device=DEV).to(dtype) * 3
+    out = torch.empty(5, 136, device=DEV, dtype=dtype)
+    kernels.silu_mul(gate_up, out)
+    g, u = gate_up.double()[:, :136], gate_up.double()[:, 136:]
+    close(out, g / (1 + torch.exp(-g)) * u, dtype, "silu_mul")
+
+
+@pytest.mark.parametrize("m,n,k", [(1, 7, 5), (33, 100, 72), (64, 64, 16), (130, 301, 257)])
+def test_gemm_f32_is_true_float32(m, n, k):
+    x = torch.randn(m, k, device=DEV)
+    w = torch.randn(n, k, device=DEV)
+    out = torch.empty(m, n, device=DEV)
+    kernels.gemm_f32(x, w, out)
+    want = x.double() @ w.double().T
+    close(out, want, torch.float32, "gemm_f32")
+    # a product that a tensor-core mode with a shortened mantissa would get wrong by 1e-3
+    x = torch.full((1, 8), 1.0 + 2 ** -12, device=DEV)
+    w = torch.full((1, 8), 1.0 + 2 ** -12, device=DEV)
+    out = torch.empty(1, 1, device=DEV)
+    kernels.gemm_f32(x, w, out)
+    assert abs(out.item() - 8 * (1 + 2 ** -12) ** 2) < 1e-5
+    # a row's result does not depend on the other rows of the batch
+    x = torch.randn(70, 72, device=DEV)
+    w = torch.randn(50, 72, device=DEV)
+    whole, alone = torch.empty(70, 50, device=DEV), torch.empty(1, 50, device=DEV)
+    kernels.gemm_f32(x, w, whole)
+    kernels.gemm_f32(x[69:70].contiguous(), w, alone)
+    assert torch.equal(whole[69:70], alone)
+
+
+def plain_qk(qkv, positions, q_w, k_w, eps, theta, nq, nkv, d):
+    """q and k after head norm and rotation, v untouched, from the plain implementation's parts."""
+    ar = P.Arith(None)
+    T = qkv.shape[0]
+    x = qkv.double().cpu().view(T, nq + 2 * nkv, d)
+    q, k, v = x[:, :nq], x[:, nq:nq + nkv], x[:, nq + nkv:]
+    if q_w is not None:
+        q = P.rms_norm(ar, q, q_w.cpu(), eps)
+        k = P.rms_norm(ar, k, k_w.cpu(), eps)
+    if theta is not None:
+        q = P.rope(ar, q, positions.cpu(), theta)
+        k = P.rope(ar, k, positions.cpu(), theta)
+    return q, k, v
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page", [(3, 3, 48, 8), (8, 2, 128, 16), (5, 1, 16, 4), (2, 1, 256, 32)])
+def test_qk_norm_rope_store(dtype, nq, nkv, d, page):
+    T, pages, eps, theta = 9, 12, 1e-5, 50000.0
+    qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV).to(dtype)
+    positions = torch.tensor([0, 1, 2, 40, 41, 1000, 7, 8, 9], dtype=torch.int32, device=DEV)
+    perm = torch.randperm(pages * page)[:T].to(torch.int32).to(DEV)       # scattered, distinct slots
+    q_w, k_w = 1 + 0.1 * torch.randn(d, device=DEV), 1 + 0.1 * torch.randn(d, device=DEV)
+    inv_freq = RotaryPosition.inverse_frequencies(d, theta).to(DEV)
+    assert torch.equal(inv_freq.cpu().double(), P.rope_inverse_frequencies(d, theta))
+    q_out = torch.empty(T, nq * d, device=DEV, dtype=dtype)
+    kc = torch.zeros(pages, nkv, page, d, device=DEV, dtype=dtype)
+    vc = torch.zeros_like(kc)
+    kernels.qk_norm_rope_store(qkv, q_out, kc, vc, positions, perm, q_w, k_w, eps, inv_freq, nq, nkv, d, page)
+    q, k, v = plain_qk(qkv, positions, q_w, k_w, eps, theta, nq, nkv, d)
+    close(q_out.view(T, nq, d), q, dtype, "q")
+    slot = perm.long().cpu()
+    got_k = kc.cpu()[slot // page, :, slot % page]
+    got_v = vc.cpu()[slot // page, :, slot % page]
+    close(got_k, k, dtype, "k in the cache")
+    assert torch.equal(got_v.double(), v)
+    assert kc.count_nonzero().item() <= T * nkv * d                     # nothing else was written
+    # no norms, no rotation, no cache: q passes through
+    q_only = torch.empty_like(q_out)
+    kernels.qk_norm_rope_store(qkv, q_only, None, None, positions, None, None, None, 0.0, None, nq, nkv, d, page)
+    assert torch.equal(q_only.view(T, nq, d), qkv.view(T, nq + 2 * nkv, d)[:, :nq])
+    with pytest.raises(BackendError, match="refused"):
+        kernels.qk_norm_rope_store(torch.zeros(1, 3 * 258, device=DEV), torch.zeros(1, 258, device=DEV), None, None,
+                                   positions[:1], None, None, None, 0.0, None, 1, 1, 258, page)
+
+
+class PagedCase:
+    """Requests with scattered pages; builds the kernel's inputs and the plain answer."""
+
+    def __init__(self, dtype, nq, nkv, d, page, spans, seed=0, window=0):
+        # spans: for every request (context already in the cache, new tokens in this step)
+        g = torch.Generator().manual_seed(seed)
+        self.nq, self.nkv, self.d, self.page, self.window, self.dtype = nq, nkv, d, page, window, dtype
+        total_pages = sum(-(-(c + n) // page) for c, n in spans) + 3
+        order = torch.randperm(total_pages, generator=g).tolist()
+        self.kc = torch.zeros(total_pages, nkv, page, d, dtype=dtype)
+        self.vc = torch.zeros_like(self.kc)
+        width = max(-(-(c + n) // page) for c, n in spans)
+        self.table = torch.full((len(spans), width), -1, dtype=torch.int32)
+        q_rows, pos, seq, self.want, self.q_start = [], [], [], [], [0]
+        self.ks, self.vs = [], []
+        for i, (c, n) in enumerate(spans):
+            L = c + n
+            k = torch.randn(L, nkv, d, generator=g).to(dtype)
+            v = torch.randn(L, nkv, d, generator=g).to(dtype)
+            q = torch.randn(n, nq, d, generator=g).to(dtype)
+            self.ks.append(k), self.vs.append(v)
+            for lp in range(-(-L // page)):
+                page_id = order.pop()
+                self.table[i, lp] = page_id
+                rows = slice(lp * page, min(L, (lp + 1) * page))
+                self.kc[page_id, :, :rows.stop - rows.start] = k[rows].transpose(0, 1)
+                self.vc[page_id, :, :rows.stop - rows.start] = v[rows].transpose(0, 1)
+            q_rows.append(q)
+            pos += list(range(c, L))
+            seq += [i] * n
+            self.q_start.append(self.q_start[-1] + n)
+        self.q = torch.cat(q_rows)
+        self.positions = torch.tensor(pos, dtype=torch.int32)
+        self.seq = torch.tensor(seq, dtype=torch.int32)
+        self.spans = spans
+
+    def plain(self):
+        ar = P.Arith(None)
+        out = []
+        for i, (c, n) in enumerate(self.spans):
+            L = c + n
+            full_q = torch.zeros(L, self.nq, self.d, dtype=torch.float64)
+            full_q[c:] = self.q[self.q_start[i]:self.q_start[i + 1]].double()
+            o = P.causal_attention(ar, full_q, self.ks[i].double(), self.vs[i].double(), self.window)
+            out.append(o[c:])
+        return torch.cat(out).reshape(-1, self.nq * self.d)
+
+    def dev(self, t):
+        return t.to(DEV)
+
+    def run_simt(self):
+        out = torch.empty(self.q.shape[0], self.nq * self.d, device=DEV, dtype=self.dtype)
+        kernels.attention_simt(self.dev(self.q.reshape(-1, self.nq * self.d)), self.dev(self.kc), self.dev(self.vc),
+                               self.dev(self.positions), self.dev(self.seq), self.dev(self.table), out, self.nq,
+                               self.nkv, self.d, self.window)
+        return out
+
+    def run_mma(self, mode, splits=1):
+        group = self.nq // self.nkv
+        per_tile = (16 if mode == "keys" else 64) // group
+        tiles = []
+        for i in range(len(self.spans)):
+            first, n = self.q_start[i], self.q_start[i + 1] - self.q_start[i]
+            for s in range(0, n, per_tile):
+                tiles.append((i, first + s, min(per_tile, n - s), 0))
+        tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
+        out = torch.zeros(self.q.shape[0], self.nq * self.d, device=DEV, dtype=self.dtype)
+        args = (self.dev(self.q.reshape(-1, self.nq * self.d)), self.dev(self.kc), self.dev(self.vc),
+                self.dev(self.positions), self.dev(self.table), tiles, out, self.nq, self.nkv, self.d, self.window)
+        if mode == "keys":
+            kernels.attention_mma_keys(*args, splits=splits)
+        else:
+            kernels.attention_mma_rows(*args)
+        return out
+
+
+SHAPES = [(3, 3, 48, 8), (8, 2, 128, 16), (6, 1, 32, 4), (4, 2, 16, 16), (2, 1, 256, 32), (5, 5, 80, 16), (12, 2, 64, 64)]
+SPANS = [(0, 1), (0, 70), (130, 3), (257, 1), (63, 66), (1, 2), (300, 1)]
+
+
+@pytest.mark.parametrize("dtype", DTYPES)
+@pytest.mark.parametrize("nq,nkv,d,page", SHAPES)
+def test_attention_simt(dtype, nq, nkv, d, page):
+    case = PagedCase(dtype, nq, nkv, d, page, SPANS, seed=nq * d)
+    close(case.run_simt(), case.plain(), dtype, "attention_simt")
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_attention_window_edges(window):
+    for dtype in DTYPES:
+        case = PagedCase(dtype, 4, 2, 32, 8, [(0, 130), (120, 1), (99, 2), (3, 4)], seed=window, window=window)
+        close(case.run_simt(), case.plain(), dtype, f"simt window {window}")
+    case = PagedCase(torch.bfloat16, 4, 2, 32, 8, [(0, 130), (120, 1), (99, 2), (3, 4)], seed=window, window=window)
+    close(case.run_mma("rows"), case.plain(), torch.bfloat16, f"mma rows window {window}")
+    close(case.run_mma("keys", 1), case.plain(), torch.bfloat16, f"mma keys window {window}")
+    close(case.run_mma("keys", 3), case.plain(), torch.bfloat16, f"mma keys split window {window}")
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", SHAPES)
+def test_attention_mma_rows_mode(nq, nkv, d, page):
+    case = PagedCase(torch.bfloat16, nq, nkv, d, page, SPANS, seed=nq + d)
+    close(case.run_mma("rows"), case.plain(), torch.bfloat16, "attention_mma rows")
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("nq,nkv,d,page", SHAPES)
+def test_attention_mma_keys_mode(nq, nkv, d, page, splits):
+    case = PagedCase(torch.bfloat16, nq, nkv, d, page, SPANS, seed=nq + d + splits)
+    close(case.run_mma("keys", splits), case.plain(), torch.bfloat16, f"attention_mma keys, {splits} splits")
+
+
+@pytest.mark.parametrize("runner", ["simt32", "simt16", "rows", "keys1", "keys7"])
+def test_one_far_key_among_hundreds(runner):
+    """One key far back scores far above the rest: the output must be that key's value row, so a
+    kernel that skips, repeats or misplaces a block of keys cannot pass."""
+    dtype = torch.float32 if runner == "simt32" else torch.bfloat16
+    nq, nkv, d, page = 4, 2, 64, 16
+    for far in (0, 15, 16, 63, 64, 200, 511, 689):
+        case = PagedCase(dtype, nq, nkv, d, page, [(700, 1), (690, 12)], seed=far)
+        for i in range(2):
+            case.ks[i].mul_(0.01)
+            case.ks[i][far] = 0
+            case.ks[i][far, :, 3] = 16.0
+        case.q.mul_(0.01)
+        case.q[:, :, 3] = 16.0
+        # rebuild the cache pages from the edited keys
+        for i, (c, n) in enumerate(case.spans):
+            L = c + n
+            for lp in range(-(-L // page)):
+                rows = slice(lp * page, min(L, (lp + 1) * page))
+                case.kc[case.table[i, lp], :, :rows.stop - rows.start] = case.ks[i][rows].transpose(0, 1)
+        got = {"simt32": case.run_simt, "simt16": case.run_simt, "rows": lambda: case.run_mma("rows"),
+               "keys1": lambda: case.run_mma("keys", 1), "keys7": lambda: case.run_mma("keys", 7)}[runner]()
+        want_rows = torch.cat([case.vs[0][far].reshape(1, -1).repeat(1, 1)] +
+                              [case.vs[1][far].reshape(1, -1)] * 12).double()
+        want = want_rows.view(13, nkv, 1, d).expand(13, nkv, nq // nkv, d).reshape(13, nq * d)
+        close(got, want, dtype, f"{runner}, far key at {far}")
+        close(got, case.plain(), dtype, f"{runner} vs plain, far key at {far}")
+
+
+def test_attention_refuses_what_it_cannot_do():
+    case = PagedCase(torch.bfloat16, 4, 2, 32, 8, [(0, 4)])
+    with pytest.raises(InvalidRequest):
+        kernels.attention_simt(case.dev(case.q.reshape(-1, 128)).float(), case.dev(case.kc), case.dev(case.vc),
+                               case.dev(case.positions), case.dev(case.seq), case.dev(case.table),
+                               torch.empty(4, 128, device=DEV), 4, 2, 32)
+    assert not kernels.attention_mma_supported(24, 1) and not kernels.attention_mma_supported(128, 128)
+    assert kernels.attention_mma_supported(112, 7)
+
+
+# --------------------------------------------------------------------------------- sampling
+def test_argmax_takes_the_smaller_id_on_a_tie():
+    logits = torch.randn(6, 1000, device=DEV)
+    logits[0, 17] = logits[0, 900] = 50.0
+    logits[1, 999] = 60.0
+    logits[2, 0] = 60.0
+    logits[3] = 0.0
+    out = torch.empty(6, dtype=torch.int32, device=DEV)
+    kernels.argmax(logits, out)
+    want = [17, 999, 0, 0] + [int(logits[i].argmax()) for i in (4, 5)]
+    assert out.tolist() == want
+
+
+def plain_draw(logits, params: SamplingParams, index: int) -> int:
+    """The kernel's draw restated: the reference's support, then the inverse CDF in id order."""
+    ids, weights = P.nucleus_support(logits.double().cpu(), params.temperature, params.top_k, params.top_p)
+    pairs = sorted(zip(ids, weights))
+    u = uniform_from_counter(params.seed, index) * sum(w for _, w in pairs)
+    run = 0.0
+    for i, w in pairs:
+        run += w
+        if run > u:
+            return i
+    return pairs[-1][0]
+
+
+@pytest.mark.parametrize("vocab", [3, 301, 5000])
+def test_sampler_support_and_repeatability(vocab):
+    sampler = Sampler(torch.device(DEV))
+    g = torch.Generator().manual_seed(vocab)
+    logits = (torch.randn(1, vocab, generator=g) * 2).to(DEV)
+    settings = [SamplingParams(temperature=1.0, seed=42), SamplingParams(temperature=0.7, top_k=2, top_p=0.9, seed=42),
+                SamplingParams(temperature=1.3, top_p=0.5, seed=7), SamplingParams(temperature=0.5, top_k=min(50, vocab), seed=9),
+                SamplingParams(temperature=2.0, top_k=vocab + 5, top_p=0.999, seed=11)]
+    for params in settings:
+        support, _ = P.nucleus_support(logits[0].cpu(), params.temperature, params.top_k, params.top_p)
+        draws = 200
+        rows = logits.expand(draws, vocab).contiguous()
+        got = sampler.sample(rows, [params] * draws, list(range(draws)))
+        assert got == sampler.sample(rows, [params] * draws, list(range(draws)))      # same seed, same draws
+        assert set(got) <= set(support), f"drew outside the support with {params}"
+        want = [plain_draw(logits[0], params, i) for i in range(draws)]
+        agree = sum(a == b for a, b in zip(got, want))
+        assert agree >= draws - 2, f"{draws - agree} of {draws} draws differ from the plain draw with {params}"
+    tiny = SamplingParams(temperature=1.0, top_k=2, top_p=0.01, seed=1)
+    assert set(sampler.sample(logits.expand(20, vocab).contiguous(), [tiny] * 20, list(range(20)))) == {int(logits[0].argmax())}
+
+
+def test_sampler_distribution_ties_and_bad_rows():
+    sampler = Sampler(torch.device(DEV))
+    logits = torch.tensor([[0.0, 2.0, 1.0, -1.0, 0.5]], device=DEV)
+    params = SamplingParams(temperature=0.7, seed=3)
+    draws = 4000
+    got = sampler.sample(logits.expand(draws, 5).contiguous(), [params] * draws, list(range(draws)))
+    probs = torch.softmax(logits[0].double().cpu() / 0.7, 0)
+    counts = torch.bincount(torch.tensor(got), minlength=5).double()
+    chi2 = ((counts - draws * probs) ** 2 / (draws * probs)).sum().item()
+    assert chi2 < 25.0, f"chi-square {chi2:.1f} over 4 degrees of freedom"
+    # all logits equal, top_k 3: the three smallest ids, as the reference's sort by (value, id) keeps them
+    flat = torch.zeros(300, 40, device=DEV)
+    got = sampler.sample(flat, [SamplingParams(temperature=1.0, top_k=3, seed=5)] * 300, list(range(300)))
+    assert set(got) == {0, 1, 2}
+    got = sampler.sample(flat, [SamplingParams(temperature=1.0, top_p=0.1, seed=5)] * 300, list(range(300)))
+    assert set(got) == {0, 1, 2, 3}
+    # greedy rows beside sampled rows
+    mixed = sampler.sample(logits.expand(3, 5).contiguous(),
+                           [SamplingParams(), SamplingParams(temperature=0.9, top_k=1), params], [0, 0, 0])
+    assert mixed[0] == 1 and mixed[1] == 1
+    bad = logits.clone()
+    bad[0, 2] = float("nan")
+    with pytest.raises(BackendError, match="nonfinite"):
+        sampler.sample(bad, [params], [0])
+    bad[0, 2] = float("inf")
+    with pytest.raises(BackendError, match="nonfinite"):
+        sampler.sample(bad, [params], [0])
