@@ -495,3 +495,63 @@ MRS_EXPORT int mrs_attention_mma_keys_mode(const void* q, const void* k_cache, c
             part_o, part_ml, (const Tile*)tiles, (bf16*)out, nq, nkv, splits);
     MRS_RETURN_LAUNCH_STATUS();
 }
+
+// ---------------------------------------------------------------------------------------------
+// The same split attention with scratch memory that the library owns (see attention_no_alloc.h).
+// ---------------------------------------------------------------------------------------------
+#include "attention_no_alloc.h"
+
+namespace {
+
+// Device memory held by every GPU that loads this library.  In host code this name is only a
+// stand-in for the symbol: its device address is looked up once per device below.
+static __device__ __align__(256) float static_scratch[MRS_ATTENTION_STATIC_SCRATCH_FLOATS];
+
+constexpr int kMaxDevices = 64;
+float* static_scratch_address[kMaxDevices] = {};
+bool static_entry_ready[kMaxDevices] = {};
+
+}  // namespace
+
+MRS_EXPORT int mrs_attention_mma_keys_mode_static_scratch(const void* q, const void* k_cache, const void* v_cache,
+                                                          const int* positions, const int* block_table,
+                                                          int table_width, const int* tiles, int num_tiles, void* out,
+                                                          int nq, int nkv, int page_size, float scale, int window,
+                                                          int splits, void* stream) {
+    if (num_tiles <= 0) return 0;
+    const int shift = page_shift_of(page_size);
+    if (shift < 0 || nkv <= 0 || nq % nkv || nq / nkv > ROWS_NARROW || splits < 1 || splits > 65535) return MRS_BAD_ARGUMENT;
+    const long long need = (long long)num_tiles * nkv * splits * ROWS_NARROW * (D + 2);
+    if (splits > 1 && need > (long long)MRS_ATTENTION_STATIC_SCRATCH_FLOATS) return MRS_STATIC_SCRATCH_TOO_SMALL;
+    int device = 0;
+    cudaError_t e = cudaGetDevice(&device);
+    if (e != cudaSuccess) return (int)e;
+    if (device < 0 || device >= kMaxDevices) return MRS_BAD_ARGUMENT;
+    if (!static_entry_ready[device]) {      // set-up, once per device, with that device current
+        e = cudaGetSymbolAddress((void**)&static_scratch_address[device], static_scratch);
+        if (e != cudaSuccess) return (int)e;
+        e = cudaFuncSetAttribute(attention_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
+        if (e != cudaSuccess) return (int)e;
+        static_entry_ready[device] = true;
+    }
+    float* part_o = static_scratch_address[device];
+    float* part_ml = part_o + (size_t)num_tiles * nkv * splits * ROWS_NARROW * D;
+    attention_keys_kernel<<<dim3(num_tiles, nkv, splits), THREADS, smem_keys, (cudaStream_t)stream>>>(
+        (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, block_table, table_width,
+        (const Tile*)tiles, (bf16*)out, part_o, part_ml, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window,
+        splits);
+    e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (splits > 1)
+        attention_combine_kernel<<<dim3(num_tiles, nkv), THREADS, 0, (cudaStream_t)stream>>>(
+            part_o, part_ml, (const Tile*)tiles, (bf16*)out, nq, nkv, splits);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+MRS_EXPORT const char* mrs_attention_mma_error_string(int code) {
+    if (code == MRS_STATIC_SCRATCH_TOO_SMALL)
+        return "the call needs more scratch than the library's fixed array holds "
+               "(tiles * kv_heads * splits * 16 * (head_dim + 2) floats must not exceed 4 Mi floats)";
+    if (code == MRS_BAD_ARGUMENT) return "arguments outside what the kernel supports (page size, head grouping, splits, device)";
+    return cudaGetErrorString((cudaError_t)code);
+}
