@@ -233,22 +233,25 @@ def main() -> int:
     e2e = None
     if not args.no_e2e:
         total = args.warmup + args.steps
-        prompt_len = context - total
-        params = SamplingParams(max_tokens=total, ignore_eos=True)
+        slack = 64                                           # every request is still live when the timing ends
+        prompt_len = context - total - slack
+        params = SamplingParams(max_tokens=total + slack, ignore_eos=True)
         streams = [engine.generate(GenerateRequest(TokenIds(random_tokens(prompt_len)), params)) for _ in range(batch)]
         while engine.scheduler.waiting() or any(engine.generated.get(s.request_id, 0) == 0 for s in streams):
             engine.run_step()                                # prompts, untimed
-        for _ in range(args.warmup - 1):
+        for _ in range(args.warmup):
             engine.run_step()
         torch.cuda.synchronize()
         h2d_before, steps_before = runner.h2d_bytes, runner.steps
+        made_before = sum(engine.generated.values())
         t0 = time.perf_counter()
         for _ in range(args.steps):
             engine.run_step()
         torch.cuda.synchronize()
         elapsed = time.perf_counter() - t0
+        made = sum(engine.generated.values()) - made_before
         timed_steps = runner.steps - steps_before
-        e2e = {"value": round(batch * args.steps / elapsed, 1), "unit": "tokens/s",
+        e2e = {"value": round(made / elapsed, 1), "unit": "tokens/s", "tokens": made,
                "h2d_bytes_per_step": (runner.h2d_bytes - h2d_before) // max(timed_steps, 1),
                "d2h_bytes_per_step": 4 * batch, "ms_per_step": round(elapsed / args.steps * 1e3, 3)}
         engine.shutdown()

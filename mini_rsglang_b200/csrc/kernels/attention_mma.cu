@@ -195,6 +195,7 @@ __global__ void __launch_bounds__(THREADS) attention_rows_kernel(
     constexpr int NT = KV_WIDE / 8;
 
     const Tile tile = tiles[blockIdx.x];
+    if (tile.tokens <= 0) return;                    // a padding entry of the tile list
     const int kv_head = blockIdx.y, group = nq / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* pages = block_table + (size_t)tile.seq * table_width;
@@ -291,6 +292,7 @@ __global__ void __launch_bounds__(THREADS) attention_keys_kernel(
     constexpr int NT = 2;                                    // 16 keys per warp and block
 
     const Tile tile = tiles[blockIdx.x];
+    if (tile.tokens <= 0) return;                    // a padding entry of the tile list
     const int kv_head = blockIdx.y, split = blockIdx.z, group = nq / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* pages = block_table + (size_t)tile.seq * table_width;

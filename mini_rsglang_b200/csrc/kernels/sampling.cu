@@ -11,6 +11,8 @@
 // kept set in id order with u from a counter-based generator keyed by (seed, draw index), so a
 // request's tokens do not depend on what else is in the batch.
 #include "common.cuh"
+#include <cooperative_groups.h>
+namespace cg = cooperative_groups;
 
 #define SAMPLE_THREADS 1024
 #define SAMPLE_WARPS 32
@@ -66,17 +68,48 @@ __device__ Best block_argmax(const float* __restrict__ row, int vocab, Best* scr
     return scratch[32];
 }
 
+// One row per thread-block cluster: every block of the cluster takes a share of the row, block 0
+// gathers the shares' results through distributed shared memory.  A row of 150k logits is then
+// read by eight SMs instead of one.
 __global__ void __launch_bounds__(SAMPLE_THREADS) argmax_kernel(const float* __restrict__ logits, int* __restrict__ out,
                                                                 int vocab) {
     __shared__ Best scratch[33];
-    const Best b = block_argmax(logits + (size_t)blockIdx.x * vocab, vocab, scratch);
-    if (threadIdx.x == 0) out[blockIdx.x] = b.id;
+    __shared__ Best shares[16];
+    cg::cluster_group cluster = cg::this_cluster();
+    const unsigned rank = cluster.block_rank(), blocks = cluster.num_blocks();
+    const int row = blockIdx.x / blocks;
+    const int share = (vocab + blocks - 1) / blocks;
+    const int begin = min(vocab, (int)rank * share), end = min(vocab, begin + share);
+    Best b = block_argmax(logits + (size_t)row * vocab + begin, end - begin, scratch);
+    if (threadIdx.x == 0) {
+        if (b.id != 0x7fffffff) b.id += begin;
+        cluster.map_shared_rank(shares, 0)[rank] = b;
+    }
+    cluster.sync();
+    if (rank == 0 && threadIdx.x == 0) {
+        Best best = shares[0];
+        for (unsigned r = 1; r < blocks; ++r) best = better(best, shares[r]);
+        out[row] = best.id;
+    }
 }
 
 MRS_EXPORT int mrs_argmax(const float* logits, int* out, int rows, int vocab, void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return MRS_BAD_ARGUMENT;
-    argmax_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, out, vocab);
+    const unsigned blocks = vocab >= 65536 ? 8 : (vocab >= 16384 ? 4 : 1);
+    cudaLaunchConfig_t config = {};
+    config.gridDim = dim3(rows * blocks);
+    config.blockDim = dim3(SAMPLE_THREADS);
+    config.stream = (cudaStream_t)stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeClusterDimension;
+    attribute.val.clusterDim.x = blocks;
+    attribute.val.clusterDim.y = 1;
+    attribute.val.clusterDim.z = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, argmax_kernel, logits, out, vocab);
+    if (e != cudaSuccess) return (int)e;
     MRS_RETURN_LAUNCH_STATUS();
 }
 

@@ -31,3 +31,6 @@ class StepContext:
     max_query_len: int = 0
     max_context_len: int = 0
     fresh: list[bool] = field(default_factory=list)   # the sequence starts at position 0 in this step
+    # when every sequence brings one token: [B, 4] int32 attention tiles (sequence, row, 1, 0), zeros for padding
+    decode_tiles: torch.Tensor | None = None
+    real_sequences: int = 0            # sequences that are not padding (padding rows come last)

@@ -30,6 +30,9 @@ def plan_attention_tiles(ctx, group: int):
         return plans[group]
     narrow_tokens = kernels.MMA_ROWS_NARROW // group
     wide_tokens = kernels.MMA_ROWS_WIDE // group
+    if ctx.decode_tiles is not None and narrow_tokens >= 1:     # single tokens: the step's own tile list
+        plans[group] = (ctx.decode_tiles, None, ctx.max_context_len)
+        return plans[group]
     narrow, wide = [], []
     longest_narrow = 0
     for i in range(ctx.num_sequences):
@@ -42,7 +45,8 @@ def plan_attention_tiles(ctx, group: int):
                 wide.append((i, first + start, min(wide_tokens, n - start), 0))
     device = ctx.positions.device
     both = torch.tensor(narrow + wide, dtype=torch.int32).view(-1, 4).to(device, non_blocking=True)
-    plans[group] = (both[:len(narrow)] if narrow else None, both[len(narrow):] if wide else None, longest_narrow)
+    plans[group] = (both[:len(narrow)] if narrow else None, both[len(narrow):] if wide else None,
+                    min(longest_narrow, ctx.max_context_len))
     return plans[group]
 
 
@@ -72,6 +76,7 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
 
 @MIXERS.register("gqa_attention")
 class GroupedQueryAttention(Mixer):
+    replayable = True      # reads the step's facts from device tensors only
     def __init__(self, prefix: str, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, q_norm: PartSpec | None = None, k_norm: PartSpec | None = None,
                  window: int = 0):

@@ -104,6 +104,11 @@ class PositionEncoding(Part):
 
 
 class Mixer(Part):
+    # True when `forward` takes everything that changes from step to step out of the context's
+    # device tensors (never from its host lists): steps of single decoded tokens may then be
+    # recorded once and replayed.  Padding rows of such a step have state slot -1 and write slot -1.
+    replayable = False
+
     def cache_need(self) -> KVNeed | None:
         return None
 

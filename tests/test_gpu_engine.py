@@ -78,6 +78,41 @@ def test_long_decoding(model_folders, dtype):
     T.check_rows(got, want, dtype, "long decoding")
 
 
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recorded_decode_steps_equal_queued_ones(model_folders, dtype):
+    """Three requests of different lengths decode together: the step is padded to four rows,
+    recorded once and replayed.  Logits equal those of a runner that queues every kernel (bit
+    for bit in float32) and the plain implementation's."""
+    name = "B"
+    vocab = TINY[name][0]["vocab_size"]
+    reqs = T.requests_for(vocab, [60, 23, 41], seed=9)
+    want = {r: plain(model_folders[name], t) for r, t in reqs.items()}
+    heads = {"r0": 30, "r1": 3, "r2": 17}
+    results = []
+    for record in (True, False):
+        runner = runner_for(model_folders[name], name, dtype)
+        assert runner.record_decode
+        runner.record_decode = record
+        for i, (r, tokens) in enumerate(reqs.items()):
+            runner.cache.open(i + 1)
+            runner.cache.extend(i + 1, heads[r])
+            runner.step([SequenceStep(i + 1, tokens[:heads[r]], 0, [])])
+        rows = []
+        for k in range(20):
+            batch = []
+            for i, (r, tokens) in enumerate(reqs.items()):
+                runner.cache.extend(i + 1, heads[r] + k + 1)
+                batch.append(SequenceStep(i + 1, [tokens[heads[r] + k]], heads[r] + k, [0]))
+            got = runner.step(batch).double().cpu()
+            T.check_rows(got, torch.stack([want[r][heads[r] + k] for r in reqs]), dtype, f"decode step {k} (recorded={record})")
+            rows.append(got)
+        if record:
+            assert len(runner._records) == 1 and next(iter(runner._records))[0] == 4
+        results.append(torch.stack(rows))
+    if dtype == "float32":
+        assert torch.equal(results[0], results[1])
+
+
 def sharpen(folder, out, factor):
     """The same model with q and k head-norm weights scaled: attention gets peaked, so a key
     read from the wrong place moves the logits by far more than rounding."""

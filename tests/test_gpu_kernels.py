@@ -312,6 +312,21 @@ def test_argmax_takes_the_smaller_id_on_a_tie():
     assert out.tolist() == want
 
 
+@pytest.mark.parametrize("vocab", [16384, 70001, 151936])
+def test_argmax_of_long_rows_shared_by_a_cluster(vocab):
+    """Rows long enough to be shared by the blocks of a cluster: ties across shares, the last id,
+    a share's edge."""
+    logits = torch.randn(5, vocab, device=DEV)
+    share = -(-vocab // (8 if vocab >= 65536 else 4))
+    logits[0, 5] = logits[0, vocab - 1] = 40.0          # a tie between the first and the last share
+    logits[1, vocab - 1] = 41.0
+    logits[2, share - 1] = logits[2, share] = 42.0      # a tie across a share's edge
+    logits[3, share] = 43.0
+    out = torch.empty(5, dtype=torch.int32, device=DEV)
+    kernels.argmax(logits, out)
+    assert out.tolist() == [5, vocab - 1, share - 1, share, int(logits[4].argmax())]
+
+
 def plain_draw(logits, params: SamplingParams, index: int) -> int:
     """The kernel's draw restated: the reference's support, then the inverse CDF in id order."""
     ids, weights = P.nucleus_support(logits.double().cpu(), params.temperature, params.top_k, params.top_p)
