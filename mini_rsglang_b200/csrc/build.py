@@ -171,4 +171,5 @@ def specialised_kernel_library(source: str, defines: dict[str, int], extra_flags
 # 16 up to 256 is compiled when a model first needs it.
 PREBUILT_HEAD_DIMS = (16, 32, 48, 64, 128)
 SPECIALISED_BUILDS = tuple((lambda d=d: specialised_kernel_library("attention_mma.cu", {"MRS_HEAD_DIM": d}))
-                           for d in PREBUILT_HEAD_DIMS)
+                           for d in PREBUILT_HEAD_DIMS) + \
+    tuple((lambda d=d: specialised_kernel_library("attention_decode_tma.cu", {"MRS_HEAD_DIM": d})) for d in (64, 128))

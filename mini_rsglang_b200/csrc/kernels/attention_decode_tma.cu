@@ -1,0 +1,365 @@
+// Paged grouped-query attention for decoded tokens and short portions (up to 16 query rows of
+// one key/value head), for head sizes that are multiples of 64: -DMRS_HEAD_DIM=64|128|192|256.
+// The step is bound by reading keys and values once from HBM, so this kernel is built around
+// the copy: a producer warp walks the request's block table and fetches every page of a
+// 64-key block with one bulk tensor copy (TMA) into a ring of shared-memory stages, 128-byte
+// swizzled; four consumer warps wait on the stage's mbarrier, take 16 keys each with
+// ldmatrix + mma.sync (float32 softmax and accumulation), and hand the stage back through a
+// second mbarrier.  No thread computes an address of a key, and no block-wide barrier stands
+// between two blocks of keys.                      (reference: ops.cu:101-147, one CTA per
+// (token, head) walking the keys with scalar loads)
+//
+// Work is cut as in the plain tensor-core kernel: a tile is up to 16 / group consecutive tokens
+// of one request; `splits` CTAs share the 64-key blocks of a tile and leave unnormalised partial
+// results in scratch memory, which `combine` merges.
+#include "tma.cuh"
+
+#ifndef MRS_HEAD_DIM
+#error "compile with -DMRS_HEAD_DIM=<head size>"
+#endif
+
+namespace {
+
+constexpr int D = MRS_HEAD_DIM;
+static_assert(D % 64 == 0 && D >= 64 && D <= 256, "this kernel takes head sizes 64, 128, 192, 256");
+constexpr int HALVES = D / 64;                  // 128-byte column groups of a row
+constexpr int ROWS = 16;                        // query rows of a tile
+constexpr int KV = 64;                          // keys per block
+constexpr int STAGES = D <= 64 ? 6 : 3;
+constexpr int CONSUMER_WARPS = 4;
+constexpr int THREADS = 32 * (CONSUMER_WARPS + 1);
+constexpr int STAGE_BYTES = 2 * KV * D * 2;     // keys and values of one block
+constexpr int TILE_BYTES = KV * D * 2;
+
+struct Tile {
+    int seq, first_token, tokens, pad;
+};
+
+__device__ __forceinline__ void ldmatrix_x4(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void ldmatrix_x4_trans(uint32_t (&r)[4], uint32_t addr) {
+    asm volatile("ldmatrix.sync.aligned.m8n8.x4.trans.shared.b16 {%0,%1,%2,%3}, [%4];\n"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]) : "r"(addr));
+}
+__device__ __forceinline__ void mma_bf16(float (&c)[4], const uint32_t (&a)[4], uint32_t b0, uint32_t b1) {
+    asm volatile("mma.sync.aligned.m16n8k16.row.col.f32.bf16.bf16.f32 {%0,%1,%2,%3}, {%4,%5,%6,%7}, {%8,%9}, {%0,%1,%2,%3};\n"
+                 : "+f"(c[0]), "+f"(c[1]), "+f"(c[2]), "+f"(c[3])
+                 : "r"(a[0]), "r"(a[1]), "r"(a[2]), "r"(a[3]), "r"(b0), "r"(b1));
+}
+__device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
+    __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
+    return *reinterpret_cast<uint32_t*>(&v);
+}
+__device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * CONSUMER_WARPS) : "memory"); }
+
+__global__ void __launch_bounds__(THREADS) attention_decode_kernel(
+    const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
+    const bf16* __restrict__ q, const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
+    const Tile* __restrict__ tiles, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
+    int nq, int nkv, int page_size, int page_shift, float scale_log2, int window, int splits) {
+    extern __shared__ unsigned char smem_raw[];
+    const Tile tile = tiles[blockIdx.x];
+    if (tile.tokens <= 0) return;                    // a padding entry of the tile list
+    // stages start on a 1024-byte boundary: the swizzle pattern of the copies is a function of the address
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
+    uint64_t* empty = full + STAGES;
+
+    const int kv_head = blockIdx.y, split = blockIdx.z, group = nq / nkv;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int* pages = block_table + (size_t)tile.seq * table_width;
+    const int rows = tile.tokens * group;
+    const int first_pos = positions[tile.first_token], last_pos = positions[tile.first_token + tile.tokens - 1];
+    const int key_end = last_pos + 1;
+    const int key_begin = window > 0 ? max(0, first_pos - window + 1) : 0;
+    // this split's share of the tile's 64-key blocks
+    const int b0 = key_begin / KV, b1 = (key_end + KV - 1) / KV;
+    const int per = (b1 - b0 + splits - 1) / splits;
+    const int block_first = min(b1, b0 + split * per), block_last = min(b1, block_first + per);
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], CONSUMER_WARPS);
+        }
+        mbar_fence_init();
+    }
+    __syncthreads();
+
+    if (warp == CONSUMER_WARPS) {
+        // ------------------------------------------------------------------ producer
+        if (lane == 0) {
+            tma_prefetch_descriptor(&k_map);
+            tma_prefetch_descriptor(&v_map);
+            const int rows_per_copy = min(page_size, KV);
+            const int copies = KV / rows_per_copy;
+            const int copy_bytes = rows_per_copy * D * 2;
+            for (int block = block_first; block < block_last; ++block) {
+                const int it = block - block_first, s = it % STAGES;
+                if (it >= STAGES) mbar_wait(&empty[s], ((it / STAGES) - 1) & 1);
+                mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
+                unsigned char* k_dst = smem + s * STAGE_BYTES;
+                unsigned char* v_dst = k_dst + TILE_BYTES;
+                for (int c = 0; c < copies; ++c) {
+                    const int key = block * KV + c * rows_per_copy;
+                    // keys past the end, before the window or on a page that was given back are masked by
+                    // their position; their copy reads page 0, which always exists and holds finite numbers
+                    int page = 0, row = 0;
+                    if (key < key_end) {
+                        page = pages[key >> page_shift];
+                        row = key & (page_size - 1);
+                        if (page < 0) page = 0, row = 0;
+                    }
+                    tma_load_5d(k_dst + c * copy_bytes, &k_map, &full[s], 0, row, 0, kv_head, page);
+                    tma_load_5d(v_dst + c * copy_bytes, &v_map, &full[s], 0, row, 0, kv_head, page);
+                }
+            }
+        }
+        return;
+    }
+
+    // ---------------------------------------------------------------------- consumers
+    // query rows as A fragments, kept in registers for every block of keys
+    uint32_t qa[D / 16][4];
+    {
+        const int g = lane >> 2, t = lane & 3;
+#pragma unroll
+        for (int half = 0; half < 2; ++half) {
+            const int row = g + 8 * half;
+            const bool valid = row < rows;
+            const bf16* src = q + ((size_t)(tile.first_token + (valid ? row / group : 0)) * nq + kv_head * group +
+                                   (valid ? row % group : 0)) * D;
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                qa[kk][half] = valid ? *reinterpret_cast<const uint32_t*>(src + kk * 16 + 2 * t) : 0u;
+                qa[kk][half + 2] = valid ? *reinterpret_cast<const uint32_t*>(src + kk * 16 + 8 + 2 * t) : 0u;
+            }
+        }
+    }
+    int row_pos[2];
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        const int row = (lane >> 2) + 8 * r;
+        row_pos[r] = row < rows ? positions[tile.first_token + row / group] : last_pos;
+    }
+    float o[D / 8][4];
+#pragma unroll
+    for (int dt = 0; dt < D / 8; ++dt)
+#pragma unroll
+        for (int e = 0; e < 4; ++e) o[dt][e] = 0.0f;
+    float row_max[2] = {-CUDART_INF_F, -CUDART_INF_F}, row_sum[2] = {0.0f, 0.0f};
+
+    // where this lane's ldmatrix rows lie in a stage: the copies put a page's rows as
+    // [column group of 64][row][64 columns], 128 bytes a row, 16-byte chunks xor-ed with row % 8
+    const int rows_per_copy = min(page_size, KV);
+    const int sub_tile_bytes = rows_per_copy * 128;
+    auto row_base = [&](int r) { return (r / rows_per_copy) * (rows_per_copy * D * 2) + (r % rows_per_copy) * 128; };
+    const int k_row = warp * 16 + (lane & 7) + ((lane >> 4) << 3);     // Q.K^T: keys are the n index
+    const int v_row = warp * 16 + (lane & 15);                         // P.V: keys are the k index
+    const uint32_t k_row_off = row_base(k_row), v_row_off = row_base(v_row);
+    const int swz = lane & 7;                                          // row % 8 of both rows above
+    const uint32_t smem_base = smem_u32(smem);
+
+    for (int block = block_first; block < block_last; ++block) {
+        const int it = block - block_first, s = it % STAGES;
+        mbar_wait(&full[s], (it / STAGES) & 1);
+        const int key0 = block * KV + warp * 16;
+        if (key0 < key_end) {
+            const uint32_t k_tile = smem_base + s * STAGE_BYTES, v_tile = k_tile + TILE_BYTES;
+            float sc[2][4] = {};
+#pragma unroll
+            for (int kk = 0; kk < D / 16; ++kk) {
+                uint32_t b[4];
+                const int chunk = 2 * kk + ((lane >> 3) & 1);
+                ldmatrix_x4(b, k_tile + k_row_off + (chunk >> 3) * sub_tile_bytes + (((chunk & 7) ^ swz) << 4));
+                mma_bf16(sc[0], qa[kk], b[0], b[1]);
+                mma_bf16(sc[1], qa[kk], b[2], b[3]);
+            }
+            // mask, running max and sum of the two rows of this lane (rows lane/4 and lane/4 + 8)
+            const int t = lane & 3;
+            float block_max[2] = {-CUDART_INF_F, -CUDART_INF_F};
+#pragma unroll
+            for (int nt = 0; nt < 2; ++nt)
+#pragma unroll
+                for (int e = 0; e < 4; ++e) {
+                    const int key = key0 + nt * 8 + 2 * t + (e & 1);
+                    const int pos = row_pos[e >> 1];
+                    const bool seen = key <= pos && key < key_end && (window <= 0 || key > pos - window);
+                    sc[nt][e] = seen ? sc[nt][e] * scale_log2 : -CUDART_INF_F;
+                    block_max[e >> 1] = fmaxf(block_max[e >> 1], sc[nt][e]);
+                }
+#pragma unroll
+            for (int r = 0; r < 2; ++r) {
+                block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 1));
+                block_max[r] = fmaxf(block_max[r], __shfl_xor_sync(0xffffffffu, block_max[r], 2));
+                const float new_max = fmaxf(row_max[r], block_max[r]);
+                const float base = new_max == -CUDART_INF_F ? 0.0f : new_max;
+                const float alpha = exp2f(row_max[r] - base);
+                row_max[r] = new_max;
+                float sum = 0.0f;
+#pragma unroll
+                for (int nt = 0; nt < 2; ++nt) {
+                    sc[nt][2 * r] = exp2f(sc[nt][2 * r] - base);
+                    sc[nt][2 * r + 1] = exp2f(sc[nt][2 * r + 1] - base);
+                    sum += sc[nt][2 * r] + sc[nt][2 * r + 1];
+                }
+                row_sum[r] = row_sum[r] * alpha + sum;
+#pragma unroll
+                for (int dt = 0; dt < D / 8; ++dt) {
+                    o[dt][2 * r] *= alpha;
+                    o[dt][2 * r + 1] *= alpha;
+                }
+            }
+            uint32_t pa[4] = {pack_bf16(sc[0][0], sc[0][1]), pack_bf16(sc[0][2], sc[0][3]),
+                              pack_bf16(sc[1][0], sc[1][1]), pack_bf16(sc[1][2], sc[1][3])};
+#pragma unroll
+            for (int dt = 0; dt < D / 8; dt += 2) {
+                uint32_t b[4];
+                const int chunk = dt + (lane >> 4);
+                ldmatrix_x4_trans(b, v_tile + v_row_off + (chunk >> 3) * sub_tile_bytes + (((chunk & 7) ^ swz) << 4));
+                mma_bf16(o[dt], pa, b[0], b[1]);
+                mma_bf16(o[dt + 1], pa, b[2], b[3]);
+            }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty[s]);
+    }
+    consumer_sync();      // every warp is done with the stages: their memory now carries the merge
+
+    float* merge_o = reinterpret_cast<float*>(smem);
+    float* merge_ml = merge_o + CONSUMER_WARPS * ROWS * D;
+#pragma unroll
+    for (int r = 0; r < 2; ++r) {
+        float sum = row_sum[r];
+        sum += __shfl_xor_sync(0xffffffffu, sum, 1);
+        sum += __shfl_xor_sync(0xffffffffu, sum, 2);
+        const int row = (lane >> 2) + 8 * r;
+        if ((lane & 3) == 0) {
+            merge_ml[(warp * ROWS + row) * 2] = row_max[r];
+            merge_ml[(warp * ROWS + row) * 2 + 1] = sum;
+        }
+#pragma unroll
+        for (int dt = 0; dt < D / 8; ++dt) {
+            const int col = dt * 8 + 2 * (lane & 3);
+            *reinterpret_cast<float2*>(&merge_o[(warp * ROWS + row) * D + col]) = make_float2(o[dt][2 * r], o[dt][2 * r + 1]);
+        }
+    }
+    consumer_sync();
+    for (int idx = threadIdx.x; idx < rows * D; idx += 32 * CONSUMER_WARPS) {
+        const int row = idx / D, col = idx % D;
+        float m = -CUDART_INF_F;
+#pragma unroll
+        for (int w = 0; w < CONSUMER_WARPS; ++w) m = fmaxf(m, merge_ml[(w * ROWS + row) * 2]);
+        const float base = m == -CUDART_INF_F ? 0.0f : m;
+        float sum = 0.0f, acc = 0.0f;
+#pragma unroll
+        for (int w = 0; w < CONSUMER_WARPS; ++w) {
+            const float f = exp2f(merge_ml[(w * ROWS + row) * 2] - base);
+            sum += merge_ml[(w * ROWS + row) * 2 + 1] * f;
+            acc += merge_o[(w * ROWS + row) * D + col] * f;
+        }
+        if (splits == 1) {
+            out[((size_t)(tile.first_token + row / group) * nq + kv_head * group + row % group) * D + col] =
+                __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+        } else {
+            const size_t slot = (((size_t)blockIdx.x * nkv + kv_head) * splits + split) * ROWS + row;
+            part_o[slot * D + col] = acc;
+            if (col == 0) {
+                part_ml[slot * 2] = m;
+                part_ml[slot * 2 + 1] = sum;
+            }
+        }
+    }
+}
+
+// Merges the `splits` partial results of every (tile, kv head, row).
+__global__ void __launch_bounds__(128) attention_decode_combine_kernel(
+    const float* __restrict__ part_o, const float* __restrict__ part_ml, const Tile* __restrict__ tiles,
+    bf16* __restrict__ out, int nq, int nkv, int splits) {
+    const Tile tile = tiles[blockIdx.x];
+    const int kv_head = blockIdx.y, group = nq / nkv, rows = tile.tokens * group;
+    const size_t base_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS;
+    for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
+        const int row = idx / D, col = idx % D;
+        float m = -CUDART_INF_F;
+        for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base_slot + (size_t)s * ROWS + row) * 2]);
+        const float base = m == -CUDART_INF_F ? 0.0f : m;
+        float sum = 0.0f, acc = 0.0f;
+        for (int s = 0; s < splits; ++s) {
+            const size_t slot = base_slot + (size_t)s * ROWS + row;
+            const float f = exp2f(part_ml[slot * 2] - base);
+            sum += part_ml[slot * 2 + 1] * f;
+            acc += part_o[slot * D + col] * f;
+        }
+        out[((size_t)(tile.first_token + row / group) * nq + kv_head * group + row % group) * D + col] =
+            __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+    }
+}
+
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 2 * STAGES * sizeof(uint64_t);
+static_assert((size_t)STAGES * STAGE_BYTES >= (size_t)CONSUMER_WARPS * ROWS * (D + 2) * sizeof(float), "merge area");
+
+int page_shift_of(int page_size) {
+    int shift = 0;
+    while ((1 << shift) < page_size) ++shift;
+    return (1 << shift) == page_size ? shift : -1;
+}
+
+}  // namespace
+
+// A tensor map of one layer's key or value pages [pages, kv_heads, page_size, D]: written to
+// `map_out` (128 bytes, 64-byte aligned), to be handed to the launcher with every call.
+MRS_EXPORT int mrs_attention_decode_tma_map(const void* cache, long long pages, int nkv, int page_size, void* map_out) {
+    if (page_shift_of(page_size) < 0 || page_size < 8 || pages <= 0 || nkv <= 0) return MRS_BAD_ARGUMENT;
+    const uint64_t dims[5] = {64, (uint64_t)page_size, (uint64_t)HALVES, (uint64_t)nkv, (uint64_t)pages};
+    const uint64_t strides[4] = {(uint64_t)D * 2, 128, (uint64_t)page_size * D * 2, (uint64_t)nkv * page_size * D * 2};
+    const uint32_t box[5] = {64, (uint32_t)(page_size < KV ? page_size : KV), (uint32_t)HALVES, 1, 1};
+    return mrs_make_tensor_map_bf16(reinterpret_cast<CUtensorMap*>(map_out), cache, 5, dims, strides, box,
+                                    CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+MRS_EXPORT long long mrs_attention_decode_tma_scratch_floats(int tiles, int nkv, int splits) {
+    return splits <= 1 ? 0 : (long long)tiles * nkv * splits * ROWS * (D + 2);
+}
+
+// Tiles of up to 16 / group tokens each; `splits` CTAs share a tile's keys.  `scratch` must hold
+// mrs_attention_decode_tma_scratch_floats(...) floats when splits > 1.
+MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, const void* q, const int* positions,
+                                        const int* block_table, int table_width, const int* tiles, int num_tiles,
+                                        void* out, float* scratch, int nq, int nkv, int page_size, float scale,
+                                        int window, int splits, void* stream) {
+    if (num_tiles <= 0) return 0;
+    const int shift = page_shift_of(page_size);
+    if (shift < 0 || page_size < 8 || nkv <= 0 || nq % nkv || nq / nkv > ROWS || splits < 1 || splits > 65535)
+        return MRS_BAD_ARGUMENT;
+    if (splits > 1 && !scratch) return MRS_BAD_ARGUMENT;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    float* part_o = scratch;
+    float* part_ml = scratch ? scratch + (size_t)num_tiles * nkv * splits * ROWS * D : nullptr;
+    attention_decode_kernel<<<dim3(num_tiles, nkv, splits), THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(
+        *reinterpret_cast<const CUtensorMap*>(k_map), *reinterpret_cast<const CUtensorMap*>(v_map), (const bf16*)q,
+        positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, part_o, part_ml, nq, nkv, page_size, shift,
+        scale * 1.4426950408889634f, window, splits);
+    cudaError_t e = cudaGetLastError();
+    if (e != cudaSuccess) return (int)e;
+    if (splits > 1)
+        attention_decode_combine_kernel<<<dim3(num_tiles, nkv), 128, 0, (cudaStream_t)stream>>>(
+            part_o, part_ml, (const Tile*)tiles, (bf16*)out, nq, nkv, splits);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// Reads and clears this library's error word (waits for the device).  0: no kernel gave up a wait.
+MRS_EXPORT int mrs_attention_decode_tma_take_error(unsigned int* word) { return mrs_take_error_word(word); }
+
+MRS_EXPORT const char* mrs_attention_decode_tma_error_string(int code) {
+    if (code == MRS_BAD_ARGUMENT) return "arguments outside what the kernel supports (page size below 8 or no power of two, head grouping, splits)";
+    if (code == MRS_TENSOR_MAP_FAILED) return "the driver refused the tensor map (address, sizes or strides)";
+    return cudaGetErrorString((cudaError_t)code);
+}

@@ -19,6 +19,7 @@ from typing import Iterator, Sequence
 
 import torch
 
+from .. import kernels
 from ..config.runtime_config import RuntimeConfig
 from ..errors import BackendError, EngineError, EngineStopped, InvalidRequest
 from ..models.registry import load_config
@@ -216,6 +217,7 @@ class EngineHandle:
             else:
                 tokens = []
                 torch.cuda.current_stream().synchronize()
+            kernels.check_device_errors()
         except (EngineError, RuntimeError) as e:
             # a failed step ends every request and gives every page back (scheduler.rs:332-359)
             self.healthy = False

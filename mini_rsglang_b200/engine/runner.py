@@ -355,6 +355,7 @@ class ModelRunner:
         try:
             logits = self.forward(sequences)
             torch.cuda.current_stream().synchronize()
+            kernels.check_device_errors()
             return logits
         except RuntimeError as e:          # a CUDA failure surfaces as torch's RuntimeError
             raise BackendError(f"step failed on the device: {e}") from e

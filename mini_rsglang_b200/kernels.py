@@ -31,6 +31,7 @@ _SIGNATURES = {
 }
 
 _lib = None
+_error_readers: list[tuple] = []
 launch_count = 0   # launches of the engine's own kernels since import (read by the benchmark)
 
 
@@ -304,3 +305,97 @@ def attention_mma_keys(q, k_cache, v_cache, positions, block_table, tiles, out, 
                                            nq, nkv, k_cache.shape[2],
                                            float(scale if scale is not None else 1.0 / math.sqrt(d)), int(window),
                                            int(splits), _stream()), "attention_mma_keys")
+
+
+# ------------------------------------------------------------------------------------------------
+# decode attention fed by bulk tensor copies (TMA), one library per head size (multiples of 64)
+# ------------------------------------------------------------------------------------------------
+_decode_libs: dict[int, ctypes.CDLL] = {}
+_tensor_maps: dict[tuple, tuple] = {}
+
+
+def attention_decode_tma_supported(d: int, group: int, page_size: int) -> bool:
+    return d % 64 == 0 and 64 <= d <= 256 and group <= MMA_ROWS_NARROW and page_size >= 8
+
+
+def attention_decode_tma_library(d: int) -> ctypes.CDLL:
+    if d not in _decode_libs:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        lib = specialised_kernel_library("attention_decode_tma.cu", {"MRS_HEAD_DIM": d})
+        lib.mrs_attention_decode_tma_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
+        lib.mrs_attention_decode_tma_map.restype = _c_int
+        lib.mrs_attention_decode_tma.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int,
+                                                 _c_float, _c_int, _c_int, _c_vp]
+        lib.mrs_attention_decode_tma.restype = _c_int
+        lib.mrs_attention_decode_tma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
+        lib.mrs_attention_decode_tma_scratch_floats.restype = ctypes.c_longlong
+        lib.mrs_attention_decode_tma_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        lib.mrs_attention_decode_tma_take_error.restype = _c_int
+        lib.mrs_attention_decode_tma_error_string.argtypes = [_c_int]
+        lib.mrs_attention_decode_tma_error_string.restype = ctypes.c_char_p
+        _decode_libs[d] = lib
+        _error_readers.append((f"attention_decode_tma (head size {d})", lib.mrs_attention_decode_tma_take_error))
+    return _decode_libs[d]
+
+
+def _aligned_block(size: int, alignment: int):
+    """Host memory for a descriptor: (object that keeps it alive, aligned address)."""
+    raw = ctypes.create_string_buffer(size + alignment)
+    address = (ctypes.addressof(raw) + alignment - 1) // alignment * alignment
+    return raw, address
+
+
+def kv_tensor_map(cache: torch.Tensor) -> int:
+    """Address of the tensor map of one layer's key or value pages [pages, kv_heads, page_size, d]
+    (made once per tensor)."""
+    key = (cache.data_ptr(), tuple(cache.shape))
+    if key not in _tensor_maps:
+        pages, nkv, page_size, d = cache.shape
+        lib = attention_decode_tma_library(d)
+        keep, address = _aligned_block(128, 64)
+        code = lib.mrs_attention_decode_tma_map(cache.data_ptr(), pages, nkv, page_size, address)
+        if code != 0:
+            raise BackendError(f"tensor map of the cache: {lib.mrs_attention_decode_tma_error_string(code).decode()}")
+        _tensor_maps[key] = (keep, address)
+    return _tensor_maps[key][1]
+
+
+def attention_decode_tma(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int,
+                         window: int = 0, splits: int = 1, scale: float | None = None,
+                         scratch: torch.Tensor | None = None) -> None:
+    """Tiles of up to 16 // (nq // nkv) tokens each; keys and values come through bulk tensor copies."""
+    global launch_count
+    _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
+    lib = attention_decode_tma_library(d)
+    if splits > 1:
+        need = lib.mrs_attention_decode_tma_scratch_floats(tiles.shape[0], nkv, splits)
+        if scratch is None:
+            scratch = attention_scratch(q.device, need)
+        _need(scratch, torch.float32, "attention scratch")
+        if scratch.numel() < need:
+            raise InvalidRequest(f"attention scratch holds {scratch.numel()} floats, {need} are needed")
+        launch_count += 1          # the combine kernel
+    code = lib.mrs_attention_decode_tma(kv_tensor_map(k_cache), kv_tensor_map(v_cache), q.data_ptr(), positions.data_ptr(),
+                                        block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(), tiles.shape[0],
+                                        out.data_ptr(), _ptr(scratch) if splits > 1 else None, nq, nkv, k_cache.shape[2],
+                                        float(scale if scale is not None else 1.0 / math.sqrt(d)), int(window),
+                                        int(splits), _stream())
+    launch_count += 1
+    if code != 0:
+        raise BackendError(f"attention_decode_tma: {lib.mrs_attention_decode_tma_error_string(code).decode()} (code {code})")
+
+
+# ------------------------------------------------------------------------------------------------
+# error words of the kernels that wait on barriers
+# ------------------------------------------------------------------------------------------------
+def check_device_errors() -> None:
+    """Reads (and clears) the error word of every loaded library whose kernels wait on barriers;
+    raises when a kernel gave up a wait.  Waits for the device, so it is called after a step."""
+    for what, reader in _error_readers:
+        word = ctypes.c_uint(0)
+        code = reader(ctypes.byref(word))
+        if code != 0:
+            raise BackendError(f"{what}: reading the error word failed (CUDA error {code})")
+        if word.value:
+            raise BackendError(f"{what}: a kernel gave up waiting (error word {word.value:#x}); the step's result is invalid")

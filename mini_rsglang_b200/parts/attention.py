@@ -50,11 +50,20 @@ def plan_attention_tiles(ctx, group: int):
     return plans[group]
 
 
-def choose_splits(tiles: int, nkv: int, longest_context: int) -> int:
-    """CTAs per tile in the keys mode: enough to fill the GPU twice, at least 256 keys each."""
+def choose_splits(tiles: int, nkv: int, longest_context: int, resident: int = 2) -> int:
+    """CTAs per tile in the keys mode.  Every CTA should get at least four 64-key blocks, and the
+    CTAs should fill the GPU's slots (`resident` per SM) in a whole number of rounds: among the
+    split counts up to 16, the smallest one within 3% of the best filling is taken."""
     blocks = -(-longest_context // 64)
-    want = -(-2 * SM_COUNT // max(tiles * nkv, 1))
-    return max(1, min(want, blocks // 4))
+    limit = max(1, min(16, blocks // 4))
+    slots = SM_COUNT * resident
+    best, best_fill = 1, 0.0
+    for splits in range(1, limit + 1):
+        ctas = tiles * nkv * splits
+        fill = ctas / (slots * -(-ctas // slots))
+        if fill > best_fill + 0.03:
+            best, best_fill = splits, fill
+    return best
 
 
 def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) -> None:
@@ -68,8 +77,11 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
         return
     narrow, wide, longest = plan_attention_tiles(ctx, group)
     if narrow is not None:
-        kernels.attention_mma_keys(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window,
-                                   choose_splits(narrow.shape[0], nkv, longest))
+        splits = choose_splits(narrow.shape[0], nkv, longest)
+        if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
+            kernels.attention_decode_tma(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
+        else:
+            kernels.attention_mma_keys(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
     if wide is not None:
         kernels.attention_mma_rows(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
 

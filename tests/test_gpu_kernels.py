@@ -208,7 +208,7 @@ class PagedCase:
 
     def run_mma(self, mode, splits=1):
         group = self.nq // self.nkv
-        per_tile = (16 if mode == "keys" else 64) // group
+        per_tile = (64 if mode == "rows" else 16) // group
         tiles = []
         for i in range(len(self.spans)):
             first, n = self.q_start[i], self.q_start[i + 1] - self.q_start[i]
@@ -220,6 +220,10 @@ class PagedCase:
                 self.dev(self.positions), self.dev(self.table), tiles, out, self.nq, self.nkv, self.d, self.window)
         if mode == "keys":
             kernels.attention_mma_keys(*args, splits=splits)
+        elif mode == "tma":
+            kernels.attention_decode_tma(*args, splits=splits)
+            torch.cuda.synchronize()
+            kernels.check_device_errors()
         else:
             kernels.attention_mma_rows(*args)
         return out
@@ -260,7 +264,34 @@ def test_attention_mma_keys_mode(nq, nkv, d, page, splits):
     close(case.run_mma("keys", splits), case.plain(), torch.bfloat16, f"attention_mma keys, {splits} splits")
 
 
-@pytest.mark.parametrize("runner", ["simt32", "simt16", "rows", "keys1", "keys7"])
+TMA_SHAPES = [(8, 2, 128, 16), (2, 1, 256, 32), (12, 2, 64, 64), (4, 4, 64, 8), (16, 1, 128, 128), (3, 1, 192, 16)]
+
+
+@pytest.mark.parametrize("splits", [1, 2, 5, 16])
+@pytest.mark.parametrize("nq,nkv,d,page", TMA_SHAPES)
+def test_attention_decode_tma(nq, nkv, d, page, splits):
+    """Head sizes 64 to 256, pages of 8 to 128 rows (a copy of a whole page, and of 64 rows of a
+    longer one), groups of 1 to 16 query heads."""
+    assert kernels.attention_decode_tma_supported(d, nq // nkv, page)
+    case = PagedCase(torch.bfloat16, nq, nkv, d, page, SPANS, seed=nq + d + splits)
+    close(case.run_mma("tma", splits), case.plain(), torch.bfloat16, f"attention_decode_tma, {splits} splits")
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100])
+def test_attention_decode_tma_window_edges(window):
+    case = PagedCase(torch.bfloat16, 4, 2, 64, 8, [(0, 130), (120, 1), (99, 2), (3, 4)], seed=window, window=window)
+    close(case.run_mma("tma", 1), case.plain(), torch.bfloat16, f"tma window {window}")
+    close(case.run_mma("tma", 3), case.plain(), torch.bfloat16, f"tma split window {window}")
+    # pages that the window has passed are gone from the table: the kernel must not need them
+    table = case.table.clone()
+    for i, (c, n) in enumerate(case.spans):
+        passed = max(0, c - window + 1) // case.page
+        case.table[i, :passed] = -1
+    close(case.run_mma("tma", 2), case.plain(), torch.bfloat16, f"tma window {window}, passed pages given back")
+    case.table = table
+
+
+@pytest.mark.parametrize("runner", ["simt32", "simt16", "rows", "keys1", "keys7", "tma1", "tma7"])
 def test_one_far_key_among_hundreds(runner):
     """One key far back scores far above the rest: the output must be that key's value row, so a
     kernel that skips, repeats or misplaces a block of keys cannot pass."""
@@ -281,7 +312,8 @@ def test_one_far_key_among_hundreds(runner):
                 rows = slice(lp * page, min(L, (lp + 1) * page))
                 case.kc[case.table[i, lp], :, :rows.stop - rows.start] = case.ks[i][rows].transpose(0, 1)
         got = {"simt32": case.run_simt, "simt16": case.run_simt, "rows": lambda: case.run_mma("rows"),
-               "keys1": lambda: case.run_mma("keys", 1), "keys7": lambda: case.run_mma("keys", 7)}[runner]()
+               "keys1": lambda: case.run_mma("keys", 1), "keys7": lambda: case.run_mma("keys", 7),
+               "tma1": lambda: case.run_mma("tma", 1), "tma7": lambda: case.run_mma("tma", 7)}[runner]()
         want_rows = torch.cat([case.vs[0][far].reshape(1, -1).repeat(1, 1)] +
                               [case.vs[1][far].reshape(1, -1)] * 12).double()
         want = want_rows.view(13, nkv, 1, d).expand(13, nkv, nq // nkv, d).reshape(13, nq * d)
@@ -297,6 +329,7 @@ def test_attention_refuses_what_it_cannot_do():
                                torch.empty(4, 128, device=DEV), 4, 2, 32)
     assert not kernels.attention_mma_supported(24, 1) and not kernels.attention_mma_supported(128, 128)
     assert kernels.attention_mma_supported(112, 7)
+    assert not kernels.attention_decode_tma_supported(48, 1, 16) and not kernels.attention_decode_tma_supported(128, 4, 4)
 
 
 # --------------------------------------------------------------------------------- sampling
