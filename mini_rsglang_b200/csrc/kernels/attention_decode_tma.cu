@@ -87,6 +87,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
         mbar_fence_init();
     }
     __syncthreads();
+    pdl_wait();                 // the newest keys and the queries come from the kernel before this one
+    pdl_launch_dependents();
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------------------------------ producer
@@ -278,6 +280,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
 __global__ void __launch_bounds__(128) attention_decode_combine_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, const Tile* __restrict__ tiles,
     bf16* __restrict__ out, int nq, int nkv, int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     const Tile tile = tiles[blockIdx.x];
     const int kv_head = blockIdx.y, group = nq / nkv, rows = tile.tokens * group;
     const size_t base_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS;
@@ -343,14 +347,14 @@ MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, co
     }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_tiles * nkv * splits * ROWS * D : nullptr;
-    attention_decode_kernel<<<dim3(num_tiles, nkv, splits), THREADS, SMEM_BYTES, (cudaStream_t)stream>>>(
+    MRS_LAUNCH(attention_decode_kernel, dim3(num_tiles, nkv, splits), THREADS, SMEM_BYTES, stream,
         *reinterpret_cast<const CUtensorMap*>(k_map), *reinterpret_cast<const CUtensorMap*>(v_map), (const bf16*)q,
         positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, part_o, part_ml, nq, nkv, page_size, shift,
         scale * 1.4426950408889634f, window, splits);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (splits > 1)
-        attention_decode_combine_kernel<<<dim3(num_tiles, nkv), 128, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(attention_decode_combine_kernel, dim3(num_tiles, nkv), 128, 0, stream,
             part_o, part_ml, (const Tile*)tiles, (bf16*)out, nq, nkv, splits);
     MRS_RETURN_LAUNCH_STATUS();
 }

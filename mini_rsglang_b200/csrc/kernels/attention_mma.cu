@@ -188,6 +188,8 @@ __global__ void __launch_bounds__(THREADS) attention_rows_kernel(
     const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
     const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv, int page_size, int page_shift,
     float scale_log2, int window) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_tiles = q_tile + ROWS_WIDE * D;
@@ -285,6 +287,8 @@ __global__ void __launch_bounds__(THREADS) attention_keys_kernel(
     const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
     const Tile* __restrict__ tiles, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nq, int nkv, int page_size, int page_shift, float scale_log2, int window, int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_tiles = q_tile + ROWS_NARROW * D;
@@ -407,6 +411,8 @@ __global__ void __launch_bounds__(THREADS) attention_keys_kernel(
 __global__ void __launch_bounds__(THREADS) attention_combine_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, const Tile* __restrict__ tiles,
     bf16* __restrict__ out, int nq, int nkv, int splits) {
+    pdl_wait();
+    pdl_launch_dependents();
     const Tile tile = tiles[blockIdx.x];
     const int kv_head = blockIdx.y, group = nq / nkv, rows = tile.tokens * group;
     const size_t base_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS_NARROW;
@@ -462,7 +468,7 @@ MRS_EXPORT int mrs_attention_mma_rows_mode(const void* q, const void* k_cache, c
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    attention_rows_kernel<<<dim3(num_tiles, nkv), THREADS, smem_rows, (cudaStream_t)stream>>>(
+    MRS_LAUNCH(attention_rows_kernel, dim3(num_tiles, nkv), THREADS, smem_rows, stream,
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, block_table, table_width,
         (const Tile*)tiles, (bf16*)out, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window);
     MRS_RETURN_LAUNCH_STATUS();
@@ -486,14 +492,14 @@ MRS_EXPORT int mrs_attention_mma_keys_mode(const void* q, const void* k_cache, c
     }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_tiles * nkv * splits * ROWS_NARROW * D : nullptr;
-    attention_keys_kernel<<<dim3(num_tiles, nkv, splits), THREADS, smem_keys, (cudaStream_t)stream>>>(
+    MRS_LAUNCH(attention_keys_kernel, dim3(num_tiles, nkv, splits), THREADS, smem_keys, stream,
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, block_table, table_width,
         (const Tile*)tiles, (bf16*)out, part_o, part_ml, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window,
         splits);
     cudaError_t e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (splits > 1)
-        attention_combine_kernel<<<dim3(num_tiles, nkv), THREADS, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(attention_combine_kernel, dim3(num_tiles, nkv), THREADS, 0, stream,
             part_o, part_ml, (const Tile*)tiles, (bf16*)out, nq, nkv, splits);
     MRS_RETURN_LAUNCH_STATUS();
 }
@@ -538,14 +544,14 @@ MRS_EXPORT int mrs_attention_mma_keys_mode_static_scratch(const void* q, const v
     }
     float* part_o = static_scratch_address[device];
     float* part_ml = part_o + (size_t)num_tiles * nkv * splits * ROWS_NARROW * D;
-    attention_keys_kernel<<<dim3(num_tiles, nkv, splits), THREADS, smem_keys, (cudaStream_t)stream>>>(
+    MRS_LAUNCH(attention_keys_kernel, dim3(num_tiles, nkv, splits), THREADS, smem_keys, stream,
         (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, block_table, table_width,
         (const Tile*)tiles, (bf16*)out, part_o, part_ml, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window,
         splits);
     e = cudaGetLastError();
     if (e != cudaSuccess) return (int)e;
     if (splits > 1)
-        attention_combine_kernel<<<dim3(num_tiles, nkv), THREADS, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(attention_combine_kernel, dim3(num_tiles, nkv), THREADS, 0, stream,
             part_o, part_ml, (const Tile*)tiles, (bf16*)out, nq, nkv, splits);
     MRS_RETURN_LAUNCH_STATUS();
 }

@@ -17,6 +17,8 @@ __global__ void attention_simt_kernel(const T* __restrict__ q, const T* __restri
                                       const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                                       T* __restrict__ out, int tokens, int nq, int nkv, int d, int page_size,
                                       int table_width, float scale, int window) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float q_s[ATTN_WARPS][ATTN_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * ATTN_WARPS + warp;
@@ -84,11 +86,11 @@ MRS_EXPORT int mrs_attention_simt(int is_bf16, const void* q, const void* k_cach
     const long long units = (long long)tokens * nq;
     const unsigned blocks = (unsigned)((units + ATTN_WARPS - 1) / ATTN_WARPS);
     if (is_bf16)
-        attention_simt_kernel<bf16><<<blocks, 32 * ATTN_WARPS, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(attention_simt_kernel<bf16>, blocks, 32 * ATTN_WARPS, 0, stream,
             (const bf16*)q, (const bf16*)k_cache, (const bf16*)v_cache, positions, seq_of_token, block_table,
             (bf16*)out, tokens, nq, nkv, d, page_size, table_width, scale, window);
     else
-        attention_simt_kernel<float><<<blocks, 32 * ATTN_WARPS, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(attention_simt_kernel<float>, blocks, 32 * ATTN_WARPS, 0, stream,
             (const float*)q, (const float*)k_cache, (const float*)v_cache, positions, seq_of_token, block_table,
             (float*)out, tokens, nq, nkv, d, page_size, table_width, scale, window);
     MRS_RETURN_LAUNCH_STATUS();

@@ -48,3 +48,40 @@ __device__ __forceinline__ float block_sum(float x, float* scratch) {
 
 // Status codes of the launchers' own argument checks (negative, so they cannot be CUDA codes).
 #define MRS_BAD_ARGUMENT (-2)
+
+// ------------------------------------------------------------------------------------------
+// Programmatic dependent launch.  Every kernel of the engine is launched with the attribute
+// that lets it start while the kernel before it in the stream is still running; it must call
+// pdl_wait() before it reads or writes anything that an earlier kernel may write or read
+// (after the wait the earlier kernels are complete and their memory is visible), and calls
+// pdl_launch_dependents() to let the kernel after it start in the same way.  What a kernel
+// does before its wait (barrier set-up, fetching weights) overlaps the end of its predecessor.
+// ------------------------------------------------------------------------------------------
+__device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
+template <typename... KernelArgs, typename... Args>
+static inline int mrs_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
+                             Args... args) {
+    cudaLaunchConfig_t config = {};
+    config.gridDim = grid;
+    config.blockDim = block;
+    config.dynamicSmemBytes = smem;
+    config.stream = stream;
+    cudaLaunchAttribute attribute;
+    attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    attribute.val.programmaticStreamSerializationAllowed = 1;
+    config.attrs = &attribute;
+    config.numAttrs = 1;
+    cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
+    if (e != cudaSuccess) return (int)e;
+    return (int)cudaGetLastError();
+}
+
+// Launches with the attribute above and returns from the enclosing launcher on failure.
+#define MRS_LAUNCH(kernel, grid, block, smem, stream, ...)                                                        \
+    do {                                                                                                          \
+        const int mrs_status_ = mrs_launch(kernel, dim3(grid), dim3(block), (size_t)(smem), (cudaStream_t)(stream), \
+                                           __VA_ARGS__);                                                          \
+        if (mrs_status_ != 0) return mrs_status_;                                                                 \
+    } while (0)

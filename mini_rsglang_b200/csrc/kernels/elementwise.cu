@@ -9,6 +9,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ residual, int width) {
+    pdl_wait();
+    pdl_launch_dependents();
     const int t = blockIdx.x;
     const T* row = table + (size_t)ids[t] * width;
     float* out = residual + (size_t)t * width;
@@ -20,9 +22,11 @@ MRS_EXPORT int mrs_embed(int is_bf16, const void* table, const int* ids, float* 
     if (tokens <= 0) return 0;
     const int threads = width >= 1024 ? 256 : 128;
     if (is_bf16)
-        embed_kernel<bf16><<<tokens, threads, 0, (cudaStream_t)stream>>>((const bf16*)table, ids, residual, width);
+        MRS_LAUNCH(embed_kernel<bf16>, tokens, threads, 0, stream,
+            (const bf16*)table, ids, residual, width);
     else
-        embed_kernel<float><<<tokens, threads, 0, (cudaStream_t)stream>>>((const float*)table, ids, residual, width);
+        MRS_LAUNCH(embed_kernel<float>, tokens, threads, 0, stream,
+            (const float*)table, ids, residual, width);
     MRS_RETURN_LAUNCH_STATUS();
 }
 
@@ -36,6 +40,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const float* __restrict__ weight, float eps, T* __restrict__ out,
                                    const int* __restrict__ rows, int width, int write_back) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
@@ -63,10 +69,10 @@ MRS_EXPORT int mrs_add_rmsnorm(int is_bf16, float* residual, const void* delta, 
     if (n_rows <= 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (is_bf16)
-        add_rmsnorm_kernel<bf16><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(add_rmsnorm_kernel<bf16>, n_rows, threads, 0, stream,
             residual, (const bf16*)delta, weight, eps, (bf16*)out, rows, width, write_back);
     else
-        add_rmsnorm_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(add_rmsnorm_kernel<float>, n_rows, threads, 0, stream,
             residual, (const float*)delta, weight, eps, (float*)out, rows, width, write_back);
     MRS_RETURN_LAUNCH_STATUS();
 }
@@ -75,6 +81,8 @@ MRS_EXPORT int mrs_add_rmsnorm(int is_bf16, float* residual, const void* delta, 
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ weight, float eps,
                                T* __restrict__ out, int width) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float scratch[33];
     const T* row = x + (size_t)blockIdx.x * width;
     float sum = 0.0f;
@@ -93,9 +101,11 @@ MRS_EXPORT int mrs_rmsnorm(int is_bf16, const void* x, const float* weight, floa
     if (n_rows <= 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
     if (is_bf16)
-        rmsnorm_kernel<bf16><<<n_rows, threads, 0, (cudaStream_t)stream>>>((const bf16*)x, weight, eps, (bf16*)out, width);
+        MRS_LAUNCH(rmsnorm_kernel<bf16>, n_rows, threads, 0, stream,
+            (const bf16*)x, weight, eps, (bf16*)out, width);
     else
-        rmsnorm_kernel<float><<<n_rows, threads, 0, (cudaStream_t)stream>>>((const float*)x, weight, eps, (float*)out, width);
+        MRS_LAUNCH(rmsnorm_kernel<float>, n_rows, threads, 0, stream,
+            (const float*)x, weight, eps, (float*)out, width);
     MRS_RETURN_LAUNCH_STATUS();
 }
 
@@ -116,6 +126,8 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, T* __restri
                                           const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                           float eps, const float* __restrict__ inv_freq,
                                           int tokens, int nq, int nkv, int d, int page_size, int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float stage[4][MRS_MAX_HEAD_DIM];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nq + 2 * nkv;
@@ -190,11 +202,11 @@ MRS_EXPORT int mrs_qk_norm_rope_store(int is_bf16, const void* qkv, void* q_out,
     const long long units = (long long)tokens * (nq + 2 * nkv);
     const unsigned blocks = (unsigned)((units + 3) / 4);
     if (is_bf16)
-        qk_norm_rope_store_kernel<bf16><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(qk_norm_rope_store_kernel<bf16>, blocks, 128, 0, stream,
             (const bf16*)qkv, (bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots, q_norm, k_norm,
             eps, inv_freq, tokens, nq, nkv, d, page_size, write_kv);
     else
-        qk_norm_rope_store_kernel<float><<<blocks, 128, 0, (cudaStream_t)stream>>>(
+        MRS_LAUNCH(qk_norm_rope_store_kernel<float>, blocks, 128, 0, stream,
             (const float*)qkv, (float*)q_out, (float*)k_cache, (float*)v_cache, positions, slots, q_norm, k_norm,
             eps, inv_freq, tokens, nq, nkv, d, page_size, write_kv);
     MRS_RETURN_LAUNCH_STATUS();
@@ -206,6 +218,8 @@ MRS_EXPORT int mrs_qk_norm_rope_store(int is_bf16, const void* qkv, void* q_out,
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter) {
+    pdl_wait();
+    pdl_launch_dependents();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const long long t = i / inter;
@@ -223,9 +237,11 @@ MRS_EXPORT int mrs_silu_mul(int is_bf16, const void* gate_up, void* out, int tok
     long long want = (total + threads - 1) / threads;
     const unsigned blocks = (unsigned)(want > 148 * 16 ? 148 * 16 : want);
     if (is_bf16)
-        silu_mul_kernel<bf16><<<blocks, threads, 0, (cudaStream_t)stream>>>((const bf16*)gate_up, (bf16*)out, total, inter);
+        MRS_LAUNCH(silu_mul_kernel<bf16>, blocks, threads, 0, stream,
+            (const bf16*)gate_up, (bf16*)out, total, inter);
     else
-        silu_mul_kernel<float><<<blocks, threads, 0, (cudaStream_t)stream>>>((const float*)gate_up, (float*)out, total, inter);
+        MRS_LAUNCH(silu_mul_kernel<float>, blocks, threads, 0, stream,
+            (const float*)gate_up, (float*)out, total, inter);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

@@ -11,6 +11,8 @@
 
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
                                                        float* __restrict__ C, int M, int N, int K) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ float a_s[GF_BK][GF_BM + 4];
     __shared__ float w_s[GF_BK][GF_BN + 4];
     const int tid = threadIdx.x;
@@ -62,6 +64,7 @@ MRS_EXPORT int mrs_gemm_f32(const float* A, const float* W, float* C, int M, int
     if (K <= 0) return MRS_BAD_ARGUMENT;
     dim3 grid((N + GF_BN - 1) / GF_BN, (M + GF_BM - 1) / GF_BM);
     if (grid.y > 65535) return MRS_BAD_ARGUMENT;
-    gemm_f32_kernel<<<grid, 256, 0, (cudaStream_t)stream>>>(A, W, C, M, N, K);
+    MRS_LAUNCH(gemm_f32_kernel, grid, 256, 0, stream,
+        A, W, C, M, N, K);
     MRS_RETURN_LAUNCH_STATUS();
 }

@@ -1,0 +1,315 @@
+// Matrix products out[M, N] = x[M, K] . w[N, K]^T for few rows (M <= 128: decoded tokens and
+// short portions), bfloat16 in, float32 accumulation, on the tcgen05 tensor cores.
+//
+// With few rows the product is bound by reading the weights once from HBM, so the kernel is a
+// weight streamer: the roles of the operands are swapped (128 weight rows are the M of the MMA,
+// the tokens its N, padded to 16/32/64/128), a producer warp fetches 128 x 64 weight tiles and
+// the matching slice of x with bulk tensor copies (TMA, 128-byte swizzle) into a ring of
+// shared-memory stages, one thread issues tcgen05.mma on the stages into an accumulator in
+// tensor memory, and four warps read finished accumulators back and store them transposed.
+// CTAs are persistent: each walks its share of the work units (a unit = 128 weight rows x a
+// range of K), with two accumulators in tensor memory, so copies and MMAs of the next unit run
+// while the last one is stored.
+//
+// K is cut into `splits` ranges so that the units fill all SMs evenly.  The cut depends on N
+// and K alone and partial sums are added in the order of the ranges by whichever CTA finishes
+// a tile last, so a row's result does not depend on M or on what else is in the batch, bit for
+// bit.                       (reference: cuBLAS in 32-row blocks, crates/kernels/src/lib.rs:241-322)
+#include "tcgen05.cuh"
+
+namespace {
+
+constexpr int TILE_N = 128;          // weight rows of a unit: the M of the MMA
+constexpr int BLOCK_K = 64;          // one 128-byte swizzled row of bfloat16
+constexpr int UMMA_K = 16;
+constexpr int THREADS = 192;         // warp 0: copies, warp 1: MMA, warps 2..5: accumulator to memory
+constexpr int W_TILE_BYTES = TILE_N * BLOCK_K * 2;
+
+template <int MPAD> struct Shape {
+    static constexpr int X_TILE_BYTES = MPAD * BLOCK_K * 2;
+    static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
+    static constexpr int STAGES = MPAD <= 32 ? 8 : (MPAD <= 64 ? 6 : 5);
+    static constexpr int TMEM_COLUMNS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
+    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16;
+};
+
+__device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
+
+template <int MPAD, typename OutT>
+__global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
+    const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map, OutT* __restrict__ out,
+    float* __restrict__ partials, int* __restrict__ counters, int M, int N, int K, int splits) {
+    using S = Shape<MPAD>;
+    extern __shared__ unsigned char smem_raw[];
+    unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
+    uint64_t* full = reinterpret_cast<uint64_t*>(smem + S::STAGES * S::STAGE_BYTES);
+    uint64_t* empty = full + S::STAGES;
+    uint64_t* acc_full = empty + S::STAGES;
+    uint64_t* acc_empty = acc_full + 2;
+    uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    __shared__ int is_last;
+
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    const int n_tiles = (N + TILE_N - 1) / TILE_N;
+    const int units = n_tiles * splits;
+
+    if (threadIdx.x == 0) {
+        for (int s = 0; s < S::STAGES; ++s) {
+            mbar_init(&full[s], 1);
+            mbar_init(&empty[s], 1);
+        }
+        for (int b = 0; b < 2; ++b) {
+            mbar_init(&acc_full[b], 1);
+            mbar_init(&acc_empty[b], 4);
+        }
+        mbar_fence_init();
+    }
+    if (warp == 1) {
+        tmem_alloc(tmem_slot, S::TMEM_COLUMNS);
+        tmem_relinquish_alloc_permit();
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    tcgen05_fence_after_sync();
+    const uint32_t tmem_base = *tmem_slot;
+    pdl_launch_dependents();
+
+    if (warp == 0) {
+        // ------------------------------------------------------------------ copies
+        if (lane == 0) {
+            tma_prefetch_descriptor(&w_map);
+            tma_prefetch_descriptor(&x_map);
+            // The weights do not depend on the kernel before this one: the first ring of weight tiles is
+            // asked for at once, and only the activations wait for that kernel to finish.
+            int it = 0;
+            int first_kb[S::STAGES];
+            bool waited = false;
+            for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+                const int tile = unit / splits, split = unit % splits;
+                const int kb0 = (int)((long long)split * k_blocks / splits), kb1 = (int)((long long)(split + 1) * k_blocks / splits);
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % S::STAGES;
+                    if (it == S::STAGES && !waited) {      // the ring is full of weights: now the activations
+                        pdl_wait();
+                        waited = true;
+                        for (int j = 0; j < S::STAGES; ++j)
+                            tma_load_2d(smem + j * S::STAGE_BYTES + W_TILE_BYTES, &x_map, &full[j], first_kb[j] * BLOCK_K, 0);
+                    }
+                    if (waited) mbar_wait(&empty[s], ((it / S::STAGES) & 1) ^ 1);
+                    mbar_arrive_expect_tx(&full[s], S::STAGE_BYTES);
+                    unsigned char* stage = smem + s * S::STAGE_BYTES;
+                    tma_load_2d(stage, &w_map, &full[s], kb * BLOCK_K, tile * TILE_N);
+                    if (waited) tma_load_2d(stage + W_TILE_BYTES, &x_map, &full[s], kb * BLOCK_K, 0);
+                    else first_kb[it] = kb;
+                }
+            }
+            if (!waited) {                                  // fewer blocks than stages
+                pdl_wait();
+                for (int j = 0; j < it; ++j)
+                    tma_load_2d(smem + j * S::STAGE_BYTES + W_TILE_BYTES, &x_map, &full[j], first_kb[j] * BLOCK_K, 0);
+            }
+        }
+    } else if (warp == 1) {
+        // ------------------------------------------------------------------ MMA
+        if (lane == 0) {
+            constexpr uint32_t idesc = umma_idesc_bf16_f32(TILE_N, MPAD);
+            int it = 0, round = 0;
+            for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++round) {
+                const int split = unit % splits;
+                const int kb0 = (int)((long long)split * k_blocks / splits), kb1 = (int)((long long)(split + 1) * k_blocks / splits);
+                const int buffer = round & 1;
+                mbar_wait(&acc_empty[buffer], ((round >> 1) & 1) ^ 1);
+                tcgen05_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + buffer * MPAD;
+                for (int kb = kb0; kb < kb1; ++kb, ++it) {
+                    const int s = it % S::STAGES;
+                    mbar_wait(&full[s], (it / S::STAGES) & 1);
+                    tcgen05_fence_after_sync();
+                    const uint32_t w_addr = smem_u32(smem + s * S::STAGE_BYTES), x_addr = w_addr + W_TILE_BYTES;
+#pragma unroll
+                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
+                        umma_bf16(d_tmem, umma_smem_desc_sw128(w_addr + k * UMMA_K * 2), umma_smem_desc_sw128(x_addr + k * UMMA_K * 2),
+                                  idesc, kb > kb0 || k > 0);
+                    umma_commit(&empty[s]);          // the stage is free once these MMAs have read it
+                }
+                umma_commit(&acc_full[buffer]);
+            }
+        }
+    } else {
+        // ------------------------------------------------------------------ accumulator -> memory
+        const int quarter = warp & 3;                      // the TMEM lanes this warp may read
+        const int row = quarter * 32 + lane;               // weight row within the tile
+        const int epi_thread = (warp - 2) * 32 + lane;
+        pdl_wait();                                        // `out`, `partials` and `counters` may still be in use before
+        int round = 0;
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++round) {
+            const int tile = unit / splits;
+            const int buffer = round & 1;
+            mbar_wait(&acc_full[buffer], (round >> 1) & 1);
+            tcgen05_fence_after_sync();
+            float acc[MPAD];
+#pragma unroll
+            for (int c = 0; c < MPAD; c += 16) {
+                float v[16];
+                tmem_load_16(tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * MPAD + c, v);
+#pragma unroll
+                for (int i = 0; i < 16; ++i) acc[c + i] = v[i];
+            }
+            tcgen05_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) mbar_arrive(&acc_empty[buffer]);      // the MMA warp may overwrite this accumulator
+
+            const int n = tile * TILE_N + row;
+            if (splits == 1) {
+                if (n < N) {
+#pragma unroll
+                    for (int m = 0; m < MPAD; ++m)
+                        if (m < M) out[(size_t)m * N + n] = from_float<OutT>(acc[m]);
+                }
+                continue;
+            }
+            // partial sums of this range of K, then: the CTA that finishes the tile last adds all ranges in order
+            constexpr int V = MPAD / 4;                                   // float4s of a padded row
+            constexpr int RANGES_AT_ONCE = MPAD == 16 ? 4 : (MPAD == 32 ? 2 : 1);
+            const int m4 = (M + 3) >> 2;
+            float4* mine = reinterpret_cast<float4*>(partials) + ((size_t)unit * TILE_N + row) * m4;
+#pragma unroll
+            for (int j = 0; j < V; ++j)
+                if (j < m4) __stcg(mine + j, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
+            __threadfence();
+            epilogue_sync();
+            if (epi_thread == 0) {
+                const int arrived = atomicAdd(&counters[tile], 1);
+                is_last = arrived == splits - 1;
+                if (is_last) counters[tile] = 0;           // ready for the next launch
+            }
+            epilogue_sync();
+            if (is_last) {
+                __threadfence();
+                if (n < N) {
+                    const float4* first = reinterpret_cast<const float4*>(partials) + ((size_t)tile * splits * TILE_N + row) * m4;
+                    float4 sum[V];
+#pragma unroll
+                    for (int j = 0; j < V; ++j) sum[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    for (int s0 = 0; s0 < splits; s0 += RANGES_AT_ONCE) {
+                        float4 v[RANGES_AT_ONCE][V];                      // all loads of a pass are in flight together
+#pragma unroll
+                        for (int u = 0; u < RANGES_AT_ONCE; ++u)
+#pragma unroll
+                            for (int j = 0; j < V; ++j)
+                                v[u][j] = (s0 + u < splits && j < m4) ? __ldcg(first + (size_t)(s0 + u) * TILE_N * m4 + j)
+                                                                      : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+                        for (int u = 0; u < RANGES_AT_ONCE; ++u)
+#pragma unroll
+                            for (int j = 0; j < V; ++j) {
+                                sum[j].x += v[u][j].x;
+                                sum[j].y += v[u][j].y;
+                                sum[j].z += v[u][j].z;
+                                sum[j].w += v[u][j].w;
+                            }
+                    }
+#pragma unroll
+                    for (int j = 0; j < V; ++j) {
+                        const float e[4] = {sum[j].x, sum[j].y, sum[j].z, sum[j].w};
+#pragma unroll
+                        for (int i = 0; i < 4; ++i)
+                            if (4 * j + i < M) out[(size_t)(4 * j + i) * N + n] = from_float<OutT>(e[i]);
+                    }
+                }
+            }
+            epilogue_sync();                               // `is_last` is rewritten in the next round
+        }
+    }
+    tcgen05_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        tcgen05_fence_after_sync();
+        tmem_dealloc(tmem_base, S::TMEM_COLUMNS);
+    }
+}
+
+template <int MPAD, typename OutT>
+int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, void* out, float* partials, int* counters, int M, int N,
+           int K, int splits, int ctas, cudaStream_t stream) {
+    using S = Shape<MPAD>;
+    static bool configured = false;
+    if (!configured) {
+        cudaError_t e = cudaFuncSetAttribute(gemm_small_m_kernel<MPAD, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
+        if (e != cudaSuccess) return (int)e;
+        configured = true;
+    }
+    return mrs_launch(gemm_small_m_kernel<MPAD, OutT>, dim3(ctas), dim3(THREADS), S::SMEM_BYTES, stream, *w_map, *x_map,
+                      (OutT*)out, partials, counters, M, N, K, splits);
+}
+
+}  // namespace
+
+// A tensor map of a row-major bfloat16 matrix [rows, cols] for copies of `box_rows` rows x 64 columns.
+MRS_EXPORT int mrs_gemm_tc_map(const void* base, long long rows, long long cols, int box_rows, void* map_out) {
+    if (rows <= 0 || cols <= 0 || cols % 8 || box_rows <= 0 || box_rows > 256 || ((uintptr_t)base & 15)) return MRS_BAD_ARGUMENT;
+    const uint64_t dims[2] = {(uint64_t)cols, (uint64_t)rows};
+    const uint64_t strides[1] = {(uint64_t)cols * 2};
+    const uint32_t box[2] = {BLOCK_K, (uint32_t)box_rows};
+    return mrs_make_tensor_map_bf16(reinterpret_cast<CUtensorMap*>(map_out), base, 2, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
+}
+
+// Ranges of K for a weight matrix [N, K] on a GPU with `sms` SMs, by a count of the time an SM
+// spends: rounds of units x (64-column blocks of a unit + a unit's fixed cost + the cost of
+// leaving and adding partial sums when there are several ranges).  It depends on N, K and the
+// GPU alone, never on the rows of the product.
+MRS_EXPORT int mrs_gemm_tc_splits(int N, int K, int sms) {
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K, n_tiles = (N + TILE_N - 1) / TILE_N;
+    int limit = k_blocks / 4;
+    limit = limit < 1 ? 1 : (limit > 16 ? 16 : limit);
+    int best = 1;
+    long long best_cost = -1;
+    for (int s = 1; s <= limit; ++s) {
+        const long long rounds = ((long long)n_tiles * s + sms - 1) / sms;
+        const long long cost = rounds * ((k_blocks + s - 1) / s + 2 + (s > 1 ? 2 : 0));
+        if (best_cost < 0 || cost < best_cost) best = s, best_cost = cost;
+    }
+    return best;
+}
+
+// Floats of `partials` and ints of `counters` (zeroed once by the caller) that a product needs.
+MRS_EXPORT long long mrs_gemm_tc_partial_floats(int M, int N, int splits) {
+    return splits <= 1 ? 0 : (long long)((N + TILE_N - 1) / TILE_N) * splits * TILE_N * ((M + 3) / 4 * 4);
+}
+MRS_EXPORT int mrs_gemm_tc_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
+
+// out[M, N] = x . w^T.  `w_map`: mrs_gemm_tc_map(w, N, K, 128); `x_map`: mrs_gemm_tc_map(x, M, K, mpad) with
+// mpad = 16, 32, 64 or 128 >= M.  `out` is bfloat16 or float32 [M, N].  `ctas`: CTAs to launch (the GPU's SMs).
+MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* out, int out_is_f32, float* partials,
+                                   int* counters, int M, int N, int K, int splits, int mpad, int ctas, void* stream) {
+    if (M <= 0 || N <= 0) return 0;
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    if (K <= 0 || K % 8 || M > mpad || splits < 1 || splits > k_blocks || ctas < 1) return MRS_BAD_ARGUMENT;
+    if (splits > 1 && (!partials || !counters)) return MRS_BAD_ARGUMENT;
+    const int units = ((N + TILE_N - 1) / TILE_N) * splits;
+    if (ctas > units) ctas = units;
+    const CUtensorMap* wm = reinterpret_cast<const CUtensorMap*>(w_map);
+    const CUtensorMap* xm = reinterpret_cast<const CUtensorMap*>(x_map);
+    cudaStream_t st = (cudaStream_t)stream;
+#define MRS_GEMM_CASE(P)                                                                                              \
+    case P:                                                                                                           \
+        return out_is_f32 ? launch<P, float>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st)              \
+                          : launch<P, bf16>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);
+    switch (mpad) {
+        MRS_GEMM_CASE(16)
+        MRS_GEMM_CASE(32)
+        MRS_GEMM_CASE(64)
+        MRS_GEMM_CASE(128)
+    }
+#undef MRS_GEMM_CASE
+    return MRS_BAD_ARGUMENT;
+}
+
+MRS_EXPORT int mrs_gemm_tc_take_error(unsigned int* word) { return mrs_take_error_word(word); }
+
+MRS_EXPORT const char* mrs_gemm_tc_error_string(int code) {
+    if (code == MRS_BAD_ARGUMENT) return "arguments outside what the kernel supports (K no multiple of 8, M above the padded size, unaligned base, splits)";
+    if (code == MRS_TENSOR_MAP_FAILED) return "the driver refused the tensor map (address, sizes or strides)";
+    return cudaGetErrorString((cudaError_t)code);
+}

@@ -179,6 +179,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
     const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
     const int* __restrict__ draw_index, int* __restrict__ out) {
+    pdl_wait();
+    pdl_launch_dependents();
     __shared__ SampleShared s;
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;
@@ -355,7 +357,8 @@ MRS_EXPORT int mrs_sample(const float* logits, int rows, int vocab, const float*
                           void* stream) {
     if (rows <= 0) return 0;
     if (vocab <= 0) return MRS_BAD_ARGUMENT;
-    sample_kernel<<<rows, SAMPLE_THREADS, 0, (cudaStream_t)stream>>>(logits, vocab, temperature, top_k, top_p, seed,
+    MRS_LAUNCH(sample_kernel, rows, SAMPLE_THREADS, 0, stream,
+        logits, vocab, temperature, top_k, top_p, seed,
                                                                      draw_index, out);
     MRS_RETURN_LAUNCH_STATUS();
 }

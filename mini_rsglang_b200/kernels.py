@@ -248,11 +248,17 @@ def attention_mma_library(d: int) -> ctypes.CDLL:
     return _attention_libs[d]
 
 
+_retired: list[torch.Tensor] = []     # outgrown scratch buffers: recorded steps may still point at them
+
+
 def attention_scratch(device: torch.device, floats: int) -> torch.Tensor:
-    """Scratch memory for split attention, kept and grown per device."""
+    """Scratch memory for split attention, kept and grown per device.  A buffer that is outgrown
+    is never freed: a step recorded earlier replays with its address."""
     have = _scratch.get(device)
     if have is None or have.numel() < floats:
-        have = torch.empty(max(floats, 1 << 20), dtype=torch.float32, device=device)
+        if have is not None:
+            _retired.append(have)
+        have = torch.empty(max(2 * floats, 1 << 22), dtype=torch.float32, device=device)
         _scratch[device] = have
     return have
 
@@ -384,6 +390,108 @@ def attention_decode_tma(q, k_cache, v_cache, positions, block_table, tiles, out
     launch_count += 1
     if code != 0:
         raise BackendError(f"attention_decode_tma: {lib.mrs_attention_decode_tma_error_string(code).decode()} (code {code})")
+
+
+# ------------------------------------------------------------------------------------------------
+# tcgen05 matrix product for few rows (decoded tokens, short portions)
+# ------------------------------------------------------------------------------------------------
+_gemm_lib = None
+_weight_maps: dict[tuple, tuple] = {}
+_gemm_state: dict[torch.device, dict] = {}
+GEMM_TC_MAX_ROWS = 128          # what the kernel takes
+GEMM_TC_BEST_ROWS = 32          # beyond this the library product is faster for now (the split sums are added by one CTA)
+
+
+def gemm_tc_library() -> ctypes.CDLL:
+    global _gemm_lib
+    if _gemm_lib is None:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        lib = specialised_kernel_library("gemm_tc.cu", {})
+        lib.mrs_gemm_tc_map.argtypes = [_c_vp, ctypes.c_longlong, ctypes.c_longlong, _c_int, _c_vp]
+        lib.mrs_gemm_tc_map.restype = _c_int
+        lib.mrs_gemm_tc_splits.argtypes = [_c_int, _c_int, _c_int]
+        lib.mrs_gemm_tc_splits.restype = _c_int
+        lib.mrs_gemm_tc_partial_floats.argtypes = [_c_int, _c_int, _c_int]
+        lib.mrs_gemm_tc_partial_floats.restype = ctypes.c_longlong
+        lib.mrs_gemm_tc_counters.argtypes = [_c_int]
+        lib.mrs_gemm_tc_counters.restype = _c_int
+        lib.mrs_gemm_tc_small_m.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int,
+                                            _c_int, _c_vp]
+        lib.mrs_gemm_tc_small_m.restype = _c_int
+        lib.mrs_gemm_tc_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        lib.mrs_gemm_tc_take_error.restype = _c_int
+        lib.mrs_gemm_tc_error_string.argtypes = [_c_int]
+        lib.mrs_gemm_tc_error_string.restype = ctypes.c_char_p
+        _gemm_lib = lib
+        _error_readers.append(("gemm_tc", lib.mrs_gemm_tc_take_error))
+    return _gemm_lib
+
+
+def gemm_tc_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Few rows, bfloat16, rows of a multiple of 8 elements on 16-byte boundaries: what the bulk
+    tensor copies need."""
+    return (x.dtype is torch.bfloat16 and weight.dtype is torch.bfloat16 and 0 < x.shape[0] <= GEMM_TC_MAX_ROWS
+            and x.shape[1] % 8 == 0 and x.data_ptr() % 16 == 0 and weight.data_ptr() % 16 == 0)
+
+
+def _gemm_device_state(device: torch.device) -> dict:
+    state = _gemm_state.get(device)
+    if state is None:
+        state = {"sms": torch.cuda.get_device_properties(device).multi_processor_count,
+                 "counters": torch.zeros(4096, dtype=torch.int32, device=device),
+                 "partials": torch.empty(1 << 24, dtype=torch.float32, device=device),
+                 "x_map": _aligned_block(128, 64)}
+        _gemm_state[device] = state
+    return state
+
+
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
+    """out[M, N] = x[M, K] . weight[N, K]^T for M <= 128; bfloat16 in, float32 sums, `out` bfloat16 or float32."""
+    m, k = x.shape
+    n = weight.shape[0]
+    _need(x, torch.bfloat16, "gemm input")
+    _need(weight, torch.bfloat16, "gemm weight", (n, k))
+    _need(out, None, "gemm out", (m, n))
+    if out.dtype not in (torch.bfloat16, torch.float32):
+        raise InvalidRequest("gemm out must be bfloat16 or float32")
+    if m > GEMM_TC_MAX_ROWS:
+        raise InvalidRequest(f"gemm_tc takes at most {GEMM_TC_MAX_ROWS} rows, got {m}")
+    lib = gemm_tc_library()
+    state = _gemm_device_state(x.device)
+
+    def fail(code, what):
+        raise BackendError(f"{what}: {lib.mrs_gemm_tc_error_string(code).decode()} (code {code})")
+
+    key = (weight.data_ptr(), n, k)
+    if key not in _weight_maps:
+        keep, address = _aligned_block(128, 64)
+        code = lib.mrs_gemm_tc_map(weight.data_ptr(), n, k, 128, address)
+        if code != 0:
+            fail(code, "tensor map of a weight")
+        _weight_maps[key] = (keep, address, lib.mrs_gemm_tc_splits(n, k, state["sms"]))
+    _, w_map, splits = _weight_maps[key]
+    mpad = 16 if m <= 16 else (32 if m <= 32 else (64 if m <= 64 else 128))
+    x_map = state["x_map"][1]
+    code = lib.mrs_gemm_tc_map(x.data_ptr(), m, k, mpad, x_map)
+    if code != 0:
+        fail(code, "tensor map of the activations")
+    if splits > 1:
+        need = lib.mrs_gemm_tc_partial_floats(m, n, splits)
+        if state["partials"].numel() < need:       # outgrown buffers stay alive: recorded steps hold their addresses
+            _retired.append(state["partials"])
+            state["partials"] = torch.empty(2 * int(need), dtype=torch.float32, device=x.device)
+        tiles = lib.mrs_gemm_tc_counters(n)
+        if state["counters"].numel() < tiles:
+            _retired.append(state["counters"])
+            state["counters"] = torch.zeros(2 * tiles, dtype=torch.int32, device=x.device)
+    global launch_count
+    launch_count += 1
+    code = lib.mrs_gemm_tc_small_m(w_map, x_map, out.data_ptr(), int(out.dtype is torch.float32),
+                                   state["partials"].data_ptr(), state["counters"].data_ptr(), m, n, k, splits, mpad,
+                                   state["sms"], _stream())
+    if code != 0:
+        fail(code, "gemm_tc")
 
 
 # ------------------------------------------------------------------------------------------------

@@ -332,6 +332,44 @@ def test_attention_refuses_what_it_cannot_do():
     assert not kernels.attention_decode_tma_supported(48, 1, 16) and not kernels.attention_decode_tma_supported(128, 4, 4)
 
 
+# --------------------------------------------------------------------------------- tcgen05 product
+@pytest.mark.parametrize("out_dtype", [torch.bfloat16, torch.float32])
+@pytest.mark.parametrize("m,n,k", [(1, 7, 8), (8, 128, 64), (16, 300, 72), (17, 1000, 1000), (64, 4096, 4096),
+                                   (100, 257, 136), (128, 6144, 520), (3, 24576, 4096)])
+def test_gemm_tc(m, n, k, out_dtype):
+    """Rows up to 128 (every padded size), widths and depths that are no multiples of the tiles,
+    one and several ranges of K."""
+    g = torch.Generator().manual_seed(m + n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    assert kernels.gemm_tc_supported(x.to(DEV), w.to(DEV))
+    out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    kernels.gemm_tc(x.to(DEV), w.to(DEV), out)
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    close(out, x.double() @ w.double().T, out_dtype, f"gemm_tc {m}x{n}x{k}")
+
+
+def test_gemm_tc_rows_do_not_depend_on_the_batch():
+    """The same row alone, among 8 and among 100 others: equal bit for bit, twice in a row (the
+    counters of the ranges of K are left ready for the next launch)."""
+    g = torch.Generator().manual_seed(5)
+    n, k = 4096, 4096
+    x = torch.randn(100, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / 64).to(torch.bfloat16).to(DEV)
+    outs = []
+    for m in (1, 8, 100, 1):
+        out = torch.empty((m, n), dtype=torch.float32, device=DEV)
+        kernels.gemm_tc(x[:m].contiguous(), w, out)
+        outs.append(out[0].clone())
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    for other in outs[1:]:
+        assert torch.equal(outs[0], other)
+    assert not kernels.gemm_tc_supported(x[:, :100].contiguous(), w[:, :100].contiguous())      # rows of 200 bytes
+    assert not kernels.gemm_tc_supported(torch.zeros(129, 64, dtype=torch.bfloat16, device=DEV), w[:, :64].contiguous())
+
+
 # --------------------------------------------------------------------------------- sampling
 def test_argmax_takes_the_smaller_id_on_a_tie():
     logits = torch.randn(6, 1000, device=DEV)
