@@ -11,7 +11,7 @@
 //
 // Work is cut as in the plain tensor-core kernel: a tile is up to 16 / group consecutive tokens
 // of one request; `splits` CTAs share the 64-key blocks of a tile and leave unnormalised partial
-// results in scratch memory, which `combine` merges.
+// results in scratch memory; the CTA that finishes a (tile, head) last merges them in order.
 #include "tma.cuh"
 
 #ifndef MRS_HEAD_DIM
@@ -58,8 +58,9 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
     const bf16* __restrict__ q, const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
     const Tile* __restrict__ tiles, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int nq, int nkv, int page_size, int page_shift, float scale_log2, int window, int splits) {
+    int* __restrict__ counters, int nq, int nkv, int page_size, int page_shift, float scale_log2, int window, int splits) {
     extern __shared__ unsigned char smem_raw[];
+    __shared__ int is_last;
     const Tile tile = tiles[blockIdx.x];
     if (tile.tokens <= 0) return;                    // a padding entry of the tile list
     // stages start on a 1024-byte boundary: the swizzle pattern of the copies is a function of the address
@@ -249,6 +250,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
         }
     }
     consumer_sync();
+    const size_t first_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS;
     for (int idx = threadIdx.x; idx < rows * D; idx += 32 * CONSUMER_WARPS) {
         const int row = idx / D, col = idx % D;
         float m = -CUDART_INF_F;
@@ -266,39 +268,59 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
             out[((size_t)(tile.first_token + row / group) * nq + kv_head * group + row % group) * D + col] =
                 __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
         } else {
-            const size_t slot = (((size_t)blockIdx.x * nkv + kv_head) * splits + split) * ROWS + row;
-            part_o[slot * D + col] = acc;
+            const size_t slot = first_slot + (size_t)split * ROWS + row;
+            __stcg(&part_o[slot * D + col], acc);
             if (col == 0) {
-                part_ml[slot * 2] = m;
-                part_ml[slot * 2 + 1] = sum;
+                __stcg(&part_ml[slot * 2], m);
+                __stcg(&part_ml[slot * 2 + 1], sum);
             }
         }
     }
-}
+    if (splits == 1) return;
 
-// Merges the `splits` partial results of every (tile, kv head, row).
-__global__ void __launch_bounds__(128) attention_decode_combine_kernel(
-    const float* __restrict__ part_o, const float* __restrict__ part_ml, const Tile* __restrict__ tiles,
-    bf16* __restrict__ out, int nq, int nkv, int splits) {
-    pdl_wait();
-    pdl_launch_dependents();
-    const Tile tile = tiles[blockIdx.x];
-    const int kv_head = blockIdx.y, group = nq / nkv, rows = tile.tokens * group;
-    const size_t base_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS;
-    for (int idx = threadIdx.x; idx < rows * D; idx += blockDim.x) {
-        const int row = idx / D, col = idx % D;
+    // The CTA that leaves its share last merges all shares of this (tile, head), in the order of the shares.
+    __threadfence();
+    consumer_sync();
+    if (threadIdx.x == 0) {
+        int* counter = &counters[blockIdx.x * nkv + kv_head];
+        const int arrived = atomicAdd(counter, 1);
+        is_last = arrived == splits - 1;
+        if (is_last) *counter = 0;                   // ready for the next launch
+    }
+    consumer_sync();
+    if (!is_last) return;
+    __threadfence();
+    float* all_ml = reinterpret_cast<float*>(smem);  // [splits][rows][2]: running max and sum of every share
+    for (int idx = threadIdx.x; idx < splits * rows * 2; idx += 32 * CONSUMER_WARPS) {
+        const int s = idx / (rows * 2), rest = idx % (rows * 2);
+        all_ml[idx] = __ldcg(&part_ml[(first_slot + (size_t)s * ROWS) * 2 + rest]);
+    }
+    consumer_sync();
+    for (int idx = threadIdx.x; idx < rows * (D / 4); idx += 32 * CONSUMER_WARPS) {
+        const int row = idx / (D / 4), col = (idx % (D / 4)) * 4;
         float m = -CUDART_INF_F;
-        for (int s = 0; s < splits; ++s) m = fmaxf(m, part_ml[(base_slot + (size_t)s * ROWS + row) * 2]);
+        for (int s = 0; s < splits; ++s) m = fmaxf(m, all_ml[(s * rows + row) * 2]);
         const float base = m == -CUDART_INF_F ? 0.0f : m;
-        float sum = 0.0f, acc = 0.0f;
-        for (int s = 0; s < splits; ++s) {
-            const size_t slot = base_slot + (size_t)s * ROWS + row;
-            const float f = exp2f(part_ml[slot * 2] - base);
-            sum += part_ml[slot * 2 + 1] * f;
-            acc += part_o[slot * D + col] * f;
+        float sum = 0.0f;
+        float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        for (int s0 = 0; s0 < splits; s0 += 4) {
+            float4 v[4];
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                v[u] = s0 + u < splits ? __ldcg(reinterpret_cast<const float4*>(&part_o[(first_slot + (size_t)(s0 + u) * ROWS + row) * D + col]))
+                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+#pragma unroll
+            for (int u = 0; u < 4; ++u)
+                if (s0 + u < splits) {
+                    const float f = exp2f(all_ml[((s0 + u) * rows + row) * 2] - base);
+                    sum += all_ml[((s0 + u) * rows + row) * 2 + 1] * f;
+                    acc.x += v[u].x * f, acc.y += v[u].y * f, acc.z += v[u].z * f, acc.w += v[u].w * f;
+                }
         }
-        out[((size_t)(tile.first_token + row / group) * nq + kv_head * group + row % group) * D + col] =
-            __float2bfloat16_rn(sum > 0.0f ? acc / sum : 0.0f);
+        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+        bf16* dst = out + ((size_t)(tile.first_token + row / group) * nq + kv_head * group + row % group) * D + col;
+        *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+        *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
     }
 }
 
@@ -328,17 +350,18 @@ MRS_EXPORT long long mrs_attention_decode_tma_scratch_floats(int tiles, int nkv,
     return splits <= 1 ? 0 : (long long)tiles * nkv * splits * ROWS * (D + 2);
 }
 
-// Tiles of up to 16 / group tokens each; `splits` CTAs share a tile's keys.  `scratch` must hold
-// mrs_attention_decode_tma_scratch_floats(...) floats when splits > 1.
+// Tiles of up to 16 / group tokens each; `splits` (at most 256) CTAs share a tile's keys.  With
+// splits > 1, `scratch` must hold mrs_attention_decode_tma_scratch_floats(...) floats and `counters`
+// num_tiles * nkv ints that are zero before the first launch (the kernel leaves them zero).
 MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, const void* q, const int* positions,
                                         const int* block_table, int table_width, const int* tiles, int num_tiles,
-                                        void* out, float* scratch, int nq, int nkv, int page_size, float scale,
-                                        int window, int splits, void* stream) {
+                                        void* out, float* scratch, int* counters, int nq, int nkv, int page_size,
+                                        float scale, int window, int splits, void* stream) {
     if (num_tiles <= 0) return 0;
     const int shift = page_shift_of(page_size);
-    if (shift < 0 || page_size < 8 || nkv <= 0 || nq % nkv || nq / nkv > ROWS || splits < 1 || splits > 65535)
+    if (shift < 0 || page_size < 8 || nkv <= 0 || nq % nkv || nq / nkv > ROWS || splits < 1 || splits > 256)
         return MRS_BAD_ARGUMENT;
-    if (splits > 1 && !scratch) return MRS_BAD_ARGUMENT;
+    if (splits > 1 && (!scratch || !counters)) return MRS_BAD_ARGUMENT;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
@@ -349,13 +372,8 @@ MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, co
     float* part_ml = scratch ? scratch + (size_t)num_tiles * nkv * splits * ROWS * D : nullptr;
     MRS_LAUNCH(attention_decode_kernel, dim3(num_tiles, nkv, splits), THREADS, SMEM_BYTES, stream,
         *reinterpret_cast<const CUtensorMap*>(k_map), *reinterpret_cast<const CUtensorMap*>(v_map), (const bf16*)q,
-        positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, part_o, part_ml, nq, nkv, page_size, shift,
-        scale * 1.4426950408889634f, window, splits);
-    cudaError_t e = cudaGetLastError();
-    if (e != cudaSuccess) return (int)e;
-    if (splits > 1)
-        MRS_LAUNCH(attention_decode_combine_kernel, dim3(num_tiles, nkv), 128, 0, stream,
-            part_o, part_ml, (const Tile*)tiles, (bf16*)out, nq, nkv, splits);
+        positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, part_o, part_ml, counters, nq, nkv, page_size,
+        shift, scale * 1.4426950408889634f, window, splits);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

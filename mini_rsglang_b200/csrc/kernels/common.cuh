@@ -4,6 +4,7 @@
 #include <cuda_runtime.h>
 #include <math_constants.h>
 #include <stdint.h>
+#include <stdlib.h>
 
 typedef __nv_bfloat16 bf16;
 
@@ -71,8 +72,9 @@ static inline int mrs_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 bloc
     cudaLaunchAttribute attribute;
     attribute.id = cudaLaunchAttributeProgrammaticStreamSerialization;
     attribute.val.programmaticStreamSerializationAllowed = 1;
+    static const bool plain = getenv("MRS_PLAIN_LAUNCH") != nullptr;    // for measuring what the overlap gives
     config.attrs = &attribute;
-    config.numAttrs = 1;
+    config.numAttrs = plain ? 0 : 1;
     cudaError_t e = cudaLaunchKernelEx(&config, kernel, static_cast<KernelArgs>(args)...);
     if (e != cudaSuccess) return (int)e;
     return (int)cudaGetLastError();

@@ -217,31 +217,33 @@ MRS_EXPORT int mrs_qk_norm_rope_store(int is_bf16, const void* qkv, void* q_out,
 //   (reference: ops.cu:91-94)
 // ---------------------------------------------------------------------------------------------
 template <typename T>
-__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter) {
+__global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter, int block) {
     pdl_wait();
     pdl_launch_dependents();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const long long t = i / inter;
         const int c = (int)(i % inter);
-        const float g = to_float(gate_up[t * 2 * inter + c]);
-        const float u = to_float(gate_up[t * 2 * inter + inter + c]);
+        // all gate columns, then all up columns; or blocks of gate columns each followed by its up columns
+        const long long gate_at = block ? (long long)(c / block) * 2 * block + c % block : c;
+        const long long up_at = block ? gate_at + block : (long long)inter + c;
+        const float g = to_float(gate_up[t * 2 * inter + gate_at]);
+        const float u = to_float(gate_up[t * 2 * inter + up_at]);
         out[i] = from_float<T>(g / (1.0f + expf(-g)) * u);
     }
 }
 
-MRS_EXPORT int mrs_silu_mul(int is_bf16, const void* gate_up, void* out, int tokens, int inter, void* stream) {
+MRS_EXPORT int mrs_silu_mul(int is_bf16, const void* gate_up, void* out, int tokens, int inter, int block, void* stream) {
     const long long total = (long long)tokens * inter;
     if (total <= 0) return 0;
+    if (block < 0 || (block && inter % block)) return MRS_BAD_ARGUMENT;
     const int threads = 256;
     long long want = (total + threads - 1) / threads;
     const unsigned blocks = (unsigned)(want > 148 * 16 ? 148 * 16 : want);
     if (is_bf16)
-        MRS_LAUNCH(silu_mul_kernel<bf16>, blocks, threads, 0, stream,
-            (const bf16*)gate_up, (bf16*)out, total, inter);
+        MRS_LAUNCH(silu_mul_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total, inter, block);
     else
-        MRS_LAUNCH(silu_mul_kernel<float>, blocks, threads, 0, stream,
-            (const float*)gate_up, (float*)out, total, inter);
+        MRS_LAUNCH(silu_mul_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total, inter, block);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

@@ -30,12 +30,13 @@ template <int MPAD> struct Shape {
     static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
     static constexpr int STAGES = MPAD <= 32 ? 8 : (MPAD <= 64 ? 6 : 5);
     static constexpr int TMEM_COLUMNS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
-    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16;
+    static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16 +
+                                         (size_t)MPAD * 64 * sizeof(float);
 };
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
-template <int MPAD, typename OutT>
+template <int MPAD, typename OutT, bool GATED>
 __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
     const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map, OutT* __restrict__ out,
     float* __restrict__ partials, int* __restrict__ counters, int M, int N, int K, int splits) {
@@ -47,6 +48,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
     uint64_t* acc_full = empty + S::STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
+    float* exchange = reinterpret_cast<float*>(tmem_slot + 4);        // [MPAD][64], gated epilogue only
     __shared__ int is_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -161,37 +163,30 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
             if (lane == 0) mbar_arrive(&acc_empty[buffer]);      // the MMA warp may overwrite this accumulator
 
             const int n = tile * TILE_N + row;
-            if (splits == 1) {
-                if (n < N) {
+            bool finished = splits == 1;                  // does this CTA hold the tile's final sums?
+            if (splits > 1) {
+                // partial sums of this range of K, then: the CTA that finishes the tile last adds all ranges in order
+                constexpr int V = MPAD / 4;                                   // float4s of a padded row
+                constexpr int RANGES_AT_ONCE = MPAD == 16 ? 4 : (MPAD == 32 ? 2 : 1);
+                const int m4 = (M + 3) >> 2;
+                float4* mine = reinterpret_cast<float4*>(partials) + ((size_t)unit * TILE_N + row) * m4;
 #pragma unroll
-                    for (int m = 0; m < MPAD; ++m)
-                        if (m < M) out[(size_t)m * N + n] = from_float<OutT>(acc[m]);
-                }
-                continue;
-            }
-            // partial sums of this range of K, then: the CTA that finishes the tile last adds all ranges in order
-            constexpr int V = MPAD / 4;                                   // float4s of a padded row
-            constexpr int RANGES_AT_ONCE = MPAD == 16 ? 4 : (MPAD == 32 ? 2 : 1);
-            const int m4 = (M + 3) >> 2;
-            float4* mine = reinterpret_cast<float4*>(partials) + ((size_t)unit * TILE_N + row) * m4;
-#pragma unroll
-            for (int j = 0; j < V; ++j)
-                if (j < m4) __stcg(mine + j, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
-            __threadfence();
-            epilogue_sync();
-            if (epi_thread == 0) {
-                const int arrived = atomicAdd(&counters[tile], 1);
-                is_last = arrived == splits - 1;
-                if (is_last) counters[tile] = 0;           // ready for the next launch
-            }
-            epilogue_sync();
-            if (is_last) {
+                for (int j = 0; j < V; ++j)
+                    if (j < m4) __stcg(mine + j, make_float4(acc[4 * j], acc[4 * j + 1], acc[4 * j + 2], acc[4 * j + 3]));
                 __threadfence();
-                if (n < N) {
+                epilogue_sync();
+                if (epi_thread == 0) {
+                    const int arrived = atomicAdd(&counters[tile], 1);
+                    is_last = arrived == splits - 1;
+                    if (is_last) counters[tile] = 0;           // ready for the next launch
+                }
+                epilogue_sync();
+                finished = is_last;
+                if (finished) {
+                    __threadfence();
                     const float4* first = reinterpret_cast<const float4*>(partials) + ((size_t)tile * splits * TILE_N + row) * m4;
-                    float4 sum[V];
 #pragma unroll
-                    for (int j = 0; j < V; ++j) sum[j] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+                    for (int m = 0; m < MPAD; ++m) acc[m] = 0.0f;
                     for (int s0 = 0; s0 < splits; s0 += RANGES_AT_ONCE) {
                         float4 v[RANGES_AT_ONCE][V];                      // all loads of a pass are in flight together
 #pragma unroll
@@ -204,19 +199,36 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
                         for (int u = 0; u < RANGES_AT_ONCE; ++u)
 #pragma unroll
                             for (int j = 0; j < V; ++j) {
-                                sum[j].x += v[u][j].x;
-                                sum[j].y += v[u][j].y;
-                                sum[j].z += v[u][j].z;
-                                sum[j].w += v[u][j].w;
+                                acc[4 * j] += v[u][j].x;
+                                acc[4 * j + 1] += v[u][j].y;
+                                acc[4 * j + 2] += v[u][j].z;
+                                acc[4 * j + 3] += v[u][j].w;
                             }
                     }
+                }
+            }
+            if (finished) {
+                if (GATED) {
+                    // the tile's rows 0..63 are gate rows, rows 64..127 the matching up rows: the upper half
+                    // hands its sums over and the lower half writes silu(gate) * up, 64 columns of [M, N / 2]
+                    if (row >= 64) {
 #pragma unroll
-                    for (int j = 0; j < V; ++j) {
-                        const float e[4] = {sum[j].x, sum[j].y, sum[j].z, sum[j].w};
-#pragma unroll
-                        for (int i = 0; i < 4; ++i)
-                            if (4 * j + i < M) out[(size_t)(4 * j + i) * N + n] = from_float<OutT>(e[i]);
+                        for (int m = 0; m < MPAD; ++m)
+                            if (m < M) exchange[m * 64 + row - 64] = acc[m];
                     }
+                    epilogue_sync();
+                    if (row < 64) {
+#pragma unroll
+                        for (int m = 0; m < MPAD; ++m)
+                            if (m < M) {
+                                const float g = acc[m], u = exchange[m * 64 + row];
+                                out[(size_t)m * (N >> 1) + tile * 64 + row] = from_float<OutT>(g / (1.0f + __expf(-g)) * u);
+                            }
+                    }
+                } else if (n < N) {
+#pragma unroll
+                    for (int m = 0; m < MPAD; ++m)
+                        if (m < M) out[(size_t)m * N + n] = from_float<OutT>(acc[m]);
                 }
             }
             epilogue_sync();                               // `is_last` is rewritten in the next round
@@ -230,17 +242,17 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
     }
 }
 
-template <int MPAD, typename OutT>
+template <int MPAD, typename OutT, bool GATED>
 int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, void* out, float* partials, int* counters, int M, int N,
            int K, int splits, int ctas, cudaStream_t stream) {
     using S = Shape<MPAD>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_small_m_kernel<MPAD, OutT>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_small_m_kernel<MPAD, OutT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return mrs_launch(gemm_small_m_kernel<MPAD, OutT>, dim3(ctas), dim3(THREADS), S::SMEM_BYTES, stream, *w_map, *x_map,
+    return mrs_launch(gemm_small_m_kernel<MPAD, OutT, GATED>, dim3(ctas), dim3(THREADS), S::SMEM_BYTES, stream, *w_map, *x_map,
                       (OutT*)out, partials, counters, M, N, K, splits);
 }
 
@@ -281,8 +293,11 @@ MRS_EXPORT int mrs_gemm_tc_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
 
 // out[M, N] = x . w^T.  `w_map`: mrs_gemm_tc_map(w, N, K, 128); `x_map`: mrs_gemm_tc_map(x, M, K, mpad) with
 // mpad = 16, 32, 64 or 128 >= M.  `out` is bfloat16 or float32 [M, N].  `ctas`: CTAs to launch (the GPU's SMs).
-MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* out, int out_is_f32, float* partials,
-                                   int* counters, int M, int N, int K, int splits, int mpad, int ctas, void* stream) {
+// With `gated`, w holds in every block of 128 rows 64 gate rows followed by the 64 matching up rows (N a
+// multiple of 128), and out[M, N / 2] = silu(x . gate^T) * (x . up^T), bfloat16.
+MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* out, int out_is_f32, int gated,
+                                   float* partials, int* counters, int M, int N, int K, int splits, int mpad, int ctas,
+                                   void* stream) {
     if (M <= 0 || N <= 0) return 0;
     const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     if (K <= 0 || K % 8 || M > mpad || splits < 1 || splits > k_blocks || ctas < 1) return MRS_BAD_ARGUMENT;
@@ -292,10 +307,12 @@ MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* o
     const CUtensorMap* wm = reinterpret_cast<const CUtensorMap*>(w_map);
     const CUtensorMap* xm = reinterpret_cast<const CUtensorMap*>(x_map);
     cudaStream_t st = (cudaStream_t)stream;
+    if (gated && (out_is_f32 || N % TILE_N)) return MRS_BAD_ARGUMENT;
 #define MRS_GEMM_CASE(P)                                                                                              \
     case P:                                                                                                           \
-        return out_is_f32 ? launch<P, float>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st)              \
-                          : launch<P, bf16>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);
+        if (gated) return launch<P, bf16, true>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);          \
+        return out_is_f32 ? launch<P, float, false>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st)       \
+                          : launch<P, bf16, false>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);
     switch (mpad) {
         MRS_GEMM_CASE(16)
         MRS_GEMM_CASE(32)

@@ -22,7 +22,7 @@ _SIGNATURES = {
     "mrs_rmsnorm": [_c_int, _c_vp, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_vp],
     "mrs_qk_norm_rope_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp,
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
-    "mrs_silu_mul": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_silu_mul": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_attention_simt": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
                            _c_int, _c_int, _c_float, _c_int, _c_vp],
     "mrs_gemm_f32": [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
@@ -155,12 +155,16 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Te
                                             page_size, int(write_kv), _stream()), "qk_norm_rope_store")
 
 
-def silu_mul(gate_up: torch.Tensor, out: torch.Tensor) -> None:
+def silu_mul(gate_up: torch.Tensor, out: torch.Tensor, block: int = 0) -> None:
+    """out = silu(gate) * up.  `gate_up` holds all gate columns and then all up columns (block 0), or
+    alternating blocks of `block` gate columns and the `block` matching up columns."""
     tokens, inter = out.shape
     _need(gate_up, out.dtype, "gate_up", (tokens, 2 * inter))
     _need(out, None, "silu_mul out")
-    _check(library().mrs_silu_mul(_is_bf16(out.dtype), gate_up.data_ptr(), out.data_ptr(), tokens, inter, _stream()),
-           "silu_mul")
+    if block < 0 or (block and inter % block):
+        raise InvalidRequest("silu_mul: the width is no multiple of the block")
+    _check(library().mrs_silu_mul(_is_bf16(out.dtype), gate_up.data_ptr(), out.data_ptr(), tokens, inter, int(block),
+                                  _stream()), "silu_mul")
 
 
 def attention_simt(q: torch.Tensor, k_cache: torch.Tensor, v_cache: torch.Tensor, positions: torch.Tensor,
@@ -263,6 +267,21 @@ def attention_scratch(device: torch.device, floats: int) -> torch.Tensor:
     return have
 
 
+_counters: dict[torch.device, torch.Tensor] = {}
+
+
+def attention_counters(device: torch.device, count: int) -> torch.Tensor:
+    """Zeroed ints by which the CTAs of a split attention find out which of them is last; the
+    kernel leaves them zero.  Outgrown buffers stay alive like the scratch."""
+    have = _counters.get(device)
+    if have is None or have.numel() < count:
+        if have is not None:
+            _retired.append(have)
+        have = torch.zeros(max(2 * count, 4096), dtype=torch.int32, device=device)
+        _counters[device] = have
+    return have
+
+
 def _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d):
     tokens = q.shape[0]
     _need(q, torch.bfloat16, "q", (tokens, nq * d))
@@ -331,8 +350,8 @@ def attention_decode_tma_library(d: int) -> ctypes.CDLL:
         lib = specialised_kernel_library("attention_decode_tma.cu", {"MRS_HEAD_DIM": d})
         lib.mrs_attention_decode_tma_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
         lib.mrs_attention_decode_tma_map.restype = _c_int
-        lib.mrs_attention_decode_tma.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int,
-                                                 _c_float, _c_int, _c_int, _c_vp]
+        lib.mrs_attention_decode_tma.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int,
+                                                 _c_int, _c_float, _c_int, _c_int, _c_vp]
         lib.mrs_attention_decode_tma.restype = _c_int
         lib.mrs_attention_decode_tma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.mrs_attention_decode_tma_scratch_floats.restype = ctypes.c_longlong
@@ -374,6 +393,7 @@ def attention_decode_tma(q, k_cache, v_cache, positions, block_table, tiles, out
     global launch_count
     _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
     lib = attention_decode_tma_library(d)
+    counters = None
     if splits > 1:
         need = lib.mrs_attention_decode_tma_scratch_floats(tiles.shape[0], nkv, splits)
         if scratch is None:
@@ -381,10 +401,11 @@ def attention_decode_tma(q, k_cache, v_cache, positions, block_table, tiles, out
         _need(scratch, torch.float32, "attention scratch")
         if scratch.numel() < need:
             raise InvalidRequest(f"attention scratch holds {scratch.numel()} floats, {need} are needed")
-        launch_count += 1          # the combine kernel
+        counters = attention_counters(q.device, tiles.shape[0] * nkv)
     code = lib.mrs_attention_decode_tma(kv_tensor_map(k_cache), kv_tensor_map(v_cache), q.data_ptr(), positions.data_ptr(),
                                         block_table.data_ptr(), block_table.shape[1], tiles.data_ptr(), tiles.shape[0],
-                                        out.data_ptr(), _ptr(scratch) if splits > 1 else None, nq, nkv, k_cache.shape[2],
+                                        out.data_ptr(), _ptr(scratch) if splits > 1 else None, _ptr(counters), nq, nkv,
+                                        k_cache.shape[2],
                                         float(scale if scale is not None else 1.0 / math.sqrt(d)), int(window),
                                         int(splits), _stream())
     launch_count += 1
@@ -416,8 +437,8 @@ def gemm_tc_library() -> ctypes.CDLL:
         lib.mrs_gemm_tc_partial_floats.restype = ctypes.c_longlong
         lib.mrs_gemm_tc_counters.argtypes = [_c_int]
         lib.mrs_gemm_tc_counters.restype = _c_int
-        lib.mrs_gemm_tc_small_m.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_int,
-                                            _c_int, _c_vp]
+        lib.mrs_gemm_tc_small_m.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
+                                            _c_int, _c_int, _c_vp]
         lib.mrs_gemm_tc_small_m.restype = _c_int
         lib.mrs_gemm_tc_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         lib.mrs_gemm_tc_take_error.restype = _c_int
@@ -446,13 +467,20 @@ def _gemm_device_state(device: torch.device) -> dict:
     return state
 
 
-def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
-    """out[M, N] = x[M, K] . weight[N, K]^T for M <= 128; bfloat16 in, float32 sums, `out` bfloat16 or float32."""
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+    """out[M, N] = x[M, K] . weight[N, K]^T for M <= 128; bfloat16 in, float32 sums, `out` bfloat16 or float32.
+    With `gated`, `weight` holds, in every block of 128 rows, 64 gate rows and then the 64 matching up rows, and
+    out[M, N / 2] = silu(x . gate^T) * (x . up^T) in bfloat16."""
     m, k = x.shape
     n = weight.shape[0]
     _need(x, torch.bfloat16, "gemm input")
     _need(weight, torch.bfloat16, "gemm weight", (n, k))
-    _need(out, None, "gemm out", (m, n))
+    if gated:
+        if n % 128:
+            raise InvalidRequest("a gated product needs whole blocks of 64 gate and 64 up rows")
+        _need(out, torch.bfloat16, "gemm out", (m, n // 2))
+    else:
+        _need(out, None, "gemm out", (m, n))
     if out.dtype not in (torch.bfloat16, torch.float32):
         raise InvalidRequest("gemm out must be bfloat16 or float32")
     if m > GEMM_TC_MAX_ROWS:
@@ -487,7 +515,7 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) -> None:
             state["counters"] = torch.zeros(2 * tiles, dtype=torch.int32, device=x.device)
     global launch_count
     launch_count += 1
-    code = lib.mrs_gemm_tc_small_m(w_map, x_map, out.data_ptr(), int(out.dtype is torch.float32),
+    code = lib.mrs_gemm_tc_small_m(w_map, x_map, out.data_ptr(), int(out.dtype is torch.float32), int(gated),
                                    state["partials"].data_ptr(), state["counters"].data_ptr(), m, n, k, splits, mpad,
                                    state["sms"], _stream())
     if code != 0:

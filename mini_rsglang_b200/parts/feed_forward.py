@@ -26,14 +26,27 @@ class SwiGLU(FeedForward):
                 WeightSpec(self.name("up_proj.weight"), (self.inner, self.width)),
                 WeightSpec(self.name("down_proj.weight"), (self.width, self.inner))]
 
+    BLOCK = 64     # gate rows of a 128-row weight tile of the tensor-core product; the other 64 are the up rows
+
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        self.gate_up = torch.cat([tensors[self.name("gate_proj.weight")], tensors[self.name("up_proj.weight")]],
-                                 dim=0).contiguous()
+        gate, up = tensors[self.name("gate_proj.weight")], tensors[self.name("up_proj.weight")]
+        # When serving in bfloat16 and the width allows it, blocks of 64 gate rows alternate with the 64
+        # matching up rows: a weight tile of the product for few rows then holds both halves of its outputs,
+        # and the product applies silu(gate) * up before it stores.
+        self.block = self.BLOCK if runtime.is_bf16 and self.inner % self.BLOCK == 0 else 0
+        if self.block:
+            b = self.block
+            self.gate_up = torch.stack([gate.view(-1, b, self.width), up.view(-1, b, self.width)], dim=1) \
+                .reshape(2 * self.inner, self.width).contiguous()
+        else:
+            self.gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.down = tensors[self.name("down_proj.weight")].contiguous()
 
     def forward(self, h, ctx):
-        gate_up = linear(h, self.gate_up)
         act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
-        kernels.silu_mul(gate_up, act)
+        if self.block and h.shape[0] <= kernels.GEMM_TC_BEST_ROWS and kernels.gemm_tc_supported(h, self.gate_up):
+            kernels.gemm_tc(h, self.gate_up, act, gated=True)
+        else:
+            kernels.silu_mul(linear(h, self.gate_up), act, self.block)
         return linear(act, self.down)

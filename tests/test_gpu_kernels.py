@@ -350,6 +350,30 @@ def test_gemm_tc(m, n, k, out_dtype):
     close(out, x.double() @ w.double().T, out_dtype, f"gemm_tc {m}x{n}x{k}")
 
 
+@pytest.mark.parametrize("m,inner,k", [(1, 64, 72), (8, 128, 64), (19, 3072, 1024), (32, 192, 4096), (100, 12288, 520)])
+def test_gemm_tc_gated(m, inner, k):
+    """silu(x . gate^T) * (x . up^T) out of one product over weights in blocks of 64 gate and 64 up rows;
+    the same result as the product followed by the kernel that does it alone."""
+    g = torch.Generator().manual_seed(m + inner)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(inner, k, generator=g) / k ** 0.5 * 2).to(torch.bfloat16)
+    up = (torch.randn(inner, k, generator=g) / k ** 0.5 * 2).to(torch.bfloat16)
+    mixed = torch.stack([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k).contiguous()
+    out = torch.full((m, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc(x.to(DEV), mixed.to(DEV), out, gated=True)
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    gd, ud = x.double() @ gate.double().T, x.double() @ up.double().T
+    want = gd / (1 + torch.exp(-gd)) * ud
+    close(out, want, torch.bfloat16, f"gated gemm_tc {m}x{inner}x{k}")
+    both = torch.cat([gd.unsqueeze(0), ud.unsqueeze(0)])      # the kernel alone on the blocked layout
+    blocked = torch.stack([gd.view(m, -1, 64), ud.view(m, -1, 64)], dim=2).reshape(m, 2 * inner).to(torch.bfloat16).to(DEV)
+    alone = torch.empty((m, inner), dtype=torch.bfloat16, device=DEV)
+    kernels.silu_mul(blocked, alone, 64)
+    close(alone, want, torch.bfloat16, "silu_mul on blocks of 64")
+    del both
+
+
 def test_gemm_tc_rows_do_not_depend_on_the_batch():
     """The same row alone, among 8 and among 100 others: equal bit for bit, twice in a row (the
     counters of the ranges of K are left ready for the next launch)."""
