@@ -149,6 +149,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
             const int tile = unit / splits;
             const int buffer = round & 1;
             mbar_wait(&acc_full[buffer], (round >> 1) & 1);
+            __syncwarp();                    // the loads from tensor memory are collective
             tcgen05_fence_after_sync();
             float acc[MPAD];
 #pragma unroll

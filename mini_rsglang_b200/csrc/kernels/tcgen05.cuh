@@ -39,11 +39,27 @@ __device__ __forceinline__ uint64_t umma_smem_desc_sw128(uint32_t address) {
     return desc;
 }
 
-// kind::f16 with bfloat16 A and B (both K-major) and a float32 accumulator of m x n.
-__host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int m, int n) {
+// A tile of k rows x n bfloat16 whose rows run along N (MN-major: what a copy of [keys][head size]
+// gives a product that contracts over the keys): 64 columns (128 bytes) a row in the same swizzle,
+// groups of 8 rows 1024 bytes apart, the next 64 columns `column_group_stride` bytes further.
+// `address` moves by 16 rows (2048 bytes) for every 16 elements of K.
+__device__ __forceinline__ uint64_t umma_smem_desc_sw128_mn(uint32_t address, uint32_t column_group_stride) {
+    uint64_t desc = 0;
+    desc |= (uint64_t)((address & 0x3FFFF) >> 4);
+    desc |= (uint64_t)((column_group_stride >> 4) & 0x3FFF) << 16;   // leading dimension: between groups of 64 columns
+    desc |= (uint64_t)(1024 >> 4) << 32;                             // stride dimension: between groups of 8 rows
+    desc |= (uint64_t)1 << 46;
+    desc |= (uint64_t)2 << 61;
+    return desc;
+}
+
+// kind::f16 with bfloat16 A and B and a float32 accumulator of m x n.  A is K-major; B is K-major
+// unless `b_mn_major`.
+__host__ __device__ constexpr uint32_t umma_idesc_bf16_f32(int m, int n, bool b_mn_major = false) {
     return (1u << 4)                     // D: float32
            | (1u << 7)                   // A: bfloat16
            | (1u << 10)                  // B: bfloat16
+           | ((b_mn_major ? 1u : 0u) << 16)
            | ((uint32_t)(n >> 3) << 17)  // N / 8
            | ((uint32_t)(m >> 4) << 24); // M / 16
 }
@@ -70,3 +86,28 @@ __device__ __forceinline__ void tmem_load_16(uint32_t address, float (&v)[16]) {
 #pragma unroll
     for (int i = 0; i < 16; ++i) v[i] = __uint_as_float(r[i]);
 }
+
+// 32 consecutive columns of this thread's lane.
+__device__ __forceinline__ void tmem_load_32(uint32_t address, float* v) {
+    uint32_t r[32];
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x32.b32 "
+                 "{%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16,%17,%18,%19,%20,%21,%22,%23,%24,%25,%26,%27,%28,%29,%30,%31}, [%32];"
+                 : "=r"(r[0]), "=r"(r[1]), "=r"(r[2]), "=r"(r[3]), "=r"(r[4]), "=r"(r[5]), "=r"(r[6]), "=r"(r[7]),
+                   "=r"(r[8]), "=r"(r[9]), "=r"(r[10]), "=r"(r[11]), "=r"(r[12]), "=r"(r[13]), "=r"(r[14]), "=r"(r[15]),
+                   "=r"(r[16]), "=r"(r[17]), "=r"(r[18]), "=r"(r[19]), "=r"(r[20]), "=r"(r[21]), "=r"(r[22]), "=r"(r[23]),
+                   "=r"(r[24]), "=r"(r[25]), "=r"(r[26]), "=r"(r[27]), "=r"(r[28]), "=r"(r[29]), "=r"(r[30]), "=r"(r[31])
+                 : "r"(address) : "memory");
+    asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory");
+#pragma unroll
+    for (int i = 0; i < 32; ++i) v[i] = __uint_as_float(r[i]);
+}
+// Writes 16 consecutive columns of this thread's lane.
+__device__ __forceinline__ void tmem_store_16(uint32_t address, const float (&v)[16]) {
+    asm volatile("tcgen05.st.sync.aligned.32x32b.x16.b32 [%0], {%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15,%16};"
+                 ::"r"(address), "r"(__float_as_uint(v[0])), "r"(__float_as_uint(v[1])), "r"(__float_as_uint(v[2])),
+                   "r"(__float_as_uint(v[3])), "r"(__float_as_uint(v[4])), "r"(__float_as_uint(v[5])), "r"(__float_as_uint(v[6])),
+                   "r"(__float_as_uint(v[7])), "r"(__float_as_uint(v[8])), "r"(__float_as_uint(v[9])), "r"(__float_as_uint(v[10])),
+                   "r"(__float_as_uint(v[11])), "r"(__float_as_uint(v[12])), "r"(__float_as_uint(v[13])), "r"(__float_as_uint(v[14])),
+                   "r"(__float_as_uint(v[15])) : "memory");
+}
+__device__ __forceinline__ void tmem_store_wait() { asm volatile("tcgen05.wait::st.sync.aligned;" ::: "memory"); }

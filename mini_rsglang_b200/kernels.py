@@ -414,6 +414,74 @@ def attention_decode_tma(q, k_cache, v_cache, positions, block_table, tiles, out
 
 
 # ------------------------------------------------------------------------------------------------
+# tcgen05 attention for prompt portions, one library per head size (64, 128)
+# ------------------------------------------------------------------------------------------------
+_prefill_libs: dict[int, ctypes.CDLL] = {}
+_prefill_kv_maps: dict[tuple, tuple] = {}
+_prefill_q_map: dict[torch.device, tuple] = {}
+PREFILL_TC_ROWS = 128
+
+
+def attention_prefill_tc_supported(d: int, group: int, page_size: int) -> bool:
+    return d in (64, 128) and PREFILL_TC_ROWS % group == 0 and page_size >= 8
+
+
+def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
+    if d not in _prefill_libs:
+        if not torch.cuda.is_available():
+            raise BackendError("no CUDA device: the engine has no CPU path")
+        lib = specialised_kernel_library("attention_prefill_tc.cu", {"MRS_HEAD_DIM": d})
+        lib.mrs_attention_prefill_tc_kv_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
+        lib.mrs_attention_prefill_tc_q_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
+        lib.mrs_attention_prefill_tc.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_int, _c_int, _c_int, _c_float,
+                                                 _c_int, _c_vp]
+        for name in ("mrs_attention_prefill_tc_kv_map", "mrs_attention_prefill_tc_q_map", "mrs_attention_prefill_tc"):
+            getattr(lib, name).restype = _c_int
+        lib.mrs_attention_prefill_tc_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
+        lib.mrs_attention_prefill_tc_take_error.restype = _c_int
+        lib.mrs_attention_prefill_tc_error_string.argtypes = [_c_int]
+        lib.mrs_attention_prefill_tc_error_string.restype = ctypes.c_char_p
+        _prefill_libs[d] = lib
+        _error_readers.append((f"attention_prefill_tc (head size {d})", lib.mrs_attention_prefill_tc_take_error))
+    return _prefill_libs[d]
+
+
+def attention_prefill_tc(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int,
+                         window: int = 0, scale: float | None = None) -> None:
+    """Tiles of up to 128 // (nq // nkv) tokens of one request each, on the tcgen05 tensor cores."""
+    global launch_count
+    _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
+    lib = attention_prefill_tc_library(d)
+
+    def fail(code, what):
+        raise BackendError(f"{what}: {lib.mrs_attention_prefill_tc_error_string(code).decode()} (code {code})")
+
+    maps = []
+    for cache in (k_cache, v_cache):
+        key = (cache.data_ptr(), tuple(cache.shape))
+        if key not in _prefill_kv_maps:
+            keep, address = _aligned_block(128, 64)
+            code = lib.mrs_attention_prefill_tc_kv_map(cache.data_ptr(), cache.shape[0], nkv, cache.shape[2], address)
+            if code != 0:
+                fail(code, "tensor map of the cache")
+            _prefill_kv_maps[key] = (keep, address)
+        maps.append(_prefill_kv_maps[key][1])
+    if q.device not in _prefill_q_map:
+        _prefill_q_map[q.device] = _aligned_block(128, 64)
+    q_map = _prefill_q_map[q.device][1]
+    code = lib.mrs_attention_prefill_tc_q_map(q.data_ptr(), q.shape[0], nq, nq // nkv, q_map)
+    if code != 0:
+        fail(code, "tensor map of the queries")
+    launch_count += 1
+    code = lib.mrs_attention_prefill_tc(q_map, maps[0], maps[1], positions.data_ptr(), block_table.data_ptr(),
+                                        block_table.shape[1], tiles.data_ptr(), tiles.shape[0], out.data_ptr(), nq, nkv,
+                                        k_cache.shape[2], float(scale if scale is not None else 1.0 / math.sqrt(d)),
+                                        int(window), _stream())
+    if code != 0:
+        fail(code, "attention_prefill_tc")
+
+
+# ------------------------------------------------------------------------------------------------
 # tcgen05 matrix product for few rows (decoded tokens, short portions)
 # ------------------------------------------------------------------------------------------------
 _gemm_lib = None

@@ -19,20 +19,22 @@ from .linear import linear
 SM_COUNT = 148
 
 
-def plan_attention_tiles(ctx, group: int):
+def plan_attention_tiles(ctx, group: int, wide_rows: int):
     """Cuts the step's sequences into tiles for the tensor-core kernels: sequences with few
-    query rows (decoded tokens, short portions) go to the keys mode in tiles of 16 // group
-    tokens, the others to the rows mode in tiles of 64 // group tokens.  Returns
-    (narrow tiles, wide tiles, splits) with the tile lists on the device, or None when a list
-    would be empty.  The plan is kept in the context for the other layers of the step."""
+    query rows (decoded tokens, short portions) go to the kernels for few rows in tiles of
+    16 // group tokens, the others in tiles of wide_rows // group tokens, those with the most
+    keys first.  Returns (narrow tiles, wide tiles, longest context of a narrow tile) with the
+    tile lists on the device, or None for an empty list.  The plan is kept in the context for
+    the other layers of the step."""
     plans = ctx.__dict__.setdefault("_attention_plans", {})
-    if group in plans:
-        return plans[group]
+    key = (group, wide_rows)
+    if key in plans:
+        return plans[key]
     narrow_tokens = kernels.MMA_ROWS_NARROW // group
-    wide_tokens = kernels.MMA_ROWS_WIDE // group
+    wide_tokens = wide_rows // group
     if ctx.decode_tiles is not None and narrow_tokens >= 1:     # single tokens: the step's own tile list
-        plans[group] = (ctx.decode_tiles, None, ctx.max_context_len)
-        return plans[group]
+        plans[key] = (ctx.decode_tiles, None, ctx.max_context_len)
+        return plans[key]
     narrow, wide = [], []
     longest_narrow = 0
     for i in range(ctx.num_sequences):
@@ -42,12 +44,14 @@ def plan_attention_tiles(ctx, group: int):
             longest_narrow = max(longest_narrow, ctx.host_start_pos[i] + n)
         else:
             for start in range(0, n, wide_tokens):
-                wide.append((i, first + start, min(wide_tokens, n - start), 0))
+                wide.append((i, first + start, min(wide_tokens, n - start), ctx.host_start_pos[i] + start))
+    wide.sort(key=lambda t: -t[3])          # a tile late in a long request walks the most keys: start it first
+    wide = [(a, b, c, 0) for a, b, c, _ in wide]
     device = ctx.positions.device
     both = torch.tensor(narrow + wide, dtype=torch.int32).view(-1, 4).to(device, non_blocking=True)
-    plans[group] = (both[:len(narrow)] if narrow else None, both[len(narrow):] if wide else None,
-                    min(longest_narrow, ctx.max_context_len))
-    return plans[group]
+    plans[key] = (both[:len(narrow)] if narrow else None, both[len(narrow):] if wide else None,
+                  min(longest_narrow, ctx.max_context_len))
+    return plans[key]
 
 
 def choose_splits(tiles: int, nkv: int, longest_context: int, resident: int = 2) -> int:
@@ -67,15 +71,20 @@ def choose_splits(tiles: int, nkv: int, longest_context: int, resident: int = 2)
 
 
 def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) -> None:
-    """Attention of this step's queries over their requests' cached keys and values: on the
-    tensor cores when the activations are bfloat16 and the head size is a multiple of 16,
-    else (the 32-bit path, odd head sizes, very wide groups) the CUDA-core kernel."""
+    """Attention of this step's queries over their requests' cached keys and values.  bfloat16
+    with a head size that is a multiple of 16 runs on the tensor cores: decoded tokens and short
+    portions through the kernels for few rows (fed by bulk tensor copies when the head size is a
+    multiple of 64), longer portions through the tcgen05 kernel (head sizes 64 and 128) or the
+    mma.sync kernel (the others).  The 32-bit path, odd head sizes and very wide groups take the
+    CUDA-core kernel."""
     table = ctx.block_tables[cache.group]
     group = nq // nkv
     if q.dtype is not torch.bfloat16 or not kernels.attention_mma_supported(d, group):
         kernels.attention_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, table, out, nq, nkv, d, window)
         return
-    narrow, wide, longest = plan_attention_tiles(ctx, group)
+    page_size = cache.k.shape[2]
+    tensor_core_rows = kernels.attention_prefill_tc_supported(d, group, page_size)
+    narrow, wide, longest = plan_attention_tiles(ctx, group, kernels.PREFILL_TC_ROWS if tensor_core_rows else kernels.MMA_ROWS_WIDE)
     if narrow is not None:
         splits = choose_splits(narrow.shape[0], nkv, longest)
         if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
@@ -83,7 +92,10 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
         else:
             kernels.attention_mma_keys(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
     if wide is not None:
-        kernels.attention_mma_rows(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
+        if tensor_core_rows:
+            kernels.attention_prefill_tc(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
+        else:
+            kernels.attention_mma_rows(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
 
 
 @MIXERS.register("gqa_attention")

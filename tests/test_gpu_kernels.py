@@ -208,7 +208,7 @@ class PagedCase:
 
     def run_mma(self, mode, splits=1):
         group = self.nq // self.nkv
-        per_tile = (64 if mode == "rows" else 16) // group
+        per_tile = {"rows": 64, "tc": 128}.get(mode, 16) // group
         tiles = []
         for i in range(len(self.spans)):
             first, n = self.q_start[i], self.q_start[i + 1] - self.q_start[i]
@@ -220,6 +220,10 @@ class PagedCase:
                 self.dev(self.positions), self.dev(self.table), tiles, out, self.nq, self.nkv, self.d, self.window)
         if mode == "keys":
             kernels.attention_mma_keys(*args, splits=splits)
+        elif mode == "tc":
+            kernels.attention_prefill_tc(*args)
+            torch.cuda.synchronize()
+            kernels.check_device_errors()
         elif mode == "tma":
             kernels.attention_decode_tma(*args, splits=splits)
             torch.cuda.synchronize()
@@ -277,6 +281,43 @@ def test_attention_decode_tma(nq, nkv, d, page, splits):
     close(case.run_mma("tma", splits), case.plain(), torch.bfloat16, f"attention_decode_tma, {splits} splits")
 
 
+TC_SHAPES = [(8, 2, 128, 16), (12, 3, 64, 8), (4, 4, 64, 64), (16, 1, 128, 128), (2, 1, 128, 32), (32, 1, 64, 16)]
+TC_SPANS = [(0, 1), (0, 70), (130, 3), (257, 1), (63, 66), (1, 2), (300, 200), (0, 513), (1000, 37)]
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", TC_SHAPES)
+def test_attention_prefill_tc(nq, nkv, d, page):
+    """Head sizes 64 and 128, groups of 1 to 32 query heads, pages of 8 to 128 rows; portions of 1 to
+    513 tokens on contexts up to 1,037: several tiles a request, several blocks of keys a tile, blocks
+    that need no mask, the diagonal, and tiles that are not full."""
+    assert kernels.attention_prefill_tc_supported(d, nq // nkv, page)
+    case = PagedCase(torch.bfloat16, nq, nkv, d, page, TC_SPANS, seed=nq + d)
+    close(case.run_mma("tc"), case.plain(), torch.bfloat16, "attention_prefill_tc")
+
+
+def test_attention_prefill_tc_rescales_when_the_maximum_grows():
+    """Keys whose scores rise block after block by far more than 2^8: the accumulator in tensor
+    memory is rescaled again and again; then keys that fall: it is not."""
+    nq, nkv, d, page = 4, 2, 64, 16
+    for rising in (True, False):
+        case = PagedCase(torch.bfloat16, nq, nkv, d, page, [(0, 600)], seed=3)
+        case.q.mul_(0.05)
+        case.q[:, :, 5] = 4.0
+        ramp = torch.arange(600, dtype=torch.float32) / 600 * 24 - 12          # scores from -6 to +6 (in natural units)
+        case.ks[0].mul_(0.05)
+        case.ks[0][:, :, 5] = (ramp if rising else -ramp).to(torch.bfloat16)[:, None] * (d ** 0.5) / 4.0 / 2
+        for lp in range(-(-600 // page)):
+            rows = slice(lp * page, min(600, (lp + 1) * page))
+            case.kc[case.table[0, lp], :, :rows.stop - rows.start] = case.ks[0][rows].transpose(0, 1)
+        close(case.run_mma("tc"), case.plain(), torch.bfloat16, f"prefill_tc, scores {'rising' if rising else 'falling'}")
+
+
+@pytest.mark.parametrize("window", [1, 5, 64, 100, 300])
+def test_attention_prefill_tc_window_edges(window):
+    case = PagedCase(torch.bfloat16, 4, 2, 64, 8, [(0, 330), (120, 40), (99, 2), (3, 4)], seed=window, window=window)
+    close(case.run_mma("tc"), case.plain(), torch.bfloat16, f"prefill_tc window {window}")
+
+
 @pytest.mark.parametrize("window", [1, 5, 64, 100])
 def test_attention_decode_tma_window_edges(window):
     case = PagedCase(torch.bfloat16, 4, 2, 64, 8, [(0, 130), (120, 1), (99, 2), (3, 4)], seed=window, window=window)
@@ -291,7 +332,7 @@ def test_attention_decode_tma_window_edges(window):
     case.table = table
 
 
-@pytest.mark.parametrize("runner", ["simt32", "simt16", "rows", "keys1", "keys7", "tma1", "tma7"])
+@pytest.mark.parametrize("runner", ["simt32", "simt16", "rows", "keys1", "keys7", "tma1", "tma7", "tc"])
 def test_one_far_key_among_hundreds(runner):
     """One key far back scores far above the rest: the output must be that key's value row, so a
     kernel that skips, repeats or misplaces a block of keys cannot pass."""
@@ -313,7 +354,8 @@ def test_one_far_key_among_hundreds(runner):
                 case.kc[case.table[i, lp], :, :rows.stop - rows.start] = case.ks[i][rows].transpose(0, 1)
         got = {"simt32": case.run_simt, "simt16": case.run_simt, "rows": lambda: case.run_mma("rows"),
                "keys1": lambda: case.run_mma("keys", 1), "keys7": lambda: case.run_mma("keys", 7),
-               "tma1": lambda: case.run_mma("tma", 1), "tma7": lambda: case.run_mma("tma", 7)}[runner]()
+               "tma1": lambda: case.run_mma("tma", 1), "tma7": lambda: case.run_mma("tma", 7),
+               "tc": lambda: case.run_mma("tc")}[runner]()
         want_rows = torch.cat([case.vs[0][far].reshape(1, -1).repeat(1, 1)] +
                               [case.vs[1][far].reshape(1, -1)] * 12).double()
         want = want_rows.view(13, nkv, 1, d).expand(13, nkv, nq // nkv, d).reshape(13, nq * d)
