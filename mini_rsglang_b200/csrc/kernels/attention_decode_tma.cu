@@ -93,31 +93,39 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------------------------------ producer
+        // Every lane owns one page of a block: it reads the page's number a block ahead of its use and
+        // issues the page's copies itself, so a block costs one trip to the block table and one round of
+        // copies issued side by side.  Lane 0 also waits for the stage and arms its barrier.
         if (lane == 0) {
             tma_prefetch_descriptor(&k_map);
             tma_prefetch_descriptor(&v_map);
-            const int rows_per_copy = min(page_size, KV);
-            const int copies = KV / rows_per_copy;
-            const int copy_bytes = rows_per_copy * D * 2;
-            for (int block = block_first; block < block_last; ++block) {
-                const int it = block - block_first, s = it % STAGES;
+        }
+        const int rows_per_copy = min(page_size, KV);
+        const int copies = KV / rows_per_copy;
+        const int copy_bytes = rows_per_copy * D * 2;
+        // keys past the end, before the window or on a page that was given back are masked by their
+        // position; their copy reads page 0, which always exists and holds finite numbers
+        auto page_of = [&](int block) {
+            const int key = block * KV + lane * rows_per_copy;
+            return (lane < copies && key < key_end) ? pages[key >> page_shift] : -1;
+        };
+        int next_page = block_first < block_last ? page_of(block_first) : -1;
+        for (int block = block_first; block < block_last; ++block) {
+            const int it = block - block_first, s = it % STAGES;
+            const int my_page = next_page;
+            if (block + 1 < block_last) next_page = page_of(block + 1);
+            if (lane == 0) {
                 if (it >= STAGES) mbar_wait(&empty[s], ((it / STAGES) - 1) & 1);
                 mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-                unsigned char* k_dst = smem + s * STAGE_BYTES;
-                unsigned char* v_dst = k_dst + TILE_BYTES;
-                for (int c = 0; c < copies; ++c) {
-                    const int key = block * KV + c * rows_per_copy;
-                    // keys past the end, before the window or on a page that was given back are masked by
-                    // their position; their copy reads page 0, which always exists and holds finite numbers
-                    int page = 0, row = 0;
-                    if (key < key_end) {
-                        page = pages[key >> page_shift];
-                        row = key & (page_size - 1);
-                        if (page < 0) page = 0, row = 0;
-                    }
-                    tma_load_5d(k_dst + c * copy_bytes, &k_map, &full[s], 0, row, 0, kv_head, page);
-                    tma_load_5d(v_dst + c * copy_bytes, &v_map, &full[s], 0, row, 0, kv_head, page);
-                }
+            }
+            __syncwarp();                                    // the stage is free and the barrier armed
+            unsigned char* k_dst = smem + s * STAGE_BYTES;
+            unsigned char* v_dst = k_dst + TILE_BYTES;
+            if (lane < copies) {                             // every lane issues the copies of its own page
+                const int key = block * KV + lane * rows_per_copy;
+                const int row = my_page < 0 ? 0 : key & (page_size - 1);
+                tma_load_5d(k_dst + lane * copy_bytes, &k_map, &full[s], 0, row, 0, kv_head, max(my_page, 0));
+                tma_load_5d(v_dst + lane * copy_bytes, &v_map, &full[s], 0, row, 0, kv_head, max(my_page, 0));
             }
         }
         return;

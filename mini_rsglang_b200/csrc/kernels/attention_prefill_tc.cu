@@ -44,6 +44,13 @@ struct Tile {
     int seq, first_token, tokens, pad;
 };
 
+// 2^x in one instruction of the special-function unit (2 ulp; -inf gives 0).
+__device__ __forceinline__ float fast_exp2(float x) {
+    float y;
+    asm("ex2.approx.ftz.f32 %0, %1;" : "=f"(y) : "f"(x));
+    return y;
+}
+
 struct Barriers {
     uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready, pv_done;
 };
@@ -102,6 +109,9 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
 
     if (warp == 0) {
         // ------------------------------------------------------------------ copies
+        // Every lane owns one page of a block: it reads the page's number a block ahead of its use and
+        // issues the page's copies itself, so a block costs one trip to the block table and one round of
+        // copies issued side by side.  Lane 0 also waits for the stage and arms its barrier.
         if (lane == 0) {
             tma_prefetch_descriptor(&q_map);
             tma_prefetch_descriptor(&k_map);
@@ -109,30 +119,35 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
             mbar_arrive_expect_tx(&bars->q_full, Q_BYTES);
             for (int h = 0; h < HALVES; ++h)
                 tma_load_3d(q_smem + h * HALF_BYTES, &q_map, &bars->q_full, h * 64, kv_head * group, tile.first_token);
-            const int rows_per_copy = min(page_size, BN);
-            const int copies = BN / rows_per_copy;
-            for (int j = 0; j < blocks; ++j) {
-                const int s = j & 1;
-                const uint32_t wait_parity = ((j >> 1) & 1) ^ 1;
-                for (int which = 0; which < 2; ++which) {            // keys, then values
-                    uint64_t* full = which ? &bars->v_full[s] : &bars->k_full[s];
+        }
+        const int rows_per_copy = min(page_size, BN);
+        const int copies = BN / rows_per_copy;
+        // keys past the end, before the window or on a page that was given back are masked by their
+        // position; their copy reads page 0, which always exists and holds finite numbers
+        auto page_of = [&](int j) {
+            const int key = (block_first + j) * BN + lane * rows_per_copy;
+            return (lane < copies && key < key_end) ? pages[key >> page_shift] : -1;
+        };
+        int next_page = page_of(0);
+        for (int j = 0; j < blocks; ++j) {
+            const int s = j & 1;
+            const int my_page = next_page;
+            if (j + 1 < blocks) next_page = page_of(j + 1);
+            const uint32_t wait_parity = ((j >> 1) & 1) ^ 1;
+            for (int which = 0; which < 2; ++which) {            // keys, then values
+                uint64_t* full = which ? &bars->v_full[s] : &bars->k_full[s];
+                if (lane == 0) {
                     mbar_wait(which ? &bars->v_empty[s] : &bars->k_empty[s], wait_parity);
                     mbar_arrive_expect_tx(full, KV_TILE_BYTES);
-                    unsigned char* dst = (which ? v_smem : k_smem) + s * KV_TILE_BYTES;
-                    const CUtensorMap* map = which ? &v_map : &k_map;
-                    for (int c = 0; c < copies; ++c) {
-                        const int key = (block_first + j) * BN + c * rows_per_copy;
-                        // keys past the end, before the window or on a page that was given back are masked by their
-                        // position; their copy reads page 0, which always exists and holds finite numbers
-                        int page = 0, row = 0;
-                        if (key < key_end) {
-                            page = pages[key >> page_shift];
-                            row = key & (page_size - 1);
-                            if (page < 0) page = 0, row = 0;
-                        }
-                        for (int h = 0; h < HALVES; ++h)
-                            tma_load_5d(dst + h * HALF_BYTES + c * rows_per_copy * 128, map, full, 0, row, h, kv_head, page);
-                    }
+                }
+                __syncwarp();                                    // the stage is free and the barrier armed
+                unsigned char* dst = (which ? v_smem : k_smem) + s * KV_TILE_BYTES;
+                const CUtensorMap* map = which ? &v_map : &k_map;
+                if (lane < copies) {                             // every lane issues the copies of its own page
+                    const int key = (block_first + j) * BN + lane * rows_per_copy;
+                    const int row = my_page < 0 ? 0 : key & (page_size - 1);
+                    for (int h = 0; h < HALVES; ++h)
+                        tma_load_5d(dst + h * HALF_BYTES + lane * rows_per_copy * 128, map, full, 0, row, h, kv_head, max(my_page, 0));
                 }
             }
         }
@@ -190,23 +205,23 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
             tcgen05_fence_after_sync();
             float x[BN];
 #pragma unroll
-            for (int c = 0; c < BN; c += 32) tmem_load_32(lane_base + S_COLUMN + s * BN + c, x + c);
+            for (int c = 0; c < BN; c += 32) tmem_load_32_async(lane_base + S_COLUMN + s * BN + c, x + c);
+            tmem_load_wait();
             const bool edge = key0 + BN - 1 > first_pos || key0 < key_begin + (window > 0 ? BN : 0);   // a block that needs masks
-            float block_max = -CUDART_INF_F;
+            float part_max[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};   // four chains, not one of 128 links
             if (edge) {
 #pragma unroll
                 for (int c = 0; c < BN; ++c) {
                     const int key = key0 + c;
-                    x[c] = (key <= pos && key >= lowest) ? x[c] * scale_log2 : -CUDART_INF_F;
-                    block_max = fmaxf(block_max, x[c]);
+                    x[c] = (key <= pos && key >= lowest) ? x[c] : -CUDART_INF_F;
+                    part_max[c & 3] = fmaxf(part_max[c & 3], x[c]);
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) {
-                    x[c] *= scale_log2;
-                    block_max = fmaxf(block_max, x[c]);
-                }
+                for (int c = 0; c < BN; ++c) part_max[c & 3] = fmaxf(part_max[c & 3], x[c]);
             }
+            // the scale is positive, so the maximum of the scaled scores is the scaled maximum
+            const float block_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])) * scale_log2;
             // the reference moves only when the maximum outgrew it by the threshold (always from -inf)
             float alpha = 1.0f;
             const bool moved = block_max > reference + RESCALE_THRESHOLD;
@@ -215,16 +230,16 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
                 reference = block_max;
             }
             const float base = reference == -CUDART_INF_F ? 0.0f : reference;
-            float block_sum = 0.0f;
+            float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
             uint32_t packed[BN / 2];
 #pragma unroll
             for (int c = 0; c < BN; c += 2) {
-                const float p0 = exp2f(x[c] - base), p1 = exp2f(x[c + 1] - base);
-                block_sum += p0 + p1;
+                const float p0 = fast_exp2(fmaf(x[c], scale_log2, -base)), p1 = fast_exp2(fmaf(x[c + 1], scale_log2, -base));
+                part_sum[(c >> 1) & 3] += p0 + p1;
                 __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
                 packed[c / 2] = *reinterpret_cast<uint32_t*>(&pair);
             }
-            sum = sum * alpha + block_sum;
+            sum = sum * alpha + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
             // the last block's P.V must be done before its probabilities are overwritten or O is rescaled
             if (j > 0) {
                 mbar_wait(&bars->pv_done, (j - 1) & 1);
