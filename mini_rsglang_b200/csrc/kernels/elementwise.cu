@@ -63,11 +63,86 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
     }
 }
 
+// The same with four elements a step and the row kept in registers between the two passes
+// (width a multiple of 4, at most 4 * ROW_CHUNKS * blockDim.x).
+#define ROW_CHUNKS 4
+template <typename T> struct Vec4;
+template <> struct Vec4<float> {
+    static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
+    static __device__ __forceinline__ void store(float* p, float4 v) { *reinterpret_cast<float4*>(p) = v; }
+};
+template <> struct Vec4<bf16> {
+    static __device__ __forceinline__ float4 load(const bf16* p) {
+        const uint2 raw = *reinterpret_cast<const uint2*>(p);
+        const float2 a = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.x));
+        const float2 b = __bfloat1622float2(*reinterpret_cast<const __nv_bfloat162*>(&raw.y));
+        return make_float4(a.x, a.y, b.x, b.y);
+    }
+    static __device__ __forceinline__ void store(bf16* p, float4 v) {
+        __nv_bfloat162 a = __floats2bfloat162_rn(v.x, v.y), b = __floats2bfloat162_rn(v.z, v.w);
+        uint2 raw;
+        raw.x = *reinterpret_cast<uint32_t*>(&a);
+        raw.y = *reinterpret_cast<uint32_t*>(&b);
+        *reinterpret_cast<uint2*>(p) = raw;
+    }
+};
+
+template <typename T>
+__global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
+                                       const float* __restrict__ weight, float eps, T* __restrict__ out,
+                                       const int* __restrict__ rows, int width, int write_back) {
+    pdl_wait();
+    pdl_launch_dependents();
+    __shared__ float scratch[33];
+    const int r = blockIdx.x;
+    const size_t src = rows ? (size_t)rows[r] : (size_t)r;
+    float* res = residual + src * width;
+    const T* del = delta ? delta + src * width : nullptr;
+    float4 v[ROW_CHUNKS];
+    float sum = 0.0f;
+#pragma unroll
+    for (int c = 0; c < ROW_CHUNKS; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        v[c] = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+        if (i < width) {
+            v[c] = Vec4<float>::load(res + i);
+            if (del) {
+                const float4 d = Vec4<T>::load(del + i);
+                v[c].x += d.x, v[c].y += d.y, v[c].z += d.z, v[c].w += d.w;
+                if (write_back) Vec4<float>::store(res + i, v[c]);
+            }
+            sum += v[c].x * v[c].x + v[c].y * v[c].y + v[c].z * v[c].z + v[c].w * v[c].w;
+        }
+    }
+    const float scale = rsqrtf(block_sum(sum, scratch) / (float)width + eps);
+    T* o = out + (size_t)r * width;
+#pragma unroll
+    for (int c = 0; c < ROW_CHUNKS; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        if (i < width) {
+            const float4 w = Vec4<float>::load(weight + i);
+            Vec4<T>::store(o + i, make_float4(v[c].x * scale * w.x, v[c].y * scale * w.y, v[c].z * scale * w.z, v[c].w * scale * w.w));
+        }
+    }
+}
+
 MRS_EXPORT int mrs_add_rmsnorm(int is_bf16, float* residual, const void* delta, const float* weight,
                                float eps, void* out, const int* rows, int n_rows, int width,
                                int write_back, void* stream) {
     if (n_rows <= 0) return 0;
     const int threads = width >= 2048 ? 512 : (width >= 512 ? 256 : 128);
+    const bool aligned = (((uintptr_t)residual | (uintptr_t)delta | (uintptr_t)weight | (uintptr_t)out) & 15) == 0;
+    if (width % 4 == 0 && aligned && width <= 4 * ROW_CHUNKS * 1024) {
+        int vec_threads = ((width + 4 * ROW_CHUNKS - 1) / (4 * ROW_CHUNKS) + 31) / 32 * 32;     // the row fits the block's registers
+        if (vec_threads < 64) vec_threads = 64;
+        if (is_bf16)
+            MRS_LAUNCH(add_rmsnorm_vec_kernel<bf16>, n_rows, vec_threads, 0, stream,
+                residual, (const bf16*)delta, weight, eps, (bf16*)out, rows, width, write_back);
+        else
+            MRS_LAUNCH(add_rmsnorm_vec_kernel<float>, n_rows, vec_threads, 0, stream,
+                residual, (const float*)delta, weight, eps, (float*)out, rows, width, write_back);
+        MRS_RETURN_LAUNCH_STATUS();
+    }
     if (is_bf16)
         MRS_LAUNCH(add_rmsnorm_kernel<bf16>, n_rows, threads, 0, stream,
             residual, (const bf16*)delta, weight, eps, (bf16*)out, rows, width, write_back);
@@ -233,11 +308,40 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     }
 }
 
+// The same with four elements a step (width and block multiples of 4).
+template <typename T>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total4, int inter, int block) {
+    pdl_wait();
+    pdl_launch_dependents();
+    const int inter4 = inter >> 2;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4;
+         i += (long long)gridDim.x * blockDim.x) {
+        const long long t = i / inter4;
+        const int c = (int)(i % inter4) * 4;
+        const long long gate_at = block ? (long long)(c / block) * 2 * block + c % block : c;
+        const long long up_at = block ? gate_at + block : (long long)inter + c;
+        const float4 g = Vec4<T>::load(gate_up + t * 2 * inter + gate_at);
+        const float4 u = Vec4<T>::load(gate_up + t * 2 * inter + up_at);
+        Vec4<T>::store(out + t * inter + c, make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
+                                                        g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+    }
+}
+
 MRS_EXPORT int mrs_silu_mul(int is_bf16, const void* gate_up, void* out, int tokens, int inter, int block, void* stream) {
     const long long total = (long long)tokens * inter;
     if (total <= 0) return 0;
     if (block < 0 || (block && inter % block)) return MRS_BAD_ARGUMENT;
     const int threads = 256;
+    const bool aligned = (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
+    if (inter % 4 == 0 && block % 4 == 0 && aligned) {
+        const long long total4 = total / 4, want = (total4 + threads - 1) / threads;
+        const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+        if (is_bf16)
+            MRS_LAUNCH(silu_mul_vec_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total4, inter, block);
+        else
+            MRS_LAUNCH(silu_mul_vec_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total4, inter, block);
+        MRS_RETURN_LAUNCH_STATUS();
+    }
     long long want = (total + threads - 1) / threads;
     const unsigned blocks = (unsigned)(want > 148 * 16 ? 148 * 16 : want);
     if (is_bf16)

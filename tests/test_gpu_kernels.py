@@ -37,7 +37,7 @@ def test_embed(dtype):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("width", [72, 1000, 4096])
+@pytest.mark.parametrize("width", [72, 75, 1000, 4096, 5120, 16384, 16388])
 def test_add_rmsnorm(dtype, width):
     rows = 7
     residual = torch.randn(rows, width, device=DEV)
@@ -72,11 +72,12 @@ def test_add_rmsnorm(dtype, width):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-def test_silu_mul(dtype):
-    gate_up = torch.randn(5, 2 * 136, device=DEV).to(dtype) * 3
-    out = torch.empty(5, 136, device=DEV, dtype=dtype)
+@pytest.mark.parametrize("inter", [136, 75, 12288])
+def test_silu_mul(dtype, inter):
+    gate_up = torch.randn(5, 2 * inter, device=DEV).to(dtype) * 3
+    out = torch.empty(5, inter, device=DEV, dtype=dtype)
     kernels.silu_mul(gate_up, out)
-    g, u = gate_up.double()[:, :136], gate_up.double()[:, 136:]
+    g, u = gate_up.double()[:, :inter], gate_up.double()[:, inter:]
     close(out, g / (1 + torch.exp(-g)) * u, dtype, "silu_mul")
 
 
