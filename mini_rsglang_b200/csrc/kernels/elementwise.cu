@@ -66,6 +66,7 @@ __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __rest
 // The same with four elements a step and the row kept in registers between the two passes
 // (width a multiple of 4, at most 4 * ROW_CHUNKS * blockDim.x).
 #define ROW_CHUNKS 4
+template <typename T, int VEC> struct alignas(sizeof(T) * VEC) Pack { T v[VEC]; };
 template <typename T> struct Vec4;
 template <> struct Vec4<float> {
     static __device__ __forceinline__ float4 load(const float* p) { return *reinterpret_cast<const float4*>(p); }
@@ -268,12 +269,104 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, T* __restri
     }
 }
 
+// The same for head sizes 64, 128 and 256: a lane owns d / 32 consecutive elements (one vector
+// load and store), its rotation partner is the lane 16 further, and the cosines and sines of a
+// token are computed once a block for all of the block's heads instead of once a head.
+#define ROPE_HEADS_PER_BLOCK 16
+
+template <typename T, int VEC>
+__global__ void __launch_bounds__(128) qk_norm_rope_store_vec_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    const int* __restrict__ positions, const int* __restrict__ slots, const float* __restrict__ q_norm,
+    const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int nq, int nkv, int page_size,
+    int write_kv) {
+    pdl_wait();
+    pdl_launch_dependents();
+    constexpr int d = 32 * VEC, half = d / 2;
+    __shared__ float cos_s[half], sin_s[half];
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int t = blockIdx.x, heads = nq + 2 * nkv;
+    const int head_end = min(heads, (int)(blockIdx.y + 1) * ROPE_HEADS_PER_BLOCK);
+    if (inv_freq) {
+        const float pos = (float)positions[t];
+        for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sin_s[j], &cos_s[j]);
+    }
+    __syncthreads();
+    for (int h = blockIdx.y * ROPE_HEADS_PER_BLOCK + warp; h < head_end; h += 4) {
+        const int kind = h < nq ? 0 : (h < nq + nkv ? 1 : 2);   // 0 q, 1 k, 2 v
+        if (kind != 0 && !write_kv) continue;
+        const Pack<T, VEC> raw = *reinterpret_cast<const Pack<T, VEC>*>(qkv + (size_t)t * heads * d + (size_t)h * d + lane * VEC);
+        float x[VEC];
+        float sum = 0.0f;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) {
+            x[i] = to_float(raw.v[i]);
+            sum += x[i] * x[i];
+        }
+        const float* norm = kind == 0 ? q_norm : (kind == 1 ? k_norm : nullptr);
+        if (norm) {
+            const float scale = rsqrtf(warp_sum(sum) / (float)d + eps);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) x[i] = x[i] * scale * norm[lane * VEC + i];
+        }
+        if (kind != 2 && inv_freq) {
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
+                const int j = (lane & 15) * VEC + i;
+                x[i] = lane < 16 ? x[i] * cos_s[j] - partner * sin_s[j] : x[i] * cos_s[j] + partner * sin_s[j];
+            }
+        }
+        T* dst;
+        if (kind == 0) {
+            dst = q_out + (size_t)t * nq * d + (size_t)h * d;
+        } else {
+            const int slot = slots[t];
+            if (slot < 0) continue;
+            const int page = slot / page_size, off = slot % page_size;
+            const int g = kind == 1 ? h - nq : h - nq - nkv;
+            dst = (kind == 1 ? k_cache : v_cache) + (((size_t)page * nkv + g) * page_size + off) * d;
+        }
+        Pack<T, VEC> packed;
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) packed.v[i] = from_float<T>(x[i]);
+        *reinterpret_cast<Pack<T, VEC>*>(dst + lane * VEC) = packed;
+    }
+}
+
+template <typename T, int VEC>
+static int launch_rope_vec(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
+                           const int* slots, const float* q_norm, const float* k_norm, float eps, const float* inv_freq,
+                           int tokens, int nq, int nkv, int page_size, int write_kv, void* stream) {
+    const int heads = nq + 2 * nkv;
+    MRS_LAUNCH((qk_norm_rope_store_vec_kernel<T, VEC>), dim3(tokens, (heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK), 128, 0,
+               stream, (const T*)qkv, (T*)q_out, (T*)k_cache, (T*)v_cache, positions, slots, q_norm, k_norm, eps, inv_freq,
+               nq, nkv, page_size, write_kv);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
 MRS_EXPORT int mrs_qk_norm_rope_store(int is_bf16, const void* qkv, void* q_out, void* k_cache, void* v_cache,
                                       const int* positions, const int* slots, const float* q_norm,
                                       const float* k_norm, float eps, const float* inv_freq, int tokens,
                                       int nq, int nkv, int d, int page_size, int write_kv, void* stream) {
     if (tokens <= 0) return 0;
     if (d <= 0 || d > MRS_MAX_HEAD_DIM || (d & 1)) return MRS_BAD_ARGUMENT;
+    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0;
+    if (aligned && (d == 64 || d == 128 || d == 256)) {
+#define MRS_ROPE_VEC(T, V)                                                                                         \
+    return launch_rope_vec<T, V>(qkv, q_out, k_cache, v_cache, positions, slots, q_norm, k_norm, eps, inv_freq, tokens, \
+                                 nq, nkv, page_size, write_kv, stream)
+        if (is_bf16) {
+            if (d == 64) MRS_ROPE_VEC(bf16, 2);
+            if (d == 128) MRS_ROPE_VEC(bf16, 4);
+            MRS_ROPE_VEC(bf16, 8);
+        } else {
+            if (d == 64) MRS_ROPE_VEC(float, 2);
+            if (d == 128) MRS_ROPE_VEC(float, 4);
+            MRS_ROPE_VEC(float, 8);
+        }
+#undef MRS_ROPE_VEC
+    }
     const long long units = (long long)tokens * (nq + 2 * nkv);
     const unsigned blocks = (unsigned)((units + 3) / 4);
     if (is_bf16)
@@ -308,22 +401,27 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     }
 }
 
-// The same with four elements a step (width and block multiples of 4).
-template <typename T>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total4, int inter, int block) {
+// The same with one 16-byte vector a step (width and block multiples of VEC).
+template <typename T, int VEC>
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total_vecs, int inter, int block) {
     pdl_wait();
     pdl_launch_dependents();
-    const int inter4 = inter >> 2;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total4;
+    const int inter_vecs = inter / VEC;
+    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs;
          i += (long long)gridDim.x * blockDim.x) {
-        const long long t = i / inter4;
-        const int c = (int)(i % inter4) * 4;
+        const long long t = i / inter_vecs;
+        const int c = (int)(i % inter_vecs) * VEC;
         const long long gate_at = block ? (long long)(c / block) * 2 * block + c % block : c;
         const long long up_at = block ? gate_at + block : (long long)inter + c;
-        const float4 g = Vec4<T>::load(gate_up + t * 2 * inter + gate_at);
-        const float4 u = Vec4<T>::load(gate_up + t * 2 * inter + up_at);
-        Vec4<T>::store(out + t * inter + c, make_float4(g.x / (1.0f + expf(-g.x)) * u.x, g.y / (1.0f + expf(-g.y)) * u.y,
-                                                        g.z / (1.0f + expf(-g.z)) * u.z, g.w / (1.0f + expf(-g.w)) * u.w));
+        const Pack<T, VEC> g = *reinterpret_cast<const Pack<T, VEC>*>(gate_up + t * 2 * inter + gate_at);
+        const Pack<T, VEC> u = *reinterpret_cast<const Pack<T, VEC>*>(gate_up + t * 2 * inter + up_at);
+        Pack<T, VEC> o;
+#pragma unroll
+        for (int j = 0; j < VEC; ++j) {
+            const float gj = to_float(g.v[j]);
+            o.v[j] = from_float<T>(gj / (1.0f + __expf(-gj)) * to_float(u.v[j]));
+        }
+        *reinterpret_cast<Pack<T, VEC>*>(out + t * inter + c) = o;
     }
 }
 
@@ -333,13 +431,14 @@ MRS_EXPORT int mrs_silu_mul(int is_bf16, const void* gate_up, void* out, int tok
     if (block < 0 || (block && inter % block)) return MRS_BAD_ARGUMENT;
     const int threads = 256;
     const bool aligned = (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
-    if (inter % 4 == 0 && block % 4 == 0 && aligned) {
-        const long long total4 = total / 4, want = (total4 + threads - 1) / threads;
+    const int vec = is_bf16 ? 8 : 4;
+    if (inter % vec == 0 && block % vec == 0 && aligned) {
+        const long long vecs = total / vec, want = (vecs + threads - 1) / threads;
         const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
         if (is_bf16)
-            MRS_LAUNCH(silu_mul_vec_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total4, inter, block);
+            MRS_LAUNCH((silu_mul_vec_kernel<bf16, 8>), blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, vecs, inter, block);
         else
-            MRS_LAUNCH(silu_mul_vec_kernel<float>, blocks, threads, 0, stream, (const float*)gate_up, (float*)out, total4, inter, block);
+            MRS_LAUNCH((silu_mul_vec_kernel<float, 4>), blocks, threads, 0, stream, (const float*)gate_up, (float*)out, vecs, inter, block);
         MRS_RETURN_LAUNCH_STATUS();
     }
     long long want = (total + threads - 1) / threads;

@@ -120,7 +120,8 @@ def plain_qk(qkv, positions, q_w, k_w, eps, theta, nq, nkv, d):
 
 
 @pytest.mark.parametrize("dtype", DTYPES)
-@pytest.mark.parametrize("nq,nkv,d,page", [(3, 3, 48, 8), (8, 2, 128, 16), (5, 1, 16, 4), (2, 1, 256, 32)])
+@pytest.mark.parametrize("nq,nkv,d,page", [(3, 3, 48, 8), (8, 2, 128, 16), (5, 1, 16, 4), (2, 1, 256, 32), (32, 8, 128, 16),
+                                           (7, 7, 64, 8), (20, 1, 64, 16)])
 def test_qk_norm_rope_store(dtype, nq, nkv, d, page):
     T, pages, eps, theta = 9, 12, 1e-5, 50000.0
     qkv = torch.randn(T, (nq + 2 * nkv) * d, device=DEV).to(dtype)
