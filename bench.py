@@ -233,12 +233,17 @@ def main() -> int:
     e2e = None
     if not args.no_e2e:
         total = args.warmup + args.steps
-        slack = 64                                           # every request is still live when the timing ends
+        # every request must still be live when the timing ends: the first one decodes while the others'
+        # prompts are still running, a step for every 2,048 prompt tokens of the batch
+        slack = batch * context // limits.prefill_budget + 16
         prompt_len = context - total - slack
         params = SamplingParams(max_tokens=total + slack, ignore_eos=True)
         streams = [engine.generate(GenerateRequest(TokenIds(random_tokens(prompt_len)), params)) for _ in range(batch)]
         while engine.scheduler.waiting() or any(engine.generated.get(s.request_id, 0) == 0 for s in streams):
-            engine.run_step()                                # prompts, untimed
+            if not engine.run_step():                        # prompts, untimed
+                raise RuntimeError("the scheduler went idle before every request had its first token")
+            if len(engine.generated) < batch:
+                raise RuntimeError("a request finished before the timing began; raise the slack")
         for _ in range(args.warmup):
             engine.run_step()
         torch.cuda.synchronize()

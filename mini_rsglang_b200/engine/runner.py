@@ -9,6 +9,7 @@ the cache manager keeps.  Reference: `Engine::run` / `forward_logits`
 position, not only the last row of a sequence."""
 from __future__ import annotations
 
+import ctypes
 from dataclasses import dataclass, field
 from typing import Sequence
 
@@ -16,7 +17,7 @@ import numpy as np
 import torch
 
 from .. import kernels
-from ..cache.manager import CacheGroup, CacheManager
+from ..cache.manager import CacheGroup, CacheManager, host_api
 from ..cache.storage import CacheStorage, bytes_per_page, plan_groups
 from ..config.runtime_config import RuntimeConfig
 from ..errors import BackendError, InvalidRequest
@@ -37,10 +38,6 @@ class SequenceStep:
     tokens: Sequence[int]
     start_pos: int
     want: Sequence[int] = field(default_factory=tuple)
-
-
-def _align(n: int) -> int:
-    return (n + 3) & ~3
 
 
 def resolve_dtype(dtype) -> torch.dtype:
@@ -124,6 +121,15 @@ class ModelRunner:
         self.cache = CacheManager(groups, limits.page_size, limits.max_running)
         self.storage = CacheStorage(kv_needs, state_needs, groups, group_of, limits.max_running, runtime)
         self._staging = _Staging(self.device)
+        lib = host_api()
+        self._step_build = lib.mrs_step_build
+        self._step_build.restype = ctypes.c_int64
+        self._step_build.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 6 + [
+            ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+        self._step_error = lib.mrs_step_last_error
+        self._step_error.restype = ctypes.c_char_p
+        # mixers written in Python read the requests' state slots from a host list
+        self._needs_host_slots = any(need is not None for need in state_needs)
         # steps of single decoded tokens are recorded and replayed when every mixer allows it
         self.record_decode = all(getattr(b.mixer, "replayable", False) for b in self.model.blocks)
         self._largest_bucket = min(256, 1 << (limits.max_running - 1).bit_length())
@@ -152,148 +158,70 @@ class ModelRunner:
         return cls(config, tensors, runtime, limits or RuntimeConfig(), kv_bytes, num_pages, spec)
 
     # ------------------------------------------------------------------ one step
-    def _check_batch(self, sequences: Sequence[SequenceStep]):
-        """The reference's batch checks (crates/kernels/src/lib.rs:407-474); returns the token
-        counts and, per group, the requests' block tables."""
+    def build_context(self, sequences: Sequence[SequenceStep], pad_to: int | None = None,
+                      table_width: int | None = None, staging: _Staging | None = None) -> StepContext:
+        """Checks the batch and copies what the kernels need to know about it to the device in
+        one transfer; the checking and the layout are the host library's (`csrc/host/step_batch.cc`).
+        With `pad_to` (single decoded tokens only) the batch is filled up to that many sequences
+        with rows that write nothing and whose results nobody reads, block tables get the given
+        fixed width and every row's logits are produced: the shapes and addresses of such a
+        context depend on `pad_to` alone, so its kernels can be recorded once and replayed."""
         if not sequences:
             raise InvalidRequest("empty batch or KV pool")
-        S = self.limits.page_size
-        seen = set()
-        counts, tables = [], [[] for _ in self.groups]
-        for s in sequences:
-            n = len(s.tokens)
-            if n == 0 or s.start_pos < 0 or s.start_pos + n > self.limits.max_seq_len:
-                raise InvalidRequest("batch sequence length/page coverage mismatch")
-            if s.request_id in seen:
-                raise InvalidRequest("aliased KV write slots in batch: a request appears twice")
-            seen.add(s.request_id)
-            for wpos in s.want:
-                if not 0 <= wpos < n:
-                    raise InvalidRequest(f"wanted place {wpos} outside the {n} tokens of the step")
-            counts.append(n)
-            need_pages = -(-(s.start_pos + n) // S)
-            for g in range(len(self.groups)):
-                table = self.cache.table(s.request_id, g)
-                if table.size < need_pages:
-                    raise InvalidRequest("batch sequence length/page coverage mismatch")
-                if (table[s.start_pos // S:need_pages] < 0).any():
-                    raise InvalidRequest("a page to be written was given back already")
-                tables[g].append(table)
-        return counts, tables
-
-    def build_context(self, sequences: Sequence[SequenceStep], pad_to: int | None = None,
-                      table_widths: list[int] | None = None, staging: _Staging | None = None) -> StepContext:
-        """Checks the batch and copies what the kernels need to know about it to the device in
-        one transfer.  With `pad_to` (single decoded tokens only) the batch is filled up to that
-        many sequences with rows that write nothing and whose results nobody reads, block tables
-        get the given fixed widths and every row's logits are produced: the shapes and addresses
-        of such a context depend on `pad_to` alone, so its kernels can be recorded once and
-        replayed."""
-        counts, tables = self._check_batch(sequences)
-        S, vocab = self.limits.page_size, self.config.vocab_size
-        real = len(sequences)
-        B = real if pad_to is None else int(pad_to)
-        pads = B - real
-        T = int(sum(counts)) + pads
-        decode = all(c == 1 for c in counts)
-        if pads and not decode:
-            raise InvalidRequest("only batches of single decoded tokens can be padded")
-        R = B if pad_to is not None else sum(len(s.want) for s in sequences)
-        widths = table_widths or [max(max(t.size for t in tables[g]), 1) for g in range(len(self.groups))]
-        layout, cursor = {}, 0
-
-        def take(name, n):
-            nonlocal cursor
-            layout[name] = (cursor, n)
-            cursor += _align(n)
-
-        for name, n in (("ids", T), ("pos", T), ("seq", T), ("q_start", B + 1), ("ctx_len", B), ("slot", B), ("want", R),
-                        ("tiles", 4 * B if decode else 0)):
-            take(name, n)
-        for g in range(len(self.groups)):
-            take(f"table{g}", B * widths[g])
-            take(f"slots{g}", T)
+        n = len(sequences)
+        requests = np.fromiter((s.request_id for s in sequences), dtype=np.int64, count=n)
+        starts = np.fromiter((s.start_pos for s in sequences), dtype=np.int64, count=n)
+        counts = np.fromiter((len(s.tokens) for s in sequences), dtype=np.int32, count=n)
+        want_counts = np.fromiter((len(s.want) for s in sequences), dtype=np.int32, count=n)
+        if counts.min() <= 0:
+            raise InvalidRequest("batch sequence length/page coverage mismatch")
+        flat = [t for s in sequences for t in s.tokens] if counts.max() > 1 else [s.tokens[0] for s in sequences]
+        tokens = np.asarray(flat, dtype=np.int64)
+        if tokens.min() < 0 or tokens.max() >= self.config.vocab_size:
+            raise InvalidRequest("token or page ID out of range")
+        tokens = tokens.astype(np.int32)
+        want = np.asarray([w for s in sequences for w in s.want], dtype=np.int32)
         staging = staging or self._staging
-        host, dev = staging.reserve(cursor)
-        buf = host.numpy()
+        G = len(self.groups)
+        layout = np.zeros(14 + 3 * G, dtype=np.int64)
+        rows, most = int(counts.sum()) + (pad_to or n), pad_to or n
+        widest = table_width or -(-self.limits.max_seq_len // self.limits.page_size)
+        guess = (4 + G) * (rows + 4) + 8 * (most + 4) + G * (most * widest + 4)     # an upper bound of the layout
+        for _ in range(2):
+            host, dev = staging.reserve(guess)
+            used = self._step_build(self.cache.handle, n, requests.ctypes.data, starts.ctypes.data, counts.ctypes.data,
+                                    tokens.ctypes.data, want_counts.ctypes.data, want.ctypes.data, int(pad_to or 0),
+                                    int(table_width or 0), self.limits.max_seq_len, self.config.vocab_size,
+                                    host.data_ptr(), host.numel(), layout.ctypes.data)
+            if used != -7:
+                break
+            guess = int(layout[0])
+        if used < 0:
+            message = self._step_error().decode("utf-8", "replace")
+            raise (BackendError if used == -100 else InvalidRequest)(message)
+        staging.upload(int(used))
+        self.h2d_bytes += 4 * int(used)
+        T, B, R, decode = (int(v) for v in layout[:4])
 
-        def view(name):
-            start, n = layout[name]
-            return buf[start:start + n]
-
-        ids, pos, seq = view("ids"), view("pos"), view("seq")
-        q_start, ctx_len, slot, want = view("q_start"), view("ctx_len"), view("slot"), view("want")
-        row, w = 0, 0
-        host_q_start, host_start, host_slots, fresh = [0], [], [], []
-        for i, s in enumerate(sequences):
-            n = counts[i]
-            tokens = np.asarray(s.tokens, dtype=np.int64)
-            if tokens.min() < 0 or tokens.max() >= vocab:
-                raise InvalidRequest("token or page ID out of range")
-            ids[row:row + n] = tokens
-            pos[row:row + n] = np.arange(s.start_pos, s.start_pos + n)
-            seq[row:row + n] = i
-            if pad_to is None:
-                for wpos in s.want:
-                    want[w] = row + wpos
-                    w += 1
-            ctx_len[i] = s.start_pos + n
-            slot[i] = self.cache.slot(s.request_id)
-            host_start.append(s.start_pos)
-            host_slots.append(int(slot[i]))
-            fresh.append(s.start_pos == 0)
-            row += n
-            q_start[i + 1] = row
-            host_q_start.append(row)
-        q_start[0] = 0
-        if pads:                               # rows that write nothing: token 0 at position 0, state slot -1
-            ids[real:], pos[real:], seq[real:] = 0, 0, np.arange(real, B)
-            ctx_len[real:], slot[real:] = 1, -1
-            q_start[real + 1:] = np.arange(real + 1, B + 1)
-            host_q_start += list(range(real + 1, B + 1))
-            host_start += [0] * pads
-            host_slots += [-1] * pads
-            fresh += [True] * pads
-        if pad_to is not None:
-            want[:] = np.arange(B)
-        if decode:                             # one attention tile per sequence; none for a padding row
-            tiles = view("tiles").reshape(B, 4)
-            tiles[:] = 0
-            tiles[:real, 0] = np.arange(real)
-            tiles[:real, 1] = np.arange(real)
-            tiles[:real, 2] = 1
-        for g in range(len(self.groups)):
-            table_view = view(f"table{g}").reshape(B, widths[g])
-            table_view[:real] = -1
-            table_view[real:] = 0              # a padding row reads page 0 and its result is dropped
-            slots_view = view(f"slots{g}")
-            slots_view[T - pads:] = -1
-            row = 0
-            for i, s in enumerate(sequences):
-                t = tables[g][i]
-                if t.size > widths[g]:
-                    raise InvalidRequest("batch sequence length/page coverage mismatch")
-                table_view[i, :t.size] = t
-                p = np.arange(s.start_pos, s.start_pos + counts[i])
-                slots_view[row:row + counts[i]] = t[p // S].astype(np.int64) * S + p % S
-                row += counts[i]
-        staging.upload(cursor)
-        self.h2d_bytes += 4 * cursor
-
-        def dview(name, shape=None):
-            start, n = layout[name]
-            t = dev[start:start + n]
+        def dview(offset, count, shape=None):
+            t = dev[int(offset):int(offset) + count]
             return t.view(shape) if shape else t
 
+        real = n
+        ends = np.cumsum(counts)
+        pads = B - real
         return StepContext(
-            num_tokens=T, num_sequences=B, token_ids=dview("ids"), positions=dview("pos"), seq_of_token=dview("seq"),
-            q_start=dview("q_start"), context_len=dview("ctx_len"), state_slots=dview("slot"),
-            want_rows=dview("want") if R else None,
-            block_tables=[dview(f"table{g}", (B, widths[g])) for g in range(len(self.groups))],
-            slots=[dview(f"slots{g}") for g in range(len(self.groups))],
-            host_q_start=host_q_start, host_start_pos=host_start, host_state_slots=host_slots,
-            max_query_len=max(counts), max_context_len=max(s.start_pos + c for s, c in zip(sequences, counts)),
-            fresh=fresh, decode_tiles=dview("tiles", (B, 4)) if decode else None, real_sequences=real)
+            num_tokens=T, num_sequences=B, token_ids=dview(layout[4], T), positions=dview(layout[5], T),
+            seq_of_token=dview(layout[6], T), q_start=dview(layout[7], B + 1), context_len=dview(layout[8], B),
+            state_slots=dview(layout[9], B), want_rows=dview(layout[10], R) if R else None,
+            block_tables=[dview(layout[12 + 3 * g], B * int(layout[13 + 3 * g]), (B, int(layout[13 + 3 * g]))) for g in range(G)],
+            slots=[dview(layout[14 + 3 * g], T) for g in range(G)],
+            host_q_start=[0] + ends.tolist() + list(range(int(ends[-1]) + 1, int(ends[-1]) + pads + 1)),
+            host_start_pos=starts.tolist() + [0] * pads,
+            host_state_slots=[self.cache.slot(s.request_id) for s in sequences] + [-1] * pads if self._needs_host_slots else [],
+            max_query_len=int(layout[13 + 3 * G]), max_context_len=int(layout[12 + 3 * G]),
+            fresh=(starts == 0).tolist() + [True] * pads,
+            decode_tiles=dview(layout[11], 4 * B, (B, 4)) if decode else None, real_sequences=real)
 
     def forward(self, sequences: Sequence[SequenceStep]) -> torch.Tensor | None:
         """Runs the batch; returns the logits [wanted, vocab] (float32, on the device) in the
@@ -325,8 +253,8 @@ class ModelRunner:
         record = self._records.get(key)
         if record is None:
             record = self._records[key] = _Recorded(self.device)
-        widths = [-(-self.limits.max_seq_len // self.limits.page_size)] * len(self.groups)
-        ctx = self.build_context(sequences, pad_to=bucket, table_widths=widths, staging=record.staging)
+        width = -(-self.limits.max_seq_len // self.limits.page_size)
+        ctx = self.build_context(sequences, pad_to=bucket, table_width=width, staging=record.staging)
         if record.graph is None:
             ctx.max_context_len = context_class      # launches are planned for the class, not for this step
             record.ctx = ctx
