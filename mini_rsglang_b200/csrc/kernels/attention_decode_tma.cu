@@ -88,8 +88,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
         mbar_fence_init();
     }
     __syncthreads();
-    pdl_wait();                 // the newest keys and the queries come from the kernel before this one
     pdl_launch_dependents();
+    pdl_wait();                 // the newest keys and the queries come from the kernel before this one
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------------------------------ producer

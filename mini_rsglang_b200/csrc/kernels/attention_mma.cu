@@ -188,8 +188,8 @@ __global__ void __launch_bounds__(THREADS) attention_rows_kernel(
     const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
     const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv, int page_size, int page_shift,
     float scale_log2, int window) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_tiles = q_tile + ROWS_WIDE * D;
@@ -287,8 +287,8 @@ __global__ void __launch_bounds__(THREADS) attention_keys_kernel(
     const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
     const Tile* __restrict__ tiles, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
     int nq, int nkv, int page_size, int page_shift, float scale_log2, int window, int splits) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     extern __shared__ __align__(128) unsigned char smem_raw[];
     bf16* q_tile = reinterpret_cast<bf16*>(smem_raw);
     bf16* k_tiles = q_tile + ROWS_NARROW * D;
@@ -411,8 +411,8 @@ __global__ void __launch_bounds__(THREADS) attention_keys_kernel(
 __global__ void __launch_bounds__(THREADS) attention_combine_kernel(
     const float* __restrict__ part_o, const float* __restrict__ part_ml, const Tile* __restrict__ tiles,
     bf16* __restrict__ out, int nq, int nkv, int splits) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const Tile tile = tiles[blockIdx.x];
     const int kv_head = blockIdx.y, group = nq / nkv, rows = tile.tokens * group;
     const size_t base_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS_NARROW;

@@ -104,8 +104,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     __syncthreads();
     tcgen05_fence_after_sync();
     const uint32_t tmem_base = *tmem_slot;
-    pdl_wait();                  // queries and the newest keys come from the kernel before this one
     pdl_launch_dependents();
+    pdl_wait();                  // queries and the newest keys come from the kernel before this one
 
     if (warp == 0) {
         // ------------------------------------------------------------------ copies

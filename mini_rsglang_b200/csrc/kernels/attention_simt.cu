@@ -17,8 +17,8 @@ __global__ void attention_simt_kernel(const T* __restrict__ q, const T* __restri
                                       const int* __restrict__ seq_of_token, const int* __restrict__ block_table,
                                       T* __restrict__ out, int tokens, int nq, int nkv, int d, int page_size,
                                       int table_width, float scale, int window) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     __shared__ float q_s[ATTN_WARPS][ATTN_MAX_D];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const long long unit = (long long)blockIdx.x * ATTN_WARPS + warp;

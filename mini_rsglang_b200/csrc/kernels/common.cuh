@@ -56,7 +56,10 @@ __device__ __forceinline__ float block_sum(float x, float* scratch) {
 // pdl_wait() before it reads or writes anything that an earlier kernel may write or read
 // (after the wait the earlier kernels are complete and their memory is visible), and calls
 // pdl_launch_dependents() to let the kernel after it start in the same way.  What a kernel
-// does before its wait (barrier set-up, fetching weights) overlaps the end of its predecessor.
+// does before its wait (barrier set-up, fetching weights) overlaps its predecessors.  The
+// kernels call pdl_launch_dependents() first: the kernel after a small kernel then becomes
+// resident while the kernel before the small one still runs (a product fetches its first
+// weight tiles under the product before it); its own wait still orders it after both.
 // ------------------------------------------------------------------------------------------
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }

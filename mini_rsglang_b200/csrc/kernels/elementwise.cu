@@ -9,8 +9,8 @@
 template <typename T>
 __global__ void embed_kernel(const T* __restrict__ table, const int* __restrict__ ids,
                              float* __restrict__ residual, int width) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int t = blockIdx.x;
     const T* row = table + (size_t)ids[t] * width;
     float* out = residual + (size_t)t * width;
@@ -40,8 +40,8 @@ template <typename T>
 __global__ void add_rmsnorm_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                    const float* __restrict__ weight, float eps, T* __restrict__ out,
                                    const int* __restrict__ rows, int width, int write_back) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
@@ -92,8 +92,8 @@ template <typename T>
 __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __restrict__ delta,
                                        const float* __restrict__ weight, float eps, T* __restrict__ out,
                                        const int* __restrict__ rows, int width, int write_back) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     const int r = blockIdx.x;
     const size_t src = rows ? (size_t)rows[r] : (size_t)r;
@@ -157,8 +157,8 @@ MRS_EXPORT int mrs_add_rmsnorm(int is_bf16, float* residual, const void* delta, 
 template <typename T>
 __global__ void rmsnorm_kernel(const T* __restrict__ x, const float* __restrict__ weight, float eps,
                                T* __restrict__ out, int width) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     __shared__ float scratch[33];
     const T* row = x + (size_t)blockIdx.x * width;
     float sum = 0.0f;
@@ -202,8 +202,8 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, T* __restri
                                           const float* __restrict__ q_norm, const float* __restrict__ k_norm,
                                           float eps, const float* __restrict__ inv_freq,
                                           int tokens, int nq, int nkv, int d, int page_size, int write_kv) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     __shared__ float stage[4][MRS_MAX_HEAD_DIM];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int heads = nq + 2 * nkv;
@@ -280,8 +280,8 @@ __global__ void __launch_bounds__(128) qk_norm_rope_store_vec_kernel(
     const int* __restrict__ positions, const int* __restrict__ slots, const float* __restrict__ q_norm,
     const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int nq, int nkv, int page_size,
     int write_kv) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     constexpr int d = 32 * VEC, half = d / 2;
     __shared__ float cos_s[half], sin_s[half];
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -386,8 +386,8 @@ MRS_EXPORT int mrs_qk_norm_rope_store(int is_bf16, const void* qkv, void* q_out,
 // ---------------------------------------------------------------------------------------------
 template <typename T>
 __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total, int inter, int block) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total;
          i += (long long)gridDim.x * blockDim.x) {
         const long long t = i / inter;
@@ -404,8 +404,8 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 // The same with one 16-byte vector a step (width and block multiples of VEC).
 template <typename T, int VEC>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total_vecs, int inter, int block) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     const int inter_vecs = inter / VEC;
     for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs;
          i += (long long)gridDim.x * blockDim.x) {

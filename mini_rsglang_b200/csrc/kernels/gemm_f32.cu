@@ -11,8 +11,8 @@
 
 __global__ void __launch_bounds__(256) gemm_f32_kernel(const float* __restrict__ A, const float* __restrict__ W,
                                                        float* __restrict__ C, int M, int N, int K) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     __shared__ float a_s[GF_BK][GF_BM + 4];
     __shared__ float w_s[GF_BK][GF_BN + 4];
     const int tid = threadIdx.x;

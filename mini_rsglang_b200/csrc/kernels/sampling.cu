@@ -179,8 +179,8 @@ __global__ void __launch_bounds__(SAMPLE_THREADS) sample_kernel(
     const float* __restrict__ logits, int vocab, const float* __restrict__ temperature,
     const int* __restrict__ top_k, const float* __restrict__ top_p, const unsigned long long* __restrict__ seed,
     const int* __restrict__ draw_index, int* __restrict__ out) {
-    pdl_wait();
     pdl_launch_dependents();
+    pdl_wait();
     __shared__ SampleShared s;
     const int r = blockIdx.x;
     const float* row = logits + (size_t)r * vocab;

@@ -535,7 +535,8 @@ def _gemm_device_state(device: torch.device) -> dict:
     return state
 
 
-def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False) -> None:
+def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
+            splits: int | None = None) -> None:
     """out[M, N] = x[M, K] . weight[N, K]^T for M <= 128; bfloat16 in, float32 sums, `out` bfloat16 or float32.
     With `gated`, `weight` holds, in every block of 128 rows, 64 gate rows and then the 64 matching up rows, and
     out[M, N / 2] = silu(x . gate^T) * (x . up^T) in bfloat16."""
@@ -566,7 +567,8 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: boo
         if code != 0:
             fail(code, "tensor map of a weight")
         _weight_maps[key] = (keep, address, lib.mrs_gemm_tc_splits(n, k, state["sms"]))
-    _, w_map, splits = _weight_maps[key]
+    _, w_map, planned = _weight_maps[key]
+    splits = planned if splits is None else int(splits)      # another count only for measurements and tests
     mpad = 16 if m <= 16 else (32 if m <= 32 else (64 if m <= 64 else 128))
     x_map = state["x_map"][1]
     code = lib.mrs_gemm_tc_map(x.data_ptr(), m, k, mpad, x_map)
