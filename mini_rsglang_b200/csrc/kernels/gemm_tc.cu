@@ -33,15 +33,33 @@ template <int MPAD> struct Shape {
     static constexpr int STAGES = MPAD <= 32 ? 8 : (MPAD <= 64 ? 6 : 5);
     static constexpr int TMEM_COLUMNS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
     static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16 +
-                                         (size_t)MPAD * 64 * sizeof(float);
+                                         (size_t)MPAD * (MPAD <= 32 ? 128 : 64) * sizeof(float) + 4 * MPAD * sizeof(float) +
+                                         (MPAD <= 32 ? (size_t)MPAD * (128 + 1) * sizeof(float) : 0);   // cosines, sines, write slots
 };
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
-template <int MPAD, typename OutT, bool GATED>
+enum { EPI_PLAIN = 0, EPI_GATED = 1, EPI_HEADS = 2 };
+
+// What the head epilogue needs beside the product: where q goes, the cache pages of k and v, the
+// tokens' positions and write slots, the head norms' scales and the rotation's frequencies.
+struct HeadEpilogue {
+    bf16* q_out;             // [M, nq, 128]
+    bf16* k_cache;           // [pages, nkv, page_size, 128]
+    bf16* v_cache;
+    const int* positions;    // [M]
+    const int* slots;        // [M] page * page_size + offset, < 0 or null: no write
+    const float* q_norm;     // [128] or null
+    const float* k_norm;
+    const float* inv_freq;   // [64] or null
+    float eps;
+    int nq, nkv, page_size;
+};
+
+template <int MPAD, typename OutT, int EPI>
 __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
     const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map, OutT* __restrict__ out,
-    float* __restrict__ partials, int* __restrict__ counters, int M, int N, int K, int splits) {
+    float* __restrict__ partials, int* __restrict__ counters, int M, int N, int K, int splits, const HeadEpilogue heads) {
     using S = Shape<MPAD>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -50,7 +68,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
     uint64_t* acc_full = empty + S::STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    float* exchange = reinterpret_cast<float*>(tmem_slot + 4);        // [MPAD][64], gated epilogue only
+    float* exchange = reinterpret_cast<float*>(tmem_slot + 4);        // rows of a tile meet here: [MPAD][64] gated, [MPAD][128] + [4][MPAD] heads (up to 32 rows)
     __shared__ int is_last;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -145,6 +163,21 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
         const int quarter = warp & 3;                      // the TMEM lanes this warp may read
         const int row = quarter * 32 + lane;               // weight row within the tile
         const int epi_thread = (warp - 2) * 32 + lane;
+        // What the head epilogue needs beside the sums is fetched and computed now, under the first weight
+        // tiles: the rotation's cosines and sines of every row, the write slots, this row's norm scales.
+        float* cos_s = exchange + MPAD * 128 + 4 * MPAD;   // [MPAD][64]
+        float* sin_s = cos_s + MPAD * 64;
+        int* slot_s = reinterpret_cast<int*>(sin_s + MPAD * 64);
+        float q_scale = 1.0f, k_scale = 1.0f;
+        if (EPI == EPI_HEADS) {
+            if (heads.inv_freq)
+                for (int idx = epi_thread; idx < M * 64; idx += 128)
+                    sincosf((float)heads.positions[idx >> 6] * heads.inv_freq[idx & 63], &sin_s[idx], &cos_s[idx]);
+            if (epi_thread < M) slot_s[epi_thread] = heads.slots ? heads.slots[epi_thread] : -1;
+            if (heads.q_norm) q_scale = heads.q_norm[row];
+            if (heads.k_norm) k_scale = heads.k_norm[row];
+            epilogue_sync();
+        }
         pdl_wait();                                        // `out`, `partials` and `counters` may still be in use before
         int round = 0;
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++round) {
@@ -211,7 +244,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
                 }
             }
             if (finished) {
-                if (GATED) {
+                if (EPI == EPI_GATED) {
                     // the tile's rows 0..63 are gate rows, rows 64..127 the matching up rows: the upper half
                     // hands its sums over and the lower half writes silu(gate) * up, 64 columns of [M, N / 2]
                     if (row >= 64) {
@@ -226,6 +259,61 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
                             if (m < M) {
                                 const float g = acc[m], u = exchange[m * 64 + row];
                                 out[(size_t)m * (N >> 1) + tile * 64 + row] = from_float<OutT>(g / (1.0f + __expf(-g)) * u);
+                            }
+                    }
+                } else if (EPI == EPI_HEADS) {
+                    // The tile is one head of the fused q/k/v projection (128 rows = the head's elements): per-head
+                    // RMSNorm of q and k, rotation of q and k by the tokens' positions, q to its tensor, k and v into
+                    // the cache pages: what a kernel of its own does after the library's product.
+                    const int head = tile, element = row;
+                    const int kind = head < heads.nq ? 0 : (head < heads.nq + heads.nkv ? 1 : 2);      // q, k, v
+                    const bool normed = kind == 0 ? heads.q_norm != nullptr : (kind == 1 ? heads.k_norm != nullptr : false);
+                    float* warp_sums = exchange + MPAD * 128;                                        // [4][MPAD]
+                    static_assert(EPI != EPI_HEADS || MPAD <= 32, "the head epilogue takes up to 32 rows");
+                    if (normed) {
+#pragma unroll
+                        for (int m = 0; m < MPAD; ++m)
+                            if (m < M) {
+                                const float sq = warp_sum(acc[m] * acc[m]);
+                                if (lane == 0) warp_sums[(warp - 2) * MPAD + m] = sq;
+                            }
+                        epilogue_sync();
+                        const float w = kind == 0 ? q_scale : k_scale;
+#pragma unroll
+                        for (int m = 0; m < MPAD; ++m)
+                            if (m < M) {
+                                const float total = (warp_sums[m] + warp_sums[MPAD + m]) + (warp_sums[2 * MPAD + m] + warp_sums[3 * MPAD + m]);
+                                acc[m] = acc[m] * rsqrtf(total / 128.0f + heads.eps) * w;
+                            }
+                    }
+                    if (kind != 2 && heads.inv_freq) {
+#pragma unroll
+                        for (int m = 0; m < MPAD; ++m)
+                            if (m < M) exchange[m * 128 + element] = acc[m];
+                        epilogue_sync();
+#pragma unroll
+                        for (int m = 0; m < MPAD; ++m)
+                            if (m < M) {
+                                const float cs = cos_s[m * 64 + (element & 63)], sn = sin_s[m * 64 + (element & 63)];
+                                const float partner = exchange[m * 128 + (element ^ 64)];
+                                acc[m] = element < 64 ? acc[m] * cs - partner * sn : acc[m] * cs + partner * sn;
+                            }
+                    }
+                    if (kind == 0) {
+#pragma unroll
+                        for (int m = 0; m < MPAD; ++m)
+                            if (m < M) heads.q_out[((size_t)m * heads.nq + head) * 128 + element] = __float2bfloat16_rn(acc[m]);
+                    } else if (heads.slots) {
+                        bf16* cache = kind == 1 ? heads.k_cache : heads.v_cache;
+                        const int g = kind == 1 ? head - heads.nq : head - heads.nq - heads.nkv;
+#pragma unroll
+                        for (int m = 0; m < MPAD; ++m)
+                            if (m < M) {
+                                const int slot = slot_s[m];
+                                if (slot >= 0) {
+                                    const int page = slot / heads.page_size, off = slot % heads.page_size;
+                                    cache[(((size_t)page * heads.nkv + g) * heads.page_size + off) * 128 + element] = __float2bfloat16_rn(acc[m]);
+                                }
                             }
                     }
                 } else if (n < N) {
@@ -245,18 +333,18 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
     }
 }
 
-template <int MPAD, typename OutT, bool GATED>
+template <int MPAD, typename OutT, int EPI>
 int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, void* out, float* partials, int* counters, int M, int N,
-           int K, int splits, int ctas, cudaStream_t stream) {
+           int K, int splits, int ctas, cudaStream_t stream, const HeadEpilogue& heads = HeadEpilogue{}) {
     using S = Shape<MPAD>;
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_small_m_kernel<MPAD, OutT, GATED>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_small_m_kernel<MPAD, OutT, EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)S::SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    return mrs_launch(gemm_small_m_kernel<MPAD, OutT, GATED>, dim3(ctas), dim3(THREADS), S::SMEM_BYTES, stream, *w_map, *x_map,
-                      (OutT*)out, partials, counters, M, N, K, splits);
+    return mrs_launch(gemm_small_m_kernel<MPAD, OutT, EPI>, dim3(ctas), dim3(THREADS), S::SMEM_BYTES, stream, *w_map, *x_map,
+                      (OutT*)out, partials, counters, M, N, K, splits, heads);
 }
 
 }  // namespace
@@ -313,9 +401,9 @@ MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* o
     if (gated && (out_is_f32 || N % TILE_N)) return MRS_BAD_ARGUMENT;
 #define MRS_GEMM_CASE(P)                                                                                              \
     case P:                                                                                                           \
-        if (gated) return launch<P, bf16, true>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);          \
-        return out_is_f32 ? launch<P, float, false>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st)       \
-                          : launch<P, bf16, false>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);
+        if (gated) return launch<P, bf16, EPI_GATED>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);     \
+        return out_is_f32 ? launch<P, float, EPI_PLAIN>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st)   \
+                          : launch<P, bf16, EPI_PLAIN>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);
     switch (mpad) {
         MRS_GEMM_CASE(16)
         MRS_GEMM_CASE(32)
@@ -323,6 +411,31 @@ MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* o
         MRS_GEMM_CASE(128)
     }
 #undef MRS_GEMM_CASE
+    return MRS_BAD_ARGUMENT;
+}
+
+// The fused q/k/v projection of an attention with heads of 128 elements, for up to 32 rows: the product, then per
+// head the RMSNorm of q and k (scales `q_norm`, `k_norm`, or null), the rotation of q and k (`inv_freq` [64] or
+// null; pairs (j, j + 64)), q into `q_out` [M, nq, 128] and k, v into the cache pages at `slots` (null: nothing
+// is written).  `w_map` covers the weights [(nq + 2 nkv) * 128, K], q heads first, then k, then v.
+MRS_EXPORT int mrs_gemm_tc_qkv_heads(const void* w_map, const void* x_map, void* q_out, void* k_cache, void* v_cache,
+                                     const int* positions, const int* slots, const float* q_norm, const float* k_norm,
+                                     const float* inv_freq, float eps, int nq, int nkv, int page_size, float* partials,
+                                     int* counters, int M, int K, int splits, int mpad, int ctas, void* stream) {
+    if (M <= 0) return 0;
+    const int N = (nq + 2 * nkv) * TILE_N;
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    if (K <= 0 || K % 8 || M > mpad || mpad > 32 || splits < 1 || splits > k_blocks || ctas < 1 || nq <= 0 || nkv <= 0 ||
+        page_size <= 0 || !q_out || !positions || (slots && (!k_cache || !v_cache)))
+        return MRS_BAD_ARGUMENT;
+    if (splits > 1 && (!partials || !counters)) return MRS_BAD_ARGUMENT;
+    const int units = (N / TILE_N) * splits;
+    if (ctas > units) ctas = units;
+    HeadEpilogue heads{(bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots, q_norm, k_norm, inv_freq, eps, nq, nkv, page_size};
+    const CUtensorMap* wm = reinterpret_cast<const CUtensorMap*>(w_map);
+    const CUtensorMap* xm = reinterpret_cast<const CUtensorMap*>(x_map);
+    if (mpad == 16) return launch<16, bf16, EPI_HEADS>(wm, xm, nullptr, partials, counters, M, N, K, splits, ctas, (cudaStream_t)stream, heads);
+    if (mpad == 32) return launch<32, bf16, EPI_HEADS>(wm, xm, nullptr, partials, counters, M, N, K, splits, ctas, (cudaStream_t)stream, heads);
     return MRS_BAD_ARGUMENT;
 }
 

@@ -508,6 +508,9 @@ def gemm_tc_library() -> ctypes.CDLL:
         lib.mrs_gemm_tc_small_m.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
                                             _c_int, _c_int, _c_vp]
         lib.mrs_gemm_tc_small_m.restype = _c_int
+        lib.mrs_gemm_tc_qkv_heads.argtypes = [_c_vp] * 10 + [_c_float, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_int,
+                                              _c_int, _c_int, _c_int, _c_vp]
+        lib.mrs_gemm_tc_qkv_heads.restype = _c_int
         lib.mrs_gemm_tc_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         lib.mrs_gemm_tc_take_error.restype = _c_int
         lib.mrs_gemm_tc_error_string.argtypes = [_c_int]
@@ -590,6 +593,73 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: boo
                                    state["sms"], _stream())
     if code != 0:
         fail(code, "gemm_tc")
+
+
+def gemm_tc_qkv_heads(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
+                      v_cache: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor | None,
+                      q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
+                      inv_freq: torch.Tensor | None, nq: int, nkv: int) -> None:
+    """The fused q/k/v projection for up to 32 rows and heads of 128 elements, with the per-head norms, the
+    rotation and the cache write in the product's epilogue (what `qk_norm_rope_store` does after a product)."""
+    m, k = x.shape
+    d = 128
+    _need(x, torch.bfloat16, "qkv input")
+    _need(weight, torch.bfloat16, "qkv weight", ((nq + 2 * nkv) * d, k))
+    _need(q_out, torch.bfloat16, "q_out", (m, nq * d))
+    _need(positions, torch.int32, "positions", (m,))
+    if m > GEMM_TC_BEST_ROWS:
+        raise InvalidRequest(f"the fused projection takes at most {GEMM_TC_BEST_ROWS} rows, got {m}")
+    page_size = 1
+    if slots is not None:
+        _need(slots, torch.int32, "slots", (m,))
+        _need(k_cache, torch.bfloat16, "k cache")
+        _need(v_cache, torch.bfloat16, "v cache", tuple(k_cache.shape))
+        if tuple(k_cache.shape[1:]) != (nkv, k_cache.shape[2], d):
+            raise InvalidRequest(f"cache shape {tuple(k_cache.shape)} does not match heads/head_dim")
+        page_size = k_cache.shape[2]
+    for w, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
+        if w is not None:
+            _need(w, torch.float32, name, (d,))
+    if inv_freq is not None:
+        _need(inv_freq, torch.float32, "inv_freq", (d // 2,))
+    lib = gemm_tc_library()
+    state = _gemm_device_state(x.device)
+
+    def fail(code, what):
+        raise BackendError(f"{what}: {lib.mrs_gemm_tc_error_string(code).decode()} (code {code})")
+
+    n = weight.shape[0]
+    key = (weight.data_ptr(), n, k)
+    if key not in _weight_maps:
+        keep, address = _aligned_block(128, 64)
+        code = lib.mrs_gemm_tc_map(weight.data_ptr(), n, k, 128, address)
+        if code != 0:
+            fail(code, "tensor map of a weight")
+        _weight_maps[key] = (keep, address, lib.mrs_gemm_tc_splits(n, k, state["sms"]))
+    _, w_map, splits = _weight_maps[key]
+    mpad = 16 if m <= 16 else 32
+    x_map = state["x_map"][1]
+    code = lib.mrs_gemm_tc_map(x.data_ptr(), m, k, mpad, x_map)
+    if code != 0:
+        fail(code, "tensor map of the activations")
+    if splits > 1:
+        need = lib.mrs_gemm_tc_partial_floats(m, n, splits)
+        if state["partials"].numel() < need:
+            _retired.append(state["partials"])
+            state["partials"] = torch.empty(2 * int(need), dtype=torch.float32, device=x.device)
+        tiles = lib.mrs_gemm_tc_counters(n)
+        if state["counters"].numel() < tiles:
+            _retired.append(state["counters"])
+            state["counters"] = torch.zeros(2 * tiles, dtype=torch.int32, device=x.device)
+    global launch_count
+    launch_count += 1
+    code = lib.mrs_gemm_tc_qkv_heads(w_map, x_map, q_out.data_ptr(), _ptr(k_cache) if slots is not None else None,
+                                     _ptr(v_cache) if slots is not None else None, positions.data_ptr(), _ptr(slots),
+                                     _ptr(q_norm), _ptr(k_norm), _ptr(inv_freq), float(eps), nq, nkv, page_size,
+                                     state["partials"].data_ptr(), state["counters"].data_ptr(), m, k, splits, mpad,
+                                     state["sms"], _stream())
+    if code != 0:
+        fail(code, "gemm_tc_qkv_heads")
 
 
 # ------------------------------------------------------------------------------------------------

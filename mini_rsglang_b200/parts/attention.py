@@ -142,10 +142,19 @@ class GroupedQueryAttention(Mixer):
 
     def forward(self, h, ctx, cache, write_cache=True):
         tokens = h.shape[0]
-        qkv = linear(h, self.qkv)
         q = torch.empty((tokens, self.nq * self.d), dtype=h.dtype, device=h.device)
         eps = self.q_norm.eps if self.q_norm else (self.k_norm.eps if self.k_norm else 0.0)
         group = cache.group
+        if self.d == 128 and tokens <= kernels.GEMM_TC_BEST_ROWS and kernels.gemm_tc_supported(h, self.qkv):
+            # few rows, heads of 128: the product's epilogue norms, rotates and writes the cache itself
+            kernels.gemm_tc_qkv_heads(
+                h, self.qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
+                ctx.slots[group] if write_cache else None, self.q_norm.weight if self.q_norm else None,
+                self.k_norm.weight if self.k_norm else None, eps, self.position.tables()["inv_freq"], self.nq, self.nkv)
+            out = torch.empty_like(q)
+            paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
+            return linear(out, self.o)
+        qkv = linear(h, self.qkv)
         kernels.qk_norm_rope_store(
             qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
             ctx.slots[group] if write_cache else None,

@@ -418,6 +418,42 @@ def test_gemm_tc_gated(m, inner, k):
     del both
 
 
+@pytest.mark.parametrize("m,nq,nkv,k,page", [(1, 2, 1, 64, 8), (8, 32, 8, 4096, 16), (19, 3, 3, 520, 4), (32, 8, 2, 1024, 32)])
+def test_gemm_tc_qkv_heads(m, nq, nkv, k, page):
+    """The fused q/k/v projection with head norms, rotation and cache write in its epilogue, against the
+    plain functions; and against the product followed by the kernel that does the rest alone."""
+    d, eps, theta, pages = 128, 1e-6, 1e6, 9
+    g = torch.Generator().manual_seed(m + nq + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * d, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    q_w, k_w = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    positions = torch.randint(0, 3000, (m,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * page, generator=g)[:m].to(torch.int32)
+    slots[m // 2] = -1 if m > 1 else slots[0]                 # a row that writes nothing
+    inv_freq = RotaryPosition.inverse_frequencies(d, theta)
+    q_out = torch.full((m, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(pages, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    kernels.gemm_tc_qkv_heads(x.to(DEV), w.to(DEV), q_out, kc, vc, positions.to(DEV), slots.to(DEV), q_w.to(DEV), k_w.to(DEV),
+                              eps, inv_freq.to(DEV), nq, nkv)
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    qkv = (x.double() @ w.double().T).float()                  # the plain functions on the unrounded product
+    q, kk, v = plain_qk(qkv.to(DEV), positions.to(DEV), q_w.to(DEV), k_w.to(DEV), eps, theta, nq, nkv, d)
+    close(q_out.view(m, nq, d), q, torch.bfloat16, "q")
+    keep = (slots >= 0).nonzero().flatten()
+    slot = slots[keep].long()
+    close(kc.cpu()[slot // page, :, slot % page], kk[keep], torch.bfloat16, "k in the cache")
+    close(vc.cpu()[slot // page, :, slot % page], v[keep], torch.bfloat16, "v in the cache")
+    assert kc.count_nonzero().item() <= keep.numel() * nkv * d and vc.count_nonzero().item() <= keep.numel() * nkv * d
+    # q only: nothing is written without slots
+    kc.zero_()
+    kernels.gemm_tc_qkv_heads(x.to(DEV), w.to(DEV), q_out, None, None, positions.to(DEV), None, q_w.to(DEV), k_w.to(DEV), eps,
+                              inv_freq.to(DEV), nq, nkv)
+    close(q_out.view(m, nq, d), q, torch.bfloat16, "q without a cache")
+    assert kc.count_nonzero().item() == 0
+
+
 def test_gemm_tc_rows_do_not_depend_on_the_batch():
     """The same row alone, among 8 and among 100 others: equal bit for bit, twice in a row (the
     counters of the ranges of K are left ready for the next launch)."""
