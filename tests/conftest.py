@@ -37,12 +37,19 @@ TINY_C = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_siz
               num_hidden_layers=2, num_attention_heads=3, num_key_value_heads=3, head_dim=48, vocab_size=301,
               max_position_embeddings=1024, rms_norm_eps=1e-6, rope_theta=50000.0, tie_word_embeddings=False,
               hidden_act="silu", eos_token_id=5)
-TINY = {"A": (TINY_A, 4), "B": (TINY_B, 16), "C": (TINY_C, 8)}   # configuration, page size used with it
+# a fourth shape with heads of 128 and a feed-forward width that is a multiple of 64: the sizes at which the
+# serving kernels of real checkpoints run (attention fed by bulk tensor copies, tcgen05 attention, the fused
+# q/k/v and gate/up products)
+TINY_D = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=136, intermediate_size=192,
+              num_hidden_layers=2, num_attention_heads=4, num_key_value_heads=2, head_dim=128, vocab_size=515,
+              max_position_embeddings=2048, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
+              hidden_act="silu", eos_token_id=3)
+TINY = {"A": (TINY_A, 4), "B": (TINY_B, 16), "C": (TINY_C, 8), "D": (TINY_D, 16)}   # configuration, page size used with it
 
 
 @pytest.fixture(scope="session")
 def model_folders(tmp_path_factory):
-    """Model folders of the tiny configurations: bfloat16 weights, seeds 11/12/13."""
+    """Model folders of the tiny configurations: bfloat16 weights, seeds 11/12/13/14."""
     from mini_rsglang_b200.models import config_from_dict
     from mini_rsglang_b200.weights import write_random_model
 

@@ -40,7 +40,7 @@ def feed(runner, request, tokens, cuts, want_all=True):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_first_tokens_of_a_sequence(model_folders, name, dtype):
     """Positions 0, 1, 2: one key, the first page, no rotation at position 0."""
     runner = runner_for(model_folders[name], name, dtype)
@@ -79,11 +79,11 @@ def test_long_decoding(model_folders, dtype):
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-def test_recorded_decode_steps_equal_queued_ones(model_folders, dtype):
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_recorded_decode_steps_equal_queued_ones(model_folders, name, dtype):
     """Three requests of different lengths decode together: the step is padded to four rows,
     recorded once and replayed.  Logits equal those of a runner that queues every kernel (bit
     for bit in float32) and the plain implementation's."""
-    name = "B"
     vocab = TINY[name][0]["vocab_size"]
     reqs = T.requests_for(vocab, [60, 23, 41], seed=9)
     want = {r: plain(model_folders[name], t) for r, t in reqs.items()}
@@ -129,19 +129,24 @@ def sharpen(folder, out, factor):
     return out
 
 
-@pytest.mark.parametrize("name", ["A", "B"])
-def test_reused_pages_with_peaked_attention_in_float32(model_folders, tmp_path, name):
+@pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("D", "float32"), ("D", "bfloat16")])
+def test_reused_pages_with_peaked_attention(model_folders, tmp_path, name, dtype):
     """Requests come and go in a pool that holds two of them, so every page is written by several
     requests in turn and block tables are out of order; with peaked attention a stale or
-    misplaced key would change the logits at once."""
-    # factor 3: scores grow ninefold; float32 rounding of a score of that size stays below the gate
-    folder = sharpen(model_folders[name], str(tmp_path / "sharp"), 3.0)
+    misplaced key would change the logits at once.  Configuration D runs it through the serving
+    kernels as well (bfloat16, heads of 128)."""
+    # factor 3: scores grow ninefold; float32 rounding of a score of that size stays below the gate.  In
+    # bfloat16 the rounding of q and k grows with the scores as well (the reference's own rounding chain,
+    # restated by the plain implementation, moves the logits of this model by an NRMSE of 0.16 at factor 3
+    # and 0.03 at factor 1.5), so the bfloat16 run sharpens by 1.5 only.
+    folder = sharpen(model_folders[name], str(tmp_path / "sharp"), 3.0 if dtype == "float32" else 1.5)
     cfg, weights = P.PlainConfig.load(folder), P.load_plain_weights(folder)
     page = TINY[name][1]
-    reqs = T.requests_for(cfg.vocab_size, [50, 33, 61, 18, 47, 29, 55], seed=3)
-    pool_pages = 2 * (-(-61 // page)) + 1
+    lengths = [50, 33, 61, 18, 47, 29, 55] if name != "D" else [150, 33, 161, 18, 47, 129, 55]
+    reqs = T.requests_for(cfg.vocab_size, lengths, seed=3)
+    pool_pages = 2 * (-(-max(lengths) // page)) + 1
     limits = RuntimeConfig(max_seq_len=512, page_size=page, max_running=4)
-    runner = ModelRunner.load(folder, dtype="float32", limits=limits, num_pages=pool_pages)
+    runner = ModelRunner.load(folder, dtype=dtype, limits=limits, num_pages=pool_pages)
     cache = runner.cache
     queue, live, fed = list(reqs), {}, {}
     ids = {r: i + 1 for i, r in enumerate(reqs)}
@@ -159,14 +164,14 @@ def test_reused_pages_with_peaked_attention_in_float32(model_folders, tmp_path, 
         batch, places = [], []
         for r in list(live):
             p, tokens = live[r], reqs[r]
-            n = min(rng.choice([1, 2, 3, 7, 12]), len(tokens) - p)
+            n = min(rng.choice([1, 2, 3, 7, 12] if name != "D" else [1, 1, 2, 7, 40, 70]), len(tokens) - p)
             cache.extend(ids[r], p + n)
             batch.append(SequenceStep(ids[r], tokens[p:p + n], p, [n - 1]))
             places.append((r, p + n - 1))
             live[r] = p + n
         got = runner.step(batch).double().cpu()
         want = torch.stack([P.logits_of_sequence(cfg, weights, reqs[r][:p + 1])[-1] for r, p in places])
-        T.check_rows(got, want, "float32", f"{name} reuse")
+        T.check_rows(got, want, dtype, f"{name} reuse")
         for r in list(live):
             if live[r] == len(reqs[r]):
                 seen_tables.append(list(cache.table(ids[r])))
@@ -179,7 +184,7 @@ def test_reused_pages_with_peaked_attention_in_float32(model_folders, tmp_path, 
 
 
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
 def test_greedy_generation_through_the_entry_point(model_folders, name, dtype):
     folder = model_folders[name]
     cfg, weights = P.PlainConfig.load(folder), P.load_plain_weights(folder)

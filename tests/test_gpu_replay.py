@@ -12,7 +12,8 @@ import trace_tools as T
 
 pytestmark = pytest.mark.gpu
 
-LENGTHS = {"A": [70, 45, 33, 100, 130, 64, 37, 90], "B": [1, 7, 17, 40, 129, 65, 96, 50], "C": [48, 80, 35, 66, 120]}
+LENGTHS = {"A": [70, 45, 33, 100, 130, 64, 37, 90], "B": [1, 7, 17, 40, 129, 65, 96, 50], "C": [48, 80, 35, 66, 120],
+           "D": [70, 45, 200, 33, 300, 131, 64]}
 MODES = ("whole", "decode_tail", "portions", "mixed")
 
 
@@ -57,7 +58,7 @@ def replay(folder: str, name: str, dtype: str, tmp_path_factory):
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C"])
+@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
 def test_replay_matches_plain(model_folders, tmp_path_factory, name, dtype, mode):
     rows = replay(model_folders[name], name, dtype, tmp_path_factory)[mode]
     assert rows
