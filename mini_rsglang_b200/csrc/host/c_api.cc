@@ -131,6 +131,24 @@ API int mrs_sched_plan(void* s, int64_t* requests, int32_t* slots, int64_t* star
         return (int)plan.size();
     });
 }
+// Copies the tokens of every sequence of the last plan, in the plan's order; returns their number, or < 0.
+API int64_t mrs_sched_plan_tokens(void* s, int32_t* out, int64_t cap) {
+    try {
+        auto* sched = static_cast<mrs::Scheduler*>(s);
+        int64_t n = 0;
+        for (const auto& p : sched->last_plan()) {
+            const mrs::Running* r = sched->find(p.request);
+            if (!r || p.start_pos < 0 || p.start_pos + p.count > (int64_t)r->tokens.size()) return mrs::kInvalid;
+            if (n + p.count > cap) return mrs::kInvalid;
+            std::memcpy(out + n, r->tokens.data() + p.start_pos, (size_t)p.count * sizeof(int32_t));
+            n += p.count;
+        }
+        return n;
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return kException;
+    }
+}
 // Copies tokens [start, start + count) of a running request.
 API int mrs_sched_tokens(void* s, int64_t request, int64_t start, int64_t count, int32_t* out) {
     return guarded([&]() -> int {

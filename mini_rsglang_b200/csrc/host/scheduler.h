@@ -80,6 +80,7 @@ public:
     // Builds the next batch (cancelled requests are finished first, then requests are admitted).
     // An empty plan means there is nothing to run.
     const std::vector<PlannedSequence>& plan();
+    const std::vector<PlannedSequence>& last_plan() const { return plan_; }
     const Running* find(int64_t request) const;
 
     // One token per planned sequence with sample == true, in plan order.

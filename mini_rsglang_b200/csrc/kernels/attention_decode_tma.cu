@@ -387,6 +387,8 @@ MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, co
 
 // Reads and clears this library's error word (waits for the device).  0: no kernel gave up a wait.
 MRS_EXPORT int mrs_attention_decode_tma_take_error(unsigned int* word) { return mrs_take_error_word(word); }
+// Mirrors the error word into a word of pinned host memory from now on.
+MRS_EXPORT int mrs_attention_decode_tma_mirror_errors(unsigned int* host_word) { return mrs_set_error_mirror(host_word); }
 
 MRS_EXPORT const char* mrs_attention_decode_tma_error_string(int code) {
     if (code == MRS_BAD_ARGUMENT) return "arguments outside what the kernel supports (page size below 8 or no power of two, head grouping, splits)";

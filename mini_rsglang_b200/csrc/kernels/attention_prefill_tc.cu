@@ -351,6 +351,8 @@ MRS_EXPORT int mrs_attention_prefill_tc(const void* q_map, const void* k_map, co
 }
 
 MRS_EXPORT int mrs_attention_prefill_tc_take_error(unsigned int* word) { return mrs_take_error_word(word); }
+// Mirrors the error word into a word of pinned host memory from now on.
+MRS_EXPORT int mrs_attention_prefill_tc_mirror_errors(unsigned int* host_word) { return mrs_set_error_mirror(host_word); }
 
 MRS_EXPORT const char* mrs_attention_prefill_tc_error_string(int code) {
     if (code == MRS_BAD_ARGUMENT) return "arguments outside what the kernel supports (page size below 8 or no power of two, a group of query heads that does not divide 128)";

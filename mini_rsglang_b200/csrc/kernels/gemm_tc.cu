@@ -440,6 +440,8 @@ MRS_EXPORT int mrs_gemm_tc_qkv_heads(const void* w_map, const void* x_map, void*
 }
 
 MRS_EXPORT int mrs_gemm_tc_take_error(unsigned int* word) { return mrs_take_error_word(word); }
+// Mirrors the error word into a word of pinned host memory from now on.
+MRS_EXPORT int mrs_gemm_tc_mirror_errors(unsigned int* host_word) { return mrs_set_error_mirror(host_word); }
 
 MRS_EXPORT const char* mrs_gemm_tc_error_string(int code) {
     if (code == MRS_BAD_ARGUMENT) return "arguments outside what the kernel supports (K no multiple of 8, M above the padded size, unaligned base, splits)";

@@ -14,8 +14,20 @@
 #define MRS_ERR_BARRIER_TIMEOUT 1u     // an mbarrier wait ran out of time
 #define MRS_ERR_TMEM 2u                // tensor memory could not be obtained
 static __device__ unsigned int mrs_error_word = 0;
+// A word in pinned host memory that mirrors the error word (set once by the host): the host then
+// learns of an error by reading its own memory after a step, without a copy from the device.
+static __device__ unsigned int* mrs_error_mirror = nullptr;
 
-__device__ __forceinline__ void mrs_raise(unsigned int bits) { atomicOr(&mrs_error_word, bits); }
+__device__ __forceinline__ void mrs_raise(unsigned int bits) {
+    atomicOr(&mrs_error_word, bits);
+    unsigned int* mirror = mrs_error_mirror;
+    if (mirror) *reinterpret_cast<volatile unsigned int*>(mirror) = bits;
+}
+
+// `host_word`: an unsigned int in pinned (device-visible) host memory, zero while all is well.
+static inline int mrs_set_error_mirror(unsigned int* host_word) {
+    return (int)cudaMemcpyToSymbol(mrs_error_mirror, &host_word, sizeof(host_word));
+}
 
 // Reads and clears the library's error word (synchronises with the device).
 static inline int mrs_take_error_word(unsigned int* out) {

@@ -158,14 +158,10 @@ class ModelRunner:
         return cls(config, tensors, runtime, limits or RuntimeConfig(), kv_bytes, num_pages, spec)
 
     # ------------------------------------------------------------------ one step
-    def build_context(self, sequences: Sequence[SequenceStep], pad_to: int | None = None,
-                      table_width: int | None = None, staging: _Staging | None = None) -> StepContext:
-        """Checks the batch and copies what the kernels need to know about it to the device in
-        one transfer; the checking and the layout are the host library's (`csrc/host/step_batch.cc`).
-        With `pad_to` (single decoded tokens only) the batch is filled up to that many sequences
-        with rows that write nothing and whose results nobody reads, block tables get the given
-        fixed width and every row's logits are produced: the shapes and addresses of such a
-        context depend on `pad_to` alone, so its kernels can be recorded once and replayed."""
+    def _fill_step(self, sequences: Sequence[SequenceStep], pad_to: int | None, table_width: int | None,
+                   staging: "_Staging"):
+        """Checks the batch, lays its facts out in the staging buffer (the host library does both) and
+        starts the copy to the device.  Returns the layout, the device buffer and the token counts."""
         if not sequences:
             raise InvalidRequest("empty batch or KV pool")
         n = len(sequences)
@@ -181,7 +177,6 @@ class ModelRunner:
             raise InvalidRequest("token or page ID out of range")
         tokens = tokens.astype(np.int32)
         want = np.asarray([w for s in sequences for w in s.want], dtype=np.int32)
-        staging = staging or self._staging
         G = len(self.groups)
         layout = np.zeros(14 + 3 * G, dtype=np.int64)
         rows, most = int(counts.sum()) + (pad_to or n), pad_to or n
@@ -201,6 +196,18 @@ class ModelRunner:
             raise (BackendError if used == -100 else InvalidRequest)(message)
         staging.upload(int(used))
         self.h2d_bytes += 4 * int(used)
+        return layout, dev, starts, counts
+
+    def build_context(self, sequences: Sequence[SequenceStep], pad_to: int | None = None,
+                      table_width: int | None = None, staging: _Staging | None = None) -> StepContext:
+        """Checks the batch and copies what the kernels need to know about it to the device in
+        one transfer; the checking and the layout are the host library's (`csrc/host/step_batch.cc`).
+        With `pad_to` (single decoded tokens only) the batch is filled up to that many sequences
+        with rows that write nothing and whose results nobody reads, block tables get the given
+        fixed width and every row's logits are produced: the shapes and addresses of such a
+        context depend on `pad_to` alone, so its kernels can be recorded once and replayed."""
+        layout, dev, starts, counts = self._fill_step(sequences, pad_to, table_width, staging or self._staging)
+        n, G = len(sequences), len(self.groups)
         T, B, R, decode = (int(v) for v in layout[:4])
 
         def dview(offset, count, shape=None):
@@ -254,6 +261,11 @@ class ModelRunner:
         if record is None:
             record = self._records[key] = _Recorded(self.device)
         width = -(-self.limits.max_seq_len // self.limits.page_size)
+        if record.graph is not None:          # the recorded context's tensors stay where they are: only their contents change
+            self._fill_step(sequences, bucket, width, record.staging)
+            record.graph.replay()
+            kernels.launch_count += record.launches
+            return record.logits[:real]
         ctx = self.build_context(sequences, pad_to=bucket, table_width=width, staging=record.staging)
         if record.graph is None:
             ctx.max_context_len = context_class      # launches are planned for the class, not for this step

@@ -97,17 +97,22 @@ class Scheduler:
                                     self._req.size)
         if n < 0:
             raise BackendError(f"scheduler plan: {last_error(self.lib)}")
-        out = []
+        if n == 0:
+            return []
+        counts = self._count[:n].tolist()
+        total = sum(counts)
+        if total > self._tokens.size:
+            self._tokens = np.empty(2 * total, dtype=np.int32)
+        got = self.lib.mrs_sched_plan_tokens(self.handle, self._tokens.ctypes.data, self._tokens.size)
+        if got != total:
+            raise BackendError("scheduler: planned tokens are not available")
+        tokens = self._tokens[:total].tolist()
+        requests, slots, starts, samples = (self._req[:n].tolist(), self._slot[:n].tolist(), self._start[:n].tolist(),
+                                            self._sample[:n].tolist())
+        out, at = [], 0
         for i in range(n):
-            count = int(self._count[i])
-            if count > self._tokens.size:
-                self._tokens = np.empty(count, dtype=np.int32)
-            got = self.lib.mrs_sched_tokens(self.handle, int(self._req[i]), int(self._start[i]), count,
-                                            self._tokens.ctypes.data)
-            if got != count:
-                raise BackendError("scheduler: planned tokens are not available")
-            out.append(PlannedSequence(int(self._req[i]), int(self._slot[i]), int(self._start[i]),
-                                       self._tokens[:count].tolist(), bool(self._sample[i])))
+            out.append(PlannedSequence(requests[i], slots[i], starts[i], tokens[at:at + counts[i]], bool(samples[i])))
+            at += counts[i]
         return out
 
     def commit(self, sampled: list[int]) -> None:

@@ -360,7 +360,7 @@ def attention_decode_tma_library(d: int) -> ctypes.CDLL:
         lib.mrs_attention_decode_tma_error_string.argtypes = [_c_int]
         lib.mrs_attention_decode_tma_error_string.restype = ctypes.c_char_p
         _decode_libs[d] = lib
-        _error_readers.append((f"attention_decode_tma (head size {d})", lib.mrs_attention_decode_tma_take_error))
+        _register_error_word(f"attention_decode_tma (head size {d})", lib, "mrs_attention_decode_tma")
     return _decode_libs[d]
 
 
@@ -442,7 +442,7 @@ def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
         lib.mrs_attention_prefill_tc_error_string.argtypes = [_c_int]
         lib.mrs_attention_prefill_tc_error_string.restype = ctypes.c_char_p
         _prefill_libs[d] = lib
-        _error_readers.append((f"attention_prefill_tc (head size {d})", lib.mrs_attention_prefill_tc_take_error))
+        _register_error_word(f"attention_prefill_tc (head size {d})", lib, "mrs_attention_prefill_tc")
     return _prefill_libs[d]
 
 
@@ -516,7 +516,7 @@ def gemm_tc_library() -> ctypes.CDLL:
         lib.mrs_gemm_tc_error_string.argtypes = [_c_int]
         lib.mrs_gemm_tc_error_string.restype = ctypes.c_char_p
         _gemm_lib = lib
-        _error_readers.append(("gemm_tc", lib.mrs_gemm_tc_take_error))
+        _register_error_word("gemm_tc", lib, "mrs_gemm_tc")
     return _gemm_lib
 
 
@@ -665,9 +665,36 @@ def gemm_tc_qkv_heads(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor
 # ------------------------------------------------------------------------------------------------
 # error words of the kernels that wait on barriers
 # ------------------------------------------------------------------------------------------------
-def check_device_errors() -> None:
-    """Reads (and clears) the error word of every loaded library whose kernels wait on barriers;
-    raises when a kernel gave up a wait.  Waits for the device, so it is called after a step."""
+_mirror_view = None
+_mirror = None          # pinned host words, one per library, that the kernels' error words are mirrored into
+
+
+def _register_error_word(what: str, lib, prefix: str) -> None:
+    """Keeps the library's reader and points its mirror at the next free pinned word."""
+    global _mirror, _mirror_view
+    if _mirror is None:
+        _mirror = torch.zeros(16, dtype=torch.int32).pin_memory()
+        _mirror_view = _mirror.numpy()
+    index = len(_error_readers)
+    reader = getattr(lib, f"{prefix}_take_error")
+    _error_readers.append((what, reader))
+    mirror = getattr(lib, f"{prefix}_mirror_errors")
+    mirror.argtypes = [_c_vp]
+    mirror.restype = _c_int
+    if index < _mirror.numel():
+        code = mirror(_mirror.data_ptr() + 4 * index)
+        if code != 0:
+            raise BackendError(f"{what}: cannot mirror the error word (CUDA error {code})")
+
+
+def check_device_errors(certain: bool = False) -> None:
+    """Raises when a kernel gave up a wait.  Called after a step, when the device is idle: the
+    kernels mirror their error words into pinned host memory, so all is well as long as those
+    words are zero; only then (or when `certain`) the words are read from the device and cleared."""
+    if _mirror is not None and not certain and len(_error_readers) <= _mirror.numel() and not _mirror_view.any():
+        return
+    if _mirror is not None:
+        _mirror.zero_()
     for what, reader in _error_readers:
         word = ctypes.c_uint(0)
         code = reader(ctypes.byref(word))
