@@ -2,21 +2,26 @@
 // sizes 64 and 128: -DMRS_HEAD_DIM=64|128.     (reference: ops.cu:101-147, one CTA per (token,
 // head) on the CUDA cores)
 //
-// A tile is 128 query rows of one key/value head: 128 / group consecutive tokens of one request
-// times the group's query heads, so a key is read once for all the heads that share it.  The
-// tile's keys are walked in blocks of 128:
-//   warp 0     one thread fetches the query tile and, page by page through the request's block
-//              table, the keys and values of every block with bulk tensor copies (TMA, 128-byte
-//              swizzle) into two-stage rings;
-//   warp 1     one thread issues the MMAs: S = Q.K^T into one of two score buffers in tensor
-//              memory (so the scores of the next block are computed while the softmax of this one
-//              runs), then O += P.V with P read from shared memory and V taken as it lies in the
-//              cache (rows of keys, the MN-major operand form);
-//   warps 2-5  one thread per query row: scores from tensor memory, mask, running maximum and
-//              sum in float32, probabilities as bfloat16 into shared memory in the operand layout.
-//              The accumulator O stays in tensor memory; it is rescaled only when a row's maximum
-//              grew by more than 2^8 since the last rescale (the sum uses the same reference, so
-//              the quotient is exact), and is normalised and stored at the end.
+// A CTA works on two tiles of 128 query rows of one key/value head: a tile is 128 / group
+// consecutive tokens of one request times the group's query heads, so a key is read once for all
+// the heads that share it, and the second tile holds the tokens that follow the first.  The keys
+// are walked in blocks of 128:
+//   warp 0      fetches the query tiles and, page by page through the request's block table, the
+//               keys and values of every block with bulk tensor copies (TMA, 128-byte swizzle)
+//               into two-stage rings; every lane owns one page of a block;
+//   warp 1      one thread issues the MMAs: S = Q.K^T of each tile into the tile's score buffer in
+//               tensor memory, then O += P.V with P read from tensor memory (it overwrites the
+//               scores it came from) and V taken as it lies in the cache (rows of keys, the MN-major
+//               operand form);
+//   warps 2-5   softmax of the first tile, warps 6-9 of the second, one thread per query row:
+//               scores from tensor memory, mask, running maximum and sum in float32, probabilities
+//               back into tensor memory as pairs of bfloat16.
+// The two tiles take turns: while one tile's exponentials run (the special-function unit makes 16
+// a clock, as long as the block's MMAs take) the tensor cores work on the other tile.  Shared
+// memory carries only Q, K and V: with P there too its bandwidth (128 bytes a clock) was the bound.
+// The accumulators stay in tensor memory; one is rescaled only when a row's maximum grew by more
+// than 2^8 since the last rescale (the sum uses the same reference, so the quotient is exact), and
+// is normalised and stored at the end.
 // Every wait is bounded (tma.cuh).
 #include "tcgen05.cuh"
 
@@ -30,14 +35,18 @@ constexpr int D = MRS_HEAD_DIM;
 static_assert(D == 64 || D == 128, "this kernel takes head sizes 64 and 128");
 constexpr int HALVES = D / 64;
 constexpr int BM = 128;                          // query rows of a tile
+constexpr int TILES = 2;                         // tiles of a CTA
 constexpr int BN = 128;                          // keys of a block
-constexpr int THREADS = 192;
-constexpr int Q_BYTES = BM * D * 2;
+constexpr int STAGES = 2;                        // of the key and of the value ring
+constexpr int THREADS = 64 + TILES * 128;
+constexpr int Q_TILE_BYTES = BM * D * 2;
+constexpr int Q_HALF_BYTES = BM * 128;           // 128 rows of 128 bytes: one group of 64 columns of a query tile
 constexpr int KV_TILE_BYTES = BN * D * 2;        // keys (or values) of a block
-constexpr int P_BYTES = BM * BN * 2;
-constexpr int HALF_BYTES = 128 * 128;            // 128 rows of 128 bytes: one group of 64 columns of a tile
+constexpr int KV_HALF_BYTES = BN * 128;
 constexpr int TMEM_COLUMNS = 512;
-constexpr int S_COLUMN = 0, O_COLUMN = 2 * BN;   // two score buffers, then the accumulator
+constexpr int S_COLUMNS = BN;                    // a tile's scores; its probabilities (pairs of bfloat16) take the first half
+constexpr int O_COLUMN = TILES * S_COLUMNS;      // the score buffers, then the accumulators
+static_assert(O_COLUMN + TILES * D <= TMEM_COLUMNS, "tensor memory");
 constexpr float RESCALE_THRESHOLD = 8.0f;        // in powers of two
 
 struct Tile {
@@ -52,10 +61,11 @@ __device__ __forceinline__ float fast_exp2(float x) {
 }
 
 struct Barriers {
-    uint64_t q_full, k_full[2], k_empty[2], v_full[2], v_empty[2], s_full[2], p_ready, pv_done;
+    uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
+    uint64_t s_full[TILES], p_ready[TILES], pv_done[TILES];
 };
 
-constexpr size_t SMEM_BYTES = 1024 + Q_BYTES + 4 * KV_TILE_BYTES + P_BYTES + sizeof(Barriers) + 16;
+constexpr size_t SMEM_BYTES = 1024 + TILES * Q_TILE_BYTES + 2 * STAGES * KV_TILE_BYTES + sizeof(Barriers) + 16;
 
 __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
@@ -63,37 +73,49 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     int table_width, const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv, int page_size,
     int page_shift, float scale_log2, int window) {
     extern __shared__ unsigned char smem_raw[];
-    const Tile tile = tiles[blockIdx.x];
-    if (tile.tokens <= 0) return;
+    const Tile work = tiles[blockIdx.x];
+    if (work.tokens <= 0) return;
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
-    unsigned char* q_smem = smem;
-    unsigned char* k_smem = q_smem + Q_BYTES;               // two stages
-    unsigned char* v_smem = k_smem + 2 * KV_TILE_BYTES;     // two stages
-    unsigned char* p_smem = v_smem + 2 * KV_TILE_BYTES;
-    Barriers* bars = reinterpret_cast<Barriers*>(p_smem + P_BYTES);
+    unsigned char* q_smem = smem;                                   // [tile][half][128 rows][64]
+    unsigned char* k_smem = q_smem + TILES * Q_TILE_BYTES;          // [stage][half][128 keys][64]
+    unsigned char* v_smem = k_smem + STAGES * KV_TILE_BYTES;
+    Barriers* bars = reinterpret_cast<Barriers*>(v_smem + STAGES * KV_TILE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
 
     const int kv_head = blockIdx.y, group = nq / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int* pages = block_table + (size_t)tile.seq * table_width;
-    const int rows = tile.tokens * group;
-    const int first_pos = positions[tile.first_token], last_pos = positions[tile.first_token + tile.tokens - 1];
-    const int key_end = last_pos + 1;
+    const int* pages = block_table + (size_t)work.seq * table_width;
+    const int tokens_per_tile = BM / group;
+    // the tokens of the two tiles, their positions (a request's tokens of a step are consecutive) and their blocks of keys
+    int tile_first[TILES], tile_tokens[TILES], tile_blocks[TILES], tile_first_pos[TILES];
+    const int first_pos = positions[work.first_token];
     const int key_begin = window > 0 ? max(0, first_pos - window + 1) : 0;
-    const int block_first = key_begin / BN, block_last = (key_end + BN - 1) / BN;
-    const int blocks = block_last - block_first;
+    const int block_first = key_begin / BN;
+    int blocks = 0;
+#pragma unroll
+    for (int i = 0; i < TILES; ++i) {
+        tile_first[i] = work.first_token + i * tokens_per_tile;
+        tile_tokens[i] = max(0, min(tokens_per_tile, work.tokens - i * tokens_per_tile));
+        tile_first_pos[i] = first_pos + i * tokens_per_tile;
+        const int last_pos = tile_first_pos[i] + tile_tokens[i] - 1;
+        tile_blocks[i] = tile_tokens[i] > 0 ? (last_pos + BN) / BN - block_first : 0;
+        blocks = max(blocks, tile_blocks[i]);
+    }
+    const int key_end = first_pos + work.tokens;
 
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 1);
-        for (int s = 0; s < 2; ++s) {
+        for (int s = 0; s < STAGES; ++s) {
             mbar_init(&bars->k_full[s], 1);
             mbar_init(&bars->k_empty[s], 1);
             mbar_init(&bars->v_full[s], 1);
             mbar_init(&bars->v_empty[s], 1);
-            mbar_init(&bars->s_full[s], 1);
         }
-        mbar_init(&bars->p_ready, 4);
-        mbar_init(&bars->pv_done, 1);
+        for (int i = 0; i < TILES; ++i) {
+            mbar_init(&bars->s_full[i], 1);
+            mbar_init(&bars->p_ready[i], 4);
+            mbar_init(&bars->pv_done[i], 1);
+        }
         mbar_fence_init();
     }
     if (warp == 1) {
@@ -116,9 +138,12 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
             tma_prefetch_descriptor(&q_map);
             tma_prefetch_descriptor(&k_map);
             tma_prefetch_descriptor(&v_map);
-            mbar_arrive_expect_tx(&bars->q_full, Q_BYTES);
-            for (int h = 0; h < HALVES; ++h)
-                tma_load_3d(q_smem + h * HALF_BYTES, &q_map, &bars->q_full, h * 64, kv_head * group, tile.first_token);
+            // rows past the last token arrive as zeros or as other tokens' queries, and are never stored
+            mbar_arrive_expect_tx(&bars->q_full, TILES * Q_TILE_BYTES);
+            for (int i = 0; i < TILES; ++i)
+                for (int h = 0; h < HALVES; ++h)
+                    tma_load_3d(q_smem + i * Q_TILE_BYTES + h * Q_HALF_BYTES, &q_map, &bars->q_full, h * 64, kv_head * group,
+                                tile_first[i]);
         }
         const int rows_per_copy = min(page_size, BN);
         const int copies = BN / rows_per_copy;
@@ -130,10 +155,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
         };
         int next_page = page_of(0);
         for (int j = 0; j < blocks; ++j) {
-            const int s = j & 1;
+            const int s = j % STAGES;
             const int my_page = next_page;
             if (j + 1 < blocks) next_page = page_of(j + 1);
-            const uint32_t wait_parity = ((j >> 1) & 1) ^ 1;
+            const uint32_t wait_parity = ((j / STAGES) & 1) ^ 1;
             for (int which = 0; which < 2; ++which) {            // keys, then values
                 uint64_t* full = which ? &bars->v_full[s] : &bars->k_full[s];
                 if (lane == 0) {
@@ -147,7 +172,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
                     const int key = (block_first + j) * BN + lane * rows_per_copy;
                     const int row = my_page < 0 ? 0 : key & (page_size - 1);
                     for (int h = 0; h < HALVES; ++h)
-                        tma_load_5d(dst + h * HALF_BYTES + lane * rows_per_copy * 128, map, full, 0, row, h, kv_head, max(my_page, 0));
+                        tma_load_5d(dst + h * KV_HALF_BYTES + lane * rows_per_copy * 128, map, full, 0, row, h, kv_head, max(my_page, 0));
                 }
             }
         }
@@ -156,58 +181,80 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
         if (lane == 0) {
             constexpr uint32_t idesc_s = umma_idesc_bf16_f32(BM, BN);
             constexpr uint32_t idesc_o = umma_idesc_bf16_f32(BM, D, true);
-            const uint32_t q_addr = smem_u32(q_smem), p_addr = smem_u32(p_smem);
-            auto issue_scores = [&](int j) {
-                const int s = j & 1;
-                mbar_wait(&bars->k_full[s], (j >> 1) & 1);
-                tcgen05_fence_after_sync();
-                const uint32_t k_addr = smem_u32(k_smem + s * KV_TILE_BYTES);
+            const uint32_t q_addr = smem_u32(q_smem);
+            // scores of block j of tile i (the keys of block j are in their stage)
+            auto issue_scores = [&](int i, int j) {
+                const uint32_t k_addr = smem_u32(k_smem + (j % STAGES) * KV_TILE_BYTES);
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k) {
-                    const uint32_t offset = (k / 4) * HALF_BYTES + (k % 4) * 32;
-                    umma_bf16(tmem_base + S_COLUMN + s * BN, umma_smem_desc_sw128(q_addr + offset),
-                              umma_smem_desc_sw128(k_addr + offset), idesc_s, k > 0);
-                }
-                umma_commit(&bars->k_empty[s]);
-                umma_commit(&bars->s_full[s]);
+                for (int k = 0; k < D / 16; ++k)
+                    umma_bf16(tmem_base + i * S_COLUMNS,
+                              umma_smem_desc_sw128(q_addr + i * Q_TILE_BYTES + (k / 4) * Q_HALF_BYTES + (k % 4) * 32),
+                              umma_smem_desc_sw128(k_addr + (k / 4) * KV_HALF_BYTES + (k % 4) * 32), idesc_s, k > 0);
+                umma_commit(&bars->s_full[i]);
             };
             mbar_wait(&bars->q_full, 0);
-            issue_scores(0);
-            for (int j = 0; j < blocks; ++j) {
-                const int s = j & 1;
-                if (j + 1 < blocks) issue_scores(j + 1);
-                mbar_wait(&bars->p_ready, j & 1);
-                mbar_wait(&bars->v_full[s], (j >> 1) & 1);
-                tcgen05_fence_after_sync();
-                const uint32_t v_addr = smem_u32(v_smem + s * KV_TILE_BYTES);
+            mbar_wait(&bars->k_full[0], 0);
+            tcgen05_fence_after_sync();
 #pragma unroll
-                for (int k = 0; k < BN / 16; ++k)
-                    umma_bf16(tmem_base + O_COLUMN, umma_smem_desc_sw128(p_addr + (k / 4) * HALF_BYTES + (k % 4) * 32),
-                              umma_smem_desc_sw128_mn(v_addr + k * 2048, HALF_BYTES), idesc_o, j > 0 || k > 0);
+            for (int i = 0; i < TILES; ++i)
+                if (tile_blocks[i] > 0) issue_scores(i, 0);
+            umma_commit(&bars->k_empty[0]);
+            // The tiles take turns: P.V of a tile's block, then at once the scores of its next block (the
+            // probabilities lie where the scores lay, and MMAs run in the order they are issued).
+            for (int j = 0; j < blocks; ++j) {
+                const int s = j % STAGES;
+                bool waited_v = false, waited_k = false;
+#pragma unroll
+                for (int i = 0; i < TILES; ++i) {
+                    if (j >= tile_blocks[i]) continue;
+                    mbar_wait(&bars->p_ready[i], j & 1);
+                    if (!waited_v) mbar_wait(&bars->v_full[s], (j / STAGES) & 1), waited_v = true;
+                    tcgen05_fence_after_sync();
+                    const uint32_t v_addr = smem_u32(v_smem + s * KV_TILE_BYTES);
+#pragma unroll
+                    for (int k = 0; k < BN / 16; ++k)
+                        umma_bf16_a_tmem(tmem_base + O_COLUMN + i * D, tmem_base + i * S_COLUMNS + k * 8,
+                                         umma_smem_desc_sw128_mn(v_addr + k * 2048, KV_HALF_BYTES), idesc_o, j > 0 || k > 0);
+                    if (j + 1 < tile_blocks[i]) {
+                        if (!waited_k) mbar_wait(&bars->k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1), waited_k = true;
+                        tcgen05_fence_after_sync();
+                        issue_scores(i, j + 1);
+                    } else {
+                        umma_commit(&bars->pv_done[i]);          // the tile's last block: its accumulator is final
+                    }
+                }
                 umma_commit(&bars->v_empty[s]);
-                umma_commit(&bars->pv_done);
+                if (waited_k) umma_commit(&bars->k_empty[(j + 1) % STAGES]);
             }
         }
     } else {
-        // ------------------------------------------------------------------ softmax, one thread per query row
+        // ------------------------------------------------------------------ softmax, one thread per query row of one tile
+        const int i = (warp - 2) >> 2;                      // the tile of this warp group
         const int quarter = warp & 3;
         const int row = quarter * 32 + lane;
+        const int rows = tile_tokens[i] * group;
         const uint32_t lane_base = tmem_base + ((uint32_t)(quarter * 32) << 16);
-        const int pos = row < rows ? positions[tile.first_token + row / group] : -1;
+        const int my_first_pos = tile_first_pos[i];
+        const int pos = row < rows ? my_first_pos + row / group : -1;
         const int lowest = window > 0 ? pos - window + 1 : 0;        // first key this row sees
+        const int my_blocks = tile_blocks[i];
+        const uint32_t s_tmem = lane_base + i * S_COLUMNS;
         float reference = -CUDART_INF_F;     // the maximum that probabilities and the accumulator are scaled by
         float sum = 0.0f;
-        for (int j = 0; j < blocks; ++j) {
-            const int s = j & 1;
+        for (int j = 0; j < my_blocks; ++j) {
             const int key0 = (block_first + j) * BN;
-            mbar_wait(&bars->s_full[s], (j >> 1) & 1);
+            // The scores of block j were issued after P.V of block j - 1, so when they are complete that
+            // product has been added and the accumulator may be rescaled.
+            mbar_wait(&bars->s_full[i], j & 1);
             __syncwarp();                    // the loads below are collective: the warp goes on together
             tcgen05_fence_after_sync();
+            // a block needs masks when a key of it lies behind the tile's first position or before a row's window
+            const bool edge = key0 + BN - 1 > my_first_pos || (window > 0 && key0 < my_first_pos + tile_tokens[i] - window + 1);
+            // all scores of the row in one trip to tensor memory (a trip costs hundreds of clocks), then the row's maximum
             float x[BN];
 #pragma unroll
-            for (int c = 0; c < BN; c += 32) tmem_load_32_async(lane_base + S_COLUMN + s * BN + c, x + c);
+            for (int c0 = 0; c0 < BN; c0 += 32) tmem_load_32_async(s_tmem + c0, x + c0);
             tmem_load_wait();
-            const bool edge = key0 + BN - 1 > first_pos || key0 < key_begin + (window > 0 ? BN : 0);   // a block that needs masks
             float part_max[4] = {-CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F, -CUDART_INF_F};   // four chains, not one of 128 links
             if (edge) {
 #pragma unroll
@@ -226,69 +273,63 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
             float alpha = 1.0f;
             const bool moved = block_max > reference + RESCALE_THRESHOLD;
             if (moved) {
-                alpha = exp2f(reference - block_max);          // 0 when the reference was -inf
+                alpha = fast_exp2(reference - block_max);      // 0 when the reference was -inf
                 reference = block_max;
             }
             const float base = reference == -CUDART_INF_F ? 0.0f : reference;
-            float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-            uint32_t packed[BN / 2];
+            if (j > 0 && __any_sync(0xffffffffu, moved)) {
 #pragma unroll
-            for (int c = 0; c < BN; c += 2) {
-                const float p0 = fast_exp2(fmaf(x[c], scale_log2, -base)), p1 = fast_exp2(fmaf(x[c + 1], scale_log2, -base));
-                part_sum[(c >> 1) & 3] += p0 + p1;
-                __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
-                packed[c / 2] = *reinterpret_cast<uint32_t*>(&pair);
-            }
-            sum = sum * alpha + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
-            // the last block's P.V must be done before its probabilities are overwritten or O is rescaled
-            if (j > 0) {
-                mbar_wait(&bars->pv_done, (j - 1) & 1);
-                __syncwarp();
-                tcgen05_fence_after_sync();
-                if (__any_sync(0xffffffffu, moved)) {
+                for (int c = 0; c < D; c += 16) {
+                    float o[16];
+                    tmem_load_16(lane_base + O_COLUMN + i * D + c, o);
 #pragma unroll
-                    for (int c = 0; c < D; c += 16) {
-                        float o[16];
-                        tmem_load_16(lane_base + O_COLUMN + c, o);
-#pragma unroll
-                        for (int i = 0; i < 16; ++i) o[i] *= alpha;
-                        tmem_store_16(lane_base + O_COLUMN + c, o);
-                    }
-                    tmem_store_wait();
+                    for (int e = 0; e < 16; ++e) o[e] *= alpha;
+                    tmem_store_16(lane_base + O_COLUMN + i * D + c, o);
                 }
             }
-            // probabilities of this row: 16-byte chunks of 8 keys, xor-ed with the row as the operand layout wants
+            // probabilities, 32 scores at a time; their 16 words of bfloat16 pairs go where the scores lay
+            float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
 #pragma unroll
-            for (int chunk = 0; chunk < BN / 8; ++chunk) {
-                unsigned char* dst = p_smem + (chunk / 8) * HALF_BYTES + row * 128 + (((chunk & 7) ^ (row & 7)) << 4);
-                *reinterpret_cast<uint4*>(dst) = make_uint4(packed[4 * chunk], packed[4 * chunk + 1], packed[4 * chunk + 2], packed[4 * chunk + 3]);
+            for (int c0 = 0; c0 < BN; c0 += 32) {
+                uint32_t packed[16];
+#pragma unroll
+                for (int c = 0; c < 32; c += 2) {
+                    const float p0 = fast_exp2(fmaf(x[c0 + c], scale_log2, -base)), p1 = fast_exp2(fmaf(x[c0 + c + 1], scale_log2, -base));
+                    part_sum[(c >> 1) & 3] += p0 + p1;
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                    packed[c / 2] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                tmem_store_16_words(s_tmem + c0 / 2, packed);
             }
-            fence_async_shared();
+            sum = sum * alpha + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
+            tmem_store_wait();
             tcgen05_fence_before_sync();
             __syncwarp();
-            if (lane == 0) mbar_arrive(&bars->p_ready);
+            if (lane == 0) mbar_arrive(&bars->p_ready[i]);
         }
-        mbar_wait(&bars->pv_done, (blocks - 1) & 1);
-        __syncwarp();
-        tcgen05_fence_after_sync();
-        const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-        // loads from tensor memory are collective: every lane of the warp takes part, rows past the
-        // tile's end drop what they read
-        bf16* dst = out + ((size_t)(tile.first_token + (row < rows ? row / group : 0)) * nq + kv_head * group +
-                           (row < rows ? row % group : 0)) * D;
+        if (my_blocks > 0) {
+            mbar_wait(&bars->pv_done[i], 0);
+            __syncwarp();
+            tcgen05_fence_after_sync();
+            const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+            // loads from tensor memory are collective: every lane of the warp takes part, rows past the
+            // tile's end drop what they read
+            bf16* dst = out + ((size_t)(tile_first[i] + (row < rows ? row / group : 0)) * nq + kv_head * group +
+                               (row < rows ? row % group : 0)) * D;
 #pragma unroll
-        for (int c = 0; c < D; c += 16) {
-            float o[16];
-            tmem_load_16(lane_base + O_COLUMN + c, o);
-            uint32_t w[8];
+            for (int c = 0; c < D; c += 16) {
+                float o[16];
+                tmem_load_16(lane_base + O_COLUMN + i * D + c, o);
+                uint32_t w[8];
 #pragma unroll
-            for (int i = 0; i < 8; ++i) {
-                __nv_bfloat162 pair = __floats2bfloat162_rn(o[2 * i] * inv, o[2 * i + 1] * inv);
-                w[i] = *reinterpret_cast<uint32_t*>(&pair);
-            }
-            if (row < rows) {
-                *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
-                *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                for (int e = 0; e < 8; ++e) {
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(o[2 * e] * inv, o[2 * e + 1] * inv);
+                    w[e] = *reinterpret_cast<uint32_t*>(&pair);
+                }
+                if (row < rows) {
+                    *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
+                    *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
+                }
             }
         }
     }
@@ -308,7 +349,8 @@ int page_shift_of(int page_size) {
 
 }  // namespace
 
-MRS_EXPORT int mrs_attention_prefill_tc_rows() { return BM; }
+// Query rows of one CTA: two tiles of 128.
+MRS_EXPORT int mrs_attention_prefill_tc_rows() { return TILES * BM; }
 
 // Tensor map of one layer's key or value pages [pages, kv_heads, page_size, D] for copies of one
 // group of 64 columns of up to 128 rows of a page.  `map_out`: 128 bytes, 64-byte aligned.
@@ -330,7 +372,7 @@ MRS_EXPORT int mrs_attention_prefill_tc_q_map(const void* q, long long tokens, i
     return mrs_make_tensor_map_bf16(reinterpret_cast<CUtensorMap*>(map_out), q, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-// Tiles of up to 128 / group tokens of one request each ((sequence, first token, tokens, 0) per tile).
+// Work entries of up to 256 / group consecutive tokens of one request each ((sequence, first token, tokens, 0)).
 MRS_EXPORT int mrs_attention_prefill_tc(const void* q_map, const void* k_map, const void* v_map, const int* positions,
                                         const int* block_table, int table_width, const int* tiles, int num_tiles,
                                         void* out, int nq, int nkv, int page_size, float scale, int window, void* stream) {

@@ -419,11 +419,11 @@ def attention_decode_tma(q, k_cache, v_cache, positions, block_table, tiles, out
 _prefill_libs: dict[int, ctypes.CDLL] = {}
 _prefill_kv_maps: dict[tuple, tuple] = {}
 _prefill_q_map: dict[torch.device, tuple] = {}
-PREFILL_TC_ROWS = 128
+PREFILL_TC_ROWS = 256          # two tiles of 128 query rows a CTA
 
 
 def attention_prefill_tc_supported(d: int, group: int, page_size: int) -> bool:
-    return d in (64, 128) and PREFILL_TC_ROWS % group == 0 and page_size >= 8
+    return d in (64, 128) and 128 % group == 0 and page_size >= 8
 
 
 def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
@@ -448,7 +448,7 @@ def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
 
 def attention_prefill_tc(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int,
                          window: int = 0, scale: float | None = None) -> None:
-    """Tiles of up to 128 // (nq // nkv) tokens of one request each, on the tcgen05 tensor cores."""
+    """Work entries of up to 256 // (nq // nkv) tokens of one request each, on the tcgen05 tensor cores."""
     global launch_count
     _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
     lib = attention_prefill_tc_library(d)

@@ -210,7 +210,7 @@ class PagedCase:
 
     def run_mma(self, mode, splits=1):
         group = self.nq // self.nkv
-        per_tile = {"rows": 64, "tc": 128}.get(mode, 16) // group
+        per_tile = {"rows": 64, "tc": 256}.get(mode, 16) // group
         tiles = []
         for i in range(len(self.spans)):
             first, n = self.q_start[i], self.q_start[i + 1] - self.q_start[i]
