@@ -316,19 +316,20 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
             // tile's end drop what they read
             bf16* dst = out + ((size_t)(tile_first[i] + (row < rows ? row / group : 0)) * nq + kv_head * group +
                                (row < rows ? row % group : 0)) * D;
+            float o[D];                        // one trip to tensor memory for the whole row
 #pragma unroll
-            for (int c = 0; c < D; c += 16) {
-                float o[16];
-                tmem_load_16(lane_base + O_COLUMN + i * D + c, o);
-                uint32_t w[8];
+            for (int c = 0; c < D; c += 32) tmem_load_32_async(lane_base + O_COLUMN + i * D + c, o + c);
+            tmem_load_wait();
+            if (row < rows) {
 #pragma unroll
-                for (int e = 0; e < 8; ++e) {
-                    __nv_bfloat162 pair = __floats2bfloat162_rn(o[2 * e] * inv, o[2 * e + 1] * inv);
-                    w[e] = *reinterpret_cast<uint32_t*>(&pair);
-                }
-                if (row < rows) {
+                for (int c = 0; c < D; c += 8) {
+                    uint32_t w[4];
+#pragma unroll
+                    for (int e = 0; e < 4; ++e) {
+                        __nv_bfloat162 pair = __floats2bfloat162_rn(o[c + 2 * e] * inv, o[c + 2 * e + 1] * inv);
+                        w[e] = *reinterpret_cast<uint32_t*>(&pair);
+                    }
                     *reinterpret_cast<uint4*>(dst + c) = make_uint4(w[0], w[1], w[2], w[3]);
-                    *reinterpret_cast<uint4*>(dst + c + 8) = make_uint4(w[4], w[5], w[6], w[7]);
                 }
             }
         }

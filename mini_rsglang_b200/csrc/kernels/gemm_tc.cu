@@ -186,14 +186,10 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
             mbar_wait(&acc_full[buffer], (round >> 1) & 1);
             __syncwarp();                    // the loads from tensor memory are collective
             tcgen05_fence_after_sync();
-            float acc[MPAD];
+            float acc[MPAD];                   // one trip to tensor memory for the whole row
 #pragma unroll
-            for (int c = 0; c < MPAD; c += 16) {
-                float v[16];
-                tmem_load_16(tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * MPAD + c, v);
-#pragma unroll
-                for (int i = 0; i < 16; ++i) acc[c + i] = v[i];
-            }
+            for (int c = 0; c < MPAD; c += 16) tmem_load_16_async(tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * MPAD + c, acc + c);
+            tmem_load_wait();
             tcgen05_fence_before_sync();
             __syncwarp();
             if (lane == 0) mbar_arrive(&acc_empty[buffer]);      // the MMA warp may overwrite this accumulator

@@ -81,6 +81,16 @@ __device__ __forceinline__ void umma_commit(uint64_t* bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(smem_u32(bar)) : "memory");
 }
 
+__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
+
+// 16 consecutive columns of this thread's lane; the values may be used after tmem_load_wait().
+__device__ __forceinline__ void tmem_load_16_async(uint32_t address, float* v) {
+    asm volatile("tcgen05.ld.sync.aligned.32x32b.x16.b32 {%0,%1,%2,%3,%4,%5,%6,%7,%8,%9,%10,%11,%12,%13,%14,%15}, [%16];"
+                 : "=f"(v[0]), "=f"(v[1]), "=f"(v[2]), "=f"(v[3]), "=f"(v[4]), "=f"(v[5]), "=f"(v[6]), "=f"(v[7]),
+                   "=f"(v[8]), "=f"(v[9]), "=f"(v[10]), "=f"(v[11]), "=f"(v[12]), "=f"(v[13]), "=f"(v[14]), "=f"(v[15])
+                 : "r"(address) : "memory");
+}
+
 // 16 consecutive columns of this thread's lane (lane = 32 * (warp % 4) + lane of the warp).
 __device__ __forceinline__ void tmem_load_16(uint32_t address, float (&v)[16]) {
     uint32_t r[16];
@@ -103,8 +113,6 @@ __device__ __forceinline__ void tmem_load_32_async(uint32_t address, float* v) {
                    "=f"(v[24]), "=f"(v[25]), "=f"(v[26]), "=f"(v[27]), "=f"(v[28]), "=f"(v[29]), "=f"(v[30]), "=f"(v[31])
                  : "r"(address) : "memory");
 }
-__device__ __forceinline__ void tmem_load_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
-
 // 32 consecutive columns of this thread's lane.
 __device__ __forceinline__ void tmem_load_32(uint32_t address, float* v) {
     uint32_t r[32];
