@@ -270,3 +270,115 @@ def test_toy_architecture_is_registered_built_and_stepped(toy_folder):
     for r in reqs:
         runner.cache.close(ids[r])
     runner.cache.check_integrity()
+
+
+# ---------------------------------------------------------------------------------------------
+# layers with different needs of the cache: a window of keys beside all keys
+# ---------------------------------------------------------------------------------------------
+@dataclass
+class WindowConfig(ModelConfig):
+    width: int = 0
+    inner: int = 0
+    heads: int = 0
+    kv_heads: int = 0
+    head_dim: int = 0
+    window: int = 0
+    theta: float = 10000.0
+    eps: float = 1e-6
+    MODEL_TYPES: ClassVar[tuple[str, ...]] = ("toy_window",)
+
+    @classmethod
+    def from_dict(cls, raw):
+        return cls(**{k: raw[k] for k in ("model_type", "architectures", "vocab_size", "max_position_embeddings",
+                                          "eos_token_id", "width", "inner", "heads", "kv_heads", "head_dim", "window",
+                                          "theta", "eps")})
+
+    def validate(self):
+        pass
+
+
+def window_spec(c: WindowConfig) -> ModelSpec:
+    """Two attention layers: the first sees the last `window` keys only, the second all of them."""
+    norm = PartSpec("rmsnorm", {"width": c.width, "eps": c.eps})
+    head_norm = PartSpec("rmsnorm", {"width": c.head_dim, "eps": c.eps})
+
+    def attention(window):
+        return PartSpec("gqa_attention", {"width": c.width, "num_heads": c.heads, "num_kv_heads": c.kv_heads,
+                                          "head_dim": c.head_dim, "q_norm": head_norm, "k_norm": head_norm, "window": window,
+                                          "position": PartSpec("rope", {"head_dim": c.head_dim, "theta": c.theta})})
+
+    gated = PartSpec("swiglu", {"width": c.width, "inner": c.inner})
+    layers = [LayerSpec("model.layers.0", "pre_norm", norm, attention(c.window), norm, gated),
+              LayerSpec("model.layers.1", "pre_norm", norm, attention(0), norm, gated)]
+    return ModelSpec(vocab_size=c.vocab_size, width=c.width, embedding_prefix="model.embed_tokens", layers=layers,
+                     final_norm=norm, final_norm_prefix="model.norm", head_prefix="lm_head", tie_head_to_embedding=False)
+
+
+def plain_window(folder, tokens, window_of_layer):
+    import plain_qwen3 as P
+    from safetensors.torch import load_file
+    w = load_file(os.path.join(folder, "model.safetensors"))
+    with open(os.path.join(folder, "config.json")) as f:
+        c = json.load(f)
+    ar = P.Arith(None)
+    n, nq, nkv, d = len(tokens), c["heads"], c["kv_heads"], c["head_dim"]
+    positions = torch.arange(n)
+    x = P.embedding(ar, w["model.embed_tokens.weight"], torch.tensor(tokens)).double()
+    for layer, window in enumerate(window_of_layer):
+        root = f"model.layers.{layer}"
+        h = P.rms_norm(ar, x, w[f"{root}.input_layernorm.weight"], c["eps"])
+        q = P.linear(ar, h, w[f"{root}.self_attn.q_proj.weight"]).view(n, nq, d)
+        k = P.linear(ar, h, w[f"{root}.self_attn.k_proj.weight"]).view(n, nkv, d)
+        v = P.linear(ar, h, w[f"{root}.self_attn.v_proj.weight"]).view(n, nkv, d)
+        q = P.rope(ar, P.rms_norm(ar, q, w[f"{root}.self_attn.q_norm.weight"], c["eps"]), positions, c["theta"])
+        k = P.rope(ar, P.rms_norm(ar, k, w[f"{root}.self_attn.k_norm.weight"], c["eps"]), positions, c["theta"])
+        a = P.causal_attention(ar, q, k, v, window).reshape(n, nq * d)
+        x = x + P.linear(ar, a, w[f"{root}.self_attn.o_proj.weight"])
+        h = P.rms_norm(ar, x, w[f"{root}.post_attention_layernorm.weight"], c["eps"])
+        x = x + P.feed_forward_part(ar, w, root, h)
+    x = P.rms_norm(ar, x, w["model.norm.weight"], c["eps"])
+    return P.linear(ar, x, w["lm_head.weight"], round_out=False)
+
+
+@pytest.mark.parametrize("dtype,head_dim", [("float32", 32), ("bfloat16", 64), ("bfloat16", 32)])
+def test_window_layers_have_pages_of_their_own_and_give_them_back(tmp_path, dtype, head_dim):
+    """A layer that sees a window of keys beside one that sees all: two page groups, the window group's
+    pages go back to its pool while the request runs (its block table gets holes), the pool is far
+    smaller than the request and is used again and again, and the logits equal the plain ones.  Head
+    size 64 runs the kernels fed by bulk tensor copies and the tcgen05 kernel with a window."""
+    register_architecture("toy_window", WindowConfig, window_spec, replace=True)
+    try:
+        window, page = 24, 8
+        config = WindowConfig(model_type="toy_window", architectures=["ToyWindow"], vocab_size=211, max_position_embeddings=1024,
+                              eos_token_id=1, width=64, inner=128, heads=4, kv_heads=2, head_dim=head_dim, window=window)
+        folder = str(tmp_path / "window")
+        write_random_model(folder, config, seed=8, dtype=torch.bfloat16)
+        limits = RuntimeConfig(max_seq_len=512, page_size=page, max_running=2, prefill_budget=64)
+        runner = ModelRunner.load(folder, dtype=dtype, limits=limits, num_pages=64)
+        assert [g.kind for g in runner.groups] == ["window", "full"] and runner.groups[0].window == window
+        tokens = T.requests_for(211, [300], seed=2)["r0"]
+        want = plain_window(folder, tokens, [window, 0])
+        cache = runner.cache
+        cache.open(1)
+        fed, step, least_free = 0, 0, cache.free_pages(0)
+        sizes = [40, 3, 1, 1, 17, 64, 1, 2, 33, 1, 1, 1, 50, 9]
+        while fed < len(tokens):
+            n = min(sizes[step % len(sizes)], len(tokens) - fed)
+            cache.extend(1, fed + n)
+            least_free = min(least_free, cache.free_pages(0))
+            got = runner.step([SequenceStep(1, tokens[fed:fed + n], fed, [0, n - 1])]).double().cpu()
+            T.check_rows(got, want[[fed, fed + n - 1]], dtype, f"window model, {dtype}, head {head_dim}, step {step}")
+            fed += n
+            cache.trim(1, fed)
+            cache.check_integrity()
+            step += 1
+        table = cache.table(1, 0)
+        assert (table[: (fed - window) // page] < 0).all() and (table[-(window // page):] >= 0).all()
+        assert (cache.table(1, 1) >= 0).all()
+        held = cache.total_pages(0) - cache.free_pages(0)
+        assert held <= -(-(window - 1) // page) + 1                      # only the window's pages are held at the end
+        assert cache.total_pages(0) - least_free <= -(-(window - 1 + 64) // page) + 1 < len(tokens) // page
+        cache.close(1)
+        cache.check_integrity()
+    finally:
+        ARCHITECTURES.pop("toy_window", None)
