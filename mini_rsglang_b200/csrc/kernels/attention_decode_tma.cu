@@ -89,7 +89,10 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     }
     __syncthreads();
     pdl_launch_dependents();
-    pdl_wait();                 // the newest keys and the queries come from the kernel before this one
+    // The queries and the keys and values of this step's tokens come from the kernel before this one;
+    // older keys lie in the cache since earlier steps.  The consumers wait before they read the
+    // queries, the producer only before the first block that holds a key of this step: blocks of
+    // older keys are fetched while the kernel before still runs.
 
     if (warp == CONSUMER_WARPS) {
         // ------------------------------------------------------------------ producer
@@ -110,8 +113,13 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
             return (lane < copies && key < key_end) ? pages[key >> page_shift] : -1;
         };
         int next_page = block_first < block_last ? page_of(block_first) : -1;
+        bool waited = false;
         for (int block = block_first; block < block_last; ++block) {
             const int it = block - block_first, s = it % STAGES;
+            if (!waited && (block + 1) * KV > first_pos) {
+                pdl_wait();
+                waited = true;
+            }
             const int my_page = next_page;
             if (block + 1 < block_last) next_page = page_of(block + 1);
             if (lane == 0) {
@@ -132,6 +140,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     }
 
     // ---------------------------------------------------------------------- consumers
+    pdl_wait();
     // query rows as A fragments, kept in registers for every block of keys
     uint32_t qa[D / 16][4];
     {
