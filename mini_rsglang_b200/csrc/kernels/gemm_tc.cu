@@ -34,12 +34,30 @@ template <int MPAD> struct Shape {
     static constexpr int TMEM_COLUMNS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
     static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16 +
                                          (size_t)MPAD * (MPAD <= 32 ? 128 : 64) * sizeof(float) + 4 * MPAD * sizeof(float) +
-                                         (MPAD <= 32 ? (size_t)MPAD * (128 + 1) * sizeof(float) : 0);   // cosines, sines, write slots
+                                         (MPAD <= 32 ? (size_t)MPAD * (128 + 1) * sizeof(float) : 0) +   // cosines, sines, write slots
+                                         MPAD * sizeof(float);                                           // the rows' norm factors
 };
 
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
-enum { EPI_PLAIN = 0, EPI_GATED = 1, EPI_HEADS = 2 };
+enum { EPI_PLAIN = 0, EPI_GATED = 1, EPI_HEADS = 2, EPI_RESIDUAL = 3 };
+
+// How a product is tied to the RMSNorms around it, so that no kernel of their own runs for them.
+// In: the activations are rows of the residual stream times the norm's weights, not yet divided by their
+// root mean square; the sums of squares of the rows come in parts (one per 128 columns) and the product
+// multiplies its sums by rsqrt(mean + eps) of their row, which gives the product of the normalised rows.
+// Out (EPI_RESIDUAL): the product's result, rounded to bfloat16, is added to the float32 stream; `out`
+// gets the new stream times the next norm's weights, and the parts of the rows' sums of squares are left
+// for the product after it.  The parts are added in their order, so a row's factor does not depend on
+// the batch.
+struct NormLink {
+    const float* in_square_sums;     // [in_parts][in_stride] or null
+    int in_parts, in_stride;
+    float in_inv_width, in_eps;
+    float* stream;                   // [M, N] float32 (EPI_RESIDUAL)
+    const float* next_weight;        // [N]
+    float* out_square_sums;          // [tiles of N][MPAD]
+};
 
 // What the head epilogue needs beside the product: where q goes, the cache pages of k and v, the
 // tokens' positions and write slots, the head norms' scales and the rotation's frequencies.
@@ -59,7 +77,8 @@ struct HeadEpilogue {
 template <int MPAD, typename OutT, int EPI>
 __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
     const __grid_constant__ CUtensorMap w_map, const __grid_constant__ CUtensorMap x_map, OutT* __restrict__ out,
-    float* __restrict__ partials, int* __restrict__ counters, int M, int N, int K, int splits, const HeadEpilogue heads) {
+    float* __restrict__ partials, int* __restrict__ counters, int M, int N, int K, int splits, const HeadEpilogue heads,
+    const NormLink link) {
     using S = Shape<MPAD>;
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
@@ -178,11 +197,34 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
             if (heads.k_norm) k_scale = heads.k_norm[row];
             epilogue_sync();
         }
+        float* row_factor = exchange + MPAD * (MPAD <= 32 ? 128 : 64) + 4 * MPAD + (MPAD <= 32 ? MPAD * (128 + 1) : 0);   // [MPAD]
         pdl_wait();                                        // `out`, `partials` and `counters` may still be in use before
+        if (link.in_square_sums) {
+            // the factor of each row's norm from the parts that the product before this one left
+            if (epi_thread < MPAD) {
+                float total = 0.0f;
+                if (epi_thread < M) {
+#pragma unroll 8
+                    for (int p = 0; p < link.in_parts; ++p) total += __ldcg(link.in_square_sums + (size_t)p * link.in_stride + epi_thread);
+                }
+                row_factor[epi_thread] = rsqrtf(total * link.in_inv_width + link.in_eps);
+            }
+            epilogue_sync();
+        }
         int round = 0;
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++round) {
             const int tile = unit / splits;
             const int buffer = round & 1;
+            // the stream's old values and the next norm's weight of this thread's column: asked for early,
+            // needed only by the CTA that finishes the tile
+            float stream_old[EPI == EPI_RESIDUAL ? MPAD : 1];
+            float next_weight = 0.0f;
+            if (EPI == EPI_RESIDUAL) {
+                const int column = tile * TILE_N + row;
+                if (column < N) next_weight = __ldg(link.next_weight + column);
+#pragma unroll
+                for (int m = 0; m < MPAD; ++m) stream_old[m] = (m < M && column < N) ? __ldcg(link.stream + (size_t)m * N + column) : 0.0f;
+            }
             mbar_wait(&acc_full[buffer], (round >> 1) & 1);
             __syncwarp();                    // the loads from tensor memory are collective
             tcgen05_fence_after_sync();
@@ -239,8 +281,32 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
                     }
                 }
             }
+            if (finished && link.in_square_sums) {
+#pragma unroll
+                for (int m = 0; m < MPAD; ++m) acc[m] *= row_factor[m];
+            }
             if (finished) {
-                if (EPI == EPI_GATED) {
+                if (EPI == EPI_RESIDUAL) {
+                    // stream += bfloat16(sum); out = bfloat16(stream * next norm's weight); this tile's part of
+                    // the rows' sums of squares
+                    float* warp_sums = exchange;                                                     // [4][MPAD]
+#pragma unroll
+                    for (int m = 0; m < MPAD; ++m)
+                        if (m < M) {
+                            float v = 0.0f;
+                            if (n < N) {
+                                v = stream_old[m] + __bfloat162float(__float2bfloat16_rn(acc[m]));
+                                link.stream[(size_t)m * N + n] = v;
+                                out[(size_t)m * N + n] = from_float<OutT>(v * next_weight);
+                            }
+                            const float sq = warp_sum(v * v);
+                            if (lane == 0) warp_sums[(warp - 2) * MPAD + m] = sq;
+                        }
+                    epilogue_sync();
+                    if (epi_thread < M)
+                        link.out_square_sums[(size_t)tile * MPAD + epi_thread] =
+                            (warp_sums[epi_thread] + warp_sums[MPAD + epi_thread]) + (warp_sums[2 * MPAD + epi_thread] + warp_sums[3 * MPAD + epi_thread]);
+                } else if (EPI == EPI_GATED) {
                     // the tile's rows 0..63 are gate rows, rows 64..127 the matching up rows: the upper half
                     // hands its sums over and the lower half writes silu(gate) * up, 64 columns of [M, N / 2]
                     if (row >= 64) {
@@ -331,7 +397,7 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
 
 template <int MPAD, typename OutT, int EPI>
 int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, void* out, float* partials, int* counters, int M, int N,
-           int K, int splits, int ctas, cudaStream_t stream, const HeadEpilogue& heads = HeadEpilogue{}) {
+           int K, int splits, int ctas, cudaStream_t stream, const NormLink& link, const HeadEpilogue& heads = HeadEpilogue{}) {
     using S = Shape<MPAD>;
     static bool configured = false;
     if (!configured) {
@@ -340,7 +406,7 @@ int launch(const CUtensorMap* w_map, const CUtensorMap* x_map, void* out, float*
         configured = true;
     }
     return mrs_launch(gemm_small_m_kernel<MPAD, OutT, EPI>, dim3(ctas), dim3(THREADS), S::SMEM_BYTES, stream, *w_map, *x_map,
-                      (OutT*)out, partials, counters, M, N, K, splits, heads);
+                      (OutT*)out, partials, counters, M, N, K, splits, heads, link);
 }
 
 }  // namespace
@@ -382,10 +448,17 @@ MRS_EXPORT int mrs_gemm_tc_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
 // mpad = 16, 32, 64 or 128 >= M.  `out` is bfloat16 or float32 [M, N].  `ctas`: CTAs to launch (the GPU's SMs).
 // With `gated`, w holds in every block of 128 rows 64 gate rows followed by the 64 matching up rows (N a
 // multiple of 128), and out[M, N / 2] = silu(x . gate^T) * (x . up^T), bfloat16.
+// `link` (or null): a NormLink.  With `in_square_sums` the sums are multiplied by their rows' norm factors; with
+// `stream` (up to 32 rows, bfloat16 out, not gated) the result is added to the stream and `out` gets the stream
+// times `next_weight`, with the parts of the rows' sums of squares in `out_square_sums` [ceil(N / 128)][mpad].
 MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* out, int out_is_f32, int gated,
                                    float* partials, int* counters, int M, int N, int K, int splits, int mpad, int ctas,
-                                   void* stream) {
+                                   const void* link_in, void* stream) {
     if (M <= 0 || N <= 0) return 0;
+    NormLink link{};
+    if (link_in) link = *reinterpret_cast<const NormLink*>(link_in);
+    if (link.in_square_sums && (link.in_parts <= 0 || link.in_stride < M)) return MRS_BAD_ARGUMENT;
+    if (link.stream && (gated || out_is_f32 || mpad > 32 || !link.next_weight || !link.out_square_sums)) return MRS_BAD_ARGUMENT;
     const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     if (K <= 0 || K % 8 || M > mpad || splits < 1 || splits > k_blocks || ctas < 1) return MRS_BAD_ARGUMENT;
     if (splits > 1 && (!partials || !counters)) return MRS_BAD_ARGUMENT;
@@ -397,9 +470,13 @@ MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* o
     if (gated && (out_is_f32 || N % TILE_N)) return MRS_BAD_ARGUMENT;
 #define MRS_GEMM_CASE(P)                                                                                              \
     case P:                                                                                                           \
-        if (gated) return launch<P, bf16, EPI_GATED>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);     \
-        return out_is_f32 ? launch<P, float, EPI_PLAIN>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st)   \
-                          : launch<P, bf16, EPI_PLAIN>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st);
+        if (gated) return launch<P, bf16, EPI_GATED>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st, link);     \
+        return out_is_f32 ? launch<P, float, EPI_PLAIN>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st, link)   \
+                          : launch<P, bf16, EPI_PLAIN>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st, link);
+    if (link.stream) {
+        if (mpad == 16) return launch<16, bf16, EPI_RESIDUAL>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st, link);
+        return launch<32, bf16, EPI_RESIDUAL>(wm, xm, out, partials, counters, M, N, K, splits, ctas, st, link);
+    }
     switch (mpad) {
         MRS_GEMM_CASE(16)
         MRS_GEMM_CASE(32)
@@ -417,8 +494,13 @@ MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* o
 MRS_EXPORT int mrs_gemm_tc_qkv_heads(const void* w_map, const void* x_map, void* q_out, void* k_cache, void* v_cache,
                                      const int* positions, const int* slots, const float* q_norm, const float* k_norm,
                                      const float* inv_freq, float eps, int nq, int nkv, int page_size, float* partials,
-                                     int* counters, int M, int K, int splits, int mpad, int ctas, void* stream) {
+                                     int* counters, int M, int K, int splits, int mpad, int ctas, const void* link_in,
+                                     void* stream) {
     if (M <= 0) return 0;
+    NormLink link{};
+    if (link_in) link = *reinterpret_cast<const NormLink*>(link_in);
+    link.stream = nullptr;
+    if (link.in_square_sums && (link.in_parts <= 0 || link.in_stride < M)) return MRS_BAD_ARGUMENT;
     const int N = (nq + 2 * nkv) * TILE_N;
     const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     if (K <= 0 || K % 8 || M > mpad || mpad > 32 || splits < 1 || splits > k_blocks || ctas < 1 || nq <= 0 || nkv <= 0 ||
@@ -430,8 +512,8 @@ MRS_EXPORT int mrs_gemm_tc_qkv_heads(const void* w_map, const void* x_map, void*
     HeadEpilogue heads{(bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots, q_norm, k_norm, inv_freq, eps, nq, nkv, page_size};
     const CUtensorMap* wm = reinterpret_cast<const CUtensorMap*>(w_map);
     const CUtensorMap* xm = reinterpret_cast<const CUtensorMap*>(x_map);
-    if (mpad == 16) return launch<16, bf16, EPI_HEADS>(wm, xm, nullptr, partials, counters, M, N, K, splits, ctas, (cudaStream_t)stream, heads);
-    if (mpad == 32) return launch<32, bf16, EPI_HEADS>(wm, xm, nullptr, partials, counters, M, N, K, splits, ctas, (cudaStream_t)stream, heads);
+    if (mpad == 16) return launch<16, bf16, EPI_HEADS>(wm, xm, nullptr, partials, counters, M, N, K, splits, ctas, (cudaStream_t)stream, link, heads);
+    if (mpad == 32) return launch<32, bf16, EPI_HEADS>(wm, xm, nullptr, partials, counters, M, N, K, splits, ctas, (cudaStream_t)stream, link, heads);
     return MRS_BAD_ARGUMENT;
 }
 

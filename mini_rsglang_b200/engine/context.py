@@ -34,3 +34,4 @@ class StepContext:
     # when every sequence brings one token: [B, 4] int32 attention tiles (sequence, row, 1, 0), zeros for padding
     decode_tiles: torch.Tensor | None = None
     real_sequences: int = 0            # sequences that are not padding (padding rows come last)
+    want_every_row: bool = False       # `want_rows` is 0, 1, ..., T - 1

@@ -228,7 +228,8 @@ class ModelRunner:
             host_state_slots=[self.cache.slot(s.request_id) for s in sequences] + [-1] * pads if self._needs_host_slots else [],
             max_query_len=int(layout[13 + 3 * G]), max_context_len=int(layout[12 + 3 * G]),
             fresh=(starts == 0).tolist() + [True] * pads,
-            decode_tiles=dview(layout[11], 4 * B, (B, 4)) if decode else None, real_sequences=real)
+            decode_tiles=dview(layout[11], 4 * B, (B, 4)) if decode else None, real_sequences=real,
+            want_every_row=bool(decode) and R == T)
 
     def forward(self, sequences: Sequence[SequenceStep]) -> torch.Tensor | None:
         """Runs the batch; returns the logits [wanted, vocab] (float32, on the device) in the

@@ -506,10 +506,10 @@ def gemm_tc_library() -> ctypes.CDLL:
         lib.mrs_gemm_tc_counters.argtypes = [_c_int]
         lib.mrs_gemm_tc_counters.restype = _c_int
         lib.mrs_gemm_tc_small_m.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
-                                            _c_int, _c_int, _c_vp]
+                                            _c_int, _c_int, _c_vp, _c_vp]
         lib.mrs_gemm_tc_small_m.restype = _c_int
         lib.mrs_gemm_tc_qkv_heads.argtypes = [_c_vp] * 10 + [_c_float, _c_int, _c_int, _c_int, _c_vp, _c_vp, _c_int, _c_int,
-                                              _c_int, _c_int, _c_int, _c_vp]
+                                              _c_int, _c_int, _c_int, _c_vp, _c_vp]
         lib.mrs_gemm_tc_qkv_heads.restype = _c_int
         lib.mrs_gemm_tc_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         lib.mrs_gemm_tc_take_error.restype = _c_int
@@ -538,11 +538,80 @@ def _gemm_device_state(device: torch.device) -> dict:
     return state
 
 
+class _NormLink(ctypes.Structure):
+    """The product's ties to the norms around it (`NormLink` of csrc/kernels/gemm_tc.cu)."""
+
+    _fields_ = [("in_square_sums", _c_vp), ("in_parts", _c_int), ("in_stride", _c_int), ("in_inv_width", _c_float),
+                ("in_eps", _c_float), ("stream", _c_vp), ("next_weight", _c_vp), ("out_square_sums", _c_vp)]
+
+
+def _gemm_tc_prepare(x: torch.Tensor, weight: torch.Tensor, splits: int | None, max_mpad: int = 128):
+    """Tensor maps, ranges of K and scratch for a product x . weight^T; returns (lib, state, w_map, x_map, splits, mpad)."""
+    m, k = x.shape
+    n = weight.shape[0]
+    lib = gemm_tc_library()
+    state = _gemm_device_state(x.device)
+    key = (weight.data_ptr(), n, k)
+    if key not in _weight_maps:
+        keep, address = _aligned_block(128, 64)
+        code = lib.mrs_gemm_tc_map(weight.data_ptr(), n, k, 128, address)
+        if code != 0:
+            _gemm_fail(lib, code, "tensor map of a weight")
+        _weight_maps[key] = (keep, address, lib.mrs_gemm_tc_splits(n, k, state["sms"]))
+    _, w_map, planned = _weight_maps[key]
+    splits = planned if splits is None else int(splits)      # another count only for measurements and tests
+    mpad = 16 if m <= 16 else (32 if m <= 32 else (64 if m <= 64 else 128))
+    if mpad > max_mpad:
+        raise InvalidRequest(f"this product takes at most {max_mpad} rows, got {m}")
+    x_map = state["x_map"][1]
+    code = lib.mrs_gemm_tc_map(x.data_ptr(), m, k, mpad, x_map)
+    if code != 0:
+        _gemm_fail(lib, code, "tensor map of the activations")
+    if splits > 1:
+        need = lib.mrs_gemm_tc_partial_floats(m, n, splits)
+        if state["partials"].numel() < need:       # outgrown buffers stay alive: recorded steps hold their addresses
+            _retired.append(state["partials"])
+            state["partials"] = torch.empty(2 * int(need), dtype=torch.float32, device=x.device)
+        tiles = lib.mrs_gemm_tc_counters(n)
+        if state["counters"].numel() < tiles:
+            _retired.append(state["counters"])
+            state["counters"] = torch.zeros(2 * tiles, dtype=torch.int32, device=x.device)
+    return lib, state, w_map, x_map, splits, mpad
+
+
+def _gemm_fail(lib, code, what):
+    raise BackendError(f"{what}: {lib.mrs_gemm_tc_error_string(code).decode()} (code {code})")
+
+
+def _norm_link(m: int, row_sums, stream=None, next_weight=None, out_sums=None):
+    """The link structure of a product (or None): `row_sums` = (parts of the rows' sums of squares [parts, stride],
+    the norm's width, its eps) of activations that are still to be divided by their root mean square."""
+    if row_sums is None and stream is None:
+        return None
+    link = _NormLink()
+    if row_sums is not None:
+        sums, width, eps = row_sums
+        _need(sums, torch.float32, "sums of squares")
+        if sums.dim() != 2 or sums.shape[1] < m:
+            raise InvalidRequest(f"sums of squares {tuple(sums.shape)} do not cover {m} rows")
+        link.in_square_sums, link.in_parts, link.in_stride = sums.data_ptr(), sums.shape[0], sums.shape[1]
+        link.in_inv_width, link.in_eps = 1.0 / float(width), float(eps)
+    if stream is not None:
+        link.stream, link.next_weight, link.out_square_sums = stream.data_ptr(), next_weight.data_ptr(), out_sums.data_ptr()
+    return link
+
+
 def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: bool = False,
-            splits: int | None = None) -> None:
+            splits: int | None = None, row_sums: tuple | None = None, residual: tuple | None = None) -> torch.Tensor | None:
     """out[M, N] = x[M, K] . weight[N, K]^T for M <= 128; bfloat16 in, float32 sums, `out` bfloat16 or float32.
     With `gated`, `weight` holds, in every block of 128 rows, 64 gate rows and then the 64 matching up rows, and
-    out[M, N / 2] = silu(x . gate^T) * (x . up^T) in bfloat16."""
+    out[M, N / 2] = silu(x . gate^T) * (x . up^T) in bfloat16.
+
+    The RMSNorms around a product can ride on it.  `row_sums` = (parts [P, >= M] float32, width, eps): x holds
+    rows that were multiplied by a norm's weights but not yet divided by their root mean square; the product
+    multiplies row i's sums by rsqrt(sum_p parts[p, i] / width + eps).  `residual` = (stream [M, N] float32,
+    next_weight [N] float32), up to 32 rows: stream += bfloat16(x . weight^T), out = bfloat16(stream *
+    next_weight), and the parts of the new rows' sums of squares are returned ([ceil(N / 128), 16 or 32])."""
     m, k = x.shape
     n = weight.shape[0]
     _need(x, torch.bfloat16, "gemm input")
@@ -557,50 +626,35 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: boo
         raise InvalidRequest("gemm out must be bfloat16 or float32")
     if m > GEMM_TC_MAX_ROWS:
         raise InvalidRequest(f"gemm_tc takes at most {GEMM_TC_MAX_ROWS} rows, got {m}")
-    lib = gemm_tc_library()
-    state = _gemm_device_state(x.device)
-
-    def fail(code, what):
-        raise BackendError(f"{what}: {lib.mrs_gemm_tc_error_string(code).decode()} (code {code})")
-
-    key = (weight.data_ptr(), n, k)
-    if key not in _weight_maps:
-        keep, address = _aligned_block(128, 64)
-        code = lib.mrs_gemm_tc_map(weight.data_ptr(), n, k, 128, address)
-        if code != 0:
-            fail(code, "tensor map of a weight")
-        _weight_maps[key] = (keep, address, lib.mrs_gemm_tc_splits(n, k, state["sms"]))
-    _, w_map, planned = _weight_maps[key]
-    splits = planned if splits is None else int(splits)      # another count only for measurements and tests
-    mpad = 16 if m <= 16 else (32 if m <= 32 else (64 if m <= 64 else 128))
-    x_map = state["x_map"][1]
-    code = lib.mrs_gemm_tc_map(x.data_ptr(), m, k, mpad, x_map)
-    if code != 0:
-        fail(code, "tensor map of the activations")
-    if splits > 1:
-        need = lib.mrs_gemm_tc_partial_floats(m, n, splits)
-        if state["partials"].numel() < need:       # outgrown buffers stay alive: recorded steps hold their addresses
-            _retired.append(state["partials"])
-            state["partials"] = torch.empty(2 * int(need), dtype=torch.float32, device=x.device)
-        tiles = lib.mrs_gemm_tc_counters(n)
-        if state["counters"].numel() < tiles:
-            _retired.append(state["counters"])
-            state["counters"] = torch.zeros(2 * tiles, dtype=torch.int32, device=x.device)
+    lib, state, w_map, x_map, splits, mpad = _gemm_tc_prepare(x, weight, splits, 32 if residual is not None else 128)
+    out_sums = None
+    if residual is not None:
+        stream, next_weight = residual
+        if gated or out.dtype is not torch.bfloat16:
+            raise InvalidRequest("the product that adds to the stream is plain and writes bfloat16")
+        _need(stream, torch.float32, "stream", (m, n))
+        _need(next_weight, torch.float32, "next norm's weight", (n,))
+        out_sums = torch.empty(((n + 127) // 128, mpad), dtype=torch.float32, device=x.device)
+        link = _norm_link(m, row_sums, stream, next_weight, out_sums)
+    else:
+        link = _norm_link(m, row_sums)
     global launch_count
     launch_count += 1
     code = lib.mrs_gemm_tc_small_m(w_map, x_map, out.data_ptr(), int(out.dtype is torch.float32), int(gated),
                                    state["partials"].data_ptr(), state["counters"].data_ptr(), m, n, k, splits, mpad,
-                                   state["sms"], _stream())
+                                   state["sms"], ctypes.byref(link) if link is not None else None, _stream())
     if code != 0:
-        fail(code, "gemm_tc")
+        _gemm_fail(lib, code, "gemm_tc")
+    return out_sums
 
 
 def gemm_tc_qkv_heads(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
                       v_cache: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor | None,
                       q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
-                      inv_freq: torch.Tensor | None, nq: int, nkv: int) -> None:
+                      inv_freq: torch.Tensor | None, nq: int, nkv: int, row_sums: tuple | None = None) -> None:
     """The fused q/k/v projection for up to 32 rows and heads of 128 elements, with the per-head norms, the
-    rotation and the cache write in the product's epilogue (what `qk_norm_rope_store` does after a product)."""
+    rotation and the cache write in the product's epilogue (what `qk_norm_rope_store` does after a product).
+    `row_sums`: as for `gemm_tc`."""
     m, k = x.shape
     d = 128
     _need(x, torch.bfloat16, "qkv input")
@@ -622,44 +676,17 @@ def gemm_tc_qkv_heads(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor
             _need(w, torch.float32, name, (d,))
     if inv_freq is not None:
         _need(inv_freq, torch.float32, "inv_freq", (d // 2,))
-    lib = gemm_tc_library()
-    state = _gemm_device_state(x.device)
-
-    def fail(code, what):
-        raise BackendError(f"{what}: {lib.mrs_gemm_tc_error_string(code).decode()} (code {code})")
-
-    n = weight.shape[0]
-    key = (weight.data_ptr(), n, k)
-    if key not in _weight_maps:
-        keep, address = _aligned_block(128, 64)
-        code = lib.mrs_gemm_tc_map(weight.data_ptr(), n, k, 128, address)
-        if code != 0:
-            fail(code, "tensor map of a weight")
-        _weight_maps[key] = (keep, address, lib.mrs_gemm_tc_splits(n, k, state["sms"]))
-    _, w_map, splits = _weight_maps[key]
-    mpad = 16 if m <= 16 else 32
-    x_map = state["x_map"][1]
-    code = lib.mrs_gemm_tc_map(x.data_ptr(), m, k, mpad, x_map)
-    if code != 0:
-        fail(code, "tensor map of the activations")
-    if splits > 1:
-        need = lib.mrs_gemm_tc_partial_floats(m, n, splits)
-        if state["partials"].numel() < need:
-            _retired.append(state["partials"])
-            state["partials"] = torch.empty(2 * int(need), dtype=torch.float32, device=x.device)
-        tiles = lib.mrs_gemm_tc_counters(n)
-        if state["counters"].numel() < tiles:
-            _retired.append(state["counters"])
-            state["counters"] = torch.zeros(2 * tiles, dtype=torch.int32, device=x.device)
+    lib, state, w_map, x_map, splits, mpad = _gemm_tc_prepare(x, weight, None, 32)
+    link = _norm_link(m, row_sums)
     global launch_count
     launch_count += 1
     code = lib.mrs_gemm_tc_qkv_heads(w_map, x_map, q_out.data_ptr(), _ptr(k_cache) if slots is not None else None,
                                      _ptr(v_cache) if slots is not None else None, positions.data_ptr(), _ptr(slots),
                                      _ptr(q_norm), _ptr(k_norm), _ptr(inv_freq), float(eps), nq, nkv, page_size,
                                      state["partials"].data_ptr(), state["counters"].data_ptr(), m, k, splits, mpad,
-                                     state["sms"], _stream())
+                                     state["sms"], ctypes.byref(link) if link is not None else None, _stream())
     if code != 0:
-        fail(code, "gemm_tc_qkv_heads")
+        _gemm_fail(lib, code, "gemm_tc_qkv_heads")
 
 
 # ------------------------------------------------------------------------------------------------

@@ -40,12 +40,18 @@ class Model:
         crates/engine/src/lib.rs:132-135)."""
         stream = self.embedding.forward(ctx)
         pending = None
-        for index, entry in enumerate(self.spec.run_order):
-            pending = self.blocks[entry.layer].forward(stream, pending, ctx, storage.entries[self.cache_entry[index]],
-                                                       self.writes_cache[index])
+        order = self.spec.run_order
+        for index, entry in enumerate(order):
+            block = self.blocks[entry.layer]
+            extra = {}
+            if block.links_norms:        # the norm that reads the stream after this block
+                extra["next_norm"] = self.blocks[order[index + 1].layer].norm1 if index + 1 < len(order) else self.final_norm
+            pending = block.forward(stream, pending, ctx, storage.entries[self.cache_entry[index]],
+                                    self.writes_cache[index], **extra)
         if ctx.want_rows is None:
             return None
-        hidden = self.final_norm.add_norm(stream, pending, rows=ctx.want_rows, write_back=False)
+        rows = None if ctx.want_every_row else ctx.want_rows
+        hidden = self.final_norm.add_norm(stream, pending, rows=rows, write_back=False)
         return self.head.forward(hidden)
 
 

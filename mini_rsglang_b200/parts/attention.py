@@ -12,8 +12,8 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec
-from .linear import linear
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, Prenormed, plain
+from .linear import few_rows, linear
 
 
 SM_COUNT = 148
@@ -97,6 +97,9 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
 @MIXERS.register("gqa_attention")
 class GroupedQueryAttention(Mixer):
     replayable = True      # reads the step's facts from device tensors only
+    adds_to_stream = True
+    takes_prenormed = True
+
     def __init__(self, prefix: str, width: int, num_heads: int, num_kv_heads: int, head_dim: int,
                  position: PartSpec, q_norm: PartSpec | None = None, k_norm: PartSpec | None = None,
                  window: int = 0):
@@ -140,20 +143,22 @@ class GroupedQueryAttention(Mixer):
         if (self.q_norm and self.k_norm and self.q_norm.eps != self.k_norm.eps):
             raise InvalidRequest("q and k head norms must share one eps")
 
-    def forward(self, h, ctx, cache, write_cache=True):
+    def forward(self, h, ctx, cache, write_cache=True, into=None):
         tokens = h.shape[0]
-        q = torch.empty((tokens, self.nq * self.d), dtype=h.dtype, device=h.device)
+        q = torch.empty((tokens, self.nq * self.d), dtype=self.runtime.dtype, device=self.o.device)
         eps = self.q_norm.eps if self.q_norm else (self.k_norm.eps if self.k_norm else 0.0)
         group = cache.group
-        if self.d == 128 and tokens <= kernels.GEMM_TC_BEST_ROWS and kernels.gemm_tc_supported(h, self.qkv):
+        if self.d == 128 and few_rows(h, self.qkv):
             # few rows, heads of 128: the product's epilogue norms, rotates and writes the cache itself
+            prenormed = isinstance(h, Prenormed)
             kernels.gemm_tc_qkv_heads(
-                h, self.qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
-                ctx.slots[group] if write_cache else None, self.q_norm.weight if self.q_norm else None,
-                self.k_norm.weight if self.k_norm else None, eps, self.position.tables()["inv_freq"], self.nq, self.nkv)
+                h.scaled if prenormed else h, self.qkv, q, cache.k if write_cache else None, cache.v if write_cache else None,
+                ctx.positions, ctx.slots[group] if write_cache else None, self.q_norm.weight if self.q_norm else None,
+                self.k_norm.weight if self.k_norm else None, eps, self.position.tables()["inv_freq"], self.nq, self.nkv,
+                row_sums=h.row_sums if prenormed else None)
             out = torch.empty_like(q)
             paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
-            return linear(out, self.o)
+            return linear(out, self.o, into=into)
         qkv = linear(h, self.qkv)
         kernels.qk_norm_rope_store(
             qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
@@ -162,4 +167,4 @@ class GroupedQueryAttention(Mixer):
             self.position.tables()["inv_freq"], self.nq, self.nkv, self.d, cache.k.shape[2])
         out = torch.empty_like(q)
         paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
-        return linear(out, self.o)
+        return linear(out, self.o, into=into)

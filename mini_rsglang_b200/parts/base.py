@@ -20,6 +20,15 @@ Interfaces (all tensors on the device; `ctx` is an `engine.context.StepContext`)
   Block.forward(stream, pending, ctx, cache, write_cache) -> pending
       `stream` is the float32 residual stream [T, width], updated in place; `pending` is a
       branch output not yet added (the next norm adds it), or None
+
+Norms that ride on products.  With few rows a norm's own kernel costs more than its arithmetic,
+so parts may opt in to two hand-overs, both optional and both invisible to parts that do not:
+  * a part with `adds_to_stream = True` is given `into=ResidualLink(stream, norm)`: its last
+    product may add its result to the stream itself and return a `Prenormed` (the stream times
+    the norm's weights, with the rows' sums of squares) instead of a tensor;
+  * a part with `takes_prenormed = True` may be handed that `Prenormed` as `h` and lets its
+    first product apply the rows' factors; any other part gets `h.materialise()`, a tensor.
+A block with `links_norms = True` is told the norm that follows it (`next_norm`).
 """
 from __future__ import annotations
 
@@ -71,6 +80,44 @@ class Runtime:
         return self.dtype is torch.bfloat16
 
 
+@dataclass
+class ResidualLink:
+    """Where a branch's output goes: the float32 stream and the norm that reads it next."""
+
+    stream: torch.Tensor
+    norm: "Norm"
+
+
+@dataclass
+class Prenormed:
+    """Rows that a norm has not finished: `scaled` = the stream times the norm's weights (in the
+    engine's dtype), `square_sums` [parts, >= rows] float32 the parts of each row's sum of squares.
+    A product over `scaled` whose sums are multiplied by rsqrt(sum of a row's parts / width + eps)
+    is the product over the normalised rows.  The stream already holds the branch's output."""
+
+    scaled: torch.Tensor
+    square_sums: torch.Tensor
+    norm: "Norm"
+    stream: torch.Tensor
+
+    @property
+    def shape(self):
+        return self.scaled.shape
+
+    @property
+    def row_sums(self) -> tuple:
+        return (self.square_sums, self.norm.width, self.norm.eps)
+
+    def materialise(self) -> torch.Tensor:
+        """The normalised rows as a tensor (the norm's own kernel over the stream)."""
+        return self.norm.add_norm(self.stream, None)
+
+
+def plain(h):
+    """`h` as a tensor."""
+    return h.materialise() if isinstance(h, Prenormed) else h
+
+
 class Part:
     """Base of every part.  `prefix` is the root of its tensor names in the checkpoint."""
 
@@ -90,6 +137,10 @@ class Part:
 
 
 class Norm(Part):
+    # True when the norm is y = x * rsqrt(mean(x^2) + eps) * weight with `weight` [width] float32, `width`
+    # and `eps` as attributes: a product may then take over its arithmetic (see `Prenormed`).
+    rides_on_products = False
+
     def forward(self, x: torch.Tensor) -> torch.Tensor:
         raise NotImplementedError
 
@@ -108,6 +159,8 @@ class Mixer(Part):
     # device tensors (never from its host lists): steps of single decoded tokens may then be
     # recorded once and replayed.  Padding rows of such a step have state slot -1 and write slot -1.
     replayable = False
+    adds_to_stream = False        # `forward` takes `into=ResidualLink` and may return a `Prenormed`
+    takes_prenormed = False       # `forward` takes a `Prenormed` as `h`
 
     def cache_need(self) -> KVNeed | None:
         return None
@@ -120,11 +173,16 @@ class Mixer(Part):
 
 
 class FeedForward(Part):
+    adds_to_stream = False
+    takes_prenormed = False
+
     def forward(self, h: torch.Tensor, ctx) -> torch.Tensor:
         raise NotImplementedError
 
 
 class Block(Part):
+    links_norms = False           # `forward` takes `next_norm`, the norm that reads the stream after this block
+
     def __init__(self, prefix: str, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
         super().__init__(prefix)
         self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward

@@ -2,16 +2,29 @@
 + feed_forward(norm2(.)) (reference: crates/models/src/qwen3.rs:176-225).
 
 The residual stream is float32.  A branch's output is not added by a kernel of its own: it
-is handed on as `pending`, and the next norm adds it while it reads the stream anyway."""
+is handed on as `pending`, and the next norm adds it while it reads the stream anyway; or,
+with few rows, the branch's last product adds it and the norm rides on the products around it
+(`Prenormed` in parts/base.py)."""
 from __future__ import annotations
 
-from .base import BLOCKS, Block
+from .base import BLOCKS, Block, Prenormed, ResidualLink, plain
+
+
+def _branch(part, h, stream, norm, *args):
+    """Runs a mixer or feed-forward on `h`, telling it where its output goes if it can use that."""
+    if isinstance(h, Prenormed) and not getattr(part, "takes_prenormed", False):
+        h = plain(h)
+    if getattr(part, "adds_to_stream", False) and norm is not None and getattr(norm, "rides_on_products", False):
+        return part.forward(h, *args, into=ResidualLink(stream, norm))
+    return part.forward(h, *args)
 
 
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
-    def forward(self, stream, pending, ctx, cache, write_cache=True):
+    links_norms = True
+
+    def forward(self, stream, pending, ctx, cache, write_cache=True, next_norm=None):
         h = self.norm1.add_norm(stream, pending)
-        a = self.mixer.forward(h, ctx, cache, write_cache)
+        a = _branch(self.mixer, h, stream, self.norm2, ctx, cache, write_cache)
         h = self.norm2.add_norm(stream, a)
-        return self.feed_forward.forward(h, ctx)
+        return _branch(self.feed_forward, h, stream, next_norm, ctx)

@@ -43,5 +43,6 @@ class OutputHead(Part):
         super().bind(tensors, runtime)
         self.weight = tensors[self.tied_to if self.tied_to else self.name("weight")]
 
-    def forward(self, hidden: torch.Tensor) -> torch.Tensor:
+    def forward(self, hidden) -> torch.Tensor:
+        """`hidden`: the normalised rows, or a `Prenormed` that the product finishes."""
         return linear(hidden, self.weight, out_dtype=torch.float32)

@@ -8,12 +8,15 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .base import FEED_FORWARDS, FeedForward
-from .linear import linear
+from .base import FEED_FORWARDS, FeedForward, Prenormed
+from .linear import few_rows, linear
 
 
 @FEED_FORWARDS.register("swiglu")
 class SwiGLU(FeedForward):
+    adds_to_stream = True
+    takes_prenormed = True
+
     def __init__(self, prefix: str, width: int, inner: int, activation: str = "silu"):
         super().__init__(prefix)
         if activation != "silu":
@@ -43,10 +46,13 @@ class SwiGLU(FeedForward):
             self.gate_up = torch.cat([gate, up], dim=0).contiguous()
         self.down = tensors[self.name("down_proj.weight")].contiguous()
 
-    def forward(self, h, ctx):
-        act = torch.empty((h.shape[0], self.inner), dtype=h.dtype, device=h.device)
-        if self.block and h.shape[0] <= kernels.GEMM_TC_BEST_ROWS and kernels.gemm_tc_supported(h, self.gate_up):
-            kernels.gemm_tc(h, self.gate_up, act, gated=True)
+    def forward(self, h, ctx, into=None):
+        act = torch.empty((h.shape[0], self.inner), dtype=self.runtime.dtype, device=self.down.device)
+        if self.block and few_rows(h, self.gate_up):
+            if isinstance(h, Prenormed):
+                kernels.gemm_tc(h.scaled, self.gate_up, act, gated=True, row_sums=h.row_sums)
+            else:
+                kernels.gemm_tc(h, self.gate_up, act, gated=True)
         else:
             kernels.silu_mul(linear(h, self.gate_up), act, self.block)
-        return linear(act, self.down)
+        return linear(act, self.down, into=into)

@@ -11,6 +11,7 @@ from __future__ import annotations
 import torch
 
 from .. import kernels
+from .base import Prenormed, ResidualLink
 
 _configured = False
 
@@ -23,18 +24,40 @@ def _configure_library() -> None:
         _configured = True
 
 
-def linear(x: torch.Tensor, weight: torch.Tensor, out_dtype: torch.dtype | None = None) -> torch.Tensor:
-    """x [M, K], weight [N, K] -> [M, N] in `out_dtype` (default: x's dtype)."""
+def few_rows(x, weight: torch.Tensor) -> bool:
+    """Whether the engine's own tensor-core product takes this one."""
+    scaled = x.scaled if isinstance(x, Prenormed) else x
+    return scaled.shape[0] <= kernels.GEMM_TC_BEST_ROWS and kernels.gemm_tc_supported(scaled, weight)
+
+
+def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, into: ResidualLink | None = None):
+    """x [M, K], weight [N, K] -> [M, N] in `out_dtype` (default: x's dtype).
+
+    `x` may be a `Prenormed`: the product for few rows finishes the norm in its epilogue; otherwise the
+    norm's own kernel runs first.  With `into` and few rows the product adds its result to the stream and
+    returns a `Prenormed` for the norm that follows; otherwise it returns the tensor and the norm adds it."""
+    if isinstance(x, Prenormed):
+        if few_rows(x, weight):
+            out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype or x.scaled.dtype, device=weight.device)
+            return _tensor_core(x.scaled, weight, out, x.row_sums, into)
+        x = x.materialise()
     out_dtype = out_dtype or x.dtype
     if x.dtype is torch.float32:
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=torch.float32, device=x.device)
         kernels.gemm_f32(x, weight, out)
         return out
-    if x.shape[0] <= kernels.GEMM_TC_BEST_ROWS and kernels.gemm_tc_supported(x, weight):
+    if few_rows(x, weight):
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
-        kernels.gemm_tc(x, weight, out)
-        return out
+        return _tensor_core(x, weight, out, None, into)
     _configure_library()
     if out_dtype is torch.float32:
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
     return torch.mm(x, weight.t())
+
+
+def _tensor_core(x, weight, out, row_sums, into):
+    if into is None or out.dtype is not torch.bfloat16 or x.shape[0] > 32:
+        kernels.gemm_tc(x, weight, out, row_sums=row_sums)
+        return out
+    sums = kernels.gemm_tc(x, weight, out, row_sums=row_sums, residual=(into.stream, into.norm.weight))
+    return Prenormed(out, sums, into.norm, into.stream)

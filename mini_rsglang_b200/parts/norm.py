@@ -6,11 +6,13 @@ import torch
 
 from .. import kernels
 from ..weights.spec import WeightSpec
-from .base import NORMS, Norm
+from .base import NORMS, Norm, Prenormed
 
 
 @NORMS.register("rmsnorm")
 class RMSNorm(Norm):
+    rides_on_products = True
+
     def __init__(self, prefix: str, width: int, eps: float):
         super().__init__(prefix)
         self.width, self.eps = int(width), float(eps)
@@ -29,6 +31,10 @@ class RMSNorm(Norm):
         return out
 
     def add_norm(self, residual, delta, rows=None, write_back=True):
+        if isinstance(delta, Prenormed):          # the stream holds the sum already
+            if delta.norm is self and rows is None:
+                return delta                      # and the product after this norm finishes it
+            delta = None
         n = residual.shape[0] if rows is None else rows.shape[0]
         out = torch.empty((n, self.width), dtype=self.runtime.dtype, device=residual.device)
         kernels.add_rmsnorm(residual, delta, self.weight, self.eps, out, rows, write_back)

@@ -454,6 +454,98 @@ def test_gemm_tc_qkv_heads(m, nq, nkv, k, page):
     assert kc.count_nonzero().item() == 0
 
 
+@pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 4096, 4096), (5, 136, 192), (8, 1000, 12288), (19, 520, 1024), (32, 256, 320)])
+def test_gemm_tc_adds_to_the_stream_and_prepares_the_next_norm(m, n, k):
+    """The product whose epilogue adds to the residual stream: stream += bfloat16(x . w^T), out = stream * the next
+    norm's weights, and parts of the rows' sums of squares that add up to the rows' sums of squares."""
+    g = torch.Generator().manual_seed(m * n + k)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    stream = 3 * torch.randn(m, n, generator=g)
+    next_w = 1 + 0.2 * torch.randn(n, generator=g)
+    on_device = stream.clone().to(DEV)
+    out = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+    sums = kernels.gemm_tc(x.to(DEV), w.to(DEV), out, residual=(on_device, next_w.to(DEV)))
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    product = (x.double() @ w.double().T)
+    want_stream = stream.double() + product
+    error = (on_device.cpu().double() - want_stream).abs()              # one bfloat16 rounding of the product, one float32 sum
+    assert (error <= 2.0 ** -8 * product.abs() + 1e-5).all(), f"stream: {error.max().item():.3e}"
+    close(out, want_stream * next_w.double(), torch.bfloat16, "stream times the next norm's weights")
+    assert sums.shape[0] == (n + 127) // 128
+    got = sums[:, :m].sum(0).cpu().double()
+    exact = (on_device.cpu().double() ** 2).sum(1)                      # of the stream that the kernel wrote
+    assert ((got - exact).abs() / exact).max().item() < 1e-5, "sums of squares"
+
+
+@pytest.mark.parametrize("m,n,k,out_dtype", [(1, 256, 136, torch.float32), (8, 151936 // 8, 4096, torch.float32),
+                                            (7, 520, 1024, torch.bfloat16), (40, 384, 512, torch.bfloat16)])
+def test_gemm_tc_finishes_a_norm(m, n, k, out_dtype):
+    """A product over rows that were multiplied by a norm's weights but not divided by their root mean square,
+    with the rows' sums of squares in parts: equal to the product over the normalised rows."""
+    eps = 1e-5
+    g = torch.Generator().manual_seed(m + n + k)
+    stream = 5 * torch.randn(m, k, generator=g) * (1 + torch.arange(m).float()[:, None])      # rows of very different size
+    norm_w = 1 + 0.2 * torch.randn(k, generator=g)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    scaled = (stream * norm_w).to(torch.bfloat16)
+    parts = 3
+    stride = 48
+    sums = torch.zeros(parts, stride)
+    cut = [0, k // 3, k // 2, k]
+    for p in range(parts):
+        sums[p, :m] = (stream[:, cut[p]:cut[p + 1]] ** 2).sum(1)
+    out = torch.full((m, n), float("nan"), dtype=out_dtype, device=DEV)
+    kernels.gemm_tc(scaled.to(DEV), w.to(DEV), out, row_sums=(sums.to(DEV), k, eps))
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    factor = torch.rsqrt((stream.double() ** 2).mean(1, keepdim=True) + eps)
+    normed = stream.double() * factor * norm_w.double()
+    close(out, normed @ w.double().T, torch.bfloat16, "product over the normalised rows")     # x was rounded to bfloat16
+
+
+@pytest.mark.parametrize("m", [1, 8])
+def test_gemm_tc_gated_and_heads_finish_a_norm(m):
+    """The same through the gated epilogue and through the q/k/v epilogue (whose head norms are not invariant
+    under the factor, because of their eps)."""
+    eps, k, inner, nq, nkv, d, page, pages, theta = 1e-6, 1024, 384, 4, 2, 128, 16, 4, 1e4
+    g = torch.Generator().manual_seed(m)
+    stream = 0.01 * torch.randn(m, k, generator=g)                         # small rows: the factor is large
+    norm_w = 1 + 0.2 * torch.randn(k, generator=g)
+    scaled = (stream * norm_w).to(torch.bfloat16)
+    sums = torch.zeros(2, 16)
+    sums[0, :m] = (stream[:, :600] ** 2).sum(1)
+    sums[1, :m] = (stream[:, 600:] ** 2).sum(1)
+    factor = torch.rsqrt((stream.double() ** 2).mean(1, keepdim=True) + eps)
+    normed = scaled.double() * factor                                       # the rounding that the kernel sees
+    gate = (torch.randn(inner, k, generator=g) / k ** 0.5 * 2).to(torch.bfloat16)
+    up = (torch.randn(inner, k, generator=g) / k ** 0.5 * 2).to(torch.bfloat16)
+    mixed = torch.stack([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k).contiguous()
+    act = torch.full((m, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_tc(scaled.to(DEV), mixed.to(DEV), act, gated=True, row_sums=(sums.to(DEV), k, eps))
+    gd, ud = normed @ gate.double().T, normed @ up.double().T
+    close(act, gd / (1 + torch.exp(-gd)) * ud, torch.bfloat16, "gated")
+    w = (torch.randn((nq + 2 * nkv) * d, k, generator=g) / k ** 0.5 * 0.02).to(torch.bfloat16)     # head norms feel their eps
+    q_w, k_w = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    positions = torch.randint(0, 3000, (m,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * page, generator=g)[:m].to(torch.int32)
+    inv_freq = RotaryPosition.inverse_frequencies(d, theta)
+    q_out = torch.full((m, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(pages, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    kernels.gemm_tc_qkv_heads(scaled.to(DEV), w.to(DEV), q_out, kc, vc, positions.to(DEV), slots.to(DEV), q_w.to(DEV), k_w.to(DEV),
+                              1e-3, inv_freq.to(DEV), nq, nkv, row_sums=(sums.to(DEV), k, eps))
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    qkv = (normed @ w.double().T).float()
+    q, kk, v = plain_qk(qkv.to(DEV), positions.to(DEV), q_w.to(DEV), k_w.to(DEV), 1e-3, theta, nq, nkv, d)
+    close(q_out.view(m, nq, d), q, torch.bfloat16, "q")
+    slot = slots.long()
+    close(kc.cpu()[slot // page, :, slot % page], kk, torch.bfloat16, "k in the cache")
+    close(vc.cpu()[slot // page, :, slot % page], v, torch.bfloat16, "v in the cache")
+
+
 def test_gemm_tc_rows_do_not_depend_on_the_batch():
     """The same row alone, among 8 and among 100 others: equal bit for bit, twice in a row (the
     counters of the ranges of K are left ready for the next launch)."""

@@ -177,6 +177,71 @@ def test_block_arrangement(dtype):
     close(stream.double().cpu() + pending.double().cpu(), want, dtype, "block output = stream + pending")
 
 
+def test_norms_ride_on_the_products_of_few_rows(monkeypatch):
+    """With few rows in bfloat16 the last product of a branch adds to the stream and hands the norm after it
+    to the next product (`Prenormed`): the same block output as the plain implementation and as the path
+    with the norm's own kernel; a part that does not take a `Prenormed` gets the finished rows."""
+    from mini_rsglang_b200 import kernels
+    from mini_rsglang_b200.parts.base import Prenormed, plain
+    dtype = torch.bfloat16
+    width, nq, nkv, d, inner, page, tokens, eps, theta = 136, 2, 1, 128, 192, 4, 6, 1e-5, 1e4
+    norm = PartSpec("rmsnorm", {"width": width, "eps": eps})
+    head_norm = PartSpec("rmsnorm", {"width": d, "eps": eps})
+
+    def build():
+        block = BLOCKS.get("pre_norm")(
+            prefix="a", norm1=NORMS.build(norm, "a.input_layernorm"),
+            mixer=MIXERS.build(PartSpec("gqa_attention", {
+                "width": width, "num_heads": nq, "num_kv_heads": nkv, "head_dim": d, "q_norm": head_norm,
+                "k_norm": head_norm, "position": PartSpec("rope", {"head_dim": d, "theta": theta})}), "a.self_attn"),
+            norm2=NORMS.build(norm, "a.post_attention_layernorm"),
+            feed_forward=FEED_FORWARDS.build(PartSpec("swiglu", {"width": width, "inner": inner}), "a.mlp"))
+        block.bind({k: v.to(DEV, torch.float32 if v.dim() == 1 else dtype) for k, v in weights.items()}, runtime(dtype, page))
+        return block
+
+    weights = attention_weights(width, nq, nkv, d, 31)
+    weights.update({"a.mlp.gate_proj.weight": draw((inner, width), 40, 0.1),
+                    "a.mlp.up_proj.weight": draw((inner, width), 41, 0.1),
+                    "a.mlp.down_proj.weight": draw((width, inner), 42, 0.1),
+                    "a.input_layernorm.weight": draw((width,), 43, 0.1, 1.0),
+                    "a.post_attention_layernorm.weight": draw((width,), 44, 0.1, 1.0)})
+    after = NORMS.build(norm, "after")
+    after.bind({"after.weight": draw((width,), 45, 0.1, 1.0).to(DEV)}, runtime(dtype, page))
+    x = draw((tokens, width), 50, 1.0)
+    cfg = P.PlainConfig(width, inner, 1, nq, nkv, d, 0, eps, theta, False)
+    as_held = {k.replace("a.", "model.layers.0.", 1): (v.to(dtype) if v.dim() == 2 else v) for k, v in weights.items()}
+    want = P.block(P.Arith(None), cfg, as_held, 0, x.double(), torch.arange(tokens))
+
+    def run(block):
+        ctx, table = whole_sequence_context(tokens, page)
+        pages = int(table.max()) + 1
+        cache = CacheEntry(group=0, k=torch.zeros((pages, nkv, page, d), dtype=dtype, device=DEV),
+                           v=torch.zeros((pages, nkv, page, d), dtype=dtype, device=DEV))
+        stream = x.clone().to(DEV)
+        norms = []
+        real = kernels.add_rmsnorm
+        monkeypatch.setattr(kernels, "add_rmsnorm", lambda *a, **k: (norms.append(1), real(*a, **k))[1])
+        pending = block.forward(stream, None, ctx, cache, True, next_norm=after)
+        monkeypatch.setattr(kernels, "add_rmsnorm", real)
+        return stream, pending, len(norms), cache
+
+    stream, pending, norm_launches, cache = run(build())
+    assert isinstance(pending, Prenormed) and pending.norm is after and norm_launches == 1      # only the block's first norm
+    close(stream.double().cpu(), want, dtype, "the stream holds the block's output")
+    sums = pending.square_sums[:, :tokens].sum(0).double().cpu()
+    assert ((sums - (stream.double().cpu() ** 2).sum(1)).abs() / sums).max().item() < 1e-5
+    close(pending.scaled.double().cpu(), stream.double().cpu() * after.weight.double().cpu(), dtype, "stream times the next weights")
+    finished = plain(pending)                                                                 # what a part that takes no Prenormed gets
+    close(finished.double().cpu(), P.rms_norm(P.Arith(None), want, after.weight.cpu(), eps), dtype, "finished rows")
+    assert after.add_norm(stream, pending) is pending
+    # the same block through the norms' own kernels
+    monkeypatch.setattr(kernels, "GEMM_TC_BEST_ROWS", 0)
+    stream2, pending2, norm_launches2, cache2 = run(build())
+    assert isinstance(pending2, torch.Tensor) and norm_launches2 == 2
+    close(stream2.double().cpu() + pending2.double().cpu(), want, dtype, "with the norms' own kernels")
+    close(cache.k.double().cpu(), cache2.k.double().cpu(), dtype, "keys in the cache")
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 def test_embedding_and_head_parts(dtype):
     vocab, width = 333, 40
