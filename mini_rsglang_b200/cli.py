@@ -3,7 +3,9 @@
 meanings where the engine has the thing they set, and its `generate` subcommand with the
 same sampling options.  Prompts are token ids (`--token-ids 1,2,3`); there is no tokenizer,
 so `--prompt`, `--chat` and `--enable-thinking` are not offered, and neither are `serve`
-(no server) and the tensor-parallel options (one GPU).  Added: `--dtype`, `--num-pages`,
+(no server) and the tensor-parallel options (one GPU).  `bench` is the reference's closed-loop
+load test (main.rs:94-113, 266-300) with seeded random prompts; `--cache-mode` takes only
+`cold`, because nothing is shared between requests here.  Added: `--dtype`, `--num-pages`,
 `--token-ids-file` (several requests at once), and `random-model`, which writes a model
 folder from a config.json and a seed."""
 from __future__ import annotations
@@ -53,6 +55,15 @@ def build_parser() -> argparse.ArgumentParser:
     g.add_argument("--top-p", type=float, default=1.0)
     g.add_argument("--seed", type=int, default=0)
     g.add_argument("--ignore-eos", action="store_true")
+
+    b = sub.add_parser("bench", help="closed-loop load test: fixed prompt and output lengths, fixed concurrency")
+    b.add_argument("--input-tokens", type=int, default=128)
+    b.add_argument("--output-tokens", type=int, default=32)
+    b.add_argument("--requests", type=int, default=16)
+    b.add_argument("--concurrency", type=int, default=8)
+    b.add_argument("--cache-mode", choices=["cold", "hot", "both"], default="cold")
+    b.add_argument("--output", help="also write the report to this file")
+    b.add_argument("--seed", type=int, default=0, help="seed of the random prompts")
 
     r = sub.add_parser("random-model", help="write a model folder with seeded random weights")
     r.add_argument("--config", required=True, help="a config.json to take the sizes from")
@@ -123,6 +134,28 @@ def command_generate(args) -> int:
     return 0
 
 
+def command_bench(args) -> int:
+    from .engine import load_test
+    from .engine.handle import EngineHandle
+
+    if args.cache_mode != "cold":
+        raise InvalidRequest("only --cache-mode cold: this engine shares nothing between requests (no prefix cache)")
+    if args.kv_mib <= 0:
+        raise InvalidRequest("kv_mib must be positive")
+    engine = EngineHandle.load(args.model, args.device, args.kv_mib * 1024 * 1024, runtime_config(args),
+                               dtype=args.dtype, num_pages=args.num_pages)
+    try:
+        result = load_test.run(engine, args.input_tokens, args.output_tokens, args.requests, args.concurrency, args.seed)
+    finally:
+        engine.shutdown()
+    report = json.dumps({"backend": "b200-tcgen05-tma", "devices": [args.device], "runs": [result]}, indent=2)
+    if args.output:
+        with open(args.output, "w") as f:
+            f.write(report)
+    print(report)
+    return 0
+
+
 def command_random_model(args) -> int:
     import torch
 
@@ -142,6 +175,8 @@ def main(argv=None) -> int:
     try:
         if args.command == "generate":
             return command_generate(args)
+        if args.command == "bench":
+            return command_bench(args)
         return command_random_model(args)
     except EngineError as e:
         print(f"error: {type(e).__name__}: {e}", file=sys.stderr)

@@ -1,0 +1,86 @@
+"""A closed-loop load test of the engine: a fixed number of requests, a fixed number of them
+in flight, fixed prompt and output lengths (reference: `mini-rsglang bench`,
+crates/server/src/bench.rs:16-170).  The reference tokenises a repeated sentence; without a
+tokenizer the prompts here are seeded uniform random token ids of the same length, every
+request's different so that nothing could be shared between them."""
+from __future__ import annotations
+
+import math
+import random
+import time
+
+from ..errors import BackendError, InvalidRequest
+from ..sampling.params import SamplingParams
+from .handle import EngineHandle, Error, Finished, GenerateRequest, Token, TokenIds
+
+
+def percentile(values: list[float], p: float) -> float:
+    """The reference's percentile: the element at round((n - 1) * p) of the sorted values, halves away from zero."""
+    if not values:
+        return 0.0
+    ordered = sorted(values)
+    return ordered[int(math.floor((len(ordered) - 1) * p + 0.5))]
+
+
+def _wave(engine: EngineHandle, prompts: list[list[int]], output_tokens: int, concurrency: int):
+    """Runs the prompts with at most `concurrency` in flight; returns per request the time to the first
+    token, the gaps between tokens and the whole latency (seconds)."""
+    sampling = SamplingParams(max_tokens=output_tokens, ignore_eos=True)
+    pending = list(prompts)
+    live: dict[int, dict] = {}
+    first, gaps, latency = [], [], []
+    while pending or live:
+        while pending and len(live) < concurrency:
+            stream = engine.generate(GenerateRequest(TokenIds(pending.pop(0)), sampling))
+            live[stream.request_id] = {"stream": stream, "start": time.perf_counter(), "last": None, "tokens": 0}
+        if not engine.run_step() and not any(state["stream"].events for state in live.values()):
+            raise BackendError("scheduler is idle but requests are unfinished")
+        now = time.perf_counter()
+        for request_id in list(live):
+            state = live[request_id]
+            while state["stream"].events:
+                event = state["stream"].events.popleft()
+                if isinstance(event, Token):
+                    if state["last"] is None:
+                        first.append(now - state["start"])
+                    else:
+                        gaps.append(now - state["last"])
+                    state["last"] = now
+                    state["tokens"] += 1
+                elif isinstance(event, Error):
+                    raise BackendError(event.message)
+                elif isinstance(event, Finished):
+                    if event.reason != "length" or state["tokens"] != output_tokens:
+                        raise BackendError("benchmark did not generate fixed output length")
+                    latency.append(now - state["start"])
+                    del live[request_id]
+                    break
+    return first, gaps, latency
+
+
+def run(engine: EngineHandle, input_tokens: int, output_tokens: int, requests: int, concurrency: int,
+        seed: int = 0, warmup_waves: int = 2) -> dict:
+    if min(input_tokens, output_tokens, requests, concurrency) <= 0 or concurrency > engine.config.max_running:
+        raise InvalidRequest("positive benchmark sizes required; concurrency must be <= max_running")
+    rng = random.Random(seed)
+    vocab = engine.info["vocab_size"]
+
+    def prompts(n):
+        return [[rng.randrange(vocab) for _ in range(input_tokens)] for _ in range(n)]
+
+    for _ in range(warmup_waves):          # the measured batch and token shapes, before the clock starts
+        _wave(engine, prompts(concurrency), output_tokens, concurrency)
+    started = time.perf_counter()
+    first, gaps, latency = _wave(engine, prompts(requests), output_tokens, concurrency)
+    elapsed = time.perf_counter() - started
+
+    def spread(values):
+        return {"p50": percentile(values, 0.5) * 1000.0, "p95": percentile(values, 0.95) * 1000.0}
+
+    after = engine.metrics()
+    return {"warmup_waves": warmup_waves, "cache_mode": "disabled", "model": engine.info["model_id"],
+            "input_tokens": input_tokens, "output_tokens": output_tokens, "requests": requests, "concurrency": concurrency,
+            "elapsed_s": elapsed, "output_tokens_per_s": requests * output_tokens / elapsed,
+            "requests_per_s": requests / elapsed, "ttft_ms": spread(first), "itl_ms": spread(gaps),
+            "latency_ms": spread(latency), "raw_ttft_s": first, "raw_itl_s": gaps, "raw_latency_s": latency,
+            "cached_tokens": 0, "peak_memory_bytes": after["peak_memory_bytes"], "metrics": after}

@@ -283,3 +283,26 @@ def test_command_line_generates_what_the_entry_point_generates(model_folders, tm
     assert tokens == P.generate_greedy(cfg, weights, [3, 1, 4, 1, 5], 5)
     bad = subprocess.run(cmd[:-6] + ["--token-ids", "3,x", "--max-tokens", "5"], capture_output=True, text=True, timeout=300)
     assert bad.returncode != 0 and "comma-separated integers" in bad.stderr
+
+
+def test_command_line_load_test_reports_fixed_lengths(model_folders, tmp_path):
+    """`bench` as the reference has it: a closed loop of requests of fixed lengths; every request ends at
+    its length, the counts add up, and the report goes to standard output and to --output."""
+    folder = model_folders["B"]
+    out = tmp_path / "report.json"
+    cmd = [sys.executable, os.path.join(ROOT, "bin", "mini-rsglang"), "--model", folder, "--page-size", "16",
+           "--max-seq-len", "128", "--num-pages", "40", "--max-running", "4", "--prefill-budget", "32", "bench",
+           "--input-tokens", "37", "--output-tokens", "6", "--requests", "7", "--concurrency", "3", "--output", str(out)]
+    proc = subprocess.run(cmd, capture_output=True, text=True, timeout=300)
+    assert proc.returncode == 0, proc.stderr
+    report = json.loads(out.read_text())
+    assert json.loads(proc.stdout[proc.stdout.index("{"):]) == report
+    run = report["runs"][0]
+    assert (run["requests"], run["concurrency"], run["input_tokens"], run["output_tokens"]) == (7, 3, 37, 6)
+    assert len(run["raw_ttft_s"]) == 7 and len(run["raw_latency_s"]) == 7 and len(run["raw_itl_s"]) == 7 * 5
+    assert run["output_tokens_per_s"] > 0 and run["ttft_ms"]["p50"] <= run["latency_ms"]["p50"]
+    assert run["metrics"]["running"] == 0 and run["metrics"]["waiting"] == 0
+    refused = subprocess.run(cmd[:-2] + ["--concurrency", "9"], capture_output=True, text=True, timeout=300)
+    assert refused.returncode != 0 and "concurrency must be <= max_running" in refused.stderr
+    hot = subprocess.run(cmd[:-2] + ["--cache-mode", "hot"], capture_output=True, text=True, timeout=300)
+    assert hot.returncode != 0 and "no prefix cache" in hot.stderr

@@ -193,3 +193,14 @@ def test_many_requests_through_a_small_pool_finish_and_free_everything():
     assert all(f.reason == "length" and (f.prompt_tokens, f.completion_tokens) == want[f.request_id] for f in finished)
     assert all(sum(n for _, _, n, _ in step) <= 7 for step in shapes)
     assert cache.free_pages() == 12 and cache.free_slots() == 3
+
+
+def test_load_test_percentile_is_the_reference_s():
+    """round((n - 1) * p) of the sorted values (crates/server/src/bench.rs:7-15)."""
+    from mini_rsglang_b200.engine.load_test import percentile
+
+    assert percentile([], 0.5) == 0.0
+    assert percentile([3.0, 1.0, 2.0], 0.5) == 2.0
+    assert percentile([4.0, 1.0, 3.0, 2.0], 0.5) == 3.0          # round(1.5) = 2
+    assert percentile(list(range(100)), 0.95) == 94
+    assert percentile([0.0, 1.0, 2.0, 3.0, 4.0, 5.0], 0.5) == 3.0    # 2.5 rounds away from zero
