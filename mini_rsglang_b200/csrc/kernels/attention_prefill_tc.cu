@@ -73,7 +73,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     int table_width, const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv, int page_size,
     int page_shift, float scale_log2, int window) {
     extern __shared__ unsigned char smem_raw[];
-    const Tile work = tiles[blockIdx.x];
+    // the grid runs over the key/value heads first: with the entries sorted by their work, all heavy CTAs start first
+    const Tile work = tiles[blockIdx.y];
     if (work.tokens <= 0) return;
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     unsigned char* q_smem = smem;                                   // [tile][half][128 rows][64]
@@ -82,7 +83,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     Barriers* bars = reinterpret_cast<Barriers*>(v_smem + STAGES * KV_TILE_BYTES);
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(bars + 1);
 
-    const int kv_head = blockIdx.y, group = nq / nkv;
+    const int kv_head = blockIdx.x, group = nq / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int* pages = block_table + (size_t)work.seq * table_width;
     const int tokens_per_tile = BM / group;
@@ -386,10 +387,13 @@ MRS_EXPORT int mrs_attention_prefill_tc(const void* q_map, const void* k_map, co
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
-    MRS_LAUNCH(attention_prefill_kernel, dim3(num_tiles, nkv), THREADS, SMEM_BYTES, stream,
-               *reinterpret_cast<const CUtensorMap*>(q_map), *reinterpret_cast<const CUtensorMap*>(k_map),
-               *reinterpret_cast<const CUtensorMap*>(v_map), positions, block_table, table_width, (const Tile*)tiles,
-               (bf16*)out, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window);
+    for (int done = 0; done < num_tiles; done += 65535) {         // a grid's second dimension ends at 65,535
+        const int now = num_tiles - done < 65535 ? num_tiles - done : 65535;
+        MRS_LAUNCH(attention_prefill_kernel, dim3(nkv, now), THREADS, SMEM_BYTES, stream,
+                   *reinterpret_cast<const CUtensorMap*>(q_map), *reinterpret_cast<const CUtensorMap*>(k_map),
+                   *reinterpret_cast<const CUtensorMap*>(v_map), positions, block_table, table_width, (const Tile*)tiles + done,
+                   (bf16*)out, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window);
+    }
     MRS_RETURN_LAUNCH_STATUS();
 }
 
