@@ -3,7 +3,10 @@
 It rests on the formulas of the reference's source (mirthfulLee/mini-rsglang), not on a run
 of it: the reference's model code is Rust over a CUDA backend and cannot be imported or
 compiled on a CPU-only machine without a Rust toolchain.  Every function cites the lines it
-restates.  Whole sequences, no cache, no batching, one function per part.  Nothing here is
+restates.  What can be compiled of the reference here is compared once: its kernels that compute
+one element a thread (`add`, `rope`, `swiglu`, `embedding`; crates/kernels/src/ops.cu) run on the
+CPU through a small shim (`tests/golden/make_golden.py`), and the bfloat16 mode below gives the
+same bits (`tests/test_plain.py`).  Whole sequences, no cache, no batching, one function per part.  Nothing here is
 imported by the engine and nothing of the engine is imported here (weights are read with
 the `safetensors` package, the engine has a reader of its own).
 

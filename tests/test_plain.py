@@ -72,3 +72,54 @@ def test_generation_is_deterministic(model_folders):
     cfg, w = folder_of(model_folders, "A")
     a = P.generate_greedy(cfg, w, [1, 2, 3], 4)
     assert a == P.generate_greedy(cfg, w, [1, 2, 3], 4) and len(a) == 4
+
+
+# ---------------------------------------------------------------------------------------------
+# against the reference's own kernels, compiled for the CPU (tests/golden/make_golden.py)
+# ---------------------------------------------------------------------------------------------
+def _golden():
+    import os
+
+    import numpy as np
+
+    data = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "elementwise.npz"))
+
+    def bf16(name):
+        return (torch.from_numpy(data[name].astype(np.int32)) << 16).view(torch.float32)      # bfloat16 bits -> float32
+
+    return data, bf16
+
+
+def _bits(x: torch.Tensor) -> torch.Tensor:
+    """bfloat16 bit patterns of float32 values that are exact in bfloat16."""
+    assert torch.equal(x.to(torch.bfloat16).to(torch.float32), x)
+    return (x.contiguous().view(torch.int32) >> 16) & 0xFFFF
+
+
+def test_bf16_mode_rounds_where_the_reference_s_kernels_round():
+    """`add`, `swiglu`, `rope` and `embedding` of crates/kernels/src/ops.cu, run thread by thread on the CPU,
+    against the plain implementation in bfloat16 mode: the same bits."""
+    import numpy as np
+
+    data, bf16 = _golden()
+    ar = P.Arith("bf16")
+    x, y = bf16("x"), bf16("y")
+    want = lambda name: torch.from_numpy(data[name].astype(np.int32))      # noqa: E731
+    assert torch.equal(_bits(ar.r(x + y)), want("add"))                    # the residual sum of `block` (ops.cu:62-65)
+    assert torch.equal(_bits(P.swiglu(ar, x, y)), want("swiglu"))
+    q = bf16("q")
+    positions = torch.from_numpy(data["pos"].astype(np.int64))
+    assert torch.equal(P.rope_inverse_frequencies(q.shape[-1], float(data["theta"])).to(torch.float32),
+                       torch.from_numpy(data["freq"]))
+    rotated = P.rope(ar, q, positions, float(data["theta"]))
+    mismatches = (_bits(rotated) != want("rope")).sum().item()
+    assert mismatches == 0, f"{mismatches} of {rotated.numel()} rotated elements differ"
+    table, ids = bf16("table"), torch.from_numpy(data["ids"].astype(np.int64))
+    assert torch.equal(_bits(P.embedding(ar, table, ids)), want("embedding"))
+    # the layouts that the engine replaces (column split, cache scatter) move bits only
+    n, width = x.shape
+    assert torch.equal(_bits(x[:, width // 4: width // 4 + width // 2]), want("split"))
+    slots = torch.from_numpy(data["slots"].astype(np.int64))
+    cache = torch.zeros(2 * n, width)
+    cache[slots] = x
+    assert torch.equal(_bits(cache), want("kcache"))
