@@ -72,6 +72,8 @@ def _ptr(t: torch.Tensor | None) -> int | None:
 
 
 def _need(t: torch.Tensor, dtype, what: str, shape: tuple | None = None) -> None:
+    if t.is_cuda and (dtype is None or t.dtype == dtype) and t.is_contiguous() and (shape is None or t.shape == shape):
+        return                 # the usual case, in one line: this runs a hundred times a step
     if not t.is_cuda:
         raise BackendError(f"{what}: tensor is not on a CUDA device")
     if dtype is not None and t.dtype != dtype:
