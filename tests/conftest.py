@@ -45,6 +45,24 @@ TINY_D = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_siz
               max_position_embeddings=2048, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
               hidden_act="silu", eos_token_id=3)
 TINY = {"A": (TINY_A, 4), "B": (TINY_B, 16), "C": (TINY_C, 8), "D": (TINY_D, 16)}   # configuration, page size used with it
+# the layer sizes of a real checkpoint (Qwen3-8B: width 4096, 32 / 8 heads of 128, feed-forward 12288), two layers
+# and a vocabulary that is no power of two: the sizes at which the serving kernels run in production
+REAL_LAYERS = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_size=4096, intermediate_size=12288,
+                   num_hidden_layers=2, num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=20011,
+                   max_position_embeddings=4096, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
+                   hidden_act="silu", eos_token_id=7)
+SHAPES = {**TINY, "R": (REAL_LAYERS, 16)}
+
+
+@pytest.fixture(scope="session")
+def real_size_folder(tmp_path_factory):
+    """A model folder with the layer sizes of a real checkpoint (about 1 GB; made only for the tests that ask for it)."""
+    from mini_rsglang_b200.models import config_from_dict
+    from mini_rsglang_b200.weights import write_random_model
+
+    folder = str(tmp_path_factory.mktemp("real_layers"))
+    write_random_model(folder, config_from_dict(REAL_LAYERS), seed=21, dtype=torch.bfloat16)
+    return folder
 
 
 @pytest.fixture(scope="session")

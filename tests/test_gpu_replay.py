@@ -5,7 +5,7 @@ import functools
 
 import pytest
 import torch
-from conftest import TINY
+from conftest import SHAPES
 
 import plain_qwen3 as P
 import trace_tools as T
@@ -13,7 +13,7 @@ import trace_tools as T
 pytestmark = pytest.mark.gpu
 
 LENGTHS = {"A": [70, 45, 33, 100, 130, 64, 37, 90], "B": [1, 7, 17, 40, 129, 65, 96, 50], "C": [48, 80, 35, 66, 120],
-           "D": [70, 45, 200, 33, 300, 131, 64]}
+           "D": [70, 45, 200, 33, 300, 131, 64], "R": [70, 45, 131, 64, 37]}
 MODES = ("whole", "decode_tail", "portions", "mixed")
 
 
@@ -33,7 +33,7 @@ def replay(folder: str, name: str, dtype: str, tmp_path_factory):
     if key in _results:
         return _results[key]
     reqs, want = plain_logits(folder, name)
-    vocab = TINY[name][0]["vocab_size"]
+    vocab = SHAPES[name][0]["vocab_size"]
     mixed, peak = T.trace_mixed(reqs, seed=7)
     traces = {"whole": T.trace_whole(reqs), "decode_tail": T.trace_decode_tail(reqs),
               "portions": T.trace_portions(reqs, seed=5), "mixed": mixed}
@@ -58,9 +58,11 @@ def replay(folder: str, name: str, dtype: str, tmp_path_factory):
 
 @pytest.mark.parametrize("mode", MODES)
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
-@pytest.mark.parametrize("name", ["A", "B", "C", "D"])
-def test_replay_matches_plain(model_folders, tmp_path_factory, name, dtype, mode):
-    rows = replay(model_folders[name], name, dtype, tmp_path_factory)[mode]
+@pytest.mark.parametrize("name", ["A", "B", "C", "D", "R"])
+def test_replay_matches_plain(request, model_folders, tmp_path_factory, name, dtype, mode):
+    """"R": two layers of a real checkpoint's sizes, so that every cutting also runs at the sizes of production."""
+    folder = request.getfixturevalue("real_size_folder") if name == "R" else model_folders[name]
+    rows = replay(folder, name, dtype, tmp_path_factory)[mode]
     assert rows
     for step, got, want in rows:
         T.check_rows(got, want, dtype, f"{name} {dtype} {mode} step {step}")
