@@ -13,7 +13,7 @@ tokens.  One JSON line is printed:
   prefill    one prompt of 2,048 tokens in one step, with its fraction of the bf16 peak;
   roofline   bytes a decode step must read (every weight once and the live requests' cache)
              divided by its time, against the measured copy bandwidth;
-  points     decode at batch 1 and batch 64.
+  points     decode at batch 1 and batch 64, each with the same fraction of the copy bandwidth.
 Peaks come from MEASURED_PEAKS.json when the file exists.  The engine runs on one GPU; for
 --gpus N > 1 a line says so and the exit code is 2.  The reference arm cannot run here (the
 reference is a Rust workspace without a Python package, and supports no sm_100 device), so
@@ -228,6 +228,8 @@ def main() -> int:
     for b in point_batches:
         run = decode_run(b, max(args.steps // 2, 8), args.warmup)
         points[f"decode_b{b}"] = round(run["tokens_per_s"], 1)
+        point_bytes = numbers["weight_bytes"] + b * run["mean_context"] * numbers["kv_bytes_per_token"]
+        points[f"decode_b{b}_hbm_frac"] = round(point_bytes / (run["ms_per_step"] * 1e-3) / 1e9 / peak["hbm_gbs"], 4)
 
     # ---------------------------------------------------------------- the same through the Python entry point
     e2e = None
