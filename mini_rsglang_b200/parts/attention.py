@@ -19,7 +19,7 @@ from .linear import few_rows, linear
 SM_COUNT = 148
 
 
-def plan_attention_tiles(ctx, group: int, wide_rows: int):
+def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1):
     """Cuts the step's sequences into tiles for the tensor-core kernels: sequences with few
     query rows (decoded tokens, short portions) go to the kernels for few rows in tiles of
     16 // group tokens, the others in tiles of wide_rows // group tokens, those with the most
@@ -27,7 +27,7 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int):
     tile lists on the device, or None for an empty list.  The plan is kept in the context for
     the other layers of the step."""
     plans = ctx.__dict__.setdefault("_attention_plans", {})
-    key = (group, wide_rows)
+    key = (group, wide_rows, kv_heads)
     if key in plans:
         return plans[key]
     narrow_tokens = kernels.MMA_ROWS_NARROW // group
@@ -35,6 +35,15 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int):
     if ctx.decode_tiles is not None and narrow_tokens >= 1:     # single tokens: the step's own tile list
         plans[key] = (ctx.decode_tiles, None, ctx.max_context_len)
         return plans[key]
+    if wide_rows == kernels.PREFILL_TC_ROWS and wide_tokens >= 2:
+        # The tcgen05 kernel takes two tiles of rows a CTA.  A short portion (a slice of a long prompt under the
+        # token budget) makes fewer CTAs than the GPU has SMs; entries of one tile then double the CTAs.  Measured:
+        # 512 tokens behind 3,584 cached ones, 8 key/value heads: 68 us against 78 us (one tile a CTA works without
+        # a partner on the tensor cores, so it pays only while SMs would stay idle).
+        portions = sum(-(-(ctx.host_q_start[i + 1] - ctx.host_q_start[i]) // wide_tokens) for i in range(ctx.num_sequences)
+                       if ctx.host_q_start[i + 1] - ctx.host_q_start[i] > narrow_tokens)
+        if 2 * portions * kv_heads <= SM_COUNT:
+            wide_tokens //= 2
     narrow, wide = [], []
     longest_narrow = 0
     for i in range(ctx.num_sequences):
@@ -48,7 +57,7 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int):
     wide.sort(key=lambda t: -t[3])          # a tile late in a long request walks the most keys: start it first
     wide = [(a, b, c, 0) for a, b, c, _ in wide]
     device = ctx.positions.device
-    both = torch.tensor(narrow + wide, dtype=torch.int32).view(-1, 4).to(device, non_blocking=True)
+    both = torch.tensor(narrow + wide, dtype=torch.int32).view(-1, 4).pin_memory().to(device, non_blocking=True)
     plans[key] = (both[:len(narrow)] if narrow else None, both[len(narrow):] if wide else None,
                   min(longest_narrow, ctx.max_context_len))
     return plans[key]
@@ -80,7 +89,7 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
         return
     page_size = cache.k.shape[2]
     tensor_core_rows = kernels.attention_prefill_tc_supported(d, group, page_size)
-    narrow, wide, longest = plan_attention_tiles(ctx, group, kernels.PREFILL_TC_ROWS if tensor_core_rows else kernels.MMA_ROWS_WIDE)
+    narrow, wide, longest = plan_attention_tiles(ctx, group, kernels.PREFILL_TC_ROWS if tensor_core_rows else kernels.MMA_ROWS_WIDE, nkv)
     if narrow is not None:
         splits = choose_splits(narrow.shape[0], nkv, longest)
         if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
