@@ -49,9 +49,14 @@ constexpr int O_COLUMN = TILES * S_COLUMNS;      // the score buffers, then the 
 static_assert(O_COLUMN + TILES * D <= TMEM_COLUMNS, "tensor memory");
 constexpr float RESCALE_THRESHOLD = 8.0f;        // in powers of two
 
+// A work entry: `tokens` consecutive tokens of request `seq` from row `first_token` of the step on.  `share` = 0:
+// the CTA walks all keys.  Otherwise share = index | count << 8: the entry is one of `count` entries (which
+// follow one another in the list) that walk one share of the key blocks each and leave their unnormalised
+// accumulators, maxima and sums in `partials`; attention_prefill_merge_kernel puts them together.
 struct Tile {
-    int seq, first_token, tokens, pad;
+    int seq, first_token, tokens, share;
 };
+constexpr int PARTIAL_STRIDE = D + 4;            // floats of a row in `partials`: the accumulator, the maximum, the sum, 2 unused
 
 // 2^x in one instruction of the special-function unit (2 ulp; -inf gives 0).
 __device__ __forceinline__ float fast_exp2(float x) {
@@ -71,7 +76,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     const __grid_constant__ CUtensorMap q_map, const __grid_constant__ CUtensorMap k_map,
     const __grid_constant__ CUtensorMap v_map, const int* __restrict__ positions, const int* __restrict__ block_table,
     int table_width, const Tile* __restrict__ tiles, bf16* __restrict__ out, int nq, int nkv, int page_size,
-    int page_shift, float scale_log2, int window) {
+    int page_shift, float scale_log2, int window, float* __restrict__ partials) {
     extern __shared__ unsigned char smem_raw[];
     // the grid runs over the key/value heads first: with the entries sorted by their work, all heavy CTAs start first
     const Tile work = tiles[blockIdx.y];
@@ -91,7 +96,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     int tile_first[TILES], tile_tokens[TILES], tile_blocks[TILES], tile_first_pos[TILES];
     const int first_pos = positions[work.first_token];
     const int key_begin = window > 0 ? max(0, first_pos - window + 1) : 0;
-    const int block_first = key_begin / BN;
+    int block_first = key_begin / BN;
     int blocks = 0;
 #pragma unroll
     for (int i = 0; i < TILES; ++i) {
@@ -103,6 +108,16 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
         blocks = max(blocks, tile_blocks[i]);
     }
     const int key_end = first_pos + work.tokens;
+    const int shares = (work.share >> 8) & 0xFF;
+    if (shares > 1) {
+        // this entry's share of the key blocks; a tile may have none of its blocks in it
+        const int share = work.share & 0xFF;
+        const int b0 = (int)((long long)blocks * share / shares), b1 = (int)((long long)blocks * (share + 1) / shares);
+#pragma unroll
+        for (int i = 0; i < TILES; ++i) tile_blocks[i] = max(0, min(tile_blocks[i], b1) - b0);
+        block_first += b0;
+        blocks = b1 - b0;
+    }
 
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 1);
@@ -179,7 +194,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA
-        if (lane == 0) {
+        if (lane == 0 && blocks > 0) {                       // (a share of the keys can be empty)
             constexpr uint32_t idesc_s = umma_idesc_bf16_f32(BM, BN);
             constexpr uint32_t idesc_o = umma_idesc_bf16_f32(BM, D, true);
             const uint32_t q_addr = smem_u32(q_smem);
@@ -308,20 +323,31 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
             __syncwarp();
             if (lane == 0) mbar_arrive(&bars->p_ready[i]);
         }
-        if (my_blocks > 0) {
-            mbar_wait(&bars->pv_done[i], 0);
-            __syncwarp();
-            tcgen05_fence_after_sync();
-            const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
-            // loads from tensor memory are collective: every lane of the warp takes part, rows past the
-            // tile's end drop what they read
-            bf16* dst = out + ((size_t)(tile_first[i] + (row < rows ? row / group : 0)) * nq + kv_head * group +
-                               (row < rows ? row % group : 0)) * D;
+        if (my_blocks > 0 || shares > 1) {
             float o[D];                        // one trip to tensor memory for the whole row
+            if (my_blocks > 0) {
+                mbar_wait(&bars->pv_done[i], 0);
+                __syncwarp();
+                tcgen05_fence_after_sync();
+                // loads from tensor memory are collective: every lane of the warp takes part, rows past the
+                // tile's end drop what they read
 #pragma unroll
-            for (int c = 0; c < D; c += 32) tmem_load_32_async(lane_base + O_COLUMN + i * D + c, o + c);
-            tmem_load_wait();
-            if (row < rows) {
+                for (int c = 0; c < D; c += 32) tmem_load_32_async(lane_base + O_COLUMN + i * D + c, o + c);
+                tmem_load_wait();
+            } else {                           // a share of the keys in which this tile has none
+#pragma unroll
+                for (int c = 0; c < D; ++c) o[c] = 0.0f;
+            }
+            if (shares > 1) {
+                // one share of the keys: the row's accumulator as it stands, with the maximum it is scaled by and its sum
+                float4* dst = reinterpret_cast<float4*>(
+                    partials + ((((size_t)blockIdx.y * gridDim.x + blockIdx.x) * TILES + i) * BM + row) * PARTIAL_STRIDE);
+#pragma unroll
+                for (int c = 0; c < D; c += 4) dst[c / 4] = make_float4(o[c], o[c + 1], o[c + 2], o[c + 3]);
+                dst[D / 4] = make_float4(reference, sum, 0.0f, 0.0f);
+            } else if (row < rows) {
+                const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+                bf16* dst = out + ((size_t)(tile_first[i] + row / group) * nq + kv_head * group + row % group) * D;
 #pragma unroll
                 for (int c = 0; c < D; c += 8) {
                     uint32_t w[4];
@@ -341,6 +367,47 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
         tcgen05_fence_after_sync();
         tmem_dealloc(tmem_base, TMEM_COLUMNS);
     }
+}
+
+// Puts the shares of an entry together: out = sum_s O_s 2^(m_s - M) / sum_s l_s 2^(m_s - M), M the largest maximum.
+// A warp per query row (grid: key/value heads x entries x 32 groups of 8 rows); only the CTAs of an entry's first share work.
+__global__ void __launch_bounds__(256) attention_prefill_merge_kernel(const Tile* __restrict__ tiles, const float* __restrict__ partials,
+                                                                    bf16* __restrict__ out, int nq, int nkv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const Tile work = tiles[blockIdx.y];
+    const int shares = (work.share >> 8) & 0xFF;
+    if (shares <= 1 || (work.share & 0xFF) != 0) return;
+    const int group = nq / nkv, kv_head = blockIdx.x, tokens_per_tile = BM / group;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    constexpr int PER_LANE = D / 32;
+    const int r = blockIdx.z * 8 + warp, i = r / BM, row = r % BM;
+    const int tile_tokens = max(0, min(tokens_per_tile, work.tokens - i * tokens_per_tile));
+    if (row >= tile_tokens * group) return;
+    auto partial_of = [&](int s) {
+        return partials + ((((size_t)(blockIdx.y + s) * gridDim.x + kv_head) * TILES + i) * BM + row) * PARTIAL_STRIDE;
+    };
+    // the maxima of all shares, a lane a share
+    float best = -CUDART_INF_F;
+    for (int s = lane; s < shares; s += 32) best = fmaxf(best, partial_of(s)[D]);
+    best = warp_max(best);
+    float acc[PER_LANE], total = 0.0f;
+#pragma unroll
+    for (int e = 0; e < PER_LANE; ++e) acc[e] = 0.0f;
+#pragma unroll 4
+    for (int s = 0; s < shares; ++s) {                 // in the order of the shares
+        const float* p = partial_of(s);
+        const float m = p[D];
+        const float w = m == -CUDART_INF_F ? 0.0f : fast_exp2(m - best);      // a share without keys for this row counts nothing
+        total += p[D + 1] * w;
+#pragma unroll
+        for (int e = 0; e < PER_LANE; ++e) acc[e] += p[lane * PER_LANE + e] * w;
+    }
+    const float inv = total > 0.0f ? 1.0f / total : 0.0f;
+    bf16* dst = out + ((size_t)(work.first_token + i * tokens_per_tile + row / group) * nq + kv_head * group + row % group) * D +
+                lane * PER_LANE;
+#pragma unroll
+    for (int e = 0; e < PER_LANE; ++e) dst[e] = __float2bfloat16_rn(acc[e] * inv);
 }
 
 int page_shift_of(int page_size) {
@@ -374,11 +441,21 @@ MRS_EXPORT int mrs_attention_prefill_tc_q_map(const void* q, long long tokens, i
     return mrs_make_tensor_map_bf16(reinterpret_cast<CUtensorMap*>(map_out), q, 3, dims, strides, box, CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-// Work entries of up to 256 / group consecutive tokens of one request each ((sequence, first token, tokens, 0)).
+// Floats of `partials` for a list of `num_tiles` entries of which some are shares.
+MRS_EXPORT long long mrs_attention_prefill_tc_partial_floats(int num_tiles, int nkv) {
+    return (long long)num_tiles * nkv * TILES * BM * PARTIAL_STRIDE;
+}
+
+// Work entries of up to 256 / group consecutive tokens of one request each: (sequence, first token, tokens, share).
+// share = 0: the entry walks all its keys.  share = index | count << 8 (count 2..255, the `count` entries of one
+// portion one after the other): every entry walks one share of the key blocks; `partials`
+// (mrs_attention_prefill_tc_partial_floats) carries their sums and `with_shares` must be set, so that the merge runs.
 MRS_EXPORT int mrs_attention_prefill_tc(const void* q_map, const void* k_map, const void* v_map, const int* positions,
                                         const int* block_table, int table_width, const int* tiles, int num_tiles,
-                                        void* out, int nq, int nkv, int page_size, float scale, int window, void* stream) {
+                                        void* out, int nq, int nkv, int page_size, float scale, int window,
+                                        float* partials, int with_shares, void* stream) {
     if (num_tiles <= 0) return 0;
+    if (with_shares && (!partials || num_tiles > 65535)) return MRS_BAD_ARGUMENT;
     const int shift = page_shift_of(page_size);
     if (shift < 0 || page_size < 8 || nkv <= 0 || nq % nkv || BM % (nq / nkv)) return MRS_BAD_ARGUMENT;
     static bool configured = false;
@@ -392,8 +469,11 @@ MRS_EXPORT int mrs_attention_prefill_tc(const void* q_map, const void* k_map, co
         MRS_LAUNCH(attention_prefill_kernel, dim3(nkv, now), THREADS, SMEM_BYTES, stream,
                    *reinterpret_cast<const CUtensorMap*>(q_map), *reinterpret_cast<const CUtensorMap*>(k_map),
                    *reinterpret_cast<const CUtensorMap*>(v_map), positions, block_table, table_width, (const Tile*)tiles + done,
-                   (bf16*)out, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window);
+                   (bf16*)out, nq, nkv, page_size, shift, scale * 1.4426950408889634f, window, with_shares ? partials : nullptr);
     }
+    if (with_shares)
+        MRS_LAUNCH(attention_prefill_merge_kernel, dim3(nkv, num_tiles, TILES * BM / 8), 256, 0, stream, (const Tile*)tiles, (const float*)partials,
+                   (bf16*)out, nq, nkv);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

@@ -441,7 +441,9 @@ def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
         lib.mrs_attention_prefill_tc_kv_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
         lib.mrs_attention_prefill_tc_q_map.argtypes = [_c_vp, ctypes.c_longlong, _c_int, _c_int, _c_vp]
         lib.mrs_attention_prefill_tc.argtypes = [_c_vp] * 5 + [_c_int, _c_vp, _c_int, _c_vp, _c_int, _c_int, _c_int, _c_float,
-                                                 _c_int, _c_vp]
+                                                 _c_int, _c_vp, _c_int, _c_vp]
+        lib.mrs_attention_prefill_tc_partial_floats.argtypes = [_c_int, _c_int]
+        lib.mrs_attention_prefill_tc_partial_floats.restype = ctypes.c_longlong
         for name in ("mrs_attention_prefill_tc_kv_map", "mrs_attention_prefill_tc_q_map", "mrs_attention_prefill_tc"):
             getattr(lib, name).restype = _c_int
         lib.mrs_attention_prefill_tc_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
@@ -454,8 +456,10 @@ def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
 
 
 def attention_prefill_tc(q, k_cache, v_cache, positions, block_table, tiles, out, nq: int, nkv: int, d: int,
-                         window: int = 0, scale: float | None = None) -> None:
-    """Work entries of up to 256 // (nq // nkv) tokens of one request each, on the tcgen05 tensor cores."""
+                         window: int = 0, scale: float | None = None, shares: bool = False) -> None:
+    """Work entries of up to 256 // (nq // nkv) tokens of one request each, on the tcgen05 tensor cores.  The
+    fourth number of an entry is 0, or index | count << 8 when `count` entries (one after the other in the list)
+    walk one share of the keys each; `shares` says that the list has such entries, whose sums a second kernel merges."""
     global launch_count
     _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
     lib = attention_prefill_tc_library(d)
@@ -479,11 +483,12 @@ def attention_prefill_tc(q, k_cache, v_cache, positions, block_table, tiles, out
     code = lib.mrs_attention_prefill_tc_q_map(q.data_ptr(), q.shape[0], nq, nq // nkv, q_map)
     if code != 0:
         fail(code, "tensor map of the queries")
-    launch_count += 1
+    launch_count += 2 if shares else 1
+    partials = attention_scratch(q.device, lib.mrs_attention_prefill_tc_partial_floats(tiles.shape[0], nkv)) if shares else None
     code = lib.mrs_attention_prefill_tc(q_map, maps[0], maps[1], positions.data_ptr(), block_table.data_ptr(),
                                         block_table.shape[1], tiles.data_ptr(), tiles.shape[0], out.data_ptr(), nq, nkv,
                                         k_cache.shape[2], float(scale if scale is not None else 1.0 / math.sqrt(d)),
-                                        int(window), _stream())
+                                        int(window), _ptr(partials), int(shares), _stream())
     if code != 0:
         fail(code, "attention_prefill_tc")
 

@@ -17,49 +17,65 @@ from .linear import few_rows, linear
 
 
 SM_COUNT = 148
+PREFILL_KEY_BLOCK = 128     # keys of a block of the tcgen05 kernel for prompt portions
 
 
-def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1):
+def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, window: int = 0):
     """Cuts the step's sequences into tiles for the tensor-core kernels: sequences with few
     query rows (decoded tokens, short portions) go to the kernels for few rows in tiles of
     16 // group tokens, the others in tiles of wide_rows // group tokens, those with the most
-    keys first.  Returns (narrow tiles, wide tiles, longest context of a narrow tile) with the
-    tile lists on the device, or None for an empty list.  The plan is kept in the context for
-    the other layers of the step."""
+    keys first.  Returns (narrow tiles, wide tiles, longest context of a narrow tile, whether
+    wide tiles share their keys) with the tile lists on the device, or None for an empty list.
+    The plan is kept in the context for the other layers of the step.
+
+    The tcgen05 kernel for wide tiles takes two tiles of rows a CTA and one CTA an SM.  A short
+    portion (a slice of a long prompt under the token budget) makes fewer CTAs than the GPU has
+    SMs.  Then, measured with 512 tokens behind 3,584 cached ones and 8 key/value heads (78 us as
+    64 CTAs): entries with at least 8 blocks of 128 keys are cut into shares of their keys, whose
+    sums a second kernel merges; shorter ones into entries of one tile (68 us as 128 CTAs; a CTA
+    with one tile has no partner on the tensor cores, so this pays only while SMs would idle)."""
     plans = ctx.__dict__.setdefault("_attention_plans", {})
-    key = (group, wide_rows, kv_heads)
+    key = (group, wide_rows, kv_heads, window)
     if key in plans:
         return plans[key]
     narrow_tokens = kernels.MMA_ROWS_NARROW // group
     wide_tokens = wide_rows // group
     if ctx.decode_tiles is not None and narrow_tokens >= 1:     # single tokens: the step's own tile list
-        plans[key] = (ctx.decode_tiles, None, ctx.max_context_len)
+        plans[key] = (ctx.decode_tiles, None, ctx.max_context_len, False)
         return plans[key]
-    if wide_rows == kernels.PREFILL_TC_ROWS and wide_tokens >= 2:
-        # The tcgen05 kernel takes two tiles of rows a CTA.  A short portion (a slice of a long prompt under the
-        # token budget) makes fewer CTAs than the GPU has SMs; entries of one tile then double the CTAs.  Measured:
-        # 512 tokens behind 3,584 cached ones, 8 key/value heads: 68 us against 78 us (one tile a CTA works without
-        # a partner on the tensor cores, so it pays only while SMs would stay idle).
-        portions = sum(-(-(ctx.host_q_start[i + 1] - ctx.host_q_start[i]) // wide_tokens) for i in range(ctx.num_sequences)
-                       if ctx.host_q_start[i + 1] - ctx.host_q_start[i] > narrow_tokens)
-        if 2 * portions * kv_heads <= SM_COUNT:
-            wide_tokens //= 2
+    lengths = [ctx.host_q_start[i + 1] - ctx.host_q_start[i] for i in range(ctx.num_sequences)]
+    tensor_core = wide_rows == kernels.PREFILL_TC_ROWS
+    entries = sum(-(-n // wide_tokens) for n in lengths if n > narrow_tokens)
+    spare = SM_COUNT // max(entries * kv_heads, 1) if tensor_core else 1      # CTAs an entry may become
     narrow, wide = [], []
     longest_narrow = 0
-    for i in range(ctx.num_sequences):
-        first, n = ctx.host_q_start[i], ctx.host_q_start[i + 1] - ctx.host_q_start[i]
+    shared = False
+    for i, n in enumerate(lengths):
+        first = ctx.host_q_start[i]
         if narrow_tokens >= 1 and n <= narrow_tokens:
             narrow.append((i, first, n, 0))
             longest_narrow = max(longest_narrow, ctx.host_start_pos[i] + n)
-        else:
-            for start in range(0, n, wide_tokens):
-                wide.append((i, first + start, min(wide_tokens, n - start), ctx.host_start_pos[i] + start))
-    wide.sort(key=lambda t: -t[3])          # a tile late in a long request walks the most keys: start it first
-    wide = [(a, b, c, 0) for a, b, c, _ in wide]
+            continue
+        for start in range(0, n, wide_tokens):
+            tokens = min(wide_tokens, n - start)
+            begin = ctx.host_start_pos[i] + start                        # position of the entry's first token
+            first_key = max(0, begin - window + 1) if window else 0
+            blocks = -(-(begin + tokens) // PREFILL_KEY_BLOCK) - first_key // PREFILL_KEY_BLOCK
+            shares = min(spare, blocks // 4, 255) if spare >= 2 else 1
+            if shares >= 2:
+                shared = True
+                wide += [(i, first + start, tokens, s | shares << 8, begin) for s in range(shares)]
+            elif spare >= 2 and tokens > wide_tokens // 2 >= 1:
+                half = wide_tokens // 2
+                wide += [(i, first + start, half, 0, begin), (i, first + start + half, tokens - half, 0, begin + half)]
+            else:
+                wide.append((i, first + start, tokens, 0, begin))
+    wide.sort(key=lambda t: -t[4])          # a tile late in a long request walks the most keys: start it first (stable:
+    wide = [t[:4] for t in wide]            # the shares of an entry stay together and in their order)
     device = ctx.positions.device
     both = torch.tensor(narrow + wide, dtype=torch.int32).view(-1, 4).pin_memory().to(device, non_blocking=True)
     plans[key] = (both[:len(narrow)] if narrow else None, both[len(narrow):] if wide else None,
-                  min(longest_narrow, ctx.max_context_len))
+                  min(longest_narrow, ctx.max_context_len), shared)
     return plans[key]
 
 
@@ -89,7 +105,8 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
         return
     page_size = cache.k.shape[2]
     tensor_core_rows = kernels.attention_prefill_tc_supported(d, group, page_size)
-    narrow, wide, longest = plan_attention_tiles(ctx, group, kernels.PREFILL_TC_ROWS if tensor_core_rows else kernels.MMA_ROWS_WIDE, nkv)
+    narrow, wide, longest, shared = plan_attention_tiles(ctx, group, kernels.PREFILL_TC_ROWS if tensor_core_rows else kernels.MMA_ROWS_WIDE,
+                                                         nkv, window)
     if narrow is not None:
         splits = choose_splits(narrow.shape[0], nkv, longest)
         if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
@@ -98,7 +115,7 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
             kernels.attention_mma_keys(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
     if wide is not None:
         if tensor_core_rows:
-            kernels.attention_prefill_tc(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
+            kernels.attention_prefill_tc(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window, shares=shared)
         else:
             kernels.attention_mma_rows(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
 

@@ -306,3 +306,24 @@ def test_command_line_load_test_reports_fixed_lengths(model_folders, tmp_path):
     assert refused.returncode != 0 and "concurrency must be <= max_running" in refused.stderr
     hot = subprocess.run(cmd[:-2] + ["--cache-mode", "hot"], capture_output=True, text=True, timeout=300)
     assert hot.returncode != 0 and "no prefix cache" in hot.stderr
+
+
+def test_portions_of_a_long_prompt_share_their_keys(model_folders, monkeypatch):
+    """A prompt of 1,500 tokens in portions of 256 and 100 with heads of 128: from the second thousand on a portion makes
+    few CTAs with many key blocks each, and the plan cuts its entries into shares of the keys, which a second kernel
+    merges.  The logits of every portion's tokens equal the plain implementation's; the early portions, with few
+    blocks, take entries of one tile."""
+    from mini_rsglang_b200 import kernels
+
+    folder = model_folders["D"]
+    runner = runner_for(folder, "D", "bfloat16", pages=120, max_seq_len=2048)
+    tokens = T.requests_for(TINY["D"][0]["vocab_size"], [1500], seed=31)["r0"]
+    want = plain(folder, tokens)
+    calls = []
+    real = kernels.attention_prefill_tc
+    monkeypatch.setattr(kernels, "attention_prefill_tc", lambda *a, **k: (calls.append((a[5].cpu().tolist(), k.get("shares"))), real(*a, **k))[1])
+    got = feed(runner, 1, tokens, [256, 256, 256, 256, 256, 100, 120])
+    T.check_rows(got, want, "bfloat16", "portions whose entries share their keys")
+    shared = [tiles for tiles, shares in calls if shares]
+    assert shared and all((t[3] >> 8) >= 2 for tiles in shared for t in tiles if t[3])
+    assert any(not shares and all(t[2] <= 64 for t in tiles) for tiles, shares in calls)      # one tile: 128 rows / 2 heads of a group

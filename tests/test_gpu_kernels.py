@@ -210,20 +210,23 @@ class PagedCase:
 
     def run_mma(self, mode, splits=1):
         group = self.nq // self.nkv
-        per_tile = {"rows": 64, "tc": 256}.get(mode, 16) // group
+        per_tile = {"rows": 64, "tc": 256, "tc_shares": 256}.get(mode, 16) // group
         tiles = []
         for i in range(len(self.spans)):
             first, n = self.q_start[i], self.q_start[i + 1] - self.q_start[i]
             for s in range(0, n, per_tile):
-                tiles.append((i, first + s, min(per_tile, n - s), 0))
+                if mode == "tc_shares":          # `splits` entries that walk one share of the keys each
+                    tiles += [(i, first + s, min(per_tile, n - s), share | splits << 8) for share in range(splits)]
+                else:
+                    tiles.append((i, first + s, min(per_tile, n - s), 0))
         tiles = torch.tensor(tiles, dtype=torch.int32, device=DEV)
         out = torch.zeros(self.q.shape[0], self.nq * self.d, device=DEV, dtype=self.dtype)
         args = (self.dev(self.q.reshape(-1, self.nq * self.d)), self.dev(self.kc), self.dev(self.vc),
                 self.dev(self.positions), self.dev(self.table), tiles, out, self.nq, self.nkv, self.d, self.window)
         if mode == "keys":
             kernels.attention_mma_keys(*args, splits=splits)
-        elif mode == "tc":
-            kernels.attention_prefill_tc(*args)
+        elif mode in ("tc", "tc_shares"):
+            kernels.attention_prefill_tc(*args, shares=mode == "tc_shares")
             torch.cuda.synchronize()
             kernels.check_device_errors()
         elif mode == "tma":
@@ -295,6 +298,16 @@ def test_attention_prefill_tc(nq, nkv, d, page):
     assert kernels.attention_prefill_tc_supported(d, nq // nkv, page)
     case = PagedCase(torch.bfloat16, nq, nkv, d, page, TC_SPANS, seed=nq + d)
     close(case.run_mma("tc"), case.plain(), torch.bfloat16, "attention_prefill_tc")
+
+
+@pytest.mark.parametrize("shares", [2, 3, 7])
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (4, 4, 64, 8), (4, 1, 128, 32)])
+def test_attention_prefill_tc_shares_of_the_keys(nq, nkv, d, page, shares):
+    """Entries that walk one share of their key blocks each, merged by the second kernel: portions deep in a long
+    context, a fresh prompt whose first entries have fewer blocks than shares (empty shares), a tile without
+    a block in the last share, a ragged last entry."""
+    case = PagedCase(torch.bfloat16, nq, nkv, d, page, [(1000, 70), (0, 300), (130, 3 + 256 // (nq // nkv)), (2000, 40)], seed=shares)
+    close(case.run_mma("tc_shares", shares), case.plain(), torch.bfloat16, f"{shares} shares of the keys")
 
 
 def test_attention_prefill_tc_rescales_when_the_maximum_grows():
