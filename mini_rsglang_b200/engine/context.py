@@ -35,3 +35,8 @@ class StepContext:
     decode_tiles: torch.Tensor | None = None
     real_sequences: int = 0            # sequences that are not padding (padding rows come last)
     want_every_row: bool = False       # `want_rows` is 0, 1, ..., T - 1
+    # Layer-by-layer inspection (the reference's observer, crates/models/src/qwen3.rs:159-229): when set, the
+    # model calls observe(label, tensor [T, width]) with what the reference's observer sees under the same
+    # labels, and the parts take the kernels that leave those tensors (no product with a fused epilogue).
+    observe: object = None
+    label: str = ""                    # the running layer's label ("layer3"), set by the model while observing

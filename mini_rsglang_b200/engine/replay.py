@@ -10,7 +10,13 @@ Input, one JSON object a line:
     {"step": 0, "entries": [{"id": "a", "tokens": [5, 17, 3], "want": [0, 2]}], "end": []}
 For a step in which something is wanted, `<out>/<step>.f32` holds the logits at the wanted
 places, in the order of the entries and of `want`, little-endian float32 [wanted, vocab].
-After every step a line `done <step>` is printed and flushed."""
+After every step a line `done <step>` is printed and flushed.
+
+`--observe ID` also writes, for every step that brings tokens of request ID, what the reference's
+observer sees layer by layer (crates/models/src/qwen3.rs:159-229; its `trace` example,
+crates/engine/examples/trace.rs): `<out>/observe/<step>.<label>.f32`, float32 [the request's tokens of the
+step, width], labels `embedding`, `layerN-input_norm`, `-q_proj`, `-q_norm`, `-q_rope`, `-k_rope`,
+`-v_proj`, `-attn`, `-swiglu`, `-output`, `final_norm`."""
 from __future__ import annotations
 
 import argparse
@@ -29,12 +35,15 @@ MAX_LIVE = 8      # state slots; a trace holds up to four live requests
 
 
 class Replayer:
-    def __init__(self, model: str, dtype: str, max_tokens: int, device: str = "cuda:0", page_size: int = 16):
+    def __init__(self, model: str, dtype: str, max_tokens: int, device: str = "cuda:0", page_size: int = 16,
+                 observe: str | None = None):
         config = load_config(model)
         pages = -(-int(max_tokens) // page_size)
         limits = RuntimeConfig(max_seq_len=min(config.max_position_embeddings, max(pages * page_size, page_size)),
                                page_size=page_size, prefill_budget=max(pages * page_size, 1), max_running=MAX_LIVE)
         self.runner = ModelRunner.load(model, dtype=dtype, device=device, limits=limits, num_pages=pages)
+        self.observed = observe            # the request whose layers are written out, or None
+        self.seen: dict[str, np.ndarray] = {}
         self.ids: dict[str, int] = {}
         self.lengths: dict[str, int] = {}
         self.next_id = 1
@@ -55,8 +64,18 @@ class Replayer:
             cache.extend(self.ids[name], start + len(tokens))
             batch.append(SequenceStep(self.ids[name], tokens, start, [int(w) for w in entry.get("want", [])]))
         logits = None
+        self.seen = {}
+        observe = None
+        names = [str(entry["id"]) for entry in record.get("entries", [])]
+        if self.observed is not None and self.observed in names:
+            at = names.index(self.observed)
+            first = sum(len(seq.tokens) for seq in batch[:at])
+            rows = slice(first, first + len(batch[at].tokens))
+
+            def observe(label, tensor):
+                self.seen[label] = tensor[rows].float().cpu().numpy().astype("<f4")
         if batch:
-            logits = self.runner.step(batch)
+            logits = self.runner.step(batch, observe)
             for seq in batch:
                 cache.trim(seq.request_id, seq.start_pos + len(seq.tokens))
             for entry, seq in zip(record["entries"], batch):
@@ -78,10 +97,13 @@ def main(argv=None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens that live requests hold at any time; the cache pool is made for this many")
     parser.add_argument("--device", default="cuda:0")
+    parser.add_argument("--observe", metavar="ID", help="also write the layers of this request, step by step, to <out>/observe/")
     args = parser.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)
+    if args.observe is not None:
+        os.makedirs(os.path.join(args.out, "observe"), exist_ok=True)
     try:
-        replayer = Replayer(args.model, args.dtype, args.max_tokens, args.device)
+        replayer = Replayer(args.model, args.dtype, args.max_tokens, args.device, observe=args.observe)
         for line in sys.stdin:
             line = line.strip()
             if not line:
@@ -90,6 +112,8 @@ def main(argv=None) -> int:
             logits = replayer.step(record)
             if logits is not None:
                 logits.tofile(os.path.join(args.out, f"{record['step']}.f32"))
+            for label, rows in replayer.seen.items():
+                rows.tofile(os.path.join(args.out, "observe", f"{record['step']}.{label}.f32"))
             print(f"done {record['step']}", flush=True)
     except EngineError as e:
         print(f"trace_run: {type(e).__name__}: {e}", file=sys.stderr, flush=True)

@@ -231,14 +231,20 @@ class ModelRunner:
             decode_tiles=dview(layout[11], 4 * B, (B, 4)) if decode else None, real_sequences=real,
             want_every_row=bool(decode) and R == T)
 
-    def forward(self, sequences: Sequence[SequenceStep]) -> torch.Tensor | None:
+    def forward(self, sequences: Sequence[SequenceStep], observe=None) -> torch.Tensor | None:
         """Runs the batch; returns the logits [wanted, vocab] (float32, on the device) in the
         order of the sequences and of their `want`, or None when nothing is wanted.  The
-        kernels are queued, not awaited.  The result is valid until the next call."""
+        kernels are queued, not awaited.  The result is valid until the next call.
+
+        `observe(label, tensor)`: called with the tensors [tokens of the step, width] that the reference's
+        observer sees, under its labels (crates/models/src/qwen3.rs:174-229: embedding, layerN-input_norm,
+        -q_proj, -q_norm, -q_rope, -k_rope, -v_proj, -attn, -swiglu, -output, final_norm); such a step runs
+        every one of those stages as a kernel of its own and is never replayed from a recording."""
         self.steps += 1
-        if self._replayable(sequences):
+        if observe is None and self._replayable(sequences):
             return self._forward_recorded(sequences)
         ctx = self.build_context(sequences)
+        ctx.observe = observe
         with torch.no_grad():
             return self.model.forward(ctx, self.storage)
 
@@ -290,11 +296,11 @@ class ModelRunner:
         kernels.launch_count += record.launches
         return record.logits[:real]
 
-    def step(self, sequences: Sequence[SequenceStep]) -> torch.Tensor | None:
+    def step(self, sequences: Sequence[SequenceStep], observe=None) -> torch.Tensor | None:
         """`forward`, then wait for the device: when it returns, the cache holds the step's
         tokens and pages may be given back (reference: crates/core/src/lib.rs:136-137)."""
         try:
-            logits = self.forward(sequences)
+            logits = self.forward(sequences, observe)
             torch.cuda.current_stream().synchronize()
             kernels.check_device_errors()
             return logits

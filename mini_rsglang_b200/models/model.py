@@ -8,6 +8,13 @@ from ..parts.base import Runtime
 from .spec import ModelSpec
 
 
+def plain_or_none(pending):
+    """A branch output that the stream does not hold yet, or None when it does (`Prenormed`) or there is none."""
+    from ..parts.base import Prenormed
+
+    return None if isinstance(pending, Prenormed) else pending
+
+
 class Model:
     def __init__(self, spec: ModelSpec, tensors: dict[str, torch.Tensor], runtime: Runtime):
         self.spec = spec
@@ -39,15 +46,20 @@ class Model:
         when no logits are wanted (the head is then skipped, as in the reference,
         crates/engine/src/lib.rs:132-135)."""
         stream = self.embedding.forward(ctx)
+        if ctx.observe:
+            ctx.observe("embedding", stream)
         pending = None
         order = self.spec.run_order
         for index, entry in enumerate(order):
             block = self.blocks[entry.layer]
+            ctx.label = f"layer{index}"
             extra = {}
             if block.links_norms:        # the norm that reads the stream after this block
                 extra["next_norm"] = self.blocks[order[index + 1].layer].norm1 if index + 1 < len(order) else self.final_norm
             pending = block.forward(stream, pending, ctx, storage.entries[self.cache_entry[index]],
                                     self.writes_cache[index], **extra)
+        if ctx.observe:              # the reference norms every row before it gathers the wanted ones (qwen3.rs:228-233)
+            ctx.observe("final_norm", self.final_norm.add_norm(stream, plain_or_none(pending), write_back=False))
         if ctx.want_rows is None:
             return None
         rows = None if ctx.want_every_row else ctx.want_rows

@@ -12,7 +12,7 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, Prenormed, plain
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, Prenormed, observing, plain
 from .linear import few_rows, linear
 
 
@@ -174,7 +174,7 @@ class GroupedQueryAttention(Mixer):
         q = torch.empty((tokens, self.nq * self.d), dtype=self.runtime.dtype, device=self.o.device)
         eps = self.q_norm.eps if self.q_norm else (self.k_norm.eps if self.k_norm else 0.0)
         group = cache.group
-        if self.d == 128 and few_rows(h, self.qkv):
+        if self.d == 128 and few_rows(h, self.qkv) and not observing(ctx):
             # few rows, heads of 128: the product's epilogue norms, rotates and writes the cache itself
             prenormed = isinstance(h, Prenormed)
             kernels.gemm_tc_qkv_heads(
@@ -186,6 +186,8 @@ class GroupedQueryAttention(Mixer):
             paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
             return linear(out, self.o, into=into)
         qkv = linear(h, self.qkv)
+        if observing(ctx):
+            self._observe_projection(qkv, ctx)
         kernels.qk_norm_rope_store(
             qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
             ctx.slots[group] if write_cache else None,
@@ -193,4 +195,24 @@ class GroupedQueryAttention(Mixer):
             self.position.tables()["inv_freq"], self.nq, self.nkv, self.d, cache.k.shape[2])
         out = torch.empty_like(q)
         paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
+        if observing(ctx):
+            self._observe_rotated(q, out, cache, ctx, write_cache)
         return linear(out, self.o, into=into)
+
+    # what the reference's observer sees in an attention layer (crates/models/src/qwen3.rs:190-201)
+    def _observe_projection(self, qkv, ctx):
+        tokens, q_width, kv_width = qkv.shape[0], self.nq * self.d, self.nkv * self.d
+        q = qkv[:, :q_width].contiguous()
+        ctx.observe(f"{ctx.label}-q_proj", q)
+        ctx.observe(f"{ctx.label}-v_proj", qkv[:, q_width + kv_width:].contiguous())
+        if self.q_norm is not None:
+            q = self.q_norm.forward(q.view(tokens * self.nq, self.d)).view(tokens, q_width)
+        ctx.observe(f"{ctx.label}-q_norm", q)
+
+    def _observe_rotated(self, q, out, cache, ctx, write_cache):
+        ctx.observe(f"{ctx.label}-q_rope", q)
+        if write_cache:               # the rotated keys as they lie in the cache pages
+            slots = ctx.slots[cache.group].long()
+            page = cache.k.shape[2]
+            ctx.observe(f"{ctx.label}-k_rope", cache.k[slots // page, :, slots % page].reshape(q.shape[0], self.nkv * self.d))
+        ctx.observe(f"{ctx.label}-attn", out)

@@ -113,6 +113,11 @@ class Prenormed:
         return self.norm.add_norm(self.stream, None)
 
 
+def observing(ctx) -> bool:
+    """Whether the step is watched layer by layer (`StepContext.observe`); a part asked without a context is not."""
+    return getattr(ctx, "observe", None) is not None
+
+
 def plain(h):
     """`h` as a tensor."""
     return h.materialise() if isinstance(h, Prenormed) else h

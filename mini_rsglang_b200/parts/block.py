@@ -7,7 +7,7 @@ with few rows, the branch's last product adds it and the norm rides on the produ
 (`Prenormed` in parts/base.py)."""
 from __future__ import annotations
 
-from .base import BLOCKS, Block, Prenormed, ResidualLink, plain
+from .base import BLOCKS, Block, Prenormed, ResidualLink, observing, plain
 
 
 def _branch(part, h, stream, norm, *args):
@@ -24,7 +24,20 @@ class PreNormBlock(Block):
     links_norms = True
 
     def forward(self, stream, pending, ctx, cache, write_cache=True, next_norm=None):
+        if observing(ctx):
+            return self.forward_observed(stream, pending, ctx, cache, write_cache)
         h = self.norm1.add_norm(stream, pending)
         a = _branch(self.mixer, h, stream, self.norm2, ctx, cache, write_cache)
         h = self.norm2.add_norm(stream, a)
         return _branch(self.feed_forward, h, stream, next_norm, ctx)
+
+    def forward_observed(self, stream, pending, ctx, cache, write_cache):
+        """The same with every norm a kernel of its own and the reference's observer called on its labels
+        (crates/models/src/qwen3.rs:177-226): input_norm here, the mixer's and feed-forward's inside them, output."""
+        h = plain(self.norm1.add_norm(stream, pending))
+        ctx.observe(f"{ctx.label}-input_norm", h)
+        a = self.mixer.forward(h, ctx, cache, write_cache)
+        h = plain(self.norm2.add_norm(stream, a))
+        f = self.feed_forward.forward(h, ctx)
+        ctx.observe(f"{ctx.label}-output", stream + f.float())
+        return f

@@ -8,7 +8,7 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .base import FEED_FORWARDS, FeedForward, Prenormed
+from .base import FEED_FORWARDS, FeedForward, Prenormed, observing
 from .linear import few_rows, linear
 
 
@@ -48,11 +48,13 @@ class SwiGLU(FeedForward):
 
     def forward(self, h, ctx, into=None):
         act = torch.empty((h.shape[0], self.inner), dtype=self.runtime.dtype, device=self.down.device)
-        if self.block and few_rows(h, self.gate_up):
+        if self.block and few_rows(h, self.gate_up) and not observing(ctx):
             if isinstance(h, Prenormed):
                 kernels.gemm_tc(h.scaled, self.gate_up, act, gated=True, row_sums=h.row_sums)
             else:
                 kernels.gemm_tc(h, self.gate_up, act, gated=True)
         else:
             kernels.silu_mul(linear(h, self.gate_up), act, self.block)
+        if observing(ctx):
+            ctx.observe(f"{ctx.label}-swiglu", act)
         return linear(act, self.down, into=into)

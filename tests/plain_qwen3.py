@@ -172,53 +172,72 @@ def swiglu(ar: Arith, gate: torch.Tensor, up: torch.Tensor) -> torch.Tensor:
     return ar.r(ar.r(gate / (1.0 + torch.exp(-gate))) * up)
 
 
+def _silent(label: str, tensor: torch.Tensor) -> None:
+    pass
+
+
 def attention_part(ar: Arith, cfg: PlainConfig, w: dict, root: str, n: torch.Tensor,
-                   positions: torch.Tensor) -> torch.Tensor:
+                   positions: torch.Tensor, observe=_silent, label: str = "") -> torch.Tensor:
     """QKV projection, per-head q/k RMSNorm, rotary, attention, output projection
-    (crates/models/src/qwen3.rs:178-202)."""
+    (crates/models/src/qwen3.rs:178-202).  `observe` is handed the tensors that the reference's
+    observer sees there, under its labels (qwen3.rs:190-201)."""
     T = n.shape[0]
     nq, nkv, d = cfg.num_attention_heads, cfg.num_key_value_heads, cfg.head_dim
     q = linear(ar, n, w[f"{root}.self_attn.q_proj.weight"]).view(T, nq, d)
     k = linear(ar, n, w[f"{root}.self_attn.k_proj.weight"]).view(T, nkv, d)
     v = linear(ar, n, w[f"{root}.self_attn.v_proj.weight"]).view(T, nkv, d)
+    observe(f"{label}-q_proj", q.reshape(T, nq * d))
     q = rms_norm(ar, q, w[f"{root}.self_attn.q_norm.weight"], cfg.rms_norm_eps)
     k = rms_norm(ar, k, w[f"{root}.self_attn.k_norm.weight"], cfg.rms_norm_eps)
+    observe(f"{label}-q_norm", q.reshape(T, nq * d))
     q = rope(ar, q, positions, cfg.rope_theta)
     k = rope(ar, k, positions, cfg.rope_theta)
+    observe(f"{label}-q_rope", q.reshape(T, nq * d))
+    observe(f"{label}-k_rope", k.reshape(T, nkv * d))
+    observe(f"{label}-v_proj", v.reshape(T, nkv * d))
     attn = causal_attention(ar, q, k, v).reshape(T, nq * d)
+    observe(f"{label}-attn", attn)
     return linear(ar, attn, w[f"{root}.self_attn.o_proj.weight"])
 
 
-def feed_forward_part(ar: Arith, w: dict, root: str, n: torch.Tensor) -> torch.Tensor:
+def feed_forward_part(ar: Arith, w: dict, root: str, n: torch.Tensor, observe=_silent, label: str = "") -> torch.Tensor:
     """down(swiglu(gate(n), up(n))) (qwen3.rs:239-262, 206-209)."""
     gate = linear(ar, n, w[f"{root}.mlp.gate_proj.weight"])
     up = linear(ar, n, w[f"{root}.mlp.up_proj.weight"])
-    return linear(ar, swiglu(ar, gate, up), w[f"{root}.mlp.down_proj.weight"])
+    activated = swiglu(ar, gate, up)
+    observe(f"{label}-swiglu", activated)
+    return linear(ar, activated, w[f"{root}.mlp.down_proj.weight"])
 
 
 def block(ar: Arith, cfg: PlainConfig, w: dict, i: int, x: torch.Tensor,
-          positions: torch.Tensor) -> torch.Tensor:
+          positions: torch.Tensor, observe=_silent) -> torch.Tensor:
     """Pre-norm block: x + attn(norm(x)), then + mlp(norm(.)); each sum rounded
     (qwen3.rs:176-225; ops.cu:62-65)."""
-    root = f"model.layers.{i}"
+    root, label = f"model.layers.{i}", f"layer{i}"
     n = rms_norm(ar, x, w[f"{root}.input_layernorm.weight"], cfg.rms_norm_eps)
-    residual = ar.r(x + attention_part(ar, cfg, w, root, n, positions))
+    observe(f"{label}-input_norm", n)
+    residual = ar.r(x + attention_part(ar, cfg, w, root, n, positions, observe, label))
     n = rms_norm(ar, residual, w[f"{root}.post_attention_layernorm.weight"], cfg.rms_norm_eps)
-    return ar.r(residual + feed_forward_part(ar, w, root, n))
+    out = ar.r(residual + feed_forward_part(ar, w, root, n, observe, label))
+    observe(f"{label}-output", out)
+    return out
 
 
 def logits_of_sequence(cfg: PlainConfig, w: dict, tokens, rounding: str | None = None,
-                       first_position: int = 0) -> torch.Tensor:
+                       first_position: int = 0, observe=_silent) -> torch.Tensor:
     """Logits [T, V] at every position of one whole sequence (qwen3.rs:170-236): embedding,
     the blocks in order, the final norm, the head (tied to the embedding when the
-    configuration says so, qwen3.rs:234), output unrounded."""
+    configuration says so, qwen3.rs:234), output unrounded.  `observe(label, tensor)` sees what the
+    reference's observer sees, under its labels (qwen3.rs:174-229)."""
     ar = Arith(rounding)
     ids = torch.as_tensor(list(tokens), dtype=torch.long)
     positions = torch.arange(first_position, first_position + ids.numel())
     x = embedding(ar, w["model.embed_tokens.weight"], ids).to(ar.dtype)
+    observe("embedding", x)
     for i in range(cfg.num_hidden_layers):
-        x = block(ar, cfg, w, i, x, positions)
+        x = block(ar, cfg, w, i, x, positions, observe)
     x = rms_norm(ar, x, w["model.norm.weight"], cfg.rms_norm_eps)
+    observe("final_norm", x)
     head = w["model.embed_tokens.weight"] if cfg.tie_word_embeddings else w["lm_head.weight"]
     return linear(ar, x, head, round_out=False)
 

@@ -108,11 +108,11 @@ def trace_mixed(reqs, seed: int, max_live: int = 4, tail: int = 32) -> tuple[Tra
 class TraceRun:
     """Drives one `bin/trace_run` process: a step is written only after the `done` of the last."""
 
-    def __init__(self, model: str, dtype: str, out: str, max_tokens: int, env=None):
+    def __init__(self, model: str, dtype: str, out: str, max_tokens: int, env=None, extra=()):
         self.out = out
         self.proc = subprocess.Popen(
-            [sys.executable, TRACE_RUN, "--model", model, "--dtype", dtype, "--out", out, "--max-tokens", str(max_tokens)],
-            stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
+            [sys.executable, TRACE_RUN, "--model", model, "--dtype", dtype, "--out", out, "--max-tokens", str(max_tokens),
+             *extra], stdin=subprocess.PIPE, stdout=subprocess.PIPE, text=True, env=env)
 
     def step(self, record: dict, vocab: int):
         self.proc.stdin.write(json.dumps(record) + "\n")
