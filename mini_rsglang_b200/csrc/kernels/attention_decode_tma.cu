@@ -10,8 +10,14 @@
 // (token, head) walking the keys with scalar loads)
 //
 // Work is cut as in the plain tensor-core kernel: a tile is up to 16 / group consecutive tokens
-// of one request; `splits` CTAs share the 64-key blocks of a tile and leave unnormalised partial
-// results in scratch memory; the CTA that finishes a (tile, head) last merges them in order.
+// of one request; `splits` CTAs share the 64-key blocks of a tile.  When the splits are 2, 4, 8 or
+// 16 they are launched as one thread-block cluster: every CTA sends each other CTA that CTA's
+// slice of the head's columns of its unnormalised result (and all of them its maxima and sums)
+// through distributed shared memory, counts the arrivals on an mbarrier of its own, and merges and
+// stores its slice, in the order of the shares.  Nothing of the merge goes through global memory,
+// whose dependent trips (result out, fence, counter, results in) cost microseconds each at the
+// end of a kernel.  Other split counts leave their results in scratch memory, and the CTA that
+// finishes a (tile, head) last merges them in order.
 #include "tma.cuh"
 
 #ifndef MRS_HEAD_DIM
@@ -52,13 +58,54 @@ __device__ __forceinline__ uint32_t pack_bf16(float lo, float hi) {
     __nv_bfloat162 v = __floats2bfloat162_rn(lo, hi);
     return *reinterpret_cast<uint32_t*>(&v);
 }
+// ---- distributed shared memory of a thread-block cluster
+__device__ __forceinline__ uint32_t in_cta(uint32_t local_address, uint32_t rank) {      // the same place in CTA `rank`
+    uint32_t a;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(a) : "r"(local_address), "r"(rank));
+    return a;
+}
+__device__ __forceinline__ void store_cluster(uint32_t address, float4 v) {
+    asm volatile("st.shared::cluster.v4.f32 [%0], {%1, %2, %3, %4};" ::"r"(address), "f"(v.x), "f"(v.y), "f"(v.z), "f"(v.w) : "memory");
+}
+__device__ __forceinline__ void store_cluster(uint32_t address, float2 v) {
+    asm volatile("st.shared::cluster.v2.f32 [%0], {%1, %2};" ::"r"(address), "f"(v.x), "f"(v.y) : "memory");
+}
+__device__ __forceinline__ void arrive_in_cluster(uint32_t barrier_address) {          // after this thread's (and, through a CTA barrier, its CTA's) stores
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(barrier_address) : "memory");
+}
+__device__ __forceinline__ bool mbar_try_wait_cluster(uint64_t* bar, uint32_t parity) {
+    uint32_t done;
+    asm volatile("{\n .reg .pred p;\n mbarrier.try_wait.parity.acquire.cluster.shared::cta.b64 p, [%1], %2;\n selp.u32 %0, 1, 0, p;\n}"
+                 : "=r"(done) : "r"(smem_u32(bar)), "r"(parity) : "memory");
+    return done != 0;
+}
+// Bounded like mbar_wait; sees what the arriving CTAs of the cluster stored.
+__device__ __forceinline__ bool mbar_wait_cluster(uint64_t* bar, uint32_t parity) {
+    if (mbar_try_wait_cluster(bar, parity)) return true;
+    const long long start = clock64();
+    unsigned int spins = 0;
+    while (!mbar_try_wait_cluster(bar, parity)) {
+        if ((++spins & 255u) == 0 && *reinterpret_cast<volatile unsigned int*>(&mrs_error_word) != 0) return false;
+        if (clock64() - start > MRS_WAIT_CYCLES) {
+            mrs_raise(MRS_ERR_BARRIER_TIMEOUT);
+            return false;
+        }
+    }
+    return true;
+}
+__device__ __forceinline__ void cluster_sync_all() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n barrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+constexpr int MAX_CLUSTER = 16;
+
 __device__ __forceinline__ void consumer_sync() { asm volatile("bar.sync 1, %0;" ::"n"(32 * CONSUMER_WARPS) : "memory"); }
 
 __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     const __grid_constant__ CUtensorMap k_map, const __grid_constant__ CUtensorMap v_map,
     const bf16* __restrict__ q, const int* __restrict__ positions, const int* __restrict__ block_table, int table_width,
     const Tile* __restrict__ tiles, bf16* __restrict__ out, float* __restrict__ part_o, float* __restrict__ part_ml,
-    int* __restrict__ counters, int nq, int nkv, int page_size, int page_shift, float scale_log2, int window, int splits) {
+    int* __restrict__ counters, int nq, int nkv, int page_size, int page_shift, float scale_log2, int window, int splits,
+    int in_cluster) {
     extern __shared__ unsigned char smem_raw[];
     __shared__ int is_last;
     const Tile tile = tiles[blockIdx.x];
@@ -67,6 +114,10 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
     uint64_t* empty = full + STAGES;
+    // what the other CTAs of a cluster send: their parts of this CTA's columns, and everybody's maxima and sums
+    uint64_t* merge_bar = empty + STAGES;
+    float* incoming_o = reinterpret_cast<float*>(merge_bar + 2);            // [splits][ROWS][D / splits]
+    float* incoming_ml = incoming_o + ROWS * D;                            // [splits][ROWS][2]
 
     const int kv_head = blockIdx.y, split = blockIdx.z, group = nq / nkv;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
@@ -85,9 +136,11 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
             mbar_init(&full[s], 1);
             mbar_init(&empty[s], CONSUMER_WARPS);
         }
+        if (in_cluster) mbar_init(merge_bar, splits);
         mbar_fence_init();
     }
     __syncthreads();
+    if (in_cluster) cluster_sync_all();          // every CTA's barrier stands before anybody can arrive at it
     pdl_launch_dependents();
     // The queries and the keys and values of this step's tokens come from the kernel before this one;
     // older keys lie in the cache since earlier steps.  The consumers wait before they read the
@@ -267,6 +320,57 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
         }
     }
     consumer_sync();
+    if (in_cluster) {
+        // ---- merge within the cluster.  This CTA's result, still scaled by its own maxima: columns
+        // [j * cols, (j + 1) * cols) of every row go to CTA j, the maxima and sums to every CTA.
+        const int cols = D / splits;
+        const uint32_t o_here = smem_u32(incoming_o) + (uint32_t)split * ROWS * cols * 4, ml_here = smem_u32(incoming_ml) + (uint32_t)split * ROWS * 8;
+        for (int idx = threadIdx.x; idx < rows * (D / 4); idx += 32 * CONSUMER_WARPS) {
+            const int row = idx / (D / 4), col = (idx % (D / 4)) * 4;
+            float m = -CUDART_INF_F;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; ++w) m = fmaxf(m, merge_ml[(w * ROWS + row) * 2]);
+            const float base = m == -CUDART_INF_F ? 0.0f : m;
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            float sum = 0.0f;
+#pragma unroll
+            for (int w = 0; w < CONSUMER_WARPS; ++w) {
+                const float f = exp2f(merge_ml[(w * ROWS + row) * 2] - base);
+                const float4 v = *reinterpret_cast<const float4*>(&merge_o[(w * ROWS + row) * D + col]);
+                acc.x += v.x * f, acc.y += v.y * f, acc.z += v.z * f, acc.w += v.w * f;
+                sum += merge_ml[(w * ROWS + row) * 2 + 1] * f;
+            }
+            const int target = col / cols;
+            store_cluster(in_cta(o_here + (uint32_t)(row * cols + col % cols) * 4, target), acc);
+            if (col == 0)
+                for (int j = 0; j < splits; ++j) store_cluster(in_cta(ml_here + (uint32_t)row * 8, j), make_float2(m, sum));
+        }
+        consumer_sync();                              // the CTA's stores are issued: one thread tells every CTA
+        if (threadIdx.x == 0) {
+            asm volatile("fence.acq_rel.cluster;" ::: "memory");
+            for (int j = 0; j < splits; ++j) arrive_in_cluster(in_cta(smem_u32(merge_bar), j));
+        }
+        mbar_wait_cluster(merge_bar, 0);              // all shares of this CTA's columns have arrived (or the time ran out)
+        for (int idx = threadIdx.x; idx < rows * (cols / 4); idx += 32 * CONSUMER_WARPS) {
+            const int row = idx / (cols / 4), col = (idx % (cols / 4)) * 4;
+            float m = -CUDART_INF_F;
+            for (int s = 0; s < splits; ++s) m = fmaxf(m, incoming_ml[(s * ROWS + row) * 2]);
+            const float base = m == -CUDART_INF_F ? 0.0f : m;
+            float sum = 0.0f;
+            float4 acc = make_float4(0.0f, 0.0f, 0.0f, 0.0f);
+            for (int s = 0; s < splits; ++s) {         // in the order of the shares
+                const float f = exp2f(incoming_ml[(s * ROWS + row) * 2] - base);
+                const float4 v = *reinterpret_cast<const float4*>(&incoming_o[(s * ROWS + row) * cols + col]);
+                sum += incoming_ml[(s * ROWS + row) * 2 + 1] * f;
+                acc.x += v.x * f, acc.y += v.y * f, acc.z += v.z * f, acc.w += v.w * f;
+            }
+            const float inv = sum > 0.0f ? 1.0f / sum : 0.0f;
+            bf16* dst = out + ((size_t)(tile.first_token + row / group) * nq + kv_head * group + row % group) * D + split * cols + col;
+            *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
+            *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
+        }
+        return;
+    }
     const size_t first_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS;
     for (int idx = threadIdx.x; idx < rows * D; idx += 32 * CONSUMER_WARPS) {
         const int row = idx / D, col = idx % D;
@@ -341,7 +445,8 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
     }
 }
 
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + 2 * STAGES * sizeof(uint64_t);
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 2) * sizeof(uint64_t) +
+                              (size_t)ROWS * D * sizeof(float) + (size_t)MAX_CLUSTER * ROWS * 2 * sizeof(float);
 static_assert((size_t)STAGES * STAGE_BYTES >= (size_t)CONSUMER_WARPS * ROWS * (D + 2) * sizeof(float), "merge area");
 
 int page_shift_of(int page_size) {
@@ -387,10 +492,47 @@ MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, co
     }
     float* part_o = scratch;
     float* part_ml = scratch ? scratch + (size_t)num_tiles * nkv * splits * ROWS * D : nullptr;
+    const float scale_log2 = scale * 1.4426950408889634f;
+    // 2, 4, 8 or 16 splits whose slices of the head's columns are whole float4s run as one cluster and merge among themselves
+    static int largest_cluster = -1;
+    if (largest_cluster < 0) {
+        largest_cluster = 8;
+        if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess) {
+            cudaLaunchConfig_t probe = {};
+            probe.gridDim = dim3(1, 1, 16), probe.blockDim = dim3(THREADS), probe.dynamicSmemBytes = SMEM_BYTES;
+            cudaLaunchAttribute shape;
+            shape.id = cudaLaunchAttributeClusterDimension;
+            shape.val.clusterDim.x = 1, shape.val.clusterDim.y = 1, shape.val.clusterDim.z = 16;
+            probe.attrs = &shape, probe.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel, &probe) == cudaSuccess && clusters > 0) largest_cluster = 16;
+        }
+        (void)cudaGetLastError();
+    }
+    const bool in_cluster = splits > 1 && (splits & (splits - 1)) == 0 && splits <= largest_cluster && D % (4 * splits) == 0;
+    if (in_cluster) {
+        cudaLaunchConfig_t config = {};
+        config.gridDim = dim3(num_tiles, nkv, splits);
+        config.blockDim = dim3(THREADS);
+        config.dynamicSmemBytes = SMEM_BYTES;
+        config.stream = (cudaStream_t)stream;
+        cudaLaunchAttribute attributes[2];
+        attributes[0].id = cudaLaunchAttributeClusterDimension;
+        attributes[0].val.clusterDim.x = 1, attributes[0].val.clusterDim.y = 1, attributes[0].val.clusterDim.z = splits;
+        attributes[1].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        attributes[1].val.programmaticStreamSerializationAllowed = 1;
+        static const bool plain = getenv("MRS_PLAIN_LAUNCH") != nullptr;
+        config.attrs = attributes;
+        config.numAttrs = plain ? 1 : 2;
+        return (int)cudaLaunchKernelEx(&config, attention_decode_kernel, *reinterpret_cast<const CUtensorMap*>(k_map),
+                                       *reinterpret_cast<const CUtensorMap*>(v_map), (const bf16*)q, positions, block_table, table_width,
+                                       (const Tile*)tiles, (bf16*)out, part_o, part_ml, counters, nq, nkv, page_size, shift, scale_log2,
+                                       window, splits, 1);
+    }
     MRS_LAUNCH(attention_decode_kernel, dim3(num_tiles, nkv, splits), THREADS, SMEM_BYTES, stream,
         *reinterpret_cast<const CUtensorMap*>(k_map), *reinterpret_cast<const CUtensorMap*>(v_map), (const bf16*)q,
         positions, block_table, table_width, (const Tile*)tiles, (bf16*)out, part_o, part_ml, counters, nq, nkv, page_size,
-        shift, scale * 1.4426950408889634f, window, splits);
+        shift, scale_log2, window, splits, 0);
     MRS_RETURN_LAUNCH_STATUS();
 }
 

@@ -84,11 +84,16 @@ def choose_splits(tiles: int, nkv: int, longest_context: int, resident: int = 2)
     heads): one round of CTAs beats several (every CTA pays for its start and for the merge), and
     more CTAs than fill the GPU's slots (`resident` per SM) only add merges.  So: the fewest splits
     that fill about 85% of the slots, at most 16 (a single request: 10.9 us with 16, 13.7 us with 32),
-    every split with at least two 64-key blocks."""
+    every split with at least two 64-key blocks, rounded up to a power of two."""
     blocks = -(-longest_context // 64)
     slots = SM_COUNT * resident
     want = -(-(85 * slots) // (100 * max(tiles * nkv, 1)))
-    return max(1, min(want, 16, blocks // 2))
+    most = max(1, min(16, blocks // 2))
+    # a power of two: 2, 4, 8 or 16 shares run as one thread-block cluster and merge through distributed shared memory
+    power = 1 << max(want - 1, 0).bit_length()
+    while power > most:
+        power //= 2
+    return max(1, power)
 
 
 def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) -> None:
