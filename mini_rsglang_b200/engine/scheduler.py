@@ -55,6 +55,8 @@ class Scheduler:
         self._count = np.empty(cap, dtype=np.int64)
         self._sample = np.empty(cap, dtype=np.int32)
         self._tokens = np.empty(max(limits.prefill_budget, 1), dtype=np.int32)
+        self._done = (np.empty(64, dtype=np.int64), np.empty(64, dtype=np.int32), np.empty(64, dtype=np.int64),
+                      np.empty(64, dtype=np.int64))          # buffers of `drain`, which runs twice a step
 
     def __del__(self):
         handle, self.handle = getattr(self, "handle", None), None
@@ -127,11 +129,8 @@ class Scheduler:
     def drain(self) -> list[FinishedRequest]:
         """Requests that ended since the last call, in the order they ended."""
         out = []
-        cap = 64
-        req = np.empty(cap, dtype=np.int64)
-        reason = np.empty(cap, dtype=np.int32)
-        prompt = np.empty(cap, dtype=np.int64)
-        done = np.empty(cap, dtype=np.int64)
+        req, reason, prompt, done = self._done
+        cap = req.size
         while True:
             n = self.lib.mrs_sched_drain(self.handle, req.ctypes.data, reason.ctypes.data, prompt.ctypes.data,
                                          done.ctypes.data, cap)
