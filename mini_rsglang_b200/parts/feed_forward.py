@@ -8,7 +8,7 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .base import FEED_FORWARDS, FeedForward, Prenormed, observing
+from .base import FEED_FORWARDS, FeedForward, Prenormed, observing, plain
 from .linear import few_rows, linear
 
 
@@ -54,7 +54,12 @@ class SwiGLU(FeedForward):
             else:
                 kernels.gemm_tc(h, self.gate_up, act, gated=True)
         else:
-            kernels.silu_mul(linear(h, self.gate_up), act, self.block)
+            h = plain(h)
+            if (self.block and not observing(ctx) and h.shape[0] >= kernels.GEMM_GATED_ROWS_MIN
+                    and kernels.gemm_gated_rows_supported(h, self.gate_up)):
+                kernels.gemm_gated_rows(h, self.gate_up, act)      # many rows: the tcgen05 product with the activation in it
+            else:
+                kernels.silu_mul(linear(h, self.gate_up), act, self.block)
         if observing(ctx):
             ctx.observe(f"{ctx.label}-swiglu", act)
         return linear(act, self.down, into=into)

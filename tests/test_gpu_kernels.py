@@ -456,6 +456,25 @@ def test_gemm_tc_gated(m, inner, k):
     del both
 
 
+@pytest.mark.parametrize("t,inner,k", [(1, 64, 72), (128, 128, 64), (200, 192, 136), (513, 3072, 1024), (2048, 12288, 4096), (300, 64, 520)])
+def test_gemm_gated_rows(t, inner, k):
+    """The gated product for many rows (tiles of 128 tokens x 256 weight rows): token counts and widths that end inside
+    a tile, a weight matrix of one and a half tiles, a depth that ends inside a block of 64."""
+    g = torch.Generator().manual_seed(t + inner)
+    x = torch.randn(t, k, generator=g).to(torch.bfloat16)
+    gate = (torch.randn(inner, k, generator=g) / k ** 0.5 * 2).to(torch.bfloat16)
+    up = (torch.randn(inner, k, generator=g) / k ** 0.5 * 2).to(torch.bfloat16)
+    mixed = torch.stack([gate.view(-1, 64, k), up.view(-1, 64, k)], dim=1).reshape(2 * inner, k).contiguous()
+    assert kernels.gemm_gated_rows_supported(x.to(DEV), mixed.to(DEV))
+    out = torch.full((t, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kernels.gemm_gated_rows(x.to(DEV), mixed.to(DEV), out)
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    gd, ud = x.double() @ gate.double().T, x.double() @ up.double().T
+    close(out, gd / (1 + torch.exp(-gd)) * ud, torch.bfloat16, f"gated rows {t}x{inner}x{k}")
+    assert not kernels.gemm_gated_rows_supported(x.to(DEV), mixed.to(DEV)[:64])          # half a block of gate rows
+
+
 @pytest.mark.parametrize("m,nq,nkv,k,page", [(1, 2, 1, 64, 8), (8, 32, 8, 4096, 16), (19, 3, 3, 520, 4), (32, 8, 2, 1024, 32)])
 def test_gemm_tc_qkv_heads(m, nq, nkv, k, page):
     """The fused q/k/v projection with head norms, rotation and cache write in its epilogue, against the
@@ -490,6 +509,37 @@ def test_gemm_tc_qkv_heads(m, nq, nkv, k, page):
                               inv_freq.to(DEV), nq, nkv)
     close(q_out.view(m, nq, d), q, torch.bfloat16, "q without a cache")
     assert kc.count_nonzero().item() == 0
+
+
+@pytest.mark.parametrize("t,nq,nkv,k,page", [(1, 2, 1, 64, 8), (130, 3, 3, 520, 4), (300, 8, 2, 1024, 32), (2048, 32, 8, 4096, 16)])
+def test_gemm_heads_rows(t, nq, nkv, k, page):
+    """The fused q/k/v projection for many rows (two heads a tile of 128 tokens): against the plain functions on the
+    unrounded product; an odd number of heads (a tile with one head), tokens that end inside a tile, a row without a slot."""
+    d, eps, theta = 128, 1e-6, 1e6
+    pages = t // page + 3
+    g = torch.Generator().manual_seed(t + nq + k)
+    x = torch.randn(t, k, generator=g).to(torch.bfloat16)
+    w = (torch.randn((nq + 2 * nkv) * d, k, generator=g) / k ** 0.5).to(torch.bfloat16)
+    q_w, k_w = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
+    positions = torch.randint(0, 30000, (t,), generator=g, dtype=torch.int32)
+    slots = torch.randperm(pages * page, generator=g)[:t].to(torch.int32)
+    slots[t // 2] = -1 if t > 1 else slots[0]
+    inv_freq = RotaryPosition.inverse_frequencies(d, theta)
+    q_out = torch.full((t, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
+    kc = torch.zeros(pages, nkv, page, d, dtype=torch.bfloat16, device=DEV)
+    vc = torch.zeros_like(kc)
+    kernels.gemm_heads_rows(x.to(DEV), w.to(DEV), q_out, kc, vc, positions.to(DEV), slots.to(DEV), q_w.to(DEV), k_w.to(DEV),
+                            eps, inv_freq.to(DEV), nq, nkv)
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+    qkv = (x.double() @ w.double().T).float()
+    q, kk, v = plain_qk(qkv.to(DEV), positions.to(DEV), q_w.to(DEV), k_w.to(DEV), eps, theta, nq, nkv, d)
+    close(q_out.view(t, nq, d), q, torch.bfloat16, "q")
+    keep = (slots >= 0).nonzero().flatten()
+    slot = slots[keep].long()
+    close(kc.cpu()[slot // page, :, slot % page], kk[keep], torch.bfloat16, "k in the cache")
+    close(vc.cpu()[slot // page, :, slot % page], v[keep], torch.bfloat16, "v in the cache")
+    assert kc.count_nonzero().item() <= keep.numel() * nkv * d and vc.count_nonzero().item() <= keep.numel() * nkv * d
 
 
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 4096, 4096), (5, 136, 192), (8, 1000, 12288), (19, 520, 1024), (32, 256, 320)])
