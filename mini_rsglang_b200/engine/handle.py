@@ -21,7 +21,7 @@ import torch
 
 from .. import kernels
 from ..config.runtime_config import RuntimeConfig
-from ..errors import BackendError, EngineError, EngineStopped, InvalidRequest
+from ..errors import BackendError, EngineError, EngineStopped
 from ..models.registry import load_config
 from ..sampling import Sampler, SamplingParams
 from .runner import ModelRunner, SequenceStep

@@ -1,8 +1,6 @@
 """Each kernel alone against a plain float32/float64 PyTorch statement of the same operation,
 at sizes other than the engine's tiny configurations (widths and vocabularies that are no power
 of two, head sizes in steps of 16, odd numbers of heads and groups)."""
-import math
-import random
 
 import pytest
 import torch

@@ -8,7 +8,6 @@ import os
 import numpy as np
 import pytest
 import torch
-from conftest import TINY
 
 import plain_qwen3 as P
 import trace_tools as T

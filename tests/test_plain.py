@@ -2,7 +2,7 @@
 import math
 
 import torch
-from conftest import TINY_A, TINY_B
+from conftest import TINY_A
 
 import plain_qwen3 as P
 
