@@ -269,101 +269,178 @@ __global__ void qk_norm_rope_store_kernel(const T* __restrict__ qkv, T* __restri
     }
 }
 
-// The same for head sizes 64, 128 and 256: a lane owns d / 32 consecutive elements (one vector
-// load and store), its rotation partner is the lane 16 further, and the cosines and sines of a
-// token are computed once a block for all of the block's heads instead of once a head.
-#define ROPE_HEADS_PER_BLOCK 16
-
-template <typename T, int VEC>
-__global__ void __launch_bounds__(128) qk_norm_rope_store_vec_kernel(
-    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
-    const int* __restrict__ positions, const int* __restrict__ slots, const float* __restrict__ q_norm,
-    const float* __restrict__ k_norm, float eps, const float* __restrict__ inv_freq, int nq, int nkv, int page_size,
-    int write_kv) {
+// The cosines and sines of every token's angles, once a step for all layers that share the
+// frequencies: out[t][j] = (cos, sin)(position[t] * inv_freq[j]), float32.
+__global__ void rotation_table_kernel(const int* __restrict__ positions, const float* __restrict__ inv_freq, long long total,
+                                      int half, float2* __restrict__ out) {
     pdl_launch_dependents();
     pdl_wait();
-    constexpr int d = 32 * VEC, half = d / 2;
-    __shared__ float cos_s[half], sin_s[half];
-    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int t = blockIdx.x, heads = nq + 2 * nkv;
-    const int head_end = min(heads, (int)(blockIdx.y + 1) * ROPE_HEADS_PER_BLOCK);
-    if (inv_freq) {
-        const float pos = (float)positions[t];
-        for (int j = threadIdx.x; j < half; j += blockDim.x) sincosf(pos * inv_freq[j], &sin_s[j], &cos_s[j]);
-    }
-    __syncthreads();
-    for (int h = blockIdx.y * ROPE_HEADS_PER_BLOCK + warp; h < head_end; h += 4) {
-        const int kind = h < nq ? 0 : (h < nq + nkv ? 1 : 2);   // 0 q, 1 k, 2 v
-        if (kind != 0 && !write_kv) continue;
-        const Pack<T, VEC> raw = *reinterpret_cast<const Pack<T, VEC>*>(qkv + (size_t)t * heads * d + (size_t)h * d + lane * VEC);
-        float x[VEC];
-        float sum = 0.0f;
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) {
-            x[i] = to_float(raw.v[i]);
-            sum += x[i] * x[i];
-        }
-        const float* norm = kind == 0 ? q_norm : (kind == 1 ? k_norm : nullptr);
-        if (norm) {
-            const float scale = rsqrtf(warp_sum(sum) / (float)d + eps);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) x[i] = x[i] * scale * norm[lane * VEC + i];
-        }
-        if (kind != 2 && inv_freq) {
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                const float partner = __shfl_xor_sync(0xffffffffu, x[i], 16);
-                const int j = (lane & 15) * VEC + i;
-                x[i] = lane < 16 ? x[i] * cos_s[j] - partner * sin_s[j] : x[i] * cos_s[j] + partner * sin_s[j];
-            }
-        }
-        T* dst;
-        if (kind == 0) {
-            dst = q_out + (size_t)t * nq * d + (size_t)h * d;
-        } else {
-            const int slot = slots[t];
-            if (slot < 0) continue;
-            const int page = slot / page_size, off = slot % page_size;
-            const int g = kind == 1 ? h - nq : h - nq - nkv;
-            dst = (kind == 1 ? k_cache : v_cache) + (((size_t)page * nkv + g) * page_size + off) * d;
-        }
-        Pack<T, VEC> packed;
-#pragma unroll
-        for (int i = 0; i < VEC; ++i) packed.v[i] = from_float<T>(x[i]);
-        *reinterpret_cast<Pack<T, VEC>*>(dst + lane * VEC) = packed;
-    }
+    const long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= total) return;
+    float s, c;
+    sincosf((float)positions[i / half] * inv_freq[i % half], &s, &c);
+    out[i] = make_float2(c, s);
 }
 
-template <typename T, int VEC>
-static int launch_rope_vec(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* positions,
-                           const int* slots, const float* q_norm, const float* k_norm, float eps, const float* inv_freq,
-                           int tokens, int nq, int nkv, int page_size, int write_kv, void* stream) {
-    const int heads = nq + 2 * nkv;
-    MRS_LAUNCH((qk_norm_rope_store_vec_kernel<T, VEC>), dim3(tokens, (heads + ROPE_HEADS_PER_BLOCK - 1) / ROPE_HEADS_PER_BLOCK), 128, 0,
-               stream, (const T*)qkv, (T*)q_out, (T*)k_cache, (T*)v_cache, positions, slots, q_norm, k_norm, eps, inv_freq,
-               nq, nkv, page_size, write_kv);
+MRS_EXPORT int mrs_rotation_table(const int* positions, const float* inv_freq, int tokens, int half, float* out, void* stream) {
+    const long long total = (long long)tokens * half;
+    if (total <= 0) return 0;
+    if (!positions || !inv_freq || !out || ((uintptr_t)out & 15)) return MRS_BAD_ARGUMENT;
+    MRS_LAUNCH(rotation_table_kernel, (unsigned)((total + 255) / 256), 256, 0, stream, positions, inv_freq, total, half,
+               reinterpret_cast<float2*>(out));
     MRS_RETURN_LAUNCH_STATUS();
 }
 
+// The same for head sizes 64, 128 and 256.  A lane owns W = VEC / 2 consecutive elements of a head's lower half
+// and the W elements that they rotate with in the upper half (two loads of 8 bytes, 16 for float32 heads of 256),
+// so the rotation needs no other lane; LANES = d / VEC lanes a head add their squares for the norm, and one load
+// of a warp covers 32 / LANES heads.  The cosines and sines come from the step's table (`rotations`
+// [tokens][d / 2] of (cos, sin); null: no rotation), so a warp's loads depend on nothing before them; a warp takes
+// four such loads of a token's heads at a time, all in flight together, and goes on with the grid's stride.
+#define ROPE_LOADS_PER_STEP 4
+#define ROPE_BLOCKS_PER_SM 3
+
+// One head's elements of a lane: RMSNorm over the head (the head's lanes add their squares), the rotation of the
+// pairs (j, j + d / 2), rounding, store.  `weights`: the norm's weights from this lane's first element on, or null.
+template <typename T, int W, int LANES>
+__device__ __forceinline__ void store_normed_rotated(const Pack<T, W>& lo, const Pack<T, W>& hi, T* dst, const float* weights, float eps,
+                                                     bool rotate, const float (&cs)[W], const float (&sn)[W], unsigned mask) {
+    constexpr int half = W * LANES;
+    float a[W], b[W];
+    float sum = 0.0f;
+#pragma unroll
+    for (int i = 0; i < W; ++i) {
+        a[i] = to_float(lo.v[i]);
+        b[i] = to_float(hi.v[i]);
+        sum += a[i] * a[i] + b[i] * b[i];
+    }
+    if (weights) {
+#pragma unroll
+        for (int offset = LANES / 2; offset > 0; offset >>= 1) sum += __shfl_xor_sync(mask, sum, offset);
+        const float scale = rsqrtf(sum / (float)(2 * half) + eps);
+        const Pack<float, W> wa = *reinterpret_cast<const Pack<float, W>*>(weights);
+        const Pack<float, W> wb = *reinterpret_cast<const Pack<float, W>*>(weights + half);
+#pragma unroll
+        for (int i = 0; i < W; ++i) {
+            a[i] = a[i] * scale * wa.v[i];
+            b[i] = b[i] * scale * wb.v[i];
+        }
+    }
+    Pack<T, W> out_lo, out_hi;
+#pragma unroll
+    for (int i = 0; i < W; ++i) {
+        out_lo.v[i] = from_float<T>(rotate ? a[i] * cs[i] - b[i] * sn[i] : a[i]);
+        out_hi.v[i] = from_float<T>(rotate ? b[i] * cs[i] + a[i] * sn[i] : b[i]);
+    }
+    *reinterpret_cast<Pack<T, W>*>(dst) = out_lo;
+    *reinterpret_cast<Pack<T, W>*>(dst + half) = out_hi;
+}
+
+template <typename T, int VEC, int LANES>
+__global__ void __launch_bounds__(256, ROPE_BLOCKS_PER_SM) qk_norm_rope_store_vec_kernel(
+    const T* __restrict__ qkv, T* __restrict__ q_out, T* __restrict__ k_cache, T* __restrict__ v_cache,
+    const int* __restrict__ slots, const float* __restrict__ q_norm, const float* __restrict__ k_norm, float eps,
+    const float2* __restrict__ rotations, int tokens, int nq, int nkv, int page_size, int write_kv) {
+    pdl_launch_dependents();
+    pdl_wait();
+    constexpr int d = VEC * LANES, half = d / 2, W = VEC / 2, G = ROPE_LOADS_PER_STEP, HEADS_PER_LOAD = 32 / LANES;
+    const int lane = threadIdx.x & 31;
+    const int first = lane % LANES * W;                     // this lane's first element in each half of its head
+    // the lanes of this lane's head: they shuffle among themselves, whatever the warp's other heads do
+    const unsigned mask = LANES == 32 ? 0xffffffffu : ((1u << (LANES & 31)) - 1u) << (lane / LANES * LANES);
+    const int heads = nq + 2 * nkv, heads_per_step = HEADS_PER_LOAD * G;
+    const int steps_per_token = (heads + heads_per_step - 1) / heads_per_step;
+    const int steps = tokens * steps_per_token;
+    const int warps = gridDim.x * (blockDim.x >> 5);
+    __shared__ __align__(16) float scales[2][d];            // the head norms' weights of q and k
+    for (int e = threadIdx.x; e < d; e += blockDim.x) {
+        scales[0][e] = q_norm ? q_norm[e] : 1.0f;
+        scales[1][e] = k_norm ? k_norm[e] : 1.0f;
+    }
+    __syncthreads();
+    for (int step = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5); step < steps; step += warps) {
+        const int t = step / steps_per_token;
+        const int h0 = (step - t * steps_per_token) * heads_per_step + lane / LANES;      // this lane's head of the first load
+        const T* row = qkv + (size_t)t * heads * d + first;
+        Pack<T, W> lo[G], hi[G];
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const int h = h0 + g * HEADS_PER_LOAD;
+            if (h < heads && (h < nq || write_kv)) {
+                lo[g] = *reinterpret_cast<const Pack<T, W>*>(row + (size_t)h * d);
+                hi[g] = *reinterpret_cast<const Pack<T, W>*>(row + (size_t)h * d + half);
+            }
+        }
+        float cs[W], sn[W];
+        if (rotations && h0 < nq + nkv) {
+            const Pack<float2, W> angles = *reinterpret_cast<const Pack<float2, W>*>(rotations + (size_t)t * half + first);
+#pragma unroll
+            for (int i = 0; i < W; ++i) cs[i] = angles.v[i].x, sn[i] = angles.v[i].y;
+        }
+        int page = 0, off = 0;
+        bool writes = false;                                // does this token have a place in the cache?
+        if (write_kv && h0 + (G - 1) * HEADS_PER_LOAD >= nq) {
+            const int slot = slots[t];
+            writes = slot >= 0;
+            if (writes) page = slot / page_size, off = slot - page * page_size;
+        }
+#pragma unroll
+        for (int g = 0; g < G; ++g) {
+            const int h = h0 + g * HEADS_PER_LOAD;
+            if (h >= heads) continue;
+            if (h >= nq) {
+                if (!writes) continue;
+                const bool is_k = h < nq + nkv;
+                T* dst = (is_k ? k_cache : v_cache) + (((size_t)page * nkv + (is_k ? h - nq : h - nq - nkv)) * page_size + off) * d + first;
+                if (!is_k) {                                // v: as it came
+                    *reinterpret_cast<Pack<T, W>*>(dst) = lo[g];
+                    *reinterpret_cast<Pack<T, W>*>(dst + half) = hi[g];
+                    continue;
+                }
+                store_normed_rotated<T, W, LANES>(lo[g], hi[g], dst, k_norm ? scales[1] + first : nullptr, eps, rotations != nullptr, cs, sn, mask);
+            } else {
+                store_normed_rotated<T, W, LANES>(lo[g], hi[g], q_out + ((size_t)t * nq + h) * d + first, q_norm ? scales[0] + first : nullptr, eps,
+                                                  rotations != nullptr, cs, sn, mask);
+            }
+        }
+    }
+}
+
+template <typename T, int VEC, int LANES>
+static int launch_rope_vec(const void* qkv, void* q_out, void* k_cache, void* v_cache, const int* slots, const float* q_norm,
+                           const float* k_norm, float eps, const float* rotations, int tokens, int nq, int nkv, int page_size,
+                           int write_kv, void* stream) {
+    const int heads_per_step = 32 / LANES * ROPE_LOADS_PER_STEP;
+    const long long steps = (long long)tokens * ((nq + 2 * nkv + heads_per_step - 1) / heads_per_step);
+    if (steps > 0x7fffffffLL) return MRS_BAD_ARGUMENT;
+    const long long want = (steps + 7) / 8;
+    MRS_LAUNCH((qk_norm_rope_store_vec_kernel<T, VEC, LANES>), (unsigned)(want > 148 * 2 * ROPE_BLOCKS_PER_SM ? 148 * 2 * ROPE_BLOCKS_PER_SM : want), 256, 0, stream, (const T*)qkv,
+               (T*)q_out, (T*)k_cache, (T*)v_cache, slots, q_norm, k_norm, eps, reinterpret_cast<const float2*>(rotations), tokens, nq,
+               nkv, page_size, write_kv);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// `rotations` (or null): the step's table of `mrs_rotation_table` for these positions and frequencies; with it (or without
+// any rotation) heads of 64, 128 and 256 elements take the vector kernel.
 MRS_EXPORT int mrs_qk_norm_rope_store(int is_bf16, const void* qkv, void* q_out, void* k_cache, void* v_cache,
                                       const int* positions, const int* slots, const float* q_norm,
-                                      const float* k_norm, float eps, const float* inv_freq, int tokens,
+                                      const float* k_norm, float eps, const float* inv_freq, const float* rotations, int tokens,
                                       int nq, int nkv, int d, int page_size, int write_kv, void* stream) {
     if (tokens <= 0) return 0;
     if (d <= 0 || d > MRS_MAX_HEAD_DIM || (d & 1)) return MRS_BAD_ARGUMENT;
-    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache) & 31) == 0;
-    if (aligned && (d == 64 || d == 128 || d == 256)) {
-#define MRS_ROPE_VEC(T, V)                                                                                         \
-    return launch_rope_vec<T, V>(qkv, q_out, k_cache, v_cache, positions, slots, q_norm, k_norm, eps, inv_freq, tokens, \
-                                 nq, nkv, page_size, write_kv, stream)
+    const bool aligned = (((uintptr_t)qkv | (uintptr_t)q_out | (uintptr_t)k_cache | (uintptr_t)v_cache | (uintptr_t)rotations) & 31) == 0;
+    if (aligned && (d == 64 || d == 128 || d == 256) && (rotations || !inv_freq)) {
+#define MRS_ROPE_VEC(T, V, L)                                                                                      \
+    return launch_rope_vec<T, V, L>(qkv, q_out, k_cache, v_cache, slots, q_norm, k_norm, eps, rotations, tokens, nq, nkv, \
+                                    page_size, write_kv, stream)
         if (is_bf16) {
-            if (d == 64) MRS_ROPE_VEC(bf16, 2);
-            if (d == 128) MRS_ROPE_VEC(bf16, 4);
-            MRS_ROPE_VEC(bf16, 8);
+            if (d == 64) MRS_ROPE_VEC(bf16, 8, 8);
+            if (d == 128) MRS_ROPE_VEC(bf16, 8, 16);
+            MRS_ROPE_VEC(bf16, 8, 32);
         } else {
-            if (d == 64) MRS_ROPE_VEC(float, 2);
-            if (d == 128) MRS_ROPE_VEC(float, 4);
-            MRS_ROPE_VEC(float, 8);
+            if (d == 64) MRS_ROPE_VEC(float, 4, 16);
+            if (d == 128) MRS_ROPE_VEC(float, 4, 32);
+            MRS_ROPE_VEC(float, 8, 32);
         }
 #undef MRS_ROPE_VEC
     }

@@ -40,3 +40,5 @@ class StepContext:
     # labels, and the parts take the kernels that leave those tensors (no product with a fused epilogue).
     observe: object = None
     label: str = ""                    # the running layer's label ("layer3"), set by the model while observing
+    # what the parts of one step share (the rotations' cosines and sines); the model empties it when a step begins
+    shared: dict = field(default_factory=dict)

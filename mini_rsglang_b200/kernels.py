@@ -20,8 +20,9 @@ _SIGNATURES = {
     "mrs_embed": [_c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
     "mrs_add_rmsnorm": [_c_int, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_rmsnorm": [_c_int, _c_vp, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_vp],
-    "mrs_qk_norm_rope_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp,
+    "mrs_qk_norm_rope_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_vp,
                                _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp],
+    "mrs_rotation_table": [_c_vp, _c_vp, _c_int, _c_int, _c_vp, _c_vp],
     "mrs_silu_mul": [_c_int, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_attention_simt": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int,
                            _c_int, _c_int, _c_float, _c_int, _c_vp],
@@ -134,12 +135,27 @@ def rmsnorm(x: torch.Tensor, weight: torch.Tensor, eps: float, out: torch.Tensor
                                  x.numel() // width, width, _stream()), "rmsnorm")
 
 
+def rotation_table(positions: torch.Tensor, inv_freq: torch.Tensor) -> torch.Tensor:
+    """[tokens, d / 2, 2] float32: (cos, sin) of position * inv_freq, computed once a step for every layer that
+    rotates by the same frequencies."""
+    tokens, half = positions.shape[0], inv_freq.shape[0]
+    _need(positions, torch.int32, "positions", (tokens,))
+    _need(inv_freq, torch.float32, "inv_freq", (half,))
+    out = torch.empty((tokens, half, 2), dtype=torch.float32, device=positions.device)
+    _check(library().mrs_rotation_table(positions.data_ptr(), inv_freq.data_ptr(), tokens, half, out.data_ptr(), _stream()),
+           "rotation_table")
+    return out
+
+
 def qk_norm_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
                        v_cache: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor | None,
                        q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
-                       inv_freq: torch.Tensor | None, nq: int, nkv: int, d: int, page_size: int) -> None:
+                       inv_freq: torch.Tensor | None, nq: int, nkv: int, d: int, page_size: int,
+                       rotations: torch.Tensor | None = None) -> None:
     """Per-head norm of q and k, rotary of q and k, q to `q_out`, k and v into the paged cache
-    ([pages, nkv, page_size, d]) at `slots`.  Without caches only q is produced."""
+    ([pages, nkv, page_size, d]) at `slots`.  Without caches only q is produced.  `rotations`: the step's
+    `rotation_table` for these positions and frequencies, if the caller has one; heads of 64, 128 and 256
+    elements read their cosines and sines from it (and get one made here otherwise)."""
     tokens = qkv.shape[0]
     write_kv = k_cache is not None
     _need(qkv, None, "qkv", (tokens, (nq + 2 * nkv) * d))
@@ -156,9 +172,17 @@ def qk_norm_rope_store(qkv: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Te
             _need(w, torch.float32, name, (d,))
     if inv_freq is not None:
         _need(inv_freq, torch.float32, "inv_freq", (d // 2,))
+        if d in (64, 128, 256):
+            if rotations is None:
+                rotations = rotation_table(positions, inv_freq)
+            _need(rotations, torch.float32, "rotations", (tokens, d // 2, 2))
+        else:
+            rotations = None
+    else:
+        rotations = None
     _check(library().mrs_qk_norm_rope_store(_is_bf16(qkv.dtype), qkv.data_ptr(), q_out.data_ptr(), _ptr(k_cache),
                                             _ptr(v_cache), positions.data_ptr(), _ptr(slots), _ptr(q_norm),
-                                            _ptr(k_norm), float(eps), _ptr(inv_freq), tokens, nq, nkv, d,
+                                            _ptr(k_norm), float(eps), _ptr(inv_freq), _ptr(rotations), tokens, nq, nkv, d,
                                             page_size, int(write_kv), _stream()), "qk_norm_rope_store")
 
 

@@ -45,6 +45,7 @@ class Model:
         """Runs the step's tokens through every layer; float32 logits [wanted, vocab], or None
         when no logits are wanted (the head is then skipped, as in the reference,
         crates/engine/src/lib.rs:132-135)."""
+        ctx.shared.clear()           # a context may be run again (a recorded step): nothing of the run before is kept
         stream = self.embedding.forward(ctx)
         if ctx.observe:
             ctx.observe("embedding", stream)

@@ -208,7 +208,8 @@ class GroupedQueryAttention(Mixer):
             qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
             ctx.slots[group] if write_cache else None,
             self.q_norm.weight if self.q_norm else None, self.k_norm.weight if self.k_norm else None, eps,
-            self.position.tables()["inv_freq"], self.nq, self.nkv, self.d, cache.k.shape[2])
+            self.position.tables()["inv_freq"], self.nq, self.nkv, self.d, cache.k.shape[2],
+            rotations=self.position.rotations(ctx) if self.d in (64, 128, 256) else None)
         out = torch.empty_like(q)
         paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
         if observing(ctx):

@@ -14,6 +14,7 @@ Interfaces (all tensors on the device; `ctx` is an `engine.context.StepContext`)
       residual float32 [T, width] (+ delta of the engine's dtype), normalised; the sum is
       written back unless told otherwise; `rows` picks source rows
   PositionEncoding.tables() -> dict                what the mixer's kernel needs (inv_freq)
+  PositionEncoding.rotations(ctx) -> table | None  optional: (cos, sin) of the step's tokens, made once a step
   Mixer.forward(h, ctx, cache, write_cache) -> y   h, y [T, width]; `cache` is the entry of
       `CacheStorage` that this run of the layer reads (and writes when `write_cache`)
   FeedForward.forward(h, ctx) -> y
@@ -157,6 +158,11 @@ class Norm(Part):
 class PositionEncoding(Part):
     def tables(self) -> dict[str, Any]:
         raise NotImplementedError
+
+    def rotations(self, ctx):
+        """The cosines and sines of the step's tokens, [T, head_dim / 2, 2] float32, if the encoding keeps them
+        for all of a step's layers; None: the mixer's kernel computes them from `tables()`."""
+        return None
 
 
 class Mixer(Part):

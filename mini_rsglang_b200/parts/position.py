@@ -1,10 +1,14 @@
 """Rotary position encoding, split-half pairing (j, j + d/2), every dimension rotary
 (reference: crates/kernels/src/ops.cu:79-90).  The part owns the table of inverse
-frequencies; the mixer's kernel computes angle = position * f_j and the rotation in float32."""
+frequencies; angle = position * f_j, its cosine and sine and the rotation are float32.  The
+cosines and sines of a step's tokens are computed once and shared by every layer that rotates
+by the same frequencies (`rotations`); kernels that have the angles at hand compute them
+themselves from `tables()`."""
 from __future__ import annotations
 
 import torch
 
+from .. import kernels
 from .base import POSITION_ENCODINGS, PositionEncoding
 
 
@@ -30,6 +34,18 @@ class RotaryPosition(PositionEncoding):
     def tables(self):
         return {"inv_freq": self.inv_freq}
 
+    def rotations(self, ctx):
+        """[tokens, head_dim / 2, 2] float32 (cos, sin) for the step's positions; kept in `ctx.shared` for the
+        step's other layers (the model empties it when a step begins)."""
+        shared = getattr(ctx, "shared", None)
+        key = ("rotations", self.head_dim, self.theta)
+        if shared is not None and key in shared:
+            return shared[key]
+        table = kernels.rotation_table(ctx.positions, self.inv_freq)
+        if shared is not None:
+            shared[key] = table
+        return table
+
 
 @POSITION_ENCODINGS.register("none")
 class NoPosition(PositionEncoding):
@@ -38,3 +54,6 @@ class NoPosition(PositionEncoding):
 
     def tables(self):
         return {"inv_freq": None}
+
+    def rotations(self, ctx):
+        return None

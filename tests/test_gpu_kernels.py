@@ -149,6 +149,42 @@ def test_qk_norm_rope_store(dtype, nq, nkv, d, page):
                                    positions[:1], None, None, None, 0.0, None, 1, 1, 258, page)
 
 
+def test_rotation_table_and_many_tokens():
+    """The step's table of cosines and sines equals float32 cos and sin of position * frequency, and the kernel that
+    reads it gives the same bits with a table handed in as with one it makes itself; 5,000 tokens with 11 heads (the
+    warps go around the grid more than once, the last four heads of a token are three), some tokens without a slot."""
+    nq, nkv, d, page, eps, theta, tokens = 5, 3, 128, 16, 1e-6, 1e6, 5000
+    g = torch.Generator().manual_seed(5)
+    positions = torch.randint(0, 40000, (tokens,), generator=g, dtype=torch.int32).to(DEV)
+    inv_freq = RotaryPosition.inverse_frequencies(d, theta).to(DEV)
+    table = kernels.rotation_table(positions, inv_freq)
+    angles = positions.float()[:, None] * inv_freq[None, :]                    # float32 products, as in the kernel
+    close(table[..., 0], torch.cos(angles.double()), torch.float32, "cosines")
+    close(table[..., 1], torch.sin(angles.double()), torch.float32, "sines")
+    qkv = torch.randn(tokens, (nq + 2 * nkv) * d, generator=g).to(torch.bfloat16).to(DEV)
+    q_w, k_w = (1 + 0.1 * torch.randn(d, generator=g)).to(DEV), (1 + 0.1 * torch.randn(d, generator=g)).to(DEV)
+    pages = tokens // page + 2
+    slots = torch.randperm(pages * page, generator=g)[:tokens].to(torch.int32)
+    slots[::7] = -1
+    outs = []
+    for rotations in (None, table):
+        q_out = torch.empty(tokens, nq * d, device=DEV, dtype=torch.bfloat16)
+        kc = torch.zeros(pages, nkv, page, d, device=DEV, dtype=torch.bfloat16)
+        vc = torch.zeros_like(kc)
+        kernels.qk_norm_rope_store(qkv, q_out, kc, vc, positions, slots.to(DEV), q_w, k_w, eps, inv_freq, nq, nkv, d, page,
+                                   rotations=rotations)
+        outs.append((q_out, kc, vc))
+    assert all(torch.equal(a, b) for a, b in zip(*outs))
+    q, k, v = plain_qk(qkv, positions, q_w, k_w, eps, theta, nq, nkv, d)
+    q_out, kc, vc = outs[0]
+    close(q_out.view(tokens, nq, d), q, torch.bfloat16, "q")
+    keep = (slots >= 0).nonzero().flatten()
+    slot = slots[keep].long()
+    close(kc.cpu()[slot // page, :, slot % page], k[keep], torch.bfloat16, "k in the cache")
+    assert torch.equal(vc.cpu()[slot // page, :, slot % page].double(), v[keep].double())
+    assert kc.count_nonzero().item() <= keep.numel() * nkv * d and vc.count_nonzero().item() <= keep.numel() * nkv * d
+
+
 class PagedCase:
     """Requests with scattered pages; builds the kernel's inputs and the plain answer."""
 
