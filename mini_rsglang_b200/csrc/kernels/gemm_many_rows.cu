@@ -1,23 +1,19 @@
-// Matrix products for many rows (prompt portions) on the tcgen05 tensor cores, bfloat16 in, float32
-// accumulation, with what follows the product in its epilogue:
-//   gated   out[T, N / 2] = silu(x . gate^T) * (x . up^T)                        (the feed-forward's first half)
-//   heads   the fused q/k/v projection of an attention with heads of 128 elements: per head the RMSNorm of
-//           q and k, their rotation by the tokens' positions, q to its tensor, k and v into the cache pages.
+// The feed-forward's first product for many rows (prompt portions) on the tcgen05 tensor cores, bfloat16 in, float32
+// accumulation, with the activation in its epilogue:
+//   out[T, N / 2] = silu(x . gate^T) * (x . up^T)
 //
 // The library's product for these sizes runs near the tensor cores' peak, but it leaves its result in
-// memory, which a second kernel reads again (the gate/up product of 2,048 tokens: 150 MB and 34 us a layer;
-// q/k/v: 50 MB and 23 us).  Here a CTA computes a tile of 128 tokens x 256 weight rows into one of two
-// accumulators in tensor memory, and four warps turn a finished accumulator into the final values and store
-// them while the next tile's MMAs run:
+// memory, which a second kernel reads again (2,048 tokens: 150 MB and 34 us a layer).  Here a CTA computes a
+// tile of 128 tokens x 256 weight rows into one of two accumulators in tensor memory, and four warps turn a
+// finished accumulator into the final values and store them while the next tile's MMAs run:
 //   warp 0   fetches 128 x 64 token tiles and 256 x 64 weight tiles with bulk tensor copies (TMA,
 //            128-byte swizzle) into a ring of stages;
 //   warp 1   one thread issues tcgen05.mma (M 128, N 256, K 16) on the stages;
 //   warps 2-5 a thread a token: the row's 256 sums from tensor memory.  A tile holds two blocks of 64 gate
-//            and 64 up rows (the weights are stored so), or two heads: everything the epilogue needs of a
-//            row (a head's sum of squares, a rotation's partner 64 columns away) lies in the thread's own registers.
+//            and 64 up rows (the weights are stored so), so a thread has both factors of its outputs.
 // CTAs are persistent; the tiles that share a weight tile are taken by neighbouring CTAs at the same
 // time, so the weights come from HBM once.  Every wait is bounded (tma.cuh).
-//   (reference: cuBLAS and kernels of their own, crates/models/src/qwen3.rs:178-198, 255-261; ops.cu:66-98)
+//   (reference: cuBLAS and a kernel of its own, crates/models/src/qwen3.rs:255-261; ops.cu:91-94)
 #include "tcgen05.cuh"
 
 namespace {
@@ -30,28 +26,10 @@ constexpr int STAGES = 4;
 constexpr int THREADS = 192;
 constexpr int A_BYTES = BM * BK * 2, B_BYTES = BN * BK * 2, STAGE_BYTES = A_BYTES + B_BYTES;
 constexpr int TMEM_COLUMNS = 2 * BN;
-constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16 + 3 * 128 * sizeof(float);
+constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16;
 
-enum { EPI_GATED = 0, EPI_HEADS = 1 };
-
-// What the head epilogue needs beside the product (as in gemm_tc.cu).
-struct HeadEpilogue {
-    bf16* q_out;             // [T, nq, 128]
-    bf16* k_cache;           // [pages, nkv, page_size, 128]
-    bf16* v_cache;
-    const int* positions;    // [T]
-    const int* slots;        // [T] page * page_size + offset, < 0 or null: no write
-    const float* q_norm;     // [128] or null
-    const float* k_norm;
-    const float* inv_freq;   // [64] or null
-    float eps;
-    int nq, nkv, page_size;
-};
-
-template <int EPI>
 __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
-    const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, bf16* __restrict__ out, int T, int N, int K,
-    const HeadEpilogue heads) {
+    const __grid_constant__ CUtensorMap x_map, const __grid_constant__ CUtensorMap w_map, bf16* __restrict__ out, int T, int N, int K) {
     extern __shared__ unsigned char smem_raw[];
     unsigned char* smem = reinterpret_cast<unsigned char*>((reinterpret_cast<uintptr_t>(smem_raw) + 1023) & ~uintptr_t(1023));
     uint64_t* full = reinterpret_cast<uint64_t*>(smem + STAGES * STAGE_BYTES);
@@ -59,9 +37,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
     uint64_t* acc_full = empty + STAGES;
     uint64_t* acc_empty = acc_full + 2;
     uint32_t* tmem_slot = reinterpret_cast<uint32_t*>(acc_empty + 2);
-    float* q_norm_s = reinterpret_cast<float*>(tmem_slot + 4);        // the head norms' scales and the rotation's frequencies
-    float* k_norm_s = q_norm_s + 128;
-    float* inv_freq_s = k_norm_s + 128;
 
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (K + BK - 1) / BK;
@@ -82,12 +57,6 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
     if (warp == 1) {
         tmem_alloc(tmem_slot, TMEM_COLUMNS);
         tmem_relinquish_alloc_permit();
-    }
-    if (EPI == EPI_HEADS && threadIdx.x >= 64) {
-        const int j = threadIdx.x - 64;
-        q_norm_s[j] = heads.q_norm ? heads.q_norm[j] : 1.0f;
-        k_norm_s[j] = heads.k_norm ? heads.k_norm[j] : 1.0f;
-        if (j < 64) inv_freq_s[j] = heads.inv_freq ? heads.inv_freq[j] : 0.0f;
     }
     tcgen05_fence_before_sync();
     __syncthreads();
@@ -150,85 +119,27 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
             tcgen05_fence_after_sync();
             const uint32_t acc = tmem_base + ((uint32_t)(quarter * 32) << 16) + buffer * BN;
             const int token = m0 + row;
-            if (EPI == EPI_HEADS) {
-                // the tile's two heads, one after the other: 128 sums of this token, norm, rotation, store
-                const bool live = token < T;
-                const float position = live ? (float)heads.positions[token] : 0.0f;
-                const int slot = live && heads.slots ? heads.slots[token] : -1;
-#pragma unroll 1
-                for (int h = 0; h < BN / 128; ++h) {
-                    const int head = n0 / 128 + h;
-                    float v[128];
-                    __syncwarp();                        // the loads from tensor memory are collective; lanes leave the loop's body early
-#pragma unroll
-                    for (int c = 0; c < 128; c += 32) tmem_load_32_async(acc + h * 128 + c, v + c);
-                    tmem_load_wait();
-                    if (!live || head >= heads.nq + 2 * heads.nkv) continue;
-                    const int kind = head < heads.nq ? 0 : (head < heads.nq + heads.nkv ? 1 : 2);      // q, k, v
-                    if (kind != 2) {
-                        const float* scales = kind == 0 ? q_norm_s : k_norm_s;
-                        if (kind == 0 ? heads.q_norm != nullptr : heads.k_norm != nullptr) {
-                            float parts[4] = {0.0f, 0.0f, 0.0f, 0.0f};
-#pragma unroll
-                            for (int j = 0; j < 128; ++j) parts[j & 3] += v[j] * v[j];
-                            const float scale = rsqrtf(((parts[0] + parts[1]) + (parts[2] + parts[3])) / 128.0f + heads.eps);
-#pragma unroll
-                            for (int j = 0; j < 128; ++j) v[j] = v[j] * scale * scales[j];
-                        }
-                        if (heads.inv_freq) {
-#pragma unroll
-                            for (int j = 0; j < 64; ++j) {
-                                float sn, cs;
-                                sincosf(position * inv_freq_s[j], &sn, &cs);
-                                const float a = v[j], b = v[j + 64];
-                                v[j] = a * cs - b * sn;
-                                v[j + 64] = b * cs + a * sn;
-                            }
-                        }
-                    }
-                    bf16* dst;
-                    if (kind == 0) {
-                        dst = heads.q_out + ((size_t)token * heads.nq + head) * 128;
-                    } else {
-                        if (slot < 0) continue;
-                        const int page = slot / heads.page_size, off = slot % heads.page_size;
-                        const int g = kind == 1 ? head - heads.nq : head - heads.nq - heads.nkv;
-                        dst = (kind == 1 ? heads.k_cache : heads.v_cache) + (((size_t)page * heads.nkv + g) * heads.page_size + off) * 128;
-                    }
-#pragma unroll
-                    for (int j = 0; j < 128; j += 8) {
-                        uint32_t w[4];
-#pragma unroll
-                        for (int p = 0; p < 4; ++p) {
-                            __nv_bfloat162 pair = __floats2bfloat162_rn(v[j + 2 * p], v[j + 2 * p + 1]);
-                            w[p] = *reinterpret_cast<uint32_t*>(&pair);
-                        }
-                        *reinterpret_cast<uint4*>(dst + j) = make_uint4(w[0], w[1], w[2], w[3]);
-                    }
-                }
-            } else {
             bf16* dst = out + (size_t)token * half_n + (n0 >> 1);
 #pragma unroll
-                for (int block = 0; block < BN / 128; ++block) {          // 64 gate columns, then their 64 up columns
+            for (int block = 0; block < BN / 128; ++block) {          // 64 gate columns, then their 64 up columns
 #pragma unroll
-                    for (int c = 0; c < 64; c += 32) {
-                        float g[32], u[32];
-                        tmem_load_32_async(acc + block * 128 + c, g);
-                        tmem_load_32_async(acc + block * 128 + 64 + c, u);
-                        tmem_load_wait();
-                        if (token < T && n0 + block * 128 < N) {
+                for (int c = 0; c < 64; c += 32) {
+                    float g[32], u[32];
+                    tmem_load_32_async(acc + block * 128 + c, g);
+                    tmem_load_32_async(acc + block * 128 + 64 + c, u);
+                    tmem_load_wait();
+                    if (token < T && n0 + block * 128 < N) {
 #pragma unroll
-                            for (int e = 0; e < 32; e += 8) {
-                                uint32_t w[4];
+                        for (int e = 0; e < 32; e += 8) {
+                            uint32_t w[4];
 #pragma unroll
-                                for (int p = 0; p < 4; ++p) {
-                                    const float g0 = g[e + 2 * p], g1 = g[e + 2 * p + 1];
-                                    __nv_bfloat162 pair = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u[e + 2 * p],
-                                                                                g1 / (1.0f + __expf(-g1)) * u[e + 2 * p + 1]);
-                                    w[p] = *reinterpret_cast<uint32_t*>(&pair);
-                                }
-                                *reinterpret_cast<uint4*>(dst + block * 64 + c + e) = make_uint4(w[0], w[1], w[2], w[3]);
+                            for (int p = 0; p < 4; ++p) {
+                                const float g0 = g[e + 2 * p], g1 = g[e + 2 * p + 1];
+                                __nv_bfloat162 pair = __floats2bfloat162_rn(g0 / (1.0f + __expf(-g0)) * u[e + 2 * p],
+                                                                            g1 / (1.0f + __expf(-g1)) * u[e + 2 * p + 1]);
+                                w[p] = *reinterpret_cast<uint32_t*>(&pair);
                             }
+                            *reinterpret_cast<uint4*>(dst + block * 64 + c + e) = make_uint4(w[0], w[1], w[2], w[3]);
                         }
                     }
                 }
@@ -246,17 +157,16 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
     }
 }
 
-template <int EPI>
-int launch(const void* x_map, const void* w_map, void* out, int T, int N, int K, int ctas, void* stream, const HeadEpilogue& heads) {
+int launch(const void* x_map, const void* w_map, void* out, int T, int N, int K, int ctas, void* stream) {
     static bool configured = false;
     if (!configured) {
-        cudaError_t e = cudaFuncSetAttribute(gemm_many_rows_kernel<EPI>, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
+        cudaError_t e = cudaFuncSetAttribute(gemm_many_rows_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
         if (e != cudaSuccess) return (int)e;
         configured = true;
     }
     const int tiles = ((T + BM - 1) / BM) * ((N + BN - 1) / BN);
-    MRS_LAUNCH(gemm_many_rows_kernel<EPI>, ctas < tiles ? ctas : tiles, THREADS, SMEM_BYTES, stream, *reinterpret_cast<const CUtensorMap*>(x_map),
-               *reinterpret_cast<const CUtensorMap*>(w_map), (bf16*)out, T, N, K, heads);
+    MRS_LAUNCH(gemm_many_rows_kernel, ctas < tiles ? ctas : tiles, THREADS, SMEM_BYTES, stream, *reinterpret_cast<const CUtensorMap*>(x_map),
+               *reinterpret_cast<const CUtensorMap*>(w_map), (bf16*)out, T, N, K);
     MRS_RETURN_LAUNCH_STATUS();
 }
 
@@ -278,22 +188,7 @@ MRS_EXPORT int mrs_gemm_many_rows_map(const void* base, long long rows, long lon
 MRS_EXPORT int mrs_gemm_gated_rows(const void* x_map, const void* w_map, void* out, int T, int N, int K, int ctas, void* stream) {
     if (T <= 0 || N <= 0) return 0;
     if (K <= 0 || K % 8 || N % 128 || ctas < 1 || !x_map || !w_map || !out || ((uintptr_t)out & 15)) return MRS_BAD_ARGUMENT;
-    return launch<EPI_GATED>(x_map, w_map, out, T, N, K, ctas, stream, HeadEpilogue{});
-}
-
-// The fused q/k/v projection of an attention with heads of 128 elements: the product, then per head the RMSNorm of q
-// and k (scales `q_norm`, `k_norm`, or null), the rotation of q and k (`inv_freq` [64] or null; pairs (j, j + 64)), q
-// into `q_out` [T, nq, 128] and k, v into the cache pages [pages, nkv, page_size, 128] at `slots` (null: nothing is
-// written).  `w_map` covers the weights [(nq + 2 nkv) * 128, K], q heads first, then k, then v.
-MRS_EXPORT int mrs_gemm_heads_rows(const void* x_map, const void* w_map, void* q_out, void* k_cache, void* v_cache, const int* positions,
-                                   const int* slots, const float* q_norm, const float* k_norm, const float* inv_freq, float eps,
-                                   int nq, int nkv, int page_size, int T, int K, int ctas, void* stream) {
-    if (T <= 0) return 0;
-    if (K <= 0 || K % 8 || ctas < 1 || nq <= 0 || nkv <= 0 || page_size <= 0 || !x_map || !w_map || !q_out || !positions ||
-        (slots && (!k_cache || !v_cache)) || ((uintptr_t)q_out & 15) || ((uintptr_t)k_cache & 15) || ((uintptr_t)v_cache & 15))
-        return MRS_BAD_ARGUMENT;
-    HeadEpilogue heads{(bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots, q_norm, k_norm, inv_freq, eps, nq, nkv, page_size};
-    return launch<EPI_HEADS>(x_map, w_map, nullptr, T, (nq + 2 * nkv) * 128, K, ctas, stream, heads);
+    return launch(x_map, w_map, out, T, N, K, ctas, stream);
 }
 
 MRS_EXPORT int mrs_gemm_many_rows_take_error(unsigned int* word) { return mrs_take_error_word(word); }

@@ -726,7 +726,7 @@ def gemm_tc_qkv_heads(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor
 
 
 # ------------------------------------------------------------------------------------------------
-# tcgen05 products for many rows (prompt portions) with what follows them in the epilogue
+# the tcgen05 gate/up product for many rows (prompt portions) with the activation in its epilogue
 # ------------------------------------------------------------------------------------------------
 _many_rows_lib = None
 _many_rows_maps: dict[tuple, tuple] = {}
@@ -734,11 +734,6 @@ _many_rows_maps: dict[tuple, tuple] = {}
 # 2,048 rows, 418 against 429 us at 3,072, 550 against 646 us at 4,096; below 2,048 rows the library's pair is ahead
 # (1,536: 221 against 217 us; 512: 90 against 83 us: the 128 x 256 tiles fill the SMs' last round badly).
 GEMM_GATED_ROWS_MIN = 2048
-# The fused q/k/v projection (N 6144: 24 x 16 tiles at 2,048 rows fill 148 SMs for 2.6 rounds, and its epilogue is the
-# heavier one) against the library's product followed by `qk_norm_rope_store`: 97 against 90 us at 2,048 rows, 163
-# against 172 us at 4,096.
-GEMM_HEADS_ROWS_MIN = 4096
-
 
 def gemm_many_rows_library() -> ctypes.CDLL:
     global _many_rows_lib
@@ -750,8 +745,6 @@ def gemm_many_rows_library() -> ctypes.CDLL:
         lib.mrs_gemm_many_rows_map.restype = _c_int
         lib.mrs_gemm_gated_rows.argtypes = [_c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_int, _c_vp]
         lib.mrs_gemm_gated_rows.restype = _c_int
-        lib.mrs_gemm_heads_rows.argtypes = [_c_vp] * 10 + [_c_float, _c_int, _c_int, _c_int, _c_int, _c_int, _c_int, _c_vp]
-        lib.mrs_gemm_heads_rows.restype = _c_int
         lib.mrs_gemm_many_rows_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         lib.mrs_gemm_many_rows_take_error.restype = _c_int
         lib.mrs_gemm_many_rows_error_string.argtypes = [_c_int]
@@ -803,46 +796,6 @@ def gemm_gated_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) ->
     del x_keep
     if code != 0:
         raise BackendError(f"gemm_gated_rows: {lib.mrs_gemm_many_rows_error_string(code).decode()} (code {code})")
-
-
-def gemm_heads_rows(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
-                    v_cache: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor | None,
-                    q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
-                    inv_freq: torch.Tensor | None, nq: int, nkv: int) -> None:
-    """The fused q/k/v projection for any number of rows and heads of 128 elements, with the per-head norms, the
-    rotation and the cache write in the product's epilogue (`gemm_tc_qkv_heads` for many rows)."""
-    global launch_count
-    t, k = x.shape
-    d = 128
-    _need(x, torch.bfloat16, "qkv input")
-    _need(weight, torch.bfloat16, "qkv weight", ((nq + 2 * nkv) * d, k))
-    _need(q_out, torch.bfloat16, "q_out", (t, nq * d))
-    _need(positions, torch.int32, "positions", (t,))
-    page_size = 1
-    if slots is not None:
-        _need(slots, torch.int32, "slots", (t,))
-        _need(k_cache, torch.bfloat16, "k cache")
-        _need(v_cache, torch.bfloat16, "v cache", tuple(k_cache.shape))
-        if tuple(k_cache.shape[1:]) != (nkv, k_cache.shape[2], d):
-            raise InvalidRequest(f"cache shape {tuple(k_cache.shape)} does not match heads/head_dim")
-        page_size = k_cache.shape[2]
-    for w, name in ((q_norm, "q_norm"), (k_norm, "k_norm")):
-        if w is not None:
-            _need(w, torch.float32, name, (d,))
-    if inv_freq is not None:
-        _need(inv_freq, torch.float32, "inv_freq", (d // 2,))
-    if k % 8 or x.data_ptr() % 16 or weight.data_ptr() % 16:
-        raise InvalidRequest("the fused projection needs K a multiple of 8 and 16-byte alignment")
-    lib = gemm_many_rows_library()
-    x_keep, x_map, w_map = _many_rows_maps_of(lib, x, weight)
-    launch_count += 1
-    code = lib.mrs_gemm_heads_rows(x_map, w_map, q_out.data_ptr(), _ptr(k_cache) if slots is not None else None,
-                                   _ptr(v_cache) if slots is not None else None, positions.data_ptr(), _ptr(slots), _ptr(q_norm),
-                                   _ptr(k_norm), _ptr(inv_freq), float(eps), nq, nkv, page_size, t, k,
-                                   torch.cuda.get_device_properties(x.device).multi_processor_count, _stream())
-    del x_keep
-    if code != 0:
-        raise BackendError(f"gemm_heads_rows: {lib.mrs_gemm_many_rows_error_string(code).decode()} (code {code})")
 
 
 # ------------------------------------------------------------------------------------------------

@@ -12,7 +12,7 @@ import torch
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, Prenormed, observing, plain
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, Prenormed, observing
 from .linear import few_rows, linear
 
 
@@ -187,17 +187,6 @@ class GroupedQueryAttention(Mixer):
                 ctx.positions, ctx.slots[group] if write_cache else None, self.q_norm.weight if self.q_norm else None,
                 self.k_norm.weight if self.k_norm else None, eps, self.position.tables()["inv_freq"], self.nq, self.nkv,
                 row_sums=h.row_sums if prenormed else None)
-            out = torch.empty_like(q)
-            paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
-            return linear(out, self.o, into=into)
-        h = plain(h)
-        if (self.d == 128 and tokens >= kernels.GEMM_HEADS_ROWS_MIN and self.runtime.is_bf16 and not observing(ctx)
-                and kernels.gemm_gated_rows_supported(h, self.qkv)):
-            # many rows, heads of 128: the tcgen05 product for many rows with the same epilogue
-            kernels.gemm_heads_rows(
-                h, self.qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
-                ctx.slots[group] if write_cache else None, self.q_norm.weight if self.q_norm else None,
-                self.k_norm.weight if self.k_norm else None, eps, self.position.tables()["inv_freq"], self.nq, self.nkv)
             out = torch.empty_like(q)
             paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
             return linear(out, self.o, into=into)

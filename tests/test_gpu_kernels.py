@@ -545,37 +545,6 @@ def test_gemm_tc_qkv_heads(m, nq, nkv, k, page):
     assert kc.count_nonzero().item() == 0
 
 
-@pytest.mark.parametrize("t,nq,nkv,k,page", [(1, 2, 1, 64, 8), (130, 3, 3, 520, 4), (300, 8, 2, 1024, 32), (2048, 32, 8, 4096, 16)])
-def test_gemm_heads_rows(t, nq, nkv, k, page):
-    """The fused q/k/v projection for many rows (two heads a tile of 128 tokens): against the plain functions on the
-    unrounded product; an odd number of heads (a tile with one head), tokens that end inside a tile, a row without a slot."""
-    d, eps, theta = 128, 1e-6, 1e6
-    pages = t // page + 3
-    g = torch.Generator().manual_seed(t + nq + k)
-    x = torch.randn(t, k, generator=g).to(torch.bfloat16)
-    w = (torch.randn((nq + 2 * nkv) * d, k, generator=g) / k ** 0.5).to(torch.bfloat16)
-    q_w, k_w = 1 + 0.1 * torch.randn(d, generator=g), 1 + 0.1 * torch.randn(d, generator=g)
-    positions = torch.randint(0, 30000, (t,), generator=g, dtype=torch.int32)
-    slots = torch.randperm(pages * page, generator=g)[:t].to(torch.int32)
-    slots[t // 2] = -1 if t > 1 else slots[0]
-    inv_freq = RotaryPosition.inverse_frequencies(d, theta)
-    q_out = torch.full((t, nq * d), float("nan"), dtype=torch.bfloat16, device=DEV)
-    kc = torch.zeros(pages, nkv, page, d, dtype=torch.bfloat16, device=DEV)
-    vc = torch.zeros_like(kc)
-    kernels.gemm_heads_rows(x.to(DEV), w.to(DEV), q_out, kc, vc, positions.to(DEV), slots.to(DEV), q_w.to(DEV), k_w.to(DEV),
-                            eps, inv_freq.to(DEV), nq, nkv)
-    torch.cuda.synchronize()
-    kernels.check_device_errors()
-    qkv = (x.double() @ w.double().T).float()
-    q, kk, v = plain_qk(qkv.to(DEV), positions.to(DEV), q_w.to(DEV), k_w.to(DEV), eps, theta, nq, nkv, d)
-    close(q_out.view(t, nq, d), q, torch.bfloat16, "q")
-    keep = (slots >= 0).nonzero().flatten()
-    slot = slots[keep].long()
-    close(kc.cpu()[slot // page, :, slot % page], kk[keep], torch.bfloat16, "k in the cache")
-    close(vc.cpu()[slot // page, :, slot % page], v[keep], torch.bfloat16, "v in the cache")
-    assert kc.count_nonzero().item() <= keep.numel() * nkv * d and vc.count_nonzero().item() <= keep.numel() * nkv * d
-
-
 @pytest.mark.parametrize("m,n,k", [(1, 128, 64), (8, 4096, 4096), (5, 136, 192), (8, 1000, 12288), (19, 520, 1024), (32, 256, 320)])
 def test_gemm_tc_adds_to_the_stream_and_prepares_the_next_norm(m, n, k):
     """The product whose epilogue adds to the residual stream: stream += bfloat16(x . w^T), out = stream * the next
