@@ -18,6 +18,7 @@ class RotaryPosition(PositionEncoding):
         super().__init__(prefix)
         self.head_dim, self.theta = int(head_dim), float(theta)
         self.inv_freq: torch.Tensor | None = None
+        self.shared_key = None
 
     @staticmethod
     def inverse_frequencies(head_dim: int, theta: float) -> torch.Tensor:
@@ -29,7 +30,9 @@ class RotaryPosition(PositionEncoding):
 
     def bind(self, tensors, runtime):
         super().bind(tensors, runtime)
-        self.inv_freq = self.inverse_frequencies(self.head_dim, self.theta).to(runtime.device)
+        frequencies = self.inverse_frequencies(self.head_dim, self.theta)
+        self.inv_freq = frequencies.to(runtime.device)
+        self.shared_key = ("rotations", frequencies.numpy().tobytes())     # layers with the same frequencies share a step's table
 
     def tables(self):
         return {"inv_freq": self.inv_freq}
@@ -38,12 +41,11 @@ class RotaryPosition(PositionEncoding):
         """[tokens, head_dim / 2, 2] float32 (cos, sin) for the step's positions; kept in `ctx.shared` for the
         step's other layers (the model empties it when a step begins)."""
         shared = getattr(ctx, "shared", None)
-        key = ("rotations", self.head_dim, self.theta)
-        if shared is not None and key in shared:
-            return shared[key]
+        if shared is not None and self.shared_key in shared:
+            return shared[self.shared_key]
         table = kernels.rotation_table(ctx.positions, self.inv_freq)
         if shared is not None:
-            shared[key] = table
+            shared[self.shared_key] = table
         return table
 
 

@@ -84,7 +84,29 @@ def test_rotary_part_tables():
         got = rope.tables()["inv_freq"].double().cpu()
         assert torch.equal(got, P.rope_inverse_frequencies(d, theta))
     none = POSITION_ENCODINGS.build(PartSpec("none", {}), "p")
-    assert none.tables()["inv_freq"] is None
+    assert none.tables()["inv_freq"] is None and none.rotations(None) is None
+
+
+def test_rotary_part_makes_a_steps_cosines_and_sines_once():
+    """Layers with the same frequencies share one table of a step; others get their own; a context without a place for
+    shared things gets a fresh table every time."""
+    from types import SimpleNamespace
+
+    def rope(d, theta):
+        part = POSITION_ENCODINGS.build(PartSpec("rope", {"head_dim": d, "theta": theta}), "p")
+        part.bind({}, runtime(torch.float32))
+        return part
+
+    first, second, other = rope(128, 1e6), rope(128, 1e6), rope(128, 1e4)
+    positions = torch.tensor([0, 1, 5, 4000, 39999], dtype=torch.int32, device=DEV)
+    ctx = SimpleNamespace(positions=positions, shared={})
+    table = first.rotations(ctx)
+    assert second.rotations(ctx) is table and other.rotations(ctx) is not table and len(ctx.shared) == 2
+    angles = (positions.float().cpu()[:, None] * P.rope_inverse_frequencies(128, 1e6)[None, :].float()).double()     # float32 products
+    close(table[..., 0], torch.cos(angles), torch.float32, "cosines")
+    close(table[..., 1], torch.sin(angles), torch.float32, "sines")
+    bare = SimpleNamespace(positions=positions)
+    assert first.rotations(bare) is not first.rotations(bare)
 
 
 def attention_weights(width, nq, nkv, d, seed):
