@@ -115,15 +115,19 @@ __global__ void add_rmsnorm_vec_kernel(float* __restrict__ residual, const T* __
             sum += v[c].x * v[c].x + v[c].y * v[c].y + v[c].z * v[c].z + v[c].w * v[c].w;
         }
     }
+    float4 w[ROW_CHUNKS];                  // asked for before the block waits for its sum
+#pragma unroll
+    for (int c = 0; c < ROW_CHUNKS; ++c) {
+        const int i = (c * blockDim.x + threadIdx.x) * 4;
+        if (i < width) w[c] = Vec4<float>::load(weight + i);
+    }
     const float scale = rsqrtf(block_sum(sum, scratch) / (float)width + eps);
     T* o = out + (size_t)r * width;
 #pragma unroll
     for (int c = 0; c < ROW_CHUNKS; ++c) {
         const int i = (c * blockDim.x + threadIdx.x) * 4;
-        if (i < width) {
-            const float4 w = Vec4<float>::load(weight + i);
-            Vec4<T>::store(o + i, make_float4(v[c].x * scale * w.x, v[c].y * scale * w.y, v[c].z * scale * w.z, v[c].w * scale * w.w));
-        }
+        if (i < width)
+            Vec4<T>::store(o + i, make_float4(v[c].x * scale * w[c].x, v[c].y * scale * w[c].y, v[c].z * scale * w[c].z, v[c].w * scale * w[c].w));
     }
 }
 
@@ -478,27 +482,29 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
     }
 }
 
-// The same with one 16-byte vector a step (width and block multiples of VEC).
+// The same with one 16-byte vector a thread and token (width and block multiples of VEC).  A thread keeps its
+// columns and walks down the tokens of the grid's second dimension, so no index is divided in the loop; when the
+// result is rounded to bfloat16 the quotient is the fast one.
 template <typename T, int VEC>
-__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, long long total_vecs, int inter, int block) {
+__global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens, int inter, int block) {
     pdl_launch_dependents();
     pdl_wait();
-    const int inter_vecs = inter / VEC;
-    for (long long i = (long long)blockIdx.x * blockDim.x + threadIdx.x; i < total_vecs;
-         i += (long long)gridDim.x * blockDim.x) {
-        const long long t = i / inter_vecs;
-        const int c = (int)(i % inter_vecs) * VEC;
-        const long long gate_at = block ? (long long)(c / block) * 2 * block + c % block : c;
-        const long long up_at = block ? gate_at + block : (long long)inter + c;
-        const Pack<T, VEC> g = *reinterpret_cast<const Pack<T, VEC>*>(gate_up + t * 2 * inter + gate_at);
-        const Pack<T, VEC> u = *reinterpret_cast<const Pack<T, VEC>*>(gate_up + t * 2 * inter + up_at);
+    const int c = (blockIdx.x * blockDim.x + threadIdx.x) * VEC;
+    if (c >= inter) return;
+    const int gate_at = block ? c / block * 2 * block + c % block : c;
+    const int up_at = block ? gate_at + block : inter + c;
+    for (int t = blockIdx.y; t < tokens; t += gridDim.y) {
+        const T* row = gate_up + (size_t)t * 2 * inter;
+        const Pack<T, VEC> g = *reinterpret_cast<const Pack<T, VEC>*>(row + gate_at);
+        const Pack<T, VEC> u = *reinterpret_cast<const Pack<T, VEC>*>(row + up_at);
         Pack<T, VEC> o;
 #pragma unroll
         for (int j = 0; j < VEC; ++j) {
             const float gj = to_float(g.v[j]);
-            o.v[j] = from_float<T>(gj / (1.0f + __expf(-gj)) * to_float(u.v[j]));
+            const float silu = sizeof(T) == 2 ? __fdividef(gj, 1.0f + __expf(-gj)) : gj / (1.0f + __expf(-gj));
+            o.v[j] = from_float<T>(silu * to_float(u.v[j]));
         }
-        *reinterpret_cast<Pack<T, VEC>*>(out + t * inter + c) = o;
+        *reinterpret_cast<Pack<T, VEC>*>(out + (size_t)t * inter + c) = o;
     }
 }
 
@@ -510,12 +516,11 @@ MRS_EXPORT int mrs_silu_mul(int is_bf16, const void* gate_up, void* out, int tok
     const bool aligned = (((uintptr_t)gate_up | (uintptr_t)out) & 15) == 0;
     const int vec = is_bf16 ? 8 : 4;
     if (inter % vec == 0 && block % vec == 0 && aligned) {
-        const long long vecs = total / vec, want = (vecs + threads - 1) / threads;
-        const unsigned blocks = (unsigned)(want > 148 * 32 ? 148 * 32 : want);
+        const dim3 grid((unsigned)((inter / vec + threads - 1) / threads), (unsigned)(tokens < 65535 ? tokens : 65535));
         if (is_bf16)
-            MRS_LAUNCH((silu_mul_vec_kernel<bf16, 8>), blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, vecs, inter, block);
+            MRS_LAUNCH((silu_mul_vec_kernel<bf16, 8>), grid, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, tokens, inter, block);
         else
-            MRS_LAUNCH((silu_mul_vec_kernel<float, 4>), blocks, threads, 0, stream, (const float*)gate_up, (float*)out, vecs, inter, block);
+            MRS_LAUNCH((silu_mul_vec_kernel<float, 4>), grid, threads, 0, stream, (const float*)gate_up, (float*)out, tokens, inter, block);
         MRS_RETURN_LAUNCH_STATUS();
     }
     long long want = (total + threads - 1) / threads;
