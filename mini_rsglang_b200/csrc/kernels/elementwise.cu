@@ -295,7 +295,7 @@ MRS_EXPORT int mrs_rotation_table(const int* positions, const float* inv_freq, i
     MRS_RETURN_LAUNCH_STATUS();
 }
 
-// The same for head sizes 64, 128 and 256.  A lane owns W = VEC / 2 consecutive elements of a head's lower half
+// The norms, rotation and cache write of above for head sizes 64, 128 and 256.  A lane owns W = VEC / 2 consecutive elements of a head's lower half
 // and the W elements that they rotate with in the upper half (two loads of 8 bytes, 16 for float32 heads of 256),
 // so the rotation needs no other lane; LANES = d / VEC lanes a head add their squares for the norm, and one load
 // of a warp covers 32 / LANES heads.  The cosines and sines come from the step's table (`rotations`
