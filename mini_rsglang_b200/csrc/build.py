@@ -30,6 +30,13 @@ BUILD_DIR = os.path.join(CSRC, "_build")
 NVCC_FLAGS = ["-gencode", "arch=compute_100a,code=sm_100a", "-O3", "-lineinfo", "-std=c++17",
               "-Xcompiler", "-fPIC", "--expt-relaxed-constexpr"]
 GXX_FLAGS = ["-O2", "-std=c++17", "-fPIC", "-Wall", "-fvisibility=hidden"]
+# MRS_HOST_SANITIZE=1 builds the host library with the address and undefined-behaviour sanitizers (a library of
+# its own name beside the ordinary one).  The process that loads it must have the sanitizer's runtime loaded first
+# (LD_PRELOAD=$(gcc -print-file-name=libasan.so)); `sanitizer_environment()` gives that environment.  The device-side
+# memory checker is a separate tool; this mode is for the cache manager, the scheduler and the batch layout, whose
+# tests run without a GPU.
+GXX_SANITIZE_FLAGS = ["-O1", "-g", "-std=c++17", "-fPIC", "-Wall", "-fvisibility=hidden", "-fno-omit-frame-pointer",
+                      "-fsanitize=address,undefined", "-fno-sanitize-recover=undefined"]
 
 _loaded: dict[str, ctypes.CDLL] = {}
 _lock = threading.Lock()
@@ -125,15 +132,40 @@ def _load(key: str, builder) -> ctypes.CDLL:
         return _loaded[key]
 
 
+def host_sanitized() -> bool:
+    return os.environ.get("MRS_HOST_SANITIZE", "") not in ("", "0")
+
+
+def sanitizer_environment(base: dict | None = None) -> dict:
+    """The environment of a process that loads the sanitized host library: MRS_HOST_SANITIZE=1 and the sanitizer
+    runtimes preloaded (Python itself is not built with them, so leak reports are off)."""
+    env = dict(os.environ if base is None else base)
+    gcc = _find("gcc")
+    runtimes = []
+    for name in ("libasan.so", "libubsan.so"):
+        path = subprocess.run([gcc, f"-print-file-name={name}"], capture_output=True, text=True).stdout.strip()
+        if not os.path.isabs(path) or not os.path.exists(path):
+            raise BackendError(f"the sanitizer runtime {name} was not found beside {gcc}")
+        runtimes.append(os.path.realpath(path))
+    env["MRS_HOST_SANITIZE"] = "1"
+    env["LD_PRELOAD"] = ":".join(runtimes + [p for p in env.get("LD_PRELOAD", "").split(":") if p])
+    env["ASAN_OPTIONS"] = "detect_leaks=0:abort_on_error=1:" + env.get("ASAN_OPTIONS", "")
+    env["UBSAN_OPTIONS"] = "print_stacktrace=1:halt_on_error=1:" + env.get("UBSAN_OPTIONS", "")
+    return env
+
+
 def host_library() -> ctypes.CDLL:
     """Cache manager and scheduler (C++, no CUDA)."""
     folder = os.path.join(CSRC, "host")
+    sanitize = host_sanitized()
 
     def builder():
         sources = [os.path.join(folder, f) for f in sorted(os.listdir(folder)) if f.endswith(".cc")]
+        if sanitize:
+            return _build("mrs_host_sanitized", sources, [_find("g++")], GXX_SANITIZE_FLAGS, ["-fsanitize=address,undefined"], folder)
         return _build("mrs_host", sources, [_find("g++")], GXX_FLAGS, [], folder)
 
-    return _load("host", builder)
+    return _load("host_sanitized" if sanitize else "host", builder)
 
 
 GENERIC_KERNEL_SOURCES = ("elementwise.cu", "attention_simt.cu", "gemm_f32.cu", "sampling.cu")

@@ -62,7 +62,7 @@ API int mrs_cache_table(void* c, int64_t request, int group, int32_t* out, int c
         if (group < 0 || group >= m->num_groups()) return mrs::kInvalid;
         const auto& table = lease->tables[(size_t)group];
         if ((int)table.size() > cap) return mrs::kInvalid;
-        std::memcpy(out, table.data(), table.size() * sizeof(int32_t));
+        if (!table.empty()) std::memcpy(out, table.data(), table.size() * sizeof(int32_t));     // an empty table has no data to point at
         return (int)table.size();
     });
 }
@@ -140,7 +140,7 @@ API int64_t mrs_sched_plan_tokens(void* s, int32_t* out, int64_t cap) {
             const mrs::Running* r = sched->find(p.request);
             if (!r || p.start_pos < 0 || p.start_pos + p.count > (int64_t)r->tokens.size()) return mrs::kInvalid;
             if (n + p.count > cap) return mrs::kInvalid;
-            std::memcpy(out + n, r->tokens.data() + p.start_pos, (size_t)p.count * sizeof(int32_t));
+            if (p.count > 0) std::memcpy(out + n, r->tokens.data() + p.start_pos, (size_t)p.count * sizeof(int32_t));
             n += p.count;
         }
         return n;
@@ -155,7 +155,7 @@ API int mrs_sched_tokens(void* s, int64_t request, int64_t start, int64_t count,
         const mrs::Running* r = static_cast<mrs::Scheduler*>(s)->find(request);
         if (!r) return mrs::kUnknown;
         if (start < 0 || count < 0 || start + count > (int64_t)r->tokens.size()) return mrs::kInvalid;
-        std::memcpy(out, r->tokens.data() + start, (size_t)count * sizeof(int32_t));
+        if (count > 0) std::memcpy(out, r->tokens.data() + start, (size_t)count * sizeof(int32_t));
         return (int)count;
     });
 }

@@ -178,7 +178,7 @@ API int64_t mrs_step_build(void* cache, int n_seq, const int64_t* requests, cons
             for (int i = 0; i < n_seq; ++i) {
                 const auto& t = leases[(size_t)i]->tables[(size_t)g];
                 int32_t* dst = table + (int64_t)i * width;
-                std::memcpy(dst, t.data(), t.size() * sizeof(int32_t));
+                if (!t.empty()) std::memcpy(dst, t.data(), t.size() * sizeof(int32_t));
                 for (int64_t c = (int64_t)t.size(); c < width; ++c) dst[c] = -1;
                 for (int64_t k = 0; k < counts[i]; ++k) {
                     const int64_t p = start_pos[i] + k;

@@ -509,6 +509,9 @@ MRS_EXPORT int mrs_attention_mma_keys_mode(const void* q, const void* k_cache, c
 // ---------------------------------------------------------------------------------------------
 #include "attention_no_alloc.h"
 
+#include <atomic>
+#include <mutex>
+
 namespace {
 
 // Device memory held by every GPU that loads this library.  In host code this name is only a
@@ -517,7 +520,8 @@ static __device__ __align__(256) float static_scratch[MRS_ATTENTION_STATIC_SCRAT
 
 constexpr int kMaxDevices = 64;
 float* static_scratch_address[kMaxDevices] = {};
-bool static_entry_ready[kMaxDevices] = {};
+std::atomic<bool> static_entry_ready[kMaxDevices];     // zero-initialised: false
+std::mutex static_entry_setup;                         // two host threads may make a device's first call together
 
 }  // namespace
 
@@ -535,12 +539,15 @@ MRS_EXPORT int mrs_attention_mma_keys_mode_static_scratch(const void* q, const v
     cudaError_t e = cudaGetDevice(&device);
     if (e != cudaSuccess) return (int)e;
     if (device < 0 || device >= kMaxDevices) return MRS_BAD_ARGUMENT;
-    if (!static_entry_ready[device]) {      // set-up, once per device, with that device current
-        e = cudaGetSymbolAddress((void**)&static_scratch_address[device], static_scratch);
-        if (e != cudaSuccess) return (int)e;
-        e = cudaFuncSetAttribute(attention_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
-        if (e != cudaSuccess) return (int)e;
-        static_entry_ready[device] = true;
+    if (!static_entry_ready[device].load(std::memory_order_acquire)) {      // set-up, once per device, with that device current
+        std::lock_guard<std::mutex> lock(static_entry_setup);
+        if (!static_entry_ready[device].load(std::memory_order_relaxed)) {
+            e = cudaGetSymbolAddress((void**)&static_scratch_address[device], static_scratch);
+            if (e != cudaSuccess) return (int)e;
+            e = cudaFuncSetAttribute(attention_keys_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)smem_keys);
+            if (e != cudaSuccess) return (int)e;
+            static_entry_ready[device].store(true, std::memory_order_release);
+        }
     }
     float* part_o = static_scratch_address[device];
     float* part_ml = part_o + (size_t)num_tiles * nkv * splits * ROWS_NARROW * D;

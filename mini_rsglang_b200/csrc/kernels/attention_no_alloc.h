@@ -4,7 +4,7 @@
 // fresh buffer for every intermediate result).  It exists for programs that embed this library
 // where device allocation is off limits: a host that hands the library a fixed set of buffers
 // and forbids cudaMalloc (for instance because another component owns the whole device heap, or
-// because an allocation would stall a latency-critical loop or break a running capture), or a
+// because an allocation would stall a latency-critical loop), or a
 // plain C caller that has no allocator of this engine at hand.  Such a caller still passes its
 // inputs and its output; only the scratch memory that the split kernel needs between its two
 // launches comes from the library itself.
@@ -18,6 +18,8 @@
 //
 // The first call on a device looks up the array's device address (cudaGetSymbolAddress) and
 // raises the kernels' shared-memory limit; make that first call outside any stream capture.
+// That set-up runs under a lock, so two host threads may make a device's first call at the same
+// time (their launches still must not overlap on the GPU, see below).
 // The function itself calls no cudaMalloc, cudaFree or any allocating routine.
 //
 // All calls share the one array and it keeps the last call's contents.  Nothing in it has to be

@@ -420,6 +420,8 @@ int page_shift_of(int page_size) {
 
 // Query rows of one CTA: two tiles of 128.
 MRS_EXPORT int mrs_attention_prefill_tc_rows() { return TILES * BM; }
+// Keys of one block that a CTA walks: the unit in which the host plans the shares of a long context.
+MRS_EXPORT int mrs_attention_prefill_tc_key_block() { return BN; }
 
 // Tensor map of one layer's key or value pages [pages, kv_heads, page_size, D] for copies of one
 // group of 64 columns of up to 128 rows of a page.  `map_out`: 128 bytes, 64-byte aligned.

@@ -64,6 +64,20 @@ __device__ __forceinline__ float block_sum(float x, float* scratch) {
 __device__ __forceinline__ void pdl_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
 __device__ __forceinline__ void pdl_launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
 
+// Multiprocessors of the current device (asked once per device and kept): grids that loop over their
+// work are capped by a multiple of it.
+static inline int mrs_sm_count() {
+    static int counts[64] = {};
+    int device = 0;
+    if (cudaGetDevice(&device) != cudaSuccess || device < 0 || device >= 64) return 1;
+    if (counts[device] == 0) {
+        int n = 0;
+        if (cudaDeviceGetAttribute(&n, cudaDevAttrMultiProcessorCount, device) != cudaSuccess || n <= 0) n = 1;
+        counts[device] = n;
+    }
+    return counts[device];
+}
+
 template <typename... KernelArgs, typename... Args>
 static inline int mrs_launch(void (*kernel)(KernelArgs...), dim3 grid, dim3 block, size_t smem, cudaStream_t stream,
                              Args... args) {

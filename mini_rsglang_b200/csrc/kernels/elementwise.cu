@@ -418,7 +418,8 @@ static int launch_rope_vec(const void* qkv, void* q_out, void* k_cache, void* v_
     const long long steps = (long long)tokens * ((nq + 2 * nkv + heads_per_step - 1) / heads_per_step);
     if (steps > 0x7fffffffLL) return MRS_BAD_ARGUMENT;
     const long long want = (steps + 7) / 8;
-    MRS_LAUNCH((qk_norm_rope_store_vec_kernel<T, VEC, LANES>), (unsigned)(want > 148 * 2 * ROPE_BLOCKS_PER_SM ? 148 * 2 * ROPE_BLOCKS_PER_SM : want), 256, 0, stream, (const T*)qkv,
+    const long long most = (long long)mrs_sm_count() * 2 * ROPE_BLOCKS_PER_SM;
+    MRS_LAUNCH((qk_norm_rope_store_vec_kernel<T, VEC, LANES>), (unsigned)(want > most ? most : want), 256, 0, stream, (const T*)qkv,
                (T*)q_out, (T*)k_cache, (T*)v_cache, slots, q_norm, k_norm, eps, reinterpret_cast<const float2*>(rotations), tokens, nq,
                nkv, page_size, write_kv);
     MRS_RETURN_LAUNCH_STATUS();
@@ -484,7 +485,7 @@ __global__ void silu_mul_kernel(const T* __restrict__ gate_up, T* __restrict__ o
 
 // The same with one 16-byte vector a thread and token (width and block multiples of VEC).  A thread keeps its
 // columns and walks down the tokens of the grid's second dimension, so no index is divided in the loop; when the
-// result is rounded to bfloat16 the quotient is the fast one.
+// result is rounded to bfloat16 the exponential and the quotient are the fast ones.
 template <typename T, int VEC>
 __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict__ out, int tokens, int inter, int block) {
     pdl_launch_dependents();
@@ -501,7 +502,8 @@ __global__ void silu_mul_vec_kernel(const T* __restrict__ gate_up, T* __restrict
 #pragma unroll
         for (int j = 0; j < VEC; ++j) {
             const float gj = to_float(g.v[j]);
-            const float silu = sizeof(T) == 2 ? __fdividef(gj, 1.0f + __expf(-gj)) : gj / (1.0f + __expf(-gj));
+            // the 32-bit path takes the accurate exponential and quotient, as the scalar kernel does: the same bits either way
+            const float silu = sizeof(T) == 2 ? __fdividef(gj, 1.0f + __expf(-gj)) : gj / (1.0f + expf(-gj));
             o.v[j] = from_float<T>(silu * to_float(u.v[j]));
         }
         *reinterpret_cast<Pack<T, VEC>*>(out + (size_t)t * inter + c) = o;
@@ -524,7 +526,8 @@ MRS_EXPORT int mrs_silu_mul(int is_bf16, const void* gate_up, void* out, int tok
         MRS_RETURN_LAUNCH_STATUS();
     }
     long long want = (total + threads - 1) / threads;
-    const unsigned blocks = (unsigned)(want > 148 * 16 ? 148 * 16 : want);
+    const long long most = (long long)mrs_sm_count() * 16;
+    const unsigned blocks = (unsigned)(want > most ? most : want);
     if (is_bf16)
         MRS_LAUNCH(silu_mul_kernel<bf16>, blocks, threads, 0, stream, (const bf16*)gate_up, (bf16*)out, total, inter, block);
     else

@@ -491,6 +491,10 @@ MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* o
 // head the RMSNorm of q and k (scales `q_norm`, `k_norm`, or null), the rotation of q and k (`inv_freq` [64] or
 // null; pairs (j, j + 64)), q into `q_out` [M, nq, 128] and k, v into the cache pages at `slots` (null: nothing
 // is written).  `w_map` covers the weights [(nq + 2 nkv) * 128, K], q heads first, then k, then v.
+// What the fused q/k/v projection takes: the head size (a weight tile is one head) and the most rows.
+MRS_EXPORT int mrs_gemm_tc_qkv_head_dim() { return TILE_N; }
+MRS_EXPORT int mrs_gemm_tc_qkv_max_rows() { return 32; }
+
 MRS_EXPORT int mrs_gemm_tc_qkv_heads(const void* w_map, const void* x_map, void* q_out, void* k_cache, void* v_cache,
                                      const int* positions, const int* slots, const float* q_norm, const float* k_norm,
                                      const float* inv_freq, float eps, int nq, int nkv, int page_size, float* partials,
@@ -515,6 +519,28 @@ MRS_EXPORT int mrs_gemm_tc_qkv_heads(const void* w_map, const void* x_map, void*
     if (mpad == 16) return launch<16, bf16, EPI_HEADS>(wm, xm, nullptr, partials, counters, M, N, K, splits, ctas, (cudaStream_t)stream, link, heads);
     if (mpad == 32) return launch<32, bf16, EPI_HEADS>(wm, xm, nullptr, partials, counters, M, N, K, splits, ctas, (cudaStream_t)stream, link, heads);
     return MRS_BAD_ARGUMENT;
+}
+
+// A wait that runs out, for the tests of the error path: one warp waits on a barrier of its own at which nobody
+// arrives, for `limit_cycles` clocks at most; the wait then gives up as every bounded wait of these kernels does
+// (it raises the library's error word and returns), and the kernel ends.  Nothing else is touched.
+__global__ void wait_probe_kernel(long long limit_cycles, int* gave_up) {
+    __shared__ uint64_t bar;
+    if (threadIdx.x == 0) {
+        mbar_init(&bar, 1);
+        mbar_fence_init();
+    }
+    __syncwarp();
+    if (threadIdx.x == 0) {
+        const bool arrived = mbar_wait(&bar, 0, limit_cycles);
+        if (gave_up) *gave_up = arrived ? 0 : 1;
+    }
+}
+
+MRS_EXPORT int mrs_gemm_tc_wait_probe(long long limit_cycles, int* gave_up, void* stream) {
+    if (limit_cycles <= 0 || limit_cycles > (1ll << 24)) return MRS_BAD_ARGUMENT;      // a few milliseconds at most
+    wait_probe_kernel<<<1, 32, 0, (cudaStream_t)stream>>>(limit_cycles, gave_up);
+    MRS_RETURN_LAUNCH_STATUS();
 }
 
 MRS_EXPORT int mrs_gemm_tc_take_error(unsigned int* word) { return mrs_take_error_word(word); }

@@ -67,13 +67,13 @@ __device__ __forceinline__ bool mbar_try_wait(uint64_t* bar, uint32_t parity) {
 // CTA has given up, every later wait gives up at once, so a kernel whose barriers are stuck
 // drains in a fraction of a second instead of a second per wait.
 #define MRS_WAIT_CYCLES (1ll << 29)
-__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity) {
+__device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, long long limit_cycles = MRS_WAIT_CYCLES) {
     if (mbar_try_wait(bar, parity)) return true;
     const long long start = clock64();
     unsigned int spins = 0;
     while (!mbar_try_wait(bar, parity)) {
         if ((++spins & 255u) == 0 && *reinterpret_cast<volatile unsigned int*>(&mrs_error_word) != 0) return false;
-        if (clock64() - start > MRS_WAIT_CYCLES) {
+        if (clock64() - start > limit_cycles) {
             mrs_raise(MRS_ERR_BARRIER_TIMEOUT);
             return false;
         }

@@ -13,6 +13,7 @@ stream's next event exists.  Requests submitted before iterating run together (c
 batching).  Prompts are token ids; there is no tokenizer."""
 from __future__ import annotations
 
+import weakref
 from collections import deque
 from dataclasses import dataclass, field
 from typing import Iterator, Sequence
@@ -72,7 +73,8 @@ class GenerationResult:
 
 
 class GenerationStream:
-    """Events of one request.  Dropping or `cancel()` stops the request at the next step."""
+    """Events of one request.  `cancel()`, leaving a `with` block or dropping the last reference stops the
+    request at the next step, as dropping the reference's stream does (crates/runtime/src/lib.rs:78-82)."""
 
     def __init__(self, engine: "EngineHandle", request_id: int):
         self.engine, self.request_id = engine, request_id
@@ -80,8 +82,20 @@ class GenerationStream:
         self.terminal = False
 
     def cancel(self) -> None:
-        if not self.terminal:
+        if not self.terminal and self.engine.healthy:
             self.engine.scheduler.cancel(self.request_id)
+
+    def __enter__(self) -> "GenerationStream":
+        return self
+
+    def __exit__(self, *exc) -> None:
+        self.cancel()
+
+    def __del__(self):
+        try:
+            self.cancel()
+        except Exception:       # the interpreter may be shutting down: the scheduler is gone with it
+            pass
 
     def __iter__(self) -> Iterator:
         return self
@@ -105,7 +119,8 @@ class EngineHandle:
         self.config = runner.limits
         self.scheduler = Scheduler(runner.cache, runner.limits, eos_ids, runner.config.vocab_size, policy)
         self.sampler = Sampler(runner.device)
-        self.streams: dict[int, GenerationStream] = {}
+        # the engine does not keep a stream alive: a caller who drops one cancels its request
+        self.streams: "weakref.WeakValueDictionary[int, GenerationStream]" = weakref.WeakValueDictionary()
         self.params: dict[int, SamplingParams] = {}
         self.generated: dict[int, int] = {}
         self.next_id = 1
@@ -222,7 +237,7 @@ class EngineHandle:
             # a failed step ends every request and gives every page back (scheduler.rs:332-359)
             self.healthy = False
             message = f"{type(e).__name__}: {e}"
-            for stream in self.streams.values():
+            for stream in list(self.streams.values()):
                 stream.events.append(Error(stream.request_id, message))
             self.scheduler.fail("error")
             self._emit_finished()
@@ -230,7 +245,9 @@ class EngineHandle:
         self.scheduler.commit(tokens)
         for request_id, token in zip(sampled_ids, tokens):
             self.generated[request_id] += 1
-            self.streams[request_id].events.append(Token(request_id, token))
+            stream = self.streams.get(request_id)
+            if stream is not None:
+                stream.events.append(Token(request_id, token))
         self._emit_finished()
         return True
 
@@ -238,8 +255,12 @@ class EngineHandle:
     def metrics(self) -> dict:
         """The reference's counters (crates/runtime/src/metrics.rs:4-20) as a dict."""
         out = self.scheduler.counters()
+        cache = self.runner.cache
+        by_group = [cache.free_pages(g) for g in range(len(self.runner.groups))]
         out.update(waiting=self.scheduler.waiting(), running=self.scheduler.running(),
-                   free_pages=self.runner.cache.free_pages(0), cached_pages=0, cached_tokens=0,
+                   free_pages=sum(by_group), free_pages_by_group=by_group,
+                   total_pages=sum(cache.total_pages(g) for g in range(len(self.runner.groups))),
+                   cached_pages=0, cached_tokens=0,
                    peak_memory_bytes=torch.cuda.max_memory_allocated(self.runner.device), healthy=self.healthy)
         return out
 

@@ -97,13 +97,15 @@ def main(argv=None) -> int:
     parser.add_argument("--max-tokens", type=int, required=True,
                         help="most tokens that live requests hold at any time; the cache pool is made for this many")
     parser.add_argument("--device", default="cuda:0")
+    parser.add_argument("--page-size", type=int, default=16,
+                        help="tokens of a cache page (a power of two); --max-tokens is rounded up to whole pages")
     parser.add_argument("--observe", metavar="ID", help="also write the layers of this request, step by step, to <out>/observe/")
     args = parser.parse_args(argv)
     os.makedirs(args.out, exist_ok=True)
     if args.observe is not None:
         os.makedirs(os.path.join(args.out, "observe"), exist_ok=True)
     try:
-        replayer = Replayer(args.model, args.dtype, args.max_tokens, args.device, observe=args.observe)
+        replayer = Replayer(args.model, args.dtype, args.max_tokens, args.device, page_size=args.page_size, observe=args.observe)
         for line in sys.stdin:
             line = line.strip()
             if not line:

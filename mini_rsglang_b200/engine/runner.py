@@ -24,6 +24,7 @@ from ..errors import BackendError, InvalidRequest
 from ..models.model import Model
 from ..models.registry import load_config, model_spec_for
 from ..parts.base import Runtime
+from ..parts.linear import configure_library_products
 from ..weights.loader import load_weights
 from ..weights.random_init import random_weights
 from .context import StepContext
@@ -46,6 +47,14 @@ def resolve_dtype(dtype) -> torch.dtype:
     if dtype not in names:
         raise InvalidRequest(f"dtype must be bfloat16 or float32, got {dtype!r}")
     return names[dtype]
+
+
+def step_layout_bound(rows: int, sequences: int, table_width: int, groups: int) -> int:
+    """An upper bound of the int32 words that `mrs_step_build` lays out for a step of `rows` tokens in
+    `sequences` sequences with block tables `table_width` wide in each of `groups` page groups: per token
+    the id, position, sequence and one write slot a group; per sequence the start row, context length, state
+    slot, a wanted row and an attention tile; the tables; every array rounded up to four words."""
+    return (3 + groups) * (rows + 4) + 8 * (sequences + 4) + (rows + 4) + groups * (sequences * table_width + 4)
 
 
 class _Staging:
@@ -90,6 +99,7 @@ class ModelRunner:
         if not torch.cuda.is_available() or runtime.device.type != "cuda":
             raise BackendError("the engine runs on a CUDA device only; none is available")
         limits.validate()
+        configure_library_products()       # process-wide: exact float32 accumulation in the library's products, no TF32
         if limits.max_seq_len > config.max_position_embeddings:
             raise InvalidRequest("invalid configured context length/page size: max_seq_len "
                                  f"{limits.max_seq_len} exceeds max_position_embeddings "
@@ -131,7 +141,7 @@ class ModelRunner:
         # mixers written in Python read the requests' state slots from a host list
         self._needs_host_slots = any(need is not None for need in state_needs)
         # steps of single decoded tokens are recorded and replayed when every mixer allows it
-        self.record_decode = all(getattr(b.mixer, "replayable", False) for b in self.model.blocks)
+        self.record_decode = self.model.replayable()
         self._largest_bucket = min(256, 1 << (limits.max_running - 1).bit_length())
         self._records: dict[tuple[int, int], _Recorded] = {}
         self._graph_pool = None
@@ -179,9 +189,10 @@ class ModelRunner:
         want = np.asarray([w for s in sequences for w in s.want], dtype=np.int32)
         G = len(self.groups)
         layout = np.zeros(14 + 3 * G, dtype=np.int64)
-        rows, most = int(counts.sum()) + (pad_to or n), pad_to or n
         widest = table_width or -(-self.limits.max_seq_len // self.limits.page_size)
-        guess = (4 + G) * (rows + 4) + 8 * (most + 4) + G * (most * widest + 4)     # an upper bound of the layout
+        # a padded step has `pad_to` rows and sequences whatever the number of real ones: its need, and with it
+        # the size of a recorded step's fixed buffers, depends on `pad_to` alone
+        guess = step_layout_bound(pad_to or int(counts.sum()), pad_to or n, widest, G)
         for _ in range(2):
             host, dev = staging.reserve(guess)
             used = self._step_build(self.cache.handle, n, requests.ctypes.data, starts.ctypes.data, counts.ctypes.data,

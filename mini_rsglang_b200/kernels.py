@@ -85,6 +85,30 @@ def _need(t: torch.Tensor, dtype, what: str, shape: tuple | None = None) -> None
         raise InvalidRequest(f"{what}: shape {tuple(t.shape)}, expected {tuple(shape)}")
 
 
+_sm_counts: dict[int, int] = {}
+
+
+def sm_count(device=None) -> int:
+    """Multiprocessors of the device (asked once): what launch plans fill."""
+    index = torch.device(device).index if device is not None else None
+    if index is None:
+        index = torch.cuda.current_device()
+    if index not in _sm_counts:
+        _sm_counts[index] = torch.cuda.get_device_properties(index).multi_processor_count
+    return _sm_counts[index]
+
+
+def check_rotation(head_dim: int, rotary_dim: int, pairing: str, magnitude: float) -> None:
+    """Refuses a rotation that the kernels do not compute.  They rotate every element of a head, element j
+    with element j + head_dim / 2, by angles position * frequency, cosines and sines unscaled."""
+    if pairing != "split_half":
+        raise InvalidRequest(f"rotation pairing {pairing!r} is not built; the kernels pair element j with j + head_dim / 2 (\"split_half\")")
+    if int(rotary_dim) != int(head_dim):
+        raise InvalidRequest(f"a rotation of {rotary_dim} of a head's {head_dim} elements is not built; the kernels rotate whole heads")
+    if float(magnitude) != 1.0:
+        raise InvalidRequest(f"a rotation whose cosines and sines are scaled by {magnitude} is not built")
+
+
 def _is_bf16(dtype: torch.dtype) -> int:
     if dtype is torch.bfloat16:
         return 1
@@ -457,6 +481,13 @@ def attention_prefill_tc_supported(d: int, group: int, page_size: int) -> bool:
     return d in (64, 128) and 128 % group == 0 and page_size >= 8
 
 
+def attention_prefill_tc_key_block(d: int) -> int:
+    """Keys of one block of the tcgen05 kernel for prompt portions (the unit of its shares of a long context)."""
+    lib = attention_prefill_tc_library(d)
+    lib.mrs_attention_prefill_tc_key_block.restype = _c_int
+    return lib.mrs_attention_prefill_tc_key_block()
+
+
 def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
     if d not in _prefill_libs:
         if not torch.cuda.is_available():
@@ -474,6 +505,9 @@ def attention_prefill_tc_library(d: int) -> ctypes.CDLL:
         lib.mrs_attention_prefill_tc_take_error.restype = _c_int
         lib.mrs_attention_prefill_tc_error_string.argtypes = [_c_int]
         lib.mrs_attention_prefill_tc_error_string.restype = ctypes.c_char_p
+        lib.mrs_attention_prefill_tc_rows.restype = _c_int
+        if lib.mrs_attention_prefill_tc_rows() != PREFILL_TC_ROWS:
+            raise BackendError(f"attention_prefill_tc takes {lib.mrs_attention_prefill_tc_rows()} rows a CTA, the planner expects {PREFILL_TC_ROWS}")
         _prefill_libs[d] = lib
         _register_error_word(f"attention_prefill_tc (head size {d})", lib, "mrs_attention_prefill_tc")
     return _prefill_libs[d]
@@ -571,7 +605,7 @@ def gemm_tc_supported(x: torch.Tensor, weight: torch.Tensor) -> bool:
 def _gemm_device_state(device: torch.device) -> dict:
     state = _gemm_state.get(device)
     if state is None:
-        state = {"sms": torch.cuda.get_device_properties(device).multi_processor_count,
+        state = {"sms": sm_count(device),
                  "counters": torch.zeros(4096, dtype=torch.int32, device=device),
                  "partials": torch.empty(1 << 24, dtype=torch.float32, device=device),
                  "x_map": _aligned_block(128, 64)}
@@ -689,6 +723,28 @@ def gemm_tc(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor, gated: boo
     return out_sums
 
 
+_qkv_heads_limits: tuple[int, int] | None = None
+
+
+def gemm_tc_qkv_heads_limits() -> tuple[int, int]:
+    """(head size, most rows) of the fused q/k/v projection, as its library states them."""
+    global _qkv_heads_limits
+    if _qkv_heads_limits is None:
+        lib = gemm_tc_library()
+        lib.mrs_gemm_tc_qkv_head_dim.restype = lib.mrs_gemm_tc_qkv_max_rows.restype = _c_int
+        _qkv_heads_limits = (lib.mrs_gemm_tc_qkv_head_dim(), lib.mrs_gemm_tc_qkv_max_rows())
+    return _qkv_heads_limits
+
+
+def gemm_tc_qkv_heads_supported(x: torch.Tensor, weight: torch.Tensor, head_dim: int) -> bool:
+    """Whether the fused q/k/v projection (head norms, rotation and cache write in the product's epilogue) takes
+    these rows: the head size that the library's tiles are made for, few enough rows, and what `gemm_tc` needs."""
+    if not gemm_tc_supported(x, weight):
+        return False
+    d, rows = gemm_tc_qkv_heads_limits()
+    return head_dim == d and x.shape[0] <= rows
+
+
 def gemm_tc_qkv_heads(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor, k_cache: torch.Tensor | None,
                       v_cache: torch.Tensor | None, positions: torch.Tensor, slots: torch.Tensor | None,
                       q_norm: torch.Tensor | None, k_norm: torch.Tensor | None, eps: float,
@@ -697,13 +753,13 @@ def gemm_tc_qkv_heads(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor
     rotation and the cache write in the product's epilogue (what `qk_norm_rope_store` does after a product).
     `row_sums`: as for `gemm_tc`."""
     m, k = x.shape
-    d = 128
+    d, most = gemm_tc_qkv_heads_limits()
     _need(x, torch.bfloat16, "qkv input")
     _need(weight, torch.bfloat16, "qkv weight", ((nq + 2 * nkv) * d, k))
     _need(q_out, torch.bfloat16, "q_out", (m, nq * d))
     _need(positions, torch.int32, "positions", (m,))
-    if m > 32:
-        raise InvalidRequest(f"the fused projection takes at most 32 rows, got {m}")
+    if m > most:
+        raise InvalidRequest(f"the fused projection takes at most {most} rows, got {m}")
     page_size = 1
     if slots is not None:
         _need(slots, torch.int32, "slots", (m,))
@@ -717,7 +773,7 @@ def gemm_tc_qkv_heads(x: torch.Tensor, weight: torch.Tensor, q_out: torch.Tensor
             _need(w, torch.float32, name, (d,))
     if inv_freq is not None:
         _need(inv_freq, torch.float32, "inv_freq", (d // 2,))
-    lib, state, w_map, x_map, splits, mpad = _gemm_tc_prepare(x, weight, None, 32)
+    lib, state, w_map, x_map, splits, mpad = _gemm_tc_prepare(x, weight, None, most)
     link = _norm_link(m, row_sums)
     global launch_count
     launch_count += 1
@@ -796,11 +852,27 @@ def gemm_gated_rows(x: torch.Tensor, weight: torch.Tensor, out: torch.Tensor) ->
     lib = gemm_many_rows_library()
     x_keep, x_map, w_map = _many_rows_maps_of(lib, x, weight)
     launch_count += 1
-    code = lib.mrs_gemm_gated_rows(x_map, w_map, out.data_ptr(), t, n, k,
-                                   torch.cuda.get_device_properties(x.device).multi_processor_count, _stream())
+    code = lib.mrs_gemm_gated_rows(x_map, w_map, out.data_ptr(), t, n, k, sm_count(x.device), _stream())
     del x_keep
     if code != 0:
         raise BackendError(f"gemm_gated_rows: {lib.mrs_gemm_many_rows_error_string(code).decode()} (code {code})")
+
+
+def wait_probe(limit_cycles: int = 1 << 16, device=None) -> bool:
+    """Runs a one-warp kernel whose only act is a bounded wait on a barrier at which nobody arrives, with a limit
+    of `limit_cycles` clocks (at most 2^24: milliseconds).  The wait gives up as every wait of the engine's
+    kernels does when its time runs out: it raises the error word of its library and the kernel returns.
+    Returns whether the wait gave up (it always does).  For the tests of the error path: `check_device_errors`
+    raises afterwards, and the device is as usable as before."""
+    lib = gemm_tc_library()
+    lib.mrs_gemm_tc_wait_probe.argtypes = [ctypes.c_longlong, _c_vp, _c_vp]
+    lib.mrs_gemm_tc_wait_probe.restype = _c_int
+    flag = torch.zeros(1, dtype=torch.int32, device=device or torch.device("cuda", torch.cuda.current_device()))
+    code = lib.mrs_gemm_tc_wait_probe(int(limit_cycles), flag.data_ptr(), _stream())
+    if code != 0:
+        _gemm_fail(lib, code, "wait_probe")
+    torch.cuda.current_stream().synchronize()
+    return bool(flag.item())
 
 
 # ------------------------------------------------------------------------------------------------
@@ -836,10 +908,17 @@ def check_device_errors(certain: bool = False) -> None:
         return
     if _mirror is not None:
         _mirror.zero_()
-    for what, reader in _error_readers:
+    failed = []
+    for what, reader in _error_readers:       # every word is read, and with that cleared
         word = ctypes.c_uint(0)
         code = reader(ctypes.byref(word))
         if code != 0:
             raise BackendError(f"{what}: reading the error word failed (CUDA error {code})")
         if word.value:
-            raise BackendError(f"{what}: a kernel gave up waiting (error word {word.value:#x}); the step's result is invalid")
+            failed.append(f"{what}: a kernel gave up waiting (error word {word.value:#x})")
+    if failed:
+        # a kernel that gave up may have left the arrival counters of its splits half counted: the next launch
+        # that shares them must find zeros
+        for counters in list(_counters.values()) + [state["counters"] for state in _gemm_state.values()]:
+            counters.zero_()
+        raise BackendError("; ".join(failed) + "; the step's result is invalid")

@@ -26,11 +26,19 @@ class Model:
         self.cache_entry = [e.cache_of if e.cache_of is not None else i for i, e in enumerate(spec.run_order)]
         self.writes_cache = [e.cache_of is None for e in spec.run_order]
 
+    def _need(self, entry, which: str):
+        part = self.blocks[entry.layer].cache_part()
+        return getattr(part, which)() if part is not None and entry.cache_of is None else None
+
     def kv_needs(self):
-        return [self.blocks[e.layer].mixer.cache_need() if e.cache_of is None else None for e in self.spec.run_order]
+        return [self._need(e, "cache_need") for e in self.spec.run_order]
 
     def state_needs(self):
-        return [self.blocks[e.layer].mixer.state_need() if e.cache_of is None else None for e in self.spec.run_order]
+        return [self._need(e, "state_need") for e in self.spec.run_order]
+
+    def replayable(self) -> bool:
+        """Whether steps of single decoded tokens may be recorded: every part that keeps a cache allows it."""
+        return all(getattr(b.cache_part(), "replayable", False) for b in self.blocks if b.cache_part() is not None)
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0
@@ -56,7 +64,7 @@ class Model:
             ctx.label = f"layer{index}"
             extra = {}
             if block.links_norms:        # the norm that reads the stream after this block
-                extra["next_norm"] = self.blocks[order[index + 1].layer].norm1 if index + 1 < len(order) else self.final_norm
+                extra["next_norm"] = self.blocks[order[index + 1].layer].entry_norm if index + 1 < len(order) else self.final_norm
             pending = block.forward(stream, pending, ctx, storage.entries[self.cache_entry[index]],
                                     self.writes_cache[index], **extra)
         if ctx.observe:              # the reference norms every row before it gathers the wanted ones (qwen3.rs:228-233)

@@ -6,7 +6,7 @@ from __future__ import annotations
 
 from ..config.model_config import Qwen3Config
 from ..parts.base import PartSpec
-from .spec import LayerSpec, ModelSpec
+from .spec import ModelSpec, pre_norm_layer
 
 
 def qwen3_spec(config: Qwen3Config) -> ModelSpec:
@@ -19,9 +19,11 @@ def qwen3_spec(config: Qwen3Config) -> ModelSpec:
         "position": PartSpec("rope", {"head_dim": c.head_dim, "theta": c.rope_theta})})
     feed_forward = PartSpec("swiglu", {"width": c.hidden_size, "inner": c.intermediate_size,
                                        "activation": c.hidden_act})
-    layers = [LayerSpec(prefix=f"model.layers.{i}", block="pre_norm", norm1=norm, mixer=mixer, norm2=norm,
-                        feed_forward=feed_forward) for i in range(c.num_hidden_layers)]
-    return ModelSpec(vocab_size=c.vocab_size, width=c.hidden_size, embedding_prefix="model.embed_tokens",
-                     layers=layers, final_norm=norm, final_norm_prefix="model.norm", head_prefix="lm_head",
-                     tie_head_to_embedding=c.tie_word_embeddings,
+    layers = [pre_norm_layer(f"model.layers.{i}", norm, mixer, norm, feed_forward) for i in range(c.num_hidden_layers)]
+    table = {"vocab": c.vocab_size, "width": c.hidden_size}
+    tied = "model.embed_tokens.weight" if c.tie_word_embeddings else None
+    return ModelSpec(vocab_size=c.vocab_size, width=c.hidden_size,
+                     embedding=PartSpec("token_embedding", table), embedding_prefix="model.embed_tokens",
+                     layers=layers, final_norm=norm, final_norm_prefix="model.norm",
+                     head=PartSpec("linear_head", dict(table, tied_to=tied)), head_prefix="lm_head",
                      ignorable_weights=("lm_head.weight",) if c.tie_word_embeddings else ())

@@ -2,28 +2,31 @@
 from __future__ import annotations
 
 from dataclasses import dataclass, field
+from typing import Mapping
 
 from ..errors import InvalidRequest
-from ..parts.base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, PartSpec
-from ..parts.embedding import OutputHead, TokenEmbedding
+from ..parts.base import BLOCKS, EMBEDDINGS, HEADS, NORMS, PartSpec
 from ..weights.spec import WeightSpec
 
 
 @dataclass(frozen=True)
 class LayerSpec:
-    """One layer: the arrangement (`block`) and the parts it arranges.  `prefix` is the root of
-    the layer's tensor names; the parts' own prefixes hang below it."""
+    """One layer: the arrangement (`block`, a registered block kind) and a part for every role that this
+    kind arranges.  `prefix` is the root of the layer's tensor names; a part's own root hangs below it
+    under `names[role]` (the role itself when `names` does not give one)."""
 
     prefix: str
     block: str
-    norm1: PartSpec
-    mixer: PartSpec
-    norm2: PartSpec
-    feed_forward: PartSpec
-    norm1_name: str = "input_layernorm"
-    mixer_name: str = "self_attn"
-    norm2_name: str = "post_attention_layernorm"
-    feed_forward_name: str = "mlp"
+    parts: Mapping[str, PartSpec]
+    names: Mapping[str, str] = field(default_factory=dict)
+
+
+def pre_norm_layer(prefix: str, norm1: PartSpec, mixer: PartSpec, norm2: PartSpec, feed_forward: PartSpec,
+                   norm1_name: str = "input_layernorm", mixer_name: str = "self_attn",
+                   norm2_name: str = "post_attention_layernorm", feed_forward_name: str = "mlp") -> LayerSpec:
+    """A layer of the "pre_norm" arrangement with the usual tensor-name roots."""
+    return LayerSpec(prefix, "pre_norm", {"norm1": norm1, "mixer": mixer, "norm2": norm2, "feed_forward": feed_forward},
+                     {"norm1": norm1_name, "mixer": mixer_name, "norm2": norm2_name, "feed_forward": feed_forward_name})
 
 
 @dataclass(frozen=True)
@@ -39,12 +42,13 @@ class RunEntry:
 class ModelSpec:
     vocab_size: int
     width: int
+    embedding: PartSpec
     embedding_prefix: str
     layers: list[LayerSpec]
     final_norm: PartSpec
     final_norm_prefix: str
+    head: PartSpec
     head_prefix: str
-    tie_head_to_embedding: bool
     run_order: list[RunEntry] = field(default_factory=list)
     ignorable_weights: tuple[str, ...] = ()
 
@@ -60,18 +64,20 @@ class ModelSpec:
 
     def build_parts(self):
         """Instantiate every part (no tensors yet): (embedding, blocks, final norm, head)."""
-        embedding = TokenEmbedding(self.embedding_prefix, self.vocab_size, self.width)
+        embedding = EMBEDDINGS.build(self.embedding, self.embedding_prefix)
         blocks = []
         for layer in self.layers:
-            blocks.append(BLOCKS.get(layer.block)(
-                prefix=layer.prefix,
-                norm1=NORMS.build(layer.norm1, f"{layer.prefix}.{layer.norm1_name}"),
-                mixer=MIXERS.build(layer.mixer, f"{layer.prefix}.{layer.mixer_name}"),
-                norm2=NORMS.build(layer.norm2, f"{layer.prefix}.{layer.norm2_name}"),
-                feed_forward=FEED_FORWARDS.build(layer.feed_forward, f"{layer.prefix}.{layer.feed_forward_name}")))
+            kind = BLOCKS.get(layer.block)
+            missing = [role for role in kind.roles if role not in layer.parts]
+            unknown = [role for role in layer.parts if role not in kind.roles]
+            if missing or unknown:
+                raise InvalidRequest(f"layer {layer.prefix!r}: block kind {layer.block!r} arranges {sorted(kind.roles)}; "
+                                     f"missing {missing}, unknown {unknown}")
+            parts = {role: registry.build(layer.parts[role], f"{layer.prefix}.{layer.names.get(role, role)}")
+                     for role, registry in kind.roles.items()}
+            blocks.append(kind(prefix=layer.prefix, **parts))
         final_norm = NORMS.build(self.final_norm, self.final_norm_prefix)
-        tied = f"{self.embedding_prefix}.weight" if self.tie_head_to_embedding else None
-        head = OutputHead(self.head_prefix, self.vocab_size, self.width, tied_to=tied)
+        head = HEADS.build(self.head, self.head_prefix)
         return embedding, blocks, final_norm, head
 
     def weight_specs(self) -> list[WeightSpec]:

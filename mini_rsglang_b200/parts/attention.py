@@ -16,11 +16,8 @@ from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, Pr
 from .linear import few_rows, linear
 
 
-SM_COUNT = 148
-PREFILL_KEY_BLOCK = 128     # keys of a block of the tcgen05 kernel for prompt portions
-
-
-def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, window: int = 0):
+def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, window: int = 0, key_block: int = 128,
+                         sms: int = 1):
     """Cuts the step's sequences into tiles for the tensor-core kernels: sequences with few
     query rows (decoded tokens, short portions) go to the kernels for few rows in tiles of
     16 // group tokens, the others in tiles of wide_rows // group tokens, those with the most
@@ -33,9 +30,11 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
     SMs.  Then, measured with 512 tokens behind 3,584 cached ones and 8 key/value heads (78 us as
     64 CTAs): entries with at least 8 blocks of 128 keys are cut into shares of their keys, whose
     sums a second kernel merges; shorter ones into entries of one tile (68 us as 128 CTAs; a CTA
-    with one tile has no partner on the tensor cores, so this pays only while SMs would idle)."""
+    with one tile has no partner on the tensor cores, so this pays only while SMs would idle).
+    `key_block` is the kernel's block of keys and `sms` the device's multiprocessors, as the kernel's
+    library and the device state them."""
     plans = ctx.__dict__.setdefault("_attention_plans", {})
-    key = (group, wide_rows, kv_heads, window)
+    key = (group, wide_rows, kv_heads, window, key_block)
     if key in plans:
         return plans[key]
     narrow_tokens = kernels.MMA_ROWS_NARROW // group
@@ -46,7 +45,7 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
     lengths = [ctx.host_q_start[i + 1] - ctx.host_q_start[i] for i in range(ctx.num_sequences)]
     tensor_core = wide_rows == kernels.PREFILL_TC_ROWS
     entries = sum(-(-n // wide_tokens) for n in lengths if n > narrow_tokens)
-    spare = SM_COUNT // max(entries * kv_heads, 1) if tensor_core else 1      # CTAs an entry may become
+    spare = sms // max(entries * kv_heads, 1) if tensor_core else 1      # CTAs an entry may become
     narrow, wide = [], []
     longest_narrow = 0
     shared = False
@@ -60,7 +59,7 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
             tokens = min(wide_tokens, n - start)
             begin = ctx.host_start_pos[i] + start                        # position of the entry's first token
             first_key = max(0, begin - window + 1) if window else 0
-            blocks = -(-(begin + tokens) // PREFILL_KEY_BLOCK) - first_key // PREFILL_KEY_BLOCK
+            blocks = -(-(begin + tokens) // key_block) - first_key // key_block
             shares = min(spare, blocks // 4, 255) if spare >= 2 else 1
             if shares >= 2:
                 shared = True
@@ -79,14 +78,14 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
     return plans[key]
 
 
-def choose_splits(tiles: int, nkv: int, longest_context: int, resident: int = 2) -> int:
+def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident: int = 2) -> int:
     """CTAs per tile in the kernels for few rows.  Measured on a B200 (context 4,096, 8 key/value
     heads): one round of CTAs beats several (every CTA pays for its start and for the merge), and
     more CTAs than fill the GPU's slots (`resident` per SM) only add merges.  So: the fewest splits
     that fill about 85% of the slots, at most 16 (a single request: 10.9 us with 16, 13.7 us with 32),
     every split with at least two 64-key blocks, rounded up to a power of two."""
     blocks = -(-longest_context // 64)
-    slots = SM_COUNT * resident
+    slots = sms * resident
     want = -(-(85 * slots) // (100 * max(tiles * nkv, 1)))
     most = max(1, min(16, blocks // 2))
     # a power of two: 2, 4, 8 or 16 shares run as one thread-block cluster and merge through distributed shared memory
@@ -109,11 +108,15 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
         kernels.attention_simt(q, cache.k, cache.v, ctx.positions, ctx.seq_of_token, table, out, nq, nkv, d, window)
         return
     page_size = cache.k.shape[2]
+    sms = kernels.sm_count(q.device)
     tensor_core_rows = kernels.attention_prefill_tc_supported(d, group, page_size)
-    narrow, wide, longest, shared = plan_attention_tiles(ctx, group, kernels.PREFILL_TC_ROWS if tensor_core_rows else kernels.MMA_ROWS_WIDE,
-                                                         nkv, window)
+    if tensor_core_rows:
+        narrow, wide, longest, shared = plan_attention_tiles(ctx, group, kernels.PREFILL_TC_ROWS, nkv, window,
+                                                             kernels.attention_prefill_tc_key_block(d), sms)
+    else:
+        narrow, wide, longest, shared = plan_attention_tiles(ctx, group, kernels.MMA_ROWS_WIDE, nkv, window, sms=sms)
     if narrow is not None:
-        splits = choose_splits(narrow.shape[0], nkv, longest)
+        splits = choose_splits(narrow.shape[0], nkv, longest, sms)
         if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
             kernels.attention_decode_tma(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
         else:
@@ -147,7 +150,7 @@ class GroupedQueryAttention(Mixer):
         for norm in (self.q_norm, self.k_norm):
             if norm is not None and norm.width != self.d:
                 raise InvalidRequest("a head norm must have the head's width")
-        self.qkv = self.o = None
+        self.qkv = self.o = self.inv_freq = None
 
     def weight_specs(self):
         specs = [WeightSpec(self.name("q_proj.weight"), (self.nq * self.d, self.width)),
@@ -173,19 +176,24 @@ class GroupedQueryAttention(Mixer):
                 norm.bind(tensors, runtime)
         if (self.q_norm and self.k_norm and self.q_norm.eps != self.k_norm.eps):
             raise InvalidRequest("q and k head norms must share one eps")
+        rotation = self.position.rotation()
+        if rotation is not None:          # the kernels' launchers say what they rotate; anything else is refused here, at load
+            kernels.check_rotation(self.d, rotation.rotary_dim, rotation.pairing, rotation.magnitude)
+        self.inv_freq = rotation.inv_freq if rotation is not None else None
 
     def forward(self, h, ctx, cache, write_cache=True, into=None):
         tokens = h.shape[0]
         q = torch.empty((tokens, self.nq * self.d), dtype=self.runtime.dtype, device=self.o.device)
         eps = self.q_norm.eps if self.q_norm else (self.k_norm.eps if self.k_norm else 0.0)
         group = cache.group
-        if self.d == 128 and few_rows(h, self.qkv) and not observing(ctx):
-            # few rows, heads of 128: the product's epilogue norms, rotates and writes the cache itself
-            prenormed = isinstance(h, Prenormed)
+        prenormed = isinstance(h, Prenormed)
+        if few_rows(h, self.qkv) and not observing(ctx) and \
+                kernels.gemm_tc_qkv_heads_supported(h.scaled if prenormed else h, self.qkv, self.d):
+            # few rows, heads of the size of the product's tiles: its epilogue norms, rotates and writes the cache itself
             kernels.gemm_tc_qkv_heads(
                 h.scaled if prenormed else h, self.qkv, q, cache.k if write_cache else None, cache.v if write_cache else None,
                 ctx.positions, ctx.slots[group] if write_cache else None, self.q_norm.weight if self.q_norm else None,
-                self.k_norm.weight if self.k_norm else None, eps, self.position.tables()["inv_freq"], self.nq, self.nkv,
+                self.k_norm.weight if self.k_norm else None, eps, self.inv_freq, self.nq, self.nkv,
                 row_sums=h.row_sums if prenormed else None)
             out = torch.empty_like(q)
             paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)
@@ -197,7 +205,7 @@ class GroupedQueryAttention(Mixer):
             qkv, q, cache.k if write_cache else None, cache.v if write_cache else None, ctx.positions,
             ctx.slots[group] if write_cache else None,
             self.q_norm.weight if self.q_norm else None, self.k_norm.weight if self.k_norm else None, eps,
-            self.position.tables()["inv_freq"], self.nq, self.nkv, self.d, cache.k.shape[2],
+            self.inv_freq, self.nq, self.nkv, self.d, cache.k.shape[2],
             rotations=self.position.rotations(ctx) if self.d in (64, 128, 256) else None)
         out = torch.empty_like(q)
         paged_attention(q, cache, ctx, out, self.nq, self.nkv, self.d, self.window)

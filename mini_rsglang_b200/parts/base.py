@@ -1,8 +1,9 @@
 """What a model is put together from, and the registries that name the kinds of each part.
 
-A model is data (`models/spec.py`): for every layer a block kind, two norms, a mixer and a
-feed-forward, each a `PartSpec` (kind + parameters), and a run order.  The classes behind
-the kinds are registered here.  A part gets its sizes and constants as parameters, declares
+A model is data (`models/spec.py`): an embedding, for every layer a block kind and the parts
+that this kind arranges (by role: two norms, a mixer and a feed-forward for the pre-norm block),
+a last norm and an output head, each a `PartSpec` (kind + parameters), and a run order.  The
+classes behind the kinds are registered here.  A part gets its sizes and constants as parameters, declares
 the tensors it wants (`weight_specs`), what it needs of the cache (`cache_need`,
 `state_need`), takes its tensors (`bind`) and computes (`forward`).  No part knows which
 model it is in: a new architecture is new specs, and new parts only where it computes
@@ -13,14 +14,19 @@ Interfaces (all tensors on the device; `ctx` is an `engine.context.StepContext`)
   Norm.add_norm(residual, delta, rows, write_back) -> y
       residual float32 [T, width] (+ delta of the engine's dtype), normalised; the sum is
       written back unless told otherwise; `rows` picks source rows
-  PositionEncoding.tables() -> dict                what the mixer's kernel needs (inv_freq)
+  Embedding.forward(ctx) -> stream                 float32 [T, width] from `ctx.token_ids`
+  Head.forward(hidden) -> logits                   float32 [rows, vocab]; `hidden` may be a `Prenormed`
+  PositionEncoding.rotation() -> Rotation | None   how the mixer's kernel rotates: frequencies, how many of the
+      head's elements turn, which elements pair, a factor on cosines and sines; None: no rotation
   PositionEncoding.rotations(ctx) -> table | None  optional: (cos, sin) of the step's tokens, made once a step
   Mixer.forward(h, ctx, cache, write_cache) -> y   h, y [T, width]; `cache` is the entry of
       `CacheStorage` that this run of the layer reads (and writes when `write_cache`)
   FeedForward.forward(h, ctx) -> y
   Block.forward(stream, pending, ctx, cache, write_cache) -> pending
       `stream` is the float32 residual stream [T, width], updated in place; `pending` is a
-      branch output not yet added (the next norm adds it), or None
+      branch output not yet added (the next norm adds it), or None.  A block kind names the
+      roles it arranges and the registry of each (`roles`); the layer's spec gives a part for
+      every role.  The part under the role `mixer`, if any, is the one that keeps a cache.
 
 Norms that ride on products.  With few rows a norm's own kernel costs more than its arithmetic,
 so parts may opt in to two hand-overs, both optional and both invisible to parts that do not:
@@ -66,6 +72,19 @@ class StateNeed:
 
     shape: tuple[int, ...]
     dtype: torch.dtype = torch.float32
+
+
+@dataclass(frozen=True)
+class Rotation:
+    """How a position encoding rotates query and key heads: element j of the first `rotary_dim` elements
+    pairs with j + rotary_dim / 2 ("split_half") or the elements pair two by two ("interleaved"); pair j
+    turns by position * inv_freq[j]; cosines and sines are multiplied by `magnitude`.  The kernels'
+    launchers refuse what the kernels do not do (`kernels.check_rotation`)."""
+
+    inv_freq: torch.Tensor           # [rotary_dim / 2] float32, on the device
+    rotary_dim: int
+    pairing: str = "split_half"
+    magnitude: float = 1.0
 
 
 @dataclass
@@ -155,13 +174,27 @@ class Norm(Part):
         raise NotImplementedError
 
 
+class Embedding(Part):
+    """Token ids -> the float32 residual stream."""
+
+    def forward(self, ctx) -> torch.Tensor:
+        raise NotImplementedError
+
+
+class Head(Part):
+    """Normalised rows -> float32 logits."""
+
+    def forward(self, hidden) -> torch.Tensor:
+        raise NotImplementedError
+
+
 class PositionEncoding(Part):
-    def tables(self) -> dict[str, Any]:
+    def rotation(self) -> Rotation | None:
         raise NotImplementedError
 
     def rotations(self, ctx):
         """The cosines and sines of the step's tokens, [T, head_dim / 2, 2] float32, if the encoding keeps them
-        for all of a step's layers; None: the mixer's kernel computes them from `tables()`."""
+        for all of a step's layers; None: the mixer's kernel computes them from `rotation()`."""
         return None
 
 
@@ -193,13 +226,30 @@ class FeedForward(Part):
 
 class Block(Part):
     links_norms = False           # `forward` takes `next_norm`, the norm that reads the stream after this block
+    # role -> registry: the parts that this arrangement puts together, built in this order; every role is
+    # also an attribute of the block.  The role `mixer`, if there is one, is the part that keeps a cache.
+    roles: dict[str, "Registry"] = {}
+    entry_role: str | None = None    # the role of the norm that reads the stream first (a block before this one may link to it)
 
-    def __init__(self, prefix: str, norm1: Norm, mixer: Mixer, norm2: Norm, feed_forward: FeedForward):
+    def __init__(self, prefix: str, **parts: Part):
         super().__init__(prefix)
-        self.norm1, self.mixer, self.norm2, self.feed_forward = norm1, mixer, norm2, feed_forward
+        missing, unknown = [r for r in self.roles if r not in parts], [r for r in parts if r not in self.roles]
+        if missing or unknown:
+            raise InvalidRequest(f"block {type(self).__name__} at {prefix!r}: missing parts {missing}, unknown parts {unknown}")
+        self.parts = {role: parts[role] for role in self.roles}
+        for role, part in self.parts.items():
+            setattr(self, role, part)
+
+    @property
+    def entry_norm(self):
+        return self.parts.get(self.entry_role) if self.entry_role else None
+
+    def cache_part(self):
+        """The part whose `cache_need` / `state_need` this layer's cache entry serves, or None."""
+        return self.parts.get("mixer")
 
     def children(self) -> list[Part]:
-        return [self.norm1, self.mixer, self.norm2, self.feed_forward]
+        return list(self.parts.values())
 
     def weight_specs(self) -> list[WeightSpec]:
         return [s for child in self.children() for s in child.weight_specs()]
@@ -238,6 +288,8 @@ class Registry:
         return self.get(spec.kind)(prefix=prefix, **spec.params, **extra)
 
 
+EMBEDDINGS = Registry("embedding")
+HEADS = Registry("output head")
 NORMS = Registry("norm")
 POSITION_ENCODINGS = Registry("position encoding")
 MIXERS = Registry("mixer")

@@ -7,7 +7,7 @@ with few rows, the branch's last product adds it and the norm rides on the produ
 (`Prenormed` in parts/base.py)."""
 from __future__ import annotations
 
-from .base import BLOCKS, Block, Prenormed, ResidualLink, observing, plain
+from .base import BLOCKS, FEED_FORWARDS, MIXERS, NORMS, Block, Prenormed, ResidualLink, observing, plain
 
 
 def _branch(part, h, stream, norm, *args):
@@ -22,6 +22,8 @@ def _branch(part, h, stream, norm, *args):
 @BLOCKS.register("pre_norm")
 class PreNormBlock(Block):
     links_norms = True
+    roles = {"norm1": NORMS, "mixer": MIXERS, "norm2": NORMS, "feed_forward": FEED_FORWARDS}
+    entry_role = "norm1"
 
     def forward(self, stream, pending, ctx, cache, write_cache=True, next_norm=None):
         if observing(ctx):

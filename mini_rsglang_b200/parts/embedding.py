@@ -7,11 +7,12 @@ import torch
 
 from .. import kernels
 from ..weights.spec import WeightSpec
-from .base import Part
+from .base import EMBEDDINGS, HEADS, Embedding, Head
 from .linear import linear
 
 
-class TokenEmbedding(Part):
+@EMBEDDINGS.register("token_embedding")
+class TokenEmbedding(Embedding):
     def __init__(self, prefix: str, vocab: int, width: int):
         super().__init__(prefix)
         self.vocab, self.width = int(vocab), int(width)
@@ -30,7 +31,8 @@ class TokenEmbedding(Part):
         return stream
 
 
-class OutputHead(Part):
+@HEADS.register("linear_head")
+class OutputHead(Head):
     def __init__(self, prefix: str, vocab: int, width: int, tied_to: str | None = None):
         super().__init__(prefix)
         self.vocab, self.width, self.tied_to = int(vocab), int(width), tied_to

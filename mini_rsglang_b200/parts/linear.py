@@ -13,15 +13,13 @@ import torch
 from .. import kernels
 from .base import Prenormed, ResidualLink
 
-_configured = False
 
-
-def _configure_library() -> None:
-    global _configured
-    if not _configured:
-        torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
-        torch.backends.cuda.matmul.allow_tf32 = False
-        _configured = True
+def configure_library_products() -> None:
+    """Process-wide settings of the library's products (torch's cuBLAS front end): float32 accumulation without
+    reduced-precision reductions, and no TF32.  The step function sets them once when it is built
+    (`ModelRunner.__init__`); they stay set for the process."""
+    torch.backends.cuda.matmul.allow_bf16_reduced_precision_reduction = False
+    torch.backends.cuda.matmul.allow_tf32 = False
 
 
 def few_rows(x, weight: torch.Tensor) -> bool:
@@ -49,7 +47,6 @@ def linear(x, weight: torch.Tensor, out_dtype: torch.dtype | None = None, into: 
     if few_rows(x, weight):
         out = torch.empty((x.shape[0], weight.shape[0]), dtype=out_dtype, device=x.device)
         return _tensor_core(x, weight, out, None, into)
-    _configure_library()
     if out_dtype is torch.float32:
         return torch.mm(x, weight.t(), out_dtype=torch.float32)
     return torch.mm(x, weight.t())

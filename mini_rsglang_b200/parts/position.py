@@ -3,13 +3,13 @@
 frequencies; angle = position * f_j, its cosine and sine and the rotation are float32.  The
 cosines and sines of a step's tokens are computed once and shared by every layer that rotates
 by the same frequencies (`rotations`); kernels that have the angles at hand compute them
-themselves from `tables()`."""
+themselves from the frequencies of `rotation()`."""
 from __future__ import annotations
 
 import torch
 
 from .. import kernels
-from .base import POSITION_ENCODINGS, PositionEncoding
+from .base import POSITION_ENCODINGS, PositionEncoding, Rotation
 
 
 @POSITION_ENCODINGS.register("rope")
@@ -34,8 +34,8 @@ class RotaryPosition(PositionEncoding):
         self.inv_freq = frequencies.to(runtime.device)
         self.shared_key = ("rotations", frequencies.numpy().tobytes())     # layers with the same frequencies share a step's table
 
-    def tables(self):
-        return {"inv_freq": self.inv_freq}
+    def rotation(self):
+        return Rotation(self.inv_freq, self.head_dim, "split_half", 1.0)
 
     def rotations(self, ctx):
         """[tokens, head_dim / 2, 2] float32 (cos, sin) for the step's positions; kept in `ctx.shared` for the
@@ -54,8 +54,8 @@ class NoPosition(PositionEncoding):
     def __init__(self, prefix: str = ""):
         super().__init__(prefix)
 
-    def tables(self):
-        return {"inv_freq": None}
+    def rotation(self):
+        return None
 
     def rotations(self, ctx):
         return None

@@ -6,7 +6,9 @@ compiled on a CPU-only machine without a Rust toolchain.  Every function cites t
 restates.  What can be compiled of the reference here is compared once: its kernels that compute
 one element a thread (`add`, `rope`, `swiglu`, `embedding`; crates/kernels/src/ops.cu) run on the
 CPU through a small shim (`tests/golden/make_golden.py`), and the bfloat16 mode below gives the
-same bits (`tests/test_plain.py`).  Whole sequences, no cache, no batching, one function per part.  Nothing here is
+same bits (`tests/test_plain.py`).  Whole sequences, no cache, no batching, one function per part; the functions compute
+where their tensors lie (the CPU, except for one test of real sizes that gives them tensors on the GPU so
+that float64 products of that size take seconds).  Nothing here is
 imported by the engine and nothing of the engine is imported here (weights are read with
 the `safetensors` package, the engine has a reader of its own).
 
@@ -129,7 +131,8 @@ def rope(ar: Arith, x: torch.Tensor, positions: torch.Tensor, theta: float) -> t
     f32(pos) * f_j, cos and sin rounded, each product rounded, the sum rounded."""
     d = x.shape[-1]
     half = d // 2
-    freq = rope_inverse_frequencies(d, theta)
+    freq = rope_inverse_frequencies(d, theta).to(x.device)
+    positions = positions.to(x.device)
     if ar.rounding is None:
         angle = positions.to(torch.float64)[:, None] * freq[None, :]
     else:
@@ -154,7 +157,7 @@ def causal_attention(ar: Arith, q: torch.Tensor, k: torch.Tensor, v: torch.Tenso
     nkv = k.shape[1]
     group = nq // nkv
     out = torch.empty_like(q)
-    rows = torch.arange(T)
+    rows = torch.arange(T, device=q.device)
     mask = rows[None, :] <= rows[:, None]
     if window > 0:
         mask &= rows[None, :] > rows[:, None] - window

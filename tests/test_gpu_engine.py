@@ -113,20 +113,7 @@ def test_recorded_decode_steps_equal_queued_ones(model_folders, name, dtype):
         assert torch.equal(results[0], results[1])
 
 
-def sharpen(folder, out, factor):
-    """The same model with q and k head-norm weights scaled: attention gets peaked, so a key
-    read from the wrong place moves the logits by far more than rounding."""
-    from safetensors.torch import load_file
-    from mini_rsglang_b200.weights import write_safetensors
-    tensors = load_file(os.path.join(folder, "model.safetensors"))
-    for name in tensors:
-        if name.endswith("q_norm.weight") or name.endswith("k_norm.weight"):
-            tensors[name] = (tensors[name].float() * factor).to(tensors[name].dtype)
-    os.makedirs(out, exist_ok=True)
-    write_safetensors(os.path.join(out, "model.safetensors"), tensors)
-    with open(os.path.join(folder, "config.json")) as f, open(os.path.join(out, "config.json"), "w") as g:
-        g.write(f.read())
-    return out
+sharpen = T.sharpen
 
 
 @pytest.mark.parametrize("name,dtype", [("A", "float32"), ("B", "float32"), ("D", "float32"), ("D", "bfloat16")])
@@ -346,3 +333,221 @@ def test_gate_up_product_for_many_rows_carries_the_activation(model_folders, mon
     T.check_rows(feed(runner, 1, tokens, [333]), want, "bfloat16", "many rows, whole")
     T.check_rows(feed(runner, 2, tokens, [200, 70, 63]), want, "bfloat16", "many rows, portions (the last one below the limit)")
     assert len(used) == 2 * 3      # two layers, three steps at or above 64 rows
+
+
+def test_a_failed_step_ends_every_request_and_gives_every_page_back(model_folders):
+    """The step function fails in the middle of a mixed run (the failure is made on the host: `forward` raises):
+    every stream gets an `Error`, every page and promise goes back, the counters say so, and the engine takes
+    no more requests (reference: crates/runtime/src/scheduler.rs:332-359 and its test at 614-635)."""
+    from mini_rsglang_b200 import BackendError, EngineStopped
+    from mini_rsglang_b200.engine import Error
+    folder = model_folders["A"]
+    limits = RuntimeConfig(max_seq_len=128, page_size=4, prefill_budget=8, max_running=2, max_waiting=8)
+    engine = EngineHandle.load(folder, 0, config=limits, dtype="float32", num_pages=40)
+    params = SamplingParams(max_tokens=12, ignore_eos=True)
+    streams = [engine.generate(GenerateRequest(TokenIds(p), params)) for p in ([3, 1, 4, 1, 5, 9, 2, 6, 5, 3, 5], [2, 7, 1], [8] * 20)]
+    for _ in range(4):
+        assert engine.run_step()
+    assert engine.scheduler.running() == 2 and engine.scheduler.waiting() == 1      # two run, the third waits
+    assert engine.runner.cache.free_pages() < 40
+
+    def broken(batch, observe=None):
+        raise BackendError("injected: the device fell over")
+
+    engine.runner.forward = broken
+    with pytest.raises(BackendError, match="injected"):
+        engine.run_step()
+    for stream in streams:
+        events = list(stream.events)
+        assert any(isinstance(e, Error) and "injected" in e.message for e in events)
+        assert isinstance(events[-1], Finished) and events[-1].reason == "error"
+    metrics = engine.metrics()
+    assert metrics["failed"] == 3 and metrics["healthy"] is False
+    assert metrics["free_pages"] == metrics["total_pages"] == 40 and metrics["running"] == 0 and metrics["waiting"] == 0
+    assert engine.runner.cache.reserved_pages() == 0 and engine.runner.cache.open_requests() == 0
+    engine.runner.cache.check_integrity()
+    with pytest.raises(EngineStopped):
+        engine.generate(GenerateRequest(TokenIds([1]), SamplingParams()))
+    with pytest.raises(EngineStopped):
+        engine.run_step()
+
+
+def test_a_wait_that_runs_out_fails_the_step_and_leaves_the_device_usable(model_folders):
+    """A kernel's bounded wait runs out (a one-warp kernel waits 65,536 clocks on a barrier at which nobody arrives,
+    then returns by itself): the error word is raised, the next check fails the step loudly, the word is clear
+    afterwards and the following steps are right.  Through the entry point the same word ends every request."""
+    from mini_rsglang_b200 import BackendError, kernels
+    from mini_rsglang_b200.engine import Error
+    folder = model_folders["D"]
+    runner = runner_for(folder, "D", "bfloat16")
+    tokens = T.requests_for(TINY["D"][0]["vocab_size"], [40], seed=5)["r0"]
+    want = plain(folder, tokens)
+    runner.cache.open(1)
+    runner.cache.extend(1, 30)
+    T.check_rows(runner.step([SequenceStep(1, tokens[:30], 0, [29])]).double().cpu(), want[29:30], "bfloat16", "before")
+    kernels.check_device_errors(certain=True)                     # nothing is wrong yet
+    assert kernels.wait_probe(1 << 16) is True
+    with pytest.raises(BackendError, match="gave up waiting"):
+        kernels.check_device_errors()
+    kernels.check_device_errors(certain=True)                     # read and cleared: all is well again
+    for p in range(30, 40):                                       # recorded decode steps after the failure
+        runner.cache.extend(1, p + 1)
+        got = runner.step([SequenceStep(1, [tokens[p]], p, [0])]).double().cpu()
+        T.check_rows(got, want[p:p + 1], "bfloat16", f"decode step at {p} after a wait ran out")
+    runner.cache.close(1)
+
+    limits = RuntimeConfig(max_seq_len=128, page_size=16, prefill_budget=16, max_running=2)
+    engine = EngineHandle.load(folder, 0, config=limits, dtype="bfloat16", num_pages=16)
+    stream = engine.generate(GenerateRequest(TokenIds(tokens[:20]), SamplingParams(max_tokens=8, ignore_eos=True)))
+    assert engine.run_step() and engine.run_step()
+    real = engine.runner.forward
+
+    def forward_with_a_stuck_wait(batch, observe=None):
+        logits = real(batch, observe)
+        kernels.wait_probe(1 << 16)
+        return logits
+
+    engine.runner.forward = forward_with_a_stuck_wait
+    with pytest.raises(BackendError, match="gave up waiting"):
+        engine.run_step()
+    events = list(stream.events)
+    assert any(isinstance(e, Error) for e in events) and events[-1].reason == "error"
+    assert engine.healthy is False and engine.metrics()["free_pages"] == 16
+    kernels.check_device_errors(certain=True)
+
+
+def test_dropping_a_stream_or_leaving_its_block_cancels_the_request(model_folders):
+    import gc
+    folder = model_folders["B"]
+    limits = RuntimeConfig(max_seq_len=128, page_size=16, prefill_budget=16, max_running=3)
+    engine = EngineHandle.load(folder, 0, config=limits, dtype="float32", num_pages=24)
+    long = SamplingParams(max_tokens=60, ignore_eos=True)
+    dropped = engine.generate(GenerateRequest(TokenIds([5, 6, 7]), long))
+    kept = engine.generate(GenerateRequest(TokenIds([9, 8, 7, 6]), SamplingParams(max_tokens=5, ignore_eos=True)))
+    assert isinstance(next(kept), Token)
+    del dropped
+    gc.collect()
+    with engine.generate(GenerateRequest(TokenIds([1, 2]), long)) as left:
+        assert isinstance(next(left), Token)
+    events = list(kept)
+    assert events[-1].reason == "length" and sum(isinstance(e, Token) for e in events) == 4
+    while engine.run_step():
+        pass
+    metrics = engine.metrics()
+    assert metrics["cancelled"] == 2 and metrics["completed"] == 1 and metrics["free_pages"] == 24
+    assert [e.reason for e in left.events if isinstance(e, Finished)] == ["cancelled"]
+    engine.shutdown()
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_recorded_decode_steps_across_classes_of_context_length(model_folders, dtype):
+    """Three requests decode from 480, 700 and 20 tokens of context until the first has passed 1,024: steps are
+    recorded once per (padded batch, class of context length), so contexts that cross 512, 1,024 and the
+    batch's changing make-up (all three, two of them, one alone) make several recordings, some made in the
+    middle of the run, with attention split counts planned for the class and block tables of 128 pages.
+    Every step's logits equal the plain implementation's; in float32 the recorded run equals, bit for bit,
+    a run that queues every kernel."""
+    name = "D"
+    folder = model_folders[name]
+    vocab = TINY[name][0]["vocab_size"]
+    starts = {"r0": 480, "r1": 700, "r2": 20}
+    reqs = T.requests_for(vocab, [1060, 1180, 760], seed=77)
+    want = {r: plain(folder, t) for r, t in reqs.items()}
+    results, keys = [], None
+    for record in (True, False):
+        runner = runner_for(folder, name, dtype, pages=200, max_seq_len=2048, running=4)
+        runner.record_decode = record
+        at = dict(starts)
+        for i, (r, tokens) in enumerate(reqs.items()):
+            runner.cache.open(i + 1)
+            runner.cache.extend(i + 1, at[r])
+            runner.step([SequenceStep(i + 1, tokens[:at[r]], 0, [])])
+        ids = {r: i + 1 for i, r in enumerate(reqs)}
+        rows, k = [], 0
+        while at["r0"] < 1040:
+            live = ["r2"] if k % 7 == 3 else (["r0", "r2"] if k % 5 == 2 else ["r0", "r1", "r2"])
+            batch = []
+            for r in live:
+                runner.cache.extend(ids[r], at[r] + 1)
+                batch.append(SequenceStep(ids[r], [reqs[r][at[r]]], at[r], [0]))
+            got = runner.step(batch).double().cpu()
+            T.check_rows(got, torch.stack([want[r][at[r]] for r in live]), dtype, f"step {k} at contexts {[at[r] for r in live]} (recorded={record})")
+            rows.append(got)
+            for r in live:
+                at[r] += 1
+            k += 1
+        assert at["r1"] > 1024 and at["r2"] > 512
+        if record:
+            keys = sorted(runner._records)
+            assert len(keys) >= 5, keys
+            assert {c for _, c in keys} == {512, 1024, 2048} and {b for b, _ in keys} == {1, 2, 4}
+            assert runner._records[keys[0]].ctx.block_tables[0].shape[1] == 128
+        else:
+            assert not runner._records
+        results.append(rows)
+    if dtype == "float32":
+        assert all(torch.equal(a, b) for a, b in zip(*results))
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_real_vocabulary_and_a_recorded_step_beyond_2048_tokens(dtype):
+    """Two layers with the sizes of a real checkpoint and its real vocabulary of 151,936: a prompt of 2,040 tokens
+    in portions of 512, then twelve decoded tokens (recorded steps whose context passes 2,048).  The logits of the
+    last prompt token and of every decoded token equal the plain implementation's, whose head product runs in
+    slices of the vocabulary, and the arg-max kernel picks the plain arg-max (or a logit within rounding of it)."""
+    from conftest import REAL_LAYERS
+    from mini_rsglang_b200 import kernels
+    from mini_rsglang_b200.models import config_from_dict
+    from mini_rsglang_b200.models.registry import model_spec_for
+    from mini_rsglang_b200.parts import Runtime
+    from mini_rsglang_b200.weights.random_init import random_weights
+
+    raw = dict(REAL_LAYERS, vocab_size=151936, max_position_embeddings=4096)
+    config = config_from_dict(raw)
+    spec = model_spec_for(config)
+    held = torch.bfloat16 if dtype == "bfloat16" else torch.float32
+    stored = random_weights(spec.weight_specs(), 33, torch.bfloat16, "cuda:0")         # a checkpoint's bfloat16 values
+    tensors = {n: (t if t.dtype is torch.float32 else t.to(held)) for n, t in stored.items()}
+    limits = RuntimeConfig(max_seq_len=2304, page_size=16, prefill_budget=512, max_running=2)
+    runner = ModelRunner(config, tensors, Runtime(torch.device("cuda:0"), held, 16), limits, num_pages=160, spec=spec)
+    prompt_len, steps = 2040, 12
+    tokens = T.requests_for(raw["vocab_size"], [prompt_len + steps], seed=12)["r0"]
+
+    # the plain implementation, part by part; the head in slices of 8,192 rows of the vocabulary
+    cfg = P.PlainConfig(raw["hidden_size"], raw["intermediate_size"], 2, raw["num_attention_heads"], raw["num_key_value_heads"],
+                        raw["head_dim"], raw["vocab_size"], raw["rms_norm_eps"], raw["rope_theta"], False)
+    weights = stored            # on the GPU: the plain functions compute where their tensors lie, in float64
+    ar = P.Arith(None)
+    ids = torch.tensor(tokens, device="cuda:0")
+    x = weights["model.embed_tokens.weight"][ids].double()
+    positions = torch.arange(len(tokens), device="cuda:0")
+    for layer in range(2):
+        x = P.block(ar, cfg, weights, layer, x, positions)
+    places = list(range(prompt_len - 1, prompt_len + steps))
+    hidden = P.rms_norm(ar, x[places], weights["model.norm.weight"], cfg.rms_norm_eps)
+    head = weights["lm_head.weight"]
+    want = torch.cat([hidden @ head[a:a + 8192].double().T for a in range(0, head.shape[0], 8192)], dim=1).cpu()
+    del x, hidden
+
+    runner.cache.open(1)
+    got, pos = [], 0
+    for n in (512, 512, 512, prompt_len - 1536):
+        runner.cache.extend(1, pos + n)
+        logits = runner.step([SequenceStep(1, tokens[pos:pos + n], pos, [n - 1] if pos + n == prompt_len else [])])
+        pos += n
+    got.append(logits.double().cpu())
+    picked = torch.empty(1, dtype=torch.int32, device="cuda:0")
+    choices = []
+    for p in range(prompt_len, prompt_len + steps):
+        runner.cache.extend(1, p + 1)
+        logits = runner.step([SequenceStep(1, [tokens[p]], p, [0])])
+        kernels.argmax(logits, picked)
+        choices.append(int(picked.item()))
+        got.append(logits.double().cpu())
+    got = torch.cat(got)
+    T.check_rows(got, want, dtype, "real vocabulary")
+    assert sorted(runner._records) == [(1, 2048), (1, 4096)]
+    for row, choice in zip(want[1:], choices):
+        best = P.greedy(row)
+        allowed = 2e-5 * max(1.0, row.abs().max().item()) if dtype == "float32" else 0.02 * row.abs().max().item()
+        assert choice == best or (row[best] - row[choice]).item() <= allowed

@@ -76,15 +76,45 @@ def test_rmsnorm_part(dtype):
     close(picked, P.rms_norm(P.Arith(None), (kept.double().cpu() + delta.double())[[5, 0]], w, eps), dtype, "rows")
 
 
-def test_rotary_part_tables():
+def test_rotary_part_states_its_rotation():
     for d, theta in ((48, 50000.0), (128, 1e6)):
         rope = POSITION_ENCODINGS.build(PartSpec("rope", {"head_dim": d, "theta": theta}), "p")
         assert rope.weight_specs() == []
         rope.bind({}, runtime(torch.float32))
-        got = rope.tables()["inv_freq"].double().cpu()
-        assert torch.equal(got, P.rope_inverse_frequencies(d, theta))
+        rotation = rope.rotation()
+        assert torch.equal(rotation.inv_freq.double().cpu(), P.rope_inverse_frequencies(d, theta))
+        assert (rotation.rotary_dim, rotation.pairing, rotation.magnitude) == (d, "split_half", 1.0)
     none = POSITION_ENCODINGS.build(PartSpec("none", {}), "p")
-    assert none.tables()["inv_freq"] is None and none.rotations(None) is None
+    assert none.rotation() is None and none.rotations(None) is None
+
+
+def test_a_rotation_that_the_kernels_do_not_compute_is_refused_when_the_mixer_takes_its_tensors():
+    """Another pairing, a rotation of part of a head and scaled cosines are a position encoding's to state and the
+    kernels' launchers' to refuse: the attention part asks once, at load, and raises instead of rotating wrongly."""
+    from mini_rsglang_b200 import InvalidRequest
+    from mini_rsglang_b200.parts import PositionEncoding, Rotation
+
+    class Odd(PositionEncoding):
+        def __init__(self, prefix, head_dim, rotary_dim, pairing, magnitude):
+            super().__init__(prefix)
+            self.args = (int(rotary_dim), pairing, float(magnitude))
+
+        def rotation(self):
+            return Rotation(torch.ones(self.args[0] // 2, device=DEV), *self.args)
+
+    POSITION_ENCODINGS.register("odd_rotation", Odd, replace=True)
+    try:
+        width, nq, nkv, d = 40, 2, 1, 16
+        for params, word in (({"rotary_dim": 8, "pairing": "split_half", "magnitude": 1.0}, "whole heads"),
+                             ({"rotary_dim": 16, "pairing": "interleaved", "magnitude": 1.0}, "pairing"),
+                             ({"rotary_dim": 16, "pairing": "split_half", "magnitude": 1.3}, "scaled")):
+            mixer = MIXERS.build(PartSpec("gqa_attention", {"width": width, "num_heads": nq, "num_kv_heads": nkv, "head_dim": d,
+                                                            "position": PartSpec("odd_rotation", dict(params, head_dim=d))}), "a.self_attn")
+            weights = {k: v.to(DEV) for k, v in attention_weights(width, nq, nkv, d, 3).items() if "norm" not in k}
+            with pytest.raises(InvalidRequest, match=word):
+                mixer.bind(weights, runtime(torch.float32))
+    finally:
+        POSITION_ENCODINGS.entries.pop("odd_rotation", None)
 
 
 def test_rotary_part_makes_a_steps_cosines_and_sines_once():

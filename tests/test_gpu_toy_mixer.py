@@ -1,8 +1,9 @@
-"""A mixer with a state of its own, a feed-forward with routing and a position encoding of another
-kind, all defined here and registered from outside: an architecture made of them and of the
-engine's attention is built, loaded from a folder and stepped in every cutting without a change
-to the package.  The toy parts compute with plain torch operations on the device; they are not
-part of any model of the engine."""
+"""A mixer with a state of its own, a feed-forward with routing, a position encoding of another
+kind, an embedding with a scale, an output head with a soft cap and a block with three norms, all
+defined here and registered from outside: an architecture made of them and of the engine's
+attention is built, loaded from a folder and stepped in every cutting without a change to the
+package.  The toy parts compute with plain torch operations on the device; they are not part of
+any model of the engine."""
 import json
 import os
 from dataclasses import dataclass
@@ -16,9 +17,9 @@ from mini_rsglang_b200 import RuntimeConfig
 from mini_rsglang_b200.config.model_config import ModelConfig
 from mini_rsglang_b200.engine import ModelRunner, SequenceStep
 from mini_rsglang_b200.models.registry import ARCHITECTURES, register_architecture
-from mini_rsglang_b200.models.spec import LayerSpec, ModelSpec, RunEntry
-from mini_rsglang_b200.parts import FEED_FORWARDS, MIXERS, POSITION_ENCODINGS, FeedForward, Mixer, PartSpec, \
-    PositionEncoding, StateNeed
+from mini_rsglang_b200.models.spec import LayerSpec, ModelSpec, RunEntry, pre_norm_layer
+from mini_rsglang_b200.parts import BLOCKS, EMBEDDINGS, FEED_FORWARDS, HEADS, MIXERS, NORMS, POSITION_ENCODINGS, Block, \
+    Embedding, FeedForward, Head, Mixer, PartSpec, PositionEncoding, Rotation, StateNeed
 from mini_rsglang_b200.weights import write_random_model
 from mini_rsglang_b200.weights.spec import WeightSpec
 
@@ -92,7 +93,7 @@ class RoutedFeedForward(FeedForward):
 
 class HalfSpeedRotary(PositionEncoding):
     """Rotary frequencies of another law (linear, not geometric): a position encoding of its own
-    that the engine's attention takes through the same `tables()`."""
+    that the engine's attention takes through the same `rotation()`."""
 
     def __init__(self, prefix, head_dim, slope):
         super().__init__(prefix)
@@ -102,8 +103,57 @@ class HalfSpeedRotary(PositionEncoding):
         super().bind(tensors, runtime)
         self.inv_freq = (self.slope / (1.0 + torch.arange(self.head_dim // 2, dtype=torch.float32))).to(runtime.device)
 
-    def tables(self):
-        return {"inv_freq": self.inv_freq}
+    def rotation(self):
+        return Rotation(self.inv_freq, self.head_dim)
+
+
+class ScaledEmbedding(Embedding):
+    """Table rows times a constant: an embedding of another kind than the engine's."""
+
+    def __init__(self, prefix, vocab, width, scale):
+        super().__init__(prefix)
+        self.vocab, self.width, self.scale = int(vocab), int(width), float(scale)
+
+    def weight_specs(self):
+        return [WeightSpec(self.name("weight"), (self.vocab, self.width))]
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.table = tensors[self.name("weight")]
+
+    def forward(self, ctx):
+        return self.table[ctx.token_ids.long()].float() * self.scale
+
+
+class CappedHead(Head):
+    """Logits squeezed into (-cap, cap) by a tanh; reads the embedding's table."""
+
+    def __init__(self, prefix, tied_to, cap):
+        super().__init__(prefix)
+        self.tied_to, self.cap = tied_to, float(cap)
+
+    def bind(self, tensors, runtime):
+        super().bind(tensors, runtime)
+        self.weight = tensors[self.tied_to]
+
+    def forward(self, hidden):
+        from mini_rsglang_b200.parts.base import plain
+        logits = plain(hidden).float() @ self.weight.float().T
+        return self.cap * torch.tanh(logits / self.cap)
+
+
+class SandwichBlock(Block):
+    """x + post_norm(mixer(norm1(x))), then + feed_forward(norm2(.)): three norms where the engine's block has two."""
+
+    roles = {"norm1": NORMS, "mixer": MIXERS, "post_norm": NORMS, "norm2": NORMS, "feed_forward": FEED_FORWARDS}
+    entry_role = "norm1"
+
+    def forward(self, stream, pending, ctx, cache, write_cache=True):
+        from mini_rsglang_b200.parts.base import plain
+        h = plain(self.norm1.add_norm(stream, pending))
+        a = self.post_norm.forward(self.mixer.forward(h, ctx, cache, write_cache))
+        h = plain(self.norm2.add_norm(stream, a))
+        return self.feed_forward.forward(h, ctx)
 
 
 @dataclass
@@ -115,21 +165,24 @@ class ToyConfig(ModelConfig):
     decay: float = 0.0
     slope: float = 0.0
     eps: float = 1e-5
+    embedding_scale: float = 1.0
+    logit_cap: float = 30.0
     MODEL_TYPES: ClassVar[tuple[str, ...]] = ("toy_mix",)
 
     @classmethod
     def from_dict(cls, raw):
         return cls(**{k: raw[k] for k in ("model_type", "architectures", "vocab_size", "max_position_embeddings",
-                                          "eos_token_id", "width", "inner", "heads", "head_dim", "decay", "slope", "eps")})
+                                          "eos_token_id", "width", "inner", "heads", "head_dim", "decay", "slope", "eps",
+                                          "embedding_scale", "logit_cap")})
 
     def validate(self):
         pass
 
 
 def toy_spec(c: ToyConfig) -> ModelSpec:
-    """Three layers: recurrence + routed experts, attention (linear rotary) + gated feed-forward,
-    recurrence + gated feed-forward; then the attention layer once more, reading the cache of its
-    first run."""
+    """Three layers: recurrence + routed experts in a block with three norms, attention (linear rotary) +
+    gated feed-forward, recurrence + gated feed-forward; then the attention layer once more, reading the
+    cache of its first run.  The embedding has a scale and the head a soft cap."""
     norm = PartSpec("rmsnorm", {"width": c.width, "eps": c.eps})
     recurrence = PartSpec("decaying_sum", {"width": c.width, "decay": c.decay})
     attention = PartSpec("gqa_attention", {"width": c.width, "num_heads": c.heads, "num_kv_heads": 1,
@@ -137,11 +190,16 @@ def toy_spec(c: ToyConfig) -> ModelSpec:
                                            "position": PartSpec("linear_rotary", {"head_dim": c.head_dim, "slope": c.slope})})
     routed = PartSpec("routed_pair", {"width": c.width, "inner": c.inner})
     gated = PartSpec("swiglu", {"width": c.width, "inner": c.inner})
-    layers = [LayerSpec("layers.0", "pre_norm", norm, recurrence, norm, routed, mixer_name="mixer"),
-              LayerSpec("layers.1", "pre_norm", norm, attention, norm, gated),
-              LayerSpec("layers.2", "pre_norm", norm, recurrence, norm, gated, mixer_name="mixer")]
-    return ModelSpec(vocab_size=c.vocab_size, width=c.width, embedding_prefix="embed", layers=layers, final_norm=norm,
-                     final_norm_prefix="norm", head_prefix="head", tie_head_to_embedding=True,
+    layers = [LayerSpec("layers.0", "sandwich",
+                        {"norm1": norm, "mixer": recurrence, "post_norm": norm, "norm2": norm, "feed_forward": routed},
+                        {"norm1": "input_layernorm", "post_norm": "post_mixer_norm", "norm2": "post_attention_layernorm",
+                         "feed_forward": "mlp"}),
+              pre_norm_layer("layers.1", norm, attention, norm, gated),
+              pre_norm_layer("layers.2", norm, recurrence, norm, gated, mixer_name="mixer")]
+    return ModelSpec(vocab_size=c.vocab_size, width=c.width,
+                     embedding=PartSpec("scaled_embedding", {"vocab": c.vocab_size, "width": c.width, "scale": c.embedding_scale}),
+                     embedding_prefix="embed", layers=layers, final_norm=norm, final_norm_prefix="norm",
+                     head=PartSpec("capped_head", {"tied_to": "embed.weight", "cap": c.logit_cap}), head_prefix="head",
                      run_order=[RunEntry(0), RunEntry(1), RunEntry(2), RunEntry(1, cache_of=1)])
 
 
@@ -150,14 +208,19 @@ def toy_folder(tmp_path_factory):
     MIXERS.register("decaying_sum", DecayingSum, replace=True)
     FEED_FORWARDS.register("routed_pair", RoutedFeedForward, replace=True)
     POSITION_ENCODINGS.register("linear_rotary", HalfSpeedRotary, replace=True)
+    EMBEDDINGS.register("scaled_embedding", ScaledEmbedding, replace=True)
+    HEADS.register("capped_head", CappedHead, replace=True)
+    BLOCKS.register("sandwich", SandwichBlock, replace=True)
     register_architecture("toy_mix", ToyConfig, toy_spec, replace=True)
     config = ToyConfig(model_type="toy_mix", architectures=["ToyMix"], vocab_size=97, max_position_embeddings=256,
-                       eos_token_id=1, width=40, inner=56, heads=2, head_dim=16, decay=0.8, slope=0.3, eps=1e-5)
+                       eos_token_id=1, width=40, inner=56, heads=2, head_dim=16, decay=0.8, slope=0.3, eps=1e-5,
+                       embedding_scale=3.0, logit_cap=2.5)
     folder = str(tmp_path_factory.mktemp("toy"))
     write_random_model(folder, config, seed=5, dtype=torch.float32)
     yield folder
     ARCHITECTURES.pop("toy_mix", None)
-    for registry, kind in ((MIXERS, "decaying_sum"), (FEED_FORWARDS, "routed_pair"), (POSITION_ENCODINGS, "linear_rotary")):
+    for registry, kind in ((MIXERS, "decaying_sum"), (FEED_FORWARDS, "routed_pair"), (POSITION_ENCODINGS, "linear_rotary"),
+                           (EMBEDDINGS, "scaled_embedding"), (HEADS, "capped_head"), (BLOCKS, "sandwich")):
         registry.entries.pop(kind, None)
 
 
@@ -219,12 +282,16 @@ def plain_toy(folder, tokens):
         g, u = h @ w[f"{root}.mlp.gate_proj.weight"].T, h @ w[f"{root}.mlp.up_proj.weight"].T
         return (g / (1 + torch.exp(-g)) * u) @ w[f"{root}.mlp.down_proj.weight"].T
 
-    x = w["embed.weight"][torch.tensor(tokens)]
+    x = w["embed.weight"][torch.tensor(tokens)] * c["embedding_scale"]
     for layer, mixer, ff in ((0, recurrence, routed), (1, attention, gated), (2, recurrence, gated), (1, attention, gated)):
         root = f"layers.{layer}"
-        x = x + mixer(norm(x, f"{root}.input_layernorm.weight"), root)
+        branch = mixer(norm(x, f"{root}.input_layernorm.weight"), root)
+        if layer == 0:                 # the block with three norms
+            branch = norm(branch, f"{root}.post_mixer_norm.weight")
+        x = x + branch
         x = x + ff(norm(x, f"{root}.post_attention_layernorm.weight"), root)
-    return norm(x, "norm.weight") @ w["embed.weight"].T
+    logits = norm(x, "norm.weight") @ w["embed.weight"].T
+    return c["logit_cap"] * torch.tanh(logits / c["logit_cap"])
 
 
 def test_toy_architecture_is_registered_built_and_stepped(toy_folder):
@@ -308,10 +375,12 @@ def window_spec(c: WindowConfig) -> ModelSpec:
                                           "position": PartSpec("rope", {"head_dim": c.head_dim, "theta": c.theta})})
 
     gated = PartSpec("swiglu", {"width": c.width, "inner": c.inner})
-    layers = [LayerSpec("model.layers.0", "pre_norm", norm, attention(c.window), norm, gated),
-              LayerSpec("model.layers.1", "pre_norm", norm, attention(0), norm, gated)]
-    return ModelSpec(vocab_size=c.vocab_size, width=c.width, embedding_prefix="model.embed_tokens", layers=layers,
-                     final_norm=norm, final_norm_prefix="model.norm", head_prefix="lm_head", tie_head_to_embedding=False)
+    layers = [pre_norm_layer("model.layers.0", norm, attention(c.window), norm, gated),
+              pre_norm_layer("model.layers.1", norm, attention(0), norm, gated)]
+    table = {"vocab": c.vocab_size, "width": c.width}
+    return ModelSpec(vocab_size=c.vocab_size, width=c.width, embedding=PartSpec("token_embedding", table),
+                     embedding_prefix="model.embed_tokens", layers=layers, final_norm=norm, final_norm_prefix="model.norm",
+                     head=PartSpec("linear_head", dict(table, tied_to=None)), head_prefix="lm_head")
 
 
 def plain_window(folder, tokens, window_of_layer):

@@ -3,8 +3,10 @@ allocator calls it: through its exported C symbol, with raw pointers and a strea
 (one that owns the whole device heap itself, or must not stall on an allocation) passes inputs and
 output only; the scratch between the two launches is the library's own fixed array.  The test
 checks the result against the engine's ordinary entry point, which takes scratch from the caller,
-on two calls in a row (the array keeps the first call's contents), and that a call too large for
-the fixed array is refused.  This file is collected last on purpose."""
+and against the attention formula written out with plain tensor operations, on two calls in a row
+(the array keeps the first call's contents); that the device's free memory is the same before and
+after a call (the driver's own count, which a cudaMalloc inside the library would move); and that
+a call too large for the fixed array is refused.  This file is collected last on purpose."""
 import ctypes
 
 import pytest
@@ -39,6 +41,26 @@ def build_case(seed, nq=8, nkv=2, d=64, page=16, contexts=(700, 333, 64, 1)):
                 tiles=torch.tensor(tiles, dtype=torch.int32, device=dev), nq=nq, nkv=nkv, d=d, page=page)
 
 
+def formula(case):
+    """softmax(q . k / sqrt(d)) . v over the keys of each request up to the query's position, read through
+    the block table, in float64."""
+    q, kc, vc = case["q"].double().cpu(), case["kc"].double().cpu(), case["vc"].double().cpu()
+    table, positions = case["table"].cpu(), case["positions"].cpu().tolist()
+    nq, nkv, d, page = case["nq"], case["nkv"], case["d"], case["page"]
+    out = torch.zeros_like(q)
+    for seq, first, tokens, _ in case["tiles"].cpu().tolist():
+        for row in range(first, first + tokens):
+            keys = positions[row] + 1
+            pages = table[seq, : -(-keys // page)].long()
+            for head in range(nq):
+                g = head // (nq // nkv)
+                k = kc[pages, g].reshape(-1, d)[:keys]
+                v = vc[pages, g].reshape(-1, d)[:keys]
+                p = torch.softmax(k @ q[row, head * d:(head + 1) * d] / d ** 0.5, dim=0)
+                out[row, head * d:(head + 1) * d] = p @ v
+    return out
+
+
 def call_static(case, splits, out):
     lib = case["lib"]
     fn = lib.mrs_attention_mma_keys_mode_static_scratch
@@ -59,13 +81,20 @@ def test_static_scratch_entry_matches_the_ordinary_one_twice_in_a_row():
         k.attention_mma_keys(case["q"], case["kc"], case["vc"], case["positions"], case["table"], case["tiles"], want,
                              case["nq"], case["nkv"], case["d"], 0, splits)
         got = torch.zeros_like(case["q"])
-        before = torch.cuda.memory_allocated()
+        exact = formula(case)
+        if call == 0:                # the first call on the device also looks up the array's address
+            assert call_static(case, splits, torch.zeros_like(case["q"])) == 0
+        torch.cuda.synchronize()
+        free_before = torch.cuda.mem_get_info()[0]           # the driver's count of free bytes on the device
         code = call_static(case, splits, got)
         assert code == 0, f"entry point returned {code}"
         torch.cuda.synchronize()
-        assert torch.cuda.memory_allocated() == before
+        assert torch.cuda.mem_get_info()[0] == free_before, "the call changed the device's free memory"
+        scale = max(1.0, want.float().abs().max().item())
         err = (got.float() - want.float()).abs().max().item()
-        assert err <= 2 ** -7 * max(1.0, want.float().abs().max().item()), f"call {call}: max error {err}"
+        assert err <= 2 ** -7 * scale, f"call {call}: max error {err} against the ordinary entry point"
+        err = (got.double().cpu() - exact).abs().max().item()
+        assert err <= 2 ** -7 * scale, f"call {call}: max error {err} against the formula"
         assert got.float().abs().max().item() > 0
 
 

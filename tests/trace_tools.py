@@ -145,6 +145,22 @@ def renumber(trace: Trace, first: int, prefix: str) -> Trace:
     return out
 
 
+def sharpen(folder, out, factor):
+    """The same model with q and k head-norm weights scaled: attention gets peaked, so a key
+    read from the wrong place moves the logits by far more than rounding."""
+    from safetensors.torch import load_file
+    from mini_rsglang_b200.weights import write_safetensors
+    tensors = load_file(os.path.join(folder, "model.safetensors"))
+    for name in tensors:
+        if name.endswith("q_norm.weight") or name.endswith("k_norm.weight"):
+            tensors[name] = (tensors[name].float() * factor).to(tensors[name].dtype)
+    os.makedirs(out, exist_ok=True)
+    write_safetensors(os.path.join(out, "model.safetensors"), tensors)
+    with open(os.path.join(folder, "config.json")) as f, open(os.path.join(out, "config.json"), "w") as g:
+        g.write(f.read())
+    return out
+
+
 # ------------------------------------------------------------------------------ gates
 # 32-bit path against the exact (float64) plain implementation: the engine sums in float32, so
 # a logit differs by rounding of order 1e-6 of the row's scale; 2e-5 leaves room for long sums.
