@@ -1,6 +1,8 @@
 """Benchmark of the engine on one B200: decode tokens a second at the Qwen3-8B shape.
 
     python bench.py [--gpus 1] [--steps K] [--warmup W] [--impl ours|reference]
+    python bench.py --shape 14b --batch 16 --context 8192        decode at the Qwen3-14B shape
+    python bench.py --shape 0.6b --continuous                    continuous batching at the Qwen3-0.6B shape
 
 A "step" is one decode step: every live request gets its next token.  The default run has the
 layer sizes of the Qwen3-8B shape with seeded random weights (bfloat16), a batch of 8 and a
@@ -14,6 +16,13 @@ tokens.  One JSON line is printed:
   roofline   bytes a decode step must read (every weight once and the live requests' cache)
              divided by its time, against the measured copy bandwidth;
   points     decode at batch 1 and batch 64, each with the same fraction of the copy bandwidth.
+  prefill also carries `chunked_4x512_ms`: the same prompt in four steps of 512 tokens.
+`--shape 14b` (40 layers, width 5120, 40 / 8 heads, feed-forward 17408) and `--shape 0.6b` (28 layers, width 1024,
+16 / 8 heads, feed-forward 3072, tied head) run the same measurement at those sizes, with `--batch` and `--context`.
+`--continuous` is the serving workload: 64 requests with seeded prompt lengths uniform in 16 to 2,048 tokens and 64
+generated tokens each, through `EngineHandle` with prompts cut into portions under a budget of 512 tokens a step; its
+line reports prompt and generated tokens a second, the mean step time and the share of steps that were replayed
+from a recording.
 Peaks come from MEASURED_PEAKS.json when the file exists.  The engine runs on one GPU; for
 --gpus N > 1 a line says so and the exit code is 2.  The reference arm cannot run here (the
 reference is a Rust workspace without a Python package, and supports no sm_100 device), so
@@ -35,7 +44,11 @@ QWEN3_8B = dict(model_type="qwen3", architectures=["Qwen3ForCausalLM"], hidden_s
                 num_hidden_layers=36, num_attention_heads=32, num_key_value_heads=8, head_dim=128, vocab_size=151936,
                 max_position_embeddings=40960, rms_norm_eps=1e-6, rope_theta=1000000.0, tie_word_embeddings=False,
                 hidden_act="silu", eos_token_id=151645)
-FULL_LAYERS = 36
+QWEN3_06B = dict(QWEN3_8B, hidden_size=1024, intermediate_size=3072, num_hidden_layers=28, num_attention_heads=16,
+                 num_key_value_heads=8, head_dim=128, tie_word_embeddings=True)
+QWEN3_14B = dict(QWEN3_8B, hidden_size=5120, intermediate_size=17408, num_hidden_layers=40, num_attention_heads=40,
+                 num_key_value_heads=8, head_dim=128)
+SHAPES = {"8b": ("Qwen3-8B shape", QWEN3_8B), "0.6b": ("Qwen3-0.6B shape", QWEN3_06B), "14b": ("Qwen3-14B shape", QWEN3_14B)}
 FALLBACK_PEAKS = {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "source": "fallback"}
 
 
@@ -98,10 +111,73 @@ def model_numbers(cfg: dict, layers: int) -> dict:
     nq, nkv, d = cfg["num_attention_heads"], cfg["num_key_value_heads"], cfg["head_dim"]
     per_layer = (nq + 2 * nkv) * d * h + h * nq * d + 2 * i * h + h * i
     return {"layer_params": per_layer, "head_params": v * h,
-            "weight_bytes": 2 * (layers * per_layer + v * h),
+            "weight_bytes": 2 * (layers * per_layer + v * h),       # a tied head reads the embedding table: the same bytes
             "kv_bytes_per_token": layers * 2 * nkv * d * 2,
             "linear_flops_per_token": 2 * layers * per_layer,
             "attn_flops_per_pair": 4 * nq * d * layers}
+
+
+def continuous_run(args, torch, shape_name: str, cfg: dict, peak: dict) -> dict:
+    """The serving workload of the 0.6B configuration: `--requests` requests (64) whose prompt lengths are drawn
+    uniformly from 16 to 2,048 (seeded), `--output-tokens` generated tokens each (64), all submitted at once to
+    `EngineHandle`; prompts are cut into portions under a budget of 512 tokens a step and run beside the decoded
+    tokens of the requests that are further on.  A first, smaller wave runs untimed so that every kernel has been
+    built and every batch size has been recorded once."""
+    import random
+
+    from mini_rsglang_b200 import RuntimeConfig, SamplingParams
+    from mini_rsglang_b200.engine import EngineHandle
+    from mini_rsglang_b200.models import config_from_dict
+
+    config = config_from_dict(cfg)
+    requests, out_tokens, budget, page = args.requests, args.output_tokens, args.prefill_budget, 16
+    rng = random.Random(20240611)
+    lengths = [rng.randint(16, 2048) for _ in range(requests)]
+    max_running = min(requests, args.max_running)
+    max_seq_len = 2048 + out_tokens
+    pages = max_running * (-(-max_seq_len // page) + 1) + 8
+    limits = RuntimeConfig(max_seq_len=max_seq_len, page_size=page, prefill_budget=budget, max_running=max_running,
+                           max_waiting=max(256, requests))
+    engine = EngineHandle.from_random(config, seed=1, dtype="bfloat16", config=limits, num_pages=pages)
+    runner = engine.runner
+    params = SamplingParams(max_tokens=out_tokens, ignore_eos=True)
+
+    def prompts(ns):
+        return [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in ns]
+
+    engine.generate_many(prompts(lengths[:max(8, requests // 4)] + [16] * max_running), params)     # warm-up wave, untimed
+    work = prompts(lengths)
+    torch.cuda.synchronize()
+    steps0, recorded0, h2d0 = runner.steps, runner.recorded_steps, runner.h2d_bytes
+    sampler = ClockSampler()
+    sampler.start()
+    t0 = time.perf_counter()
+    results = engine.generate_many(work, params)
+    torch.cuda.synchronize()
+    elapsed = time.perf_counter() - t0
+    clocks = sampler.stop()
+    steps = runner.steps - steps0
+    generated = sum(r.completion_tokens for r in results)
+    prompt_tokens = sum(lengths)
+    assert all(r.finish_reason == "length" and r.completion_tokens == out_tokens for r in results)
+    engine.shutdown()
+    total = prompt_tokens + generated
+    return {
+        "metric": f"continuous batching tok/s, {requests} requests of 16-2048 prompt tokens, {out_tokens} generated each ({shape_name})",
+        "value": round(total / elapsed, 1), "unit": "tokens/s (prompt + generated)", "n_gpus": 1, "steps": steps, "warmup": 1,
+        "ms_per_step": round(elapsed / steps * 1e3, 4), "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+        "dtype": "bf16", "data": "synthetic: seeded random weights, seeded prompt lengths, uniform random token ids",
+        "prompt_tokens_per_s": round(prompt_tokens / elapsed, 1), "generated_tokens_per_s": round(generated / elapsed, 1),
+        "prompt_tokens": prompt_tokens, "generated_tokens": generated, "elapsed_s": round(elapsed, 4),
+        "recorded_step_share": round((runner.recorded_steps - recorded0) / max(steps, 1), 4),
+        "h2d_bytes_per_step": (runner.h2d_bytes - h2d0) // max(steps, 1),
+        "config": {"model": shape_name, "layers": cfg["num_hidden_layers"], "layers_of_shape": cfg["num_hidden_layers"],
+                   "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
+                   "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
+                   "tied_head": cfg["tie_word_embeddings"], "requests": requests, "max_running": max_running,
+                   "prefill_budget": budget, "output_tokens": out_tokens, "page_size": page, "parallelism": "single GPU",
+                   "timing": "wall clock around EngineHandle.generate_many, host tokens in and out", "peaks": peak["source"]},
+        "clocks": clocks, "impl": "ours"}
 
 
 def main() -> int:
@@ -110,11 +186,17 @@ def main() -> int:
     parser.add_argument("--steps", type=int, default=64)
     parser.add_argument("--warmup", type=int, default=8)
     parser.add_argument("--impl", choices=["ours", "reference"], default="ours")
+    parser.add_argument("--shape", choices=sorted(SHAPES), default="8b", help="layer sizes: Qwen3-8B (the default line), 0.6B or 14B")
     parser.add_argument("--batch", type=int, default=8)
     parser.add_argument("--context", type=int, default=4096)
-    parser.add_argument("--layers", type=int, default=FULL_LAYERS, help="fewer layers than the 36 of the shape (named in config)")
+    parser.add_argument("--layers", type=int, default=0, help="fewer layers than the shape has (named in config); 0: all of them")
     parser.add_argument("--no-points", action="store_true", help="skip the batch-1 and batch-64 points")
     parser.add_argument("--no-e2e", action="store_true")
+    parser.add_argument("--continuous", action="store_true", help="the continuous-batching workload instead of the decode measurement")
+    parser.add_argument("--requests", type=int, default=64, help="--continuous: requests")
+    parser.add_argument("--output-tokens", type=int, default=64, help="--continuous: generated tokens a request")
+    parser.add_argument("--prefill-budget", type=int, default=512, help="--continuous: tokens a step")
+    parser.add_argument("--max-running", type=int, default=64, help="--continuous: requests in flight at most")
     args = parser.parse_args()
 
     if args.impl == "reference":
@@ -135,12 +217,19 @@ def main() -> int:
     from mini_rsglang_b200.models import config_from_dict
 
     torch.cuda.set_device(0)
-    cfg = dict(QWEN3_8B, num_hidden_layers=args.layers)
-    config = config_from_dict(cfg)
-    numbers = model_numbers(cfg, args.layers)
+    shape_name, shape = SHAPES[args.shape]
+    full_layers = shape["num_hidden_layers"]
+    layers = args.layers or full_layers
+    cfg = dict(shape, num_hidden_layers=layers)
     peak = peaks()
+    if args.continuous:
+        print(json.dumps(continuous_run(args, torch, shape_name, cfg, peak)))
+        return 0
+    config = config_from_dict(cfg)
+    numbers = model_numbers(cfg, layers)
     context, batch = args.context, args.batch
-    point_batches = [] if args.no_points else [1, 64]
+    default_line = args.shape == "8b"
+    point_batches = [] if args.no_points or not default_line else [1, 64]
     max_batch = max([batch] + point_batches)
     page = 16
     pages = max_batch * (-(-context // page)) + 2 * (-(-2048 // page)) + 8
@@ -165,25 +254,34 @@ def main() -> int:
         torch.cuda.synchronize()
         return start.elapsed_time(end)
 
-    # ---------------------------------------------------------------- prefill of 2,048 tokens in one step
+    # ---------------------------------------------------------------- prefill of 2,048 tokens: in one step, and in four of 512
     prefill_tokens = 2048
     prompt = random_tokens(prefill_tokens)
-    prefill_ms = []
-    for trial in range(3 + 3):
-        request = 10_000 + trial
+
+    def prefill_once(request, portion):
         runner.cache.open(request)
-        runner.cache.extend(request, prefill_tokens)
-        ms = timed(lambda: runner.forward([SequenceStep(request, prompt, 0, [prefill_tokens - 1])]), 1)
-        runner.cache.close(request)
-        if trial >= 3:
-            prefill_ms.append(ms)
-    prefill_time = statistics.median(prefill_ms)
+        for at in range(0, prefill_tokens, portion):
+            runner.cache.extend(request, at + portion)
+            runner.forward([SequenceStep(request, prompt[at:at + portion], at, [portion - 1] if at + portion == prefill_tokens else [])])
+
+    def prefill_median(portion, first_id):
+        samples = []
+        for trial in range(3 + 3):
+            ms = timed(lambda: prefill_once(first_id + trial, portion), 1)
+            runner.cache.close(first_id + trial)
+            if trial >= 3:
+                samples.append(ms)
+        return statistics.median(samples)
+
+    prefill_time = prefill_median(prefill_tokens, 10_000)
+    chunked_time = prefill_median(512, 11_000)
     prefill_flops = (prefill_tokens * numbers["linear_flops_per_token"]
                      + numbers["attn_flops_per_pair"] * prefill_tokens * (prefill_tokens + 1) // 2
                      + 2 * numbers["head_params"])
     prefill = {"value": round(prefill_tokens / prefill_time * 1e3, 1), "tokens": prefill_tokens,
                "ms": round(prefill_time, 3), "frac": round(prefill_flops / (prefill_time * 1e-3) / (peak["bf16_tflops"] * 1e12), 4),
-               "flops": prefill_flops, "peak_tflops": peak["bf16_tflops"]}
+               "flops": prefill_flops, "peak_tflops": peak["bf16_tflops"], "chunked_4x512_ms": round(chunked_time, 3),
+               "chunked_4x512_value": round(prefill_tokens / chunked_time * 1e3, 1)}
 
     # ---------------------------------------------------------------- decode, timed on the device
     def decode_run(b, steps, warmup, sample_clocks=False):
@@ -264,11 +362,11 @@ def main() -> int:
         engine.shutdown()
 
     line = {
-        "metric": "decode tok/s at batch 8, context 4096 (Qwen3-8B shape)", "value": round(main_run["tokens_per_s"], 1),
+        "metric": f"decode tok/s at batch {batch}, context {context} ({shape_name})", "value": round(main_run["tokens_per_s"], 1),
         "unit": "tokens/s", "n_gpus": 1, "steps": args.steps, "warmup": args.warmup,
         "ms_per_step": round(main_run["ms_per_step"], 4), "higher_is_better": True, "scaling": "weak",
         "vs_baseline": None, "dtype": "bf16", "data": "synthetic: seeded random weights, uniform random token ids",
-        "config": {"model": "Qwen3-8B shape", "layers": args.layers, "layers_of_shape": FULL_LAYERS,
+        "config": {"model": shape_name, "layers": layers, "layers_of_shape": full_layers,
                    "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"],
                    "kv_heads": cfg["num_key_value_heads"], "head_dim": cfg["head_dim"],
                    "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"], "global_batch": batch,

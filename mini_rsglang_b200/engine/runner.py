@@ -146,6 +146,7 @@ class ModelRunner:
         self._records: dict[tuple[int, int], _Recorded] = {}
         self._graph_pool = None
         self.steps = 0
+        self.recorded_steps = 0     # steps that were replayed from a recording
         self.h2d_bytes = 0      # bytes of batch metadata copied to the device so far
 
     # ------------------------------------------------------------------ construction
@@ -270,6 +271,7 @@ class ModelRunner:
                 and all(len(s.tokens) == 1 and len(s.want) == 1 for s in sequences))
 
     def _forward_recorded(self, sequences) -> torch.Tensor:
+        self.recorded_steps += 1
         real = len(sequences)
         bucket = 1 << (real - 1).bit_length()
         longest = max(s.start_pos + 1 for s in sequences)

@@ -3,10 +3,13 @@
 It rests on the formulas of the reference's source (mirthfulLee/mini-rsglang), not on a run
 of it: the reference's model code is Rust over a CUDA backend and cannot be imported or
 compiled on a CPU-only machine without a Rust toolchain.  Every function cites the lines it
-restates.  What can be compiled of the reference here is compared once: its kernels that compute
-one element a thread (`add`, `rope`, `swiglu`, `embedding`; crates/kernels/src/ops.cu) run on the
-CPU through a small shim (`tests/golden/make_golden.py`), and the bfloat16 mode below gives the
-same bits (`tests/test_plain.py`).  Whole sequences, no cache, no batching, one function per part; the functions compute
+restates.  What can be compiled of the reference here is compared once: its one CUDA source
+(crates/kernels/src/ops.cu) runs on the CPU through small shims.  The kernels that compute one
+element a thread (`add`, `rope`, `swiglu`, `embedding`) run thread by thread
+(`tests/golden/make_golden.py`); the kernels that work a block together (`rms`, `attention`,
+`argmax`) run as one fiber a thread, and a whole two-layer forward pass is put together from those
+kernels in the order of the reference's Rust source (`tests/golden/make_model_golden.py`).  The
+bfloat16 mode below gives the same bits as all of them (`tests/test_plain.py`).  Whole sequences, no cache, no batching, one function per part; the functions compute
 where their tensors lie (the CPU, except for one test of real sizes that gives them tensors on the GPU so
 that float64 products of that size take seconds).  Nothing here is
 imported by the engine and nothing of the engine is imported here (weights are read with
