@@ -189,6 +189,7 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
                 tma_load_5d(v_dst + lane * copy_bytes, &v_map, &full[s], 0, row, 0, kv_head, max(my_page, 0));
             }
         }
+        if (in_cluster) cluster_sync_all();      // nobody leaves a cluster while a peer may still write into its shared memory
         return;
     }
 
@@ -350,8 +351,10 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
             asm volatile("fence.acq_rel.cluster;" ::: "memory");
             for (int j = 0; j < splits; ++j) arrive_in_cluster(in_cta(smem_u32(merge_bar), j));
         }
-        mbar_wait_cluster(merge_bar, 0);              // all shares of this CTA's columns have arrived (or the time ran out)
-        for (int idx = threadIdx.x; idx < rows * (cols / 4); idx += 32 * CONSUMER_WARPS) {
+        // all shares of this CTA's columns have arrived, or the time ran out: then nothing is stored (the error
+        // word is raised and the host fails the step)
+        const bool merged = mbar_wait_cluster(merge_bar, 0);
+        for (int idx = threadIdx.x; merged && idx < rows * (cols / 4); idx += 32 * CONSUMER_WARPS) {
             const int row = idx / (cols / 4), col = (idx % (cols / 4)) * 4;
             float m = -CUDART_INF_F;
             for (int s = 0; s < splits; ++s) m = fmaxf(m, incoming_ml[(s * ROWS + row) * 2]);
@@ -369,6 +372,9 @@ __global__ void __launch_bounds__(THREADS) attention_decode_kernel(
             *reinterpret_cast<__nv_bfloat162*>(dst) = __floats2bfloat162_rn(acc.x * inv, acc.y * inv);
             *reinterpret_cast<__nv_bfloat162*>(dst + 2) = __floats2bfloat162_rn(acc.z * inv, acc.w * inv);
         }
+        // Every wait above is bounded, so every thread of the cluster gets here; a CTA whose wait ran out stays
+        // until its peers have sent what they still had to send into its shared memory.
+        cluster_sync_all();
         return;
     }
     const size_t first_slot = ((size_t)blockIdx.x * nkv + kv_head) * splits * ROWS;
