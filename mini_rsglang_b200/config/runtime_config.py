@@ -15,6 +15,7 @@ class RuntimeConfig:
     max_running: int = 32        # requests that hold cache pages at the same time
     max_waiting: int = 256       # requests queued before admission
     prefix_cache: bool = False   # accepted for the reference's flag; sharing is not built
+    record_mixed_steps: bool = True   # steps with prompt portions are recorded with fixed shapes and replayed
 
     def validate(self) -> None:
         limits = (self.max_seq_len, self.page_size, self.prefill_budget, self.max_running,

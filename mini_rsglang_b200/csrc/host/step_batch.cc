@@ -23,16 +23,21 @@ API const char* mrs_step_last_error() { return g_step_error.c_str(); }
 // Inputs: n_seq sequences (request id, first position, token count), their tokens and wanted places
 // (flat, in sequence order).  pad_to > 0 (single tokens only): the batch is filled up to pad_to
 // sequences with rows that write nothing, every row's logits are wanted, block tables are
-// fixed_width wide.  Output: buf (capacity cap ints) and layout:
+// fixed_width wide.  pad_rows > 0 (with pad_to > 0; any batch): the step is filled up to pad_to
+// sequences and pad_rows token rows; the added sequences have no rows, the added rows (token 0 at
+// position 0 of the last sequence) write nothing and belong to no attention tile, and there are pad_to
+// wanted rows: the real ones first (at most one a sequence), then row 0 again and again.  The shapes
+// of such a step depend on pad_to, pad_rows and fixed_width alone.
+// Output: buf (capacity cap ints) and layout:
 //   [0] tokens T  [1] sequences B  [2] wanted rows R  [3] 1 when every sequence brings one token
 //   [4..11] offsets of ids, pos, seq, q_start, ctx_len, state slot, want, tiles
 //   [12 + 3g ..] per group: offset of the table, its width, offset of the write slots
 //   [12 + 3G] longest context after the step   [13 + 3G] longest run of tokens of a sequence
 // Returns the ints used, kNeedMore (-7) with the need in layout[0], or kInvalid (-6) with a message.
-API int64_t mrs_step_build(void* cache, int n_seq, const int64_t* requests, const int64_t* start_pos, const int32_t* counts,
-                           const int32_t* tokens, const int32_t* want_counts, const int32_t* want, int pad_to,
-                           int fixed_width, int64_t max_seq_len, int64_t vocab, int32_t* buf, int64_t cap,
-                           int64_t* layout) {
+API int64_t mrs_step_build_padded(void* cache, int n_seq, const int64_t* requests, const int64_t* start_pos,
+                                  const int32_t* counts, const int32_t* tokens, const int32_t* want_counts,
+                                  const int32_t* want, int pad_to, int pad_rows, int fixed_width, int64_t max_seq_len,
+                                  int64_t vocab, int32_t* buf, int64_t cap, int64_t* layout) {
     try {
         auto* m = static_cast<mrs::CacheManager*>(cache);
         const int G = m->num_groups();
@@ -90,19 +95,29 @@ API int64_t mrs_step_build(void* cache, int n_seq, const int64_t* requests, cons
                     return mrs::kInvalid;
                 }
             }
+            if (pad_rows > 0 && want_counts[i] > 1) {
+                g_step_error = "a step padded to fixed shapes takes at most one wanted place a sequence";
+                return mrs::kInvalid;
+            }
             wanted += want_counts[i];
             real_tokens += n;
             if (n != 1) decode = false;
             if (start + n > longest) longest = start + n;
             if (n > longest_run) longest_run = n;
         }
+        const bool fixed_rows = pad_rows > 0;
+        if (fixed_rows) decode = false;            // a list of attention tiles is planned for such a step by its mixers
         const int64_t B = pad_to > 0 ? pad_to : n_seq;
         const int64_t pads = B - n_seq;
-        if (pads < 0 || (pads > 0 && !decode)) {
+        if (pads < 0 || (pads > 0 && !decode && !fixed_rows)) {
             g_step_error = "only batches of single decoded tokens can be padded";
             return mrs::kInvalid;
         }
-        const int64_t T = real_tokens + pads;
+        if (fixed_rows && (pad_to <= 0 || pad_rows < real_tokens)) {
+            g_step_error = "a step padded to fixed shapes needs pad_to sequences and at least its own rows";
+            return mrs::kInvalid;
+        }
+        const int64_t T = fixed_rows ? pad_rows : real_tokens + pads;
         const int64_t R = pad_to > 0 ? B : wanted;
         if (fixed_width > 0)
             for (int g = 0; g < G; ++g) {
@@ -150,7 +165,7 @@ API int64_t mrs_step_build(void* cache, int n_seq, const int64_t* requests, cons
                 pos[row + t] = (int32_t)(start + t);
                 seq[row + t] = i;
             }
-            if (pad_to <= 0)
+            if (pad_to <= 0 || fixed_rows)
                 for (int k = 0; k < want_counts[i]; ++k) want_rows[w + k] = (int32_t)(row + want[w + k]);
             w += want_counts[i];
             ctx_len[i] = (int32_t)(start + n);
@@ -158,14 +173,23 @@ API int64_t mrs_step_build(void* cache, int n_seq, const int64_t* requests, cons
             row += n;
             q_start[i + 1] = (int32_t)row;
         }
-        for (int64_t i = n_seq; i < B; ++i) {      // rows that write nothing: token 0 at position 0, state slot -1
-            ids[row] = 0, pos[row] = 0, seq[row] = (int32_t)i;
-            ctx_len[i] = 1, slot[i] = -1;
-            ++row;
-            q_start[i + 1] = (int32_t)row;
+        if (fixed_rows) {
+            for (int64_t i = n_seq; i < B; ++i) {  // sequences without rows
+                ctx_len[i] = 0, slot[i] = -1;
+                q_start[i + 1] = (int32_t)row;
+            }
+            for (int64_t r = row; r < T; ++r) ids[r] = 0, pos[r] = 0, seq[r] = (int32_t)(B - 1);
+            for (int64_t k = w; k < R; ++k) want_rows[k] = 0;
+        } else {
+            for (int64_t i = n_seq; i < B; ++i) {  // rows that write nothing: token 0 at position 0, state slot -1
+                ids[row] = 0, pos[row] = 0, seq[row] = (int32_t)i;
+                ctx_len[i] = 1, slot[i] = -1;
+                ++row;
+                q_start[i + 1] = (int32_t)row;
+            }
+            if (pad_to > 0)
+                for (int64_t i = 0; i < B; ++i) want_rows[i] = (int32_t)i;
         }
-        if (pad_to > 0)
-            for (int64_t i = 0; i < B; ++i) want_rows[i] = (int32_t)i;
         if (decode) {                              // one attention tile a sequence; none for a padding row
             std::memset(tiles, 0, (size_t)(4 * B) * sizeof(int32_t));
             for (int i = 0; i < n_seq; ++i) tiles[4 * i] = i, tiles[4 * i + 1] = i, tiles[4 * i + 2] = 1;
@@ -188,12 +212,21 @@ API int64_t mrs_step_build(void* cache, int n_seq, const int64_t* requests, cons
             }
             for (int64_t i = n_seq; i < B; ++i) {  // a padding row reads page 0 and its result is dropped
                 std::memset(table + i * width, 0, (size_t)width * sizeof(int32_t));
-                slots[r++] = -1;
+                if (!fixed_rows) slots[r++] = -1;
             }
+            for (; fixed_rows && r < T; ++r) slots[r] = -1;
         }
         return cursor;
     } catch (const std::exception& e) {
         g_step_error = e.what();
         return -100;
     }
+}
+
+API int64_t mrs_step_build(void* cache, int n_seq, const int64_t* requests, const int64_t* start_pos, const int32_t* counts,
+                           const int32_t* tokens, const int32_t* want_counts, const int32_t* want, int pad_to,
+                           int fixed_width, int64_t max_seq_len, int64_t vocab, int32_t* buf, int64_t cap,
+                           int64_t* layout) {
+    return mrs_step_build_padded(cache, n_seq, requests, start_pos, counts, tokens, want_counts, want, pad_to, 0,
+                                 fixed_width, max_seq_len, vocab, buf, cap, layout);
 }

@@ -10,6 +10,8 @@ from dataclasses import dataclass, field
 
 import torch
 
+from ..parts.base import StepFacts
+
 
 @dataclass
 class StepContext:
@@ -42,3 +44,7 @@ class StepContext:
     label: str = ""                    # the running layer's label ("layer3"), set by the model while observing
     # what the parts of one step share (the rotations' cosines and sines); the model empties it when a step begins
     shared: dict = field(default_factory=dict)
+    # A step with fixed shapes (recorded once, replayed with other contents): the host's facts of the running
+    # step, and for every plan that `facts.plans` holds the device copy of its words, at an address that stays.
+    facts: StepFacts | None = None
+    plan_views: dict | None = None

@@ -27,7 +27,7 @@ from ..parts.base import Runtime
 from ..parts.linear import configure_library_products
 from ..weights.loader import load_weights
 from ..weights.random_init import random_weights
-from .context import StepContext
+from .context import StepContext, StepFacts
 
 
 @dataclass
@@ -83,12 +83,18 @@ class _Staging:
 
 
 class _Recorded:
-    """One recorded decode step: its context buffers (fixed addresses), graph and logits."""
+    """One recorded step: its context buffers (fixed addresses), graph and logits."""
 
     def __init__(self, device: torch.device):
         self.staging = _Staging(device, fixed=True)
         self.ctx = self.graph = self.logits = None
         self.launches = 0          # the engine's own kernels in the recording
+        self.plan_offset = 0       # a step with fixed shapes: where the mixers' plans lie in the staging buffer
+
+
+def fixed_rows(rows: int) -> int:
+    """Rows of a recorded step that holds `rows` real ones: 16, 32, 64, then multiples of 64."""
+    return max(16, 1 << (rows - 1).bit_length()) if rows <= 64 else -(-rows // 64) * 64
 
 
 class ModelRunner:
@@ -132,10 +138,11 @@ class ModelRunner:
         self.storage = CacheStorage(kv_needs, state_needs, groups, group_of, limits.max_running, runtime)
         self._staging = _Staging(self.device)
         lib = host_api()
-        self._step_build = lib.mrs_step_build
+        self._step_build = lib.mrs_step_build_padded
         self._step_build.restype = ctypes.c_int64
         self._step_build.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 6 + [
-            ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64, ctypes.c_void_p]
+            ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64,
+            ctypes.c_void_p]
         self._step_error = lib.mrs_step_last_error
         self._step_error.restype = ctypes.c_char_p
         # mixers written in Python read the requests' state slots from a host list
@@ -143,11 +150,18 @@ class ModelRunner:
         # steps of single decoded tokens are recorded and replayed when every mixer allows it
         self.record_decode = self.model.replayable()
         self._largest_bucket = min(256, 1 << (limits.max_running - 1).bit_length())
-        self._records: dict[tuple[int, int], _Recorded] = {}
+        self._records: dict[tuple, _Recorded] = {}
         self._graph_pool = None
+        # steps with prompt portions: recorded with fixed shapes once a key has been seen `record_after` times
+        self.record_mixed = self.record_decode and limits.record_mixed_steps
+        self.record_after = 1
+        self.max_records = 96
+        self.mixed_rows_max = 1024
+        self._seen: dict[tuple, int] = {}
         self.steps = 0
         self.recorded_steps = 0     # steps that were replayed from a recording
         self.h2d_bytes = 0      # bytes of batch metadata copied to the device so far
+        self.h2d_last_layout_words = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -170,9 +184,11 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ one step
     def _fill_step(self, sequences: Sequence[SequenceStep], pad_to: int | None, table_width: int | None,
-                   staging: "_Staging"):
+                   staging: "_Staging", pad_rows: int = 0, extra: np.ndarray | None = None):
         """Checks the batch, lays its facts out in the staging buffer (the host library does both) and
-        starts the copy to the device.  Returns the layout, the device buffer and the token counts."""
+        starts the copy to the device.  `extra`: int32 words that follow the layout in the same copy (the
+        mixers' plans of a step with fixed shapes).  Returns the layout, the device buffer, the first
+        positions, the token counts and the words that the layout took."""
         if not sequences:
             raise InvalidRequest("empty batch or KV pool")
         n = len(sequences)
@@ -193,34 +209,56 @@ class ModelRunner:
         widest = table_width or -(-self.limits.max_seq_len // self.limits.page_size)
         # a padded step has `pad_to` rows and sequences whatever the number of real ones: its need, and with it
         # the size of a recorded step's fixed buffers, depends on `pad_to` alone
-        guess = step_layout_bound(pad_to or int(counts.sum()), pad_to or n, widest, G)
+        more = 0 if extra is None else int(extra.size)
+        guess = step_layout_bound(pad_rows or pad_to or int(counts.sum()), pad_to or n, widest, G)
         for _ in range(2):
-            host, dev = staging.reserve(guess)
+            host, dev = staging.reserve(guess + more)
             used = self._step_build(self.cache.handle, n, requests.ctypes.data, starts.ctypes.data, counts.ctypes.data,
                                     tokens.ctypes.data, want_counts.ctypes.data, want.ctypes.data, int(pad_to or 0),
-                                    int(table_width or 0), self.limits.max_seq_len, self.config.vocab_size,
-                                    host.data_ptr(), host.numel(), layout.ctypes.data)
+                                    int(pad_rows), int(table_width or 0), self.limits.max_seq_len, self.config.vocab_size,
+                                    host.data_ptr(), host.numel() - more, layout.ctypes.data)
             if used != -7:
                 break
             guess = int(layout[0])
         if used < 0:
             message = self._step_error().decode("utf-8", "replace")
             raise (BackendError if used == -100 else InvalidRequest)(message)
-        staging.upload(int(used))
-        self.h2d_bytes += 4 * int(used)
-        return layout, dev, starts, counts
+        used = int(used)
+        self.h2d_last_layout_words = used
+        if more:
+            host[used:used + more] = torch.from_numpy(extra)
+        staging.upload(used + more)
+        self.h2d_bytes += 4 * (used + more)
+        return layout, dev, starts, counts, used
 
     def build_context(self, sequences: Sequence[SequenceStep], pad_to: int | None = None,
-                      table_width: int | None = None, staging: _Staging | None = None) -> StepContext:
+                      table_width: int | None = None, staging: _Staging | None = None, pad_rows: int = 0,
+                      facts: StepFacts | None = None) -> StepContext:
         """Checks the batch and copies what the kernels need to know about it to the device in
         one transfer; the checking and the layout are the host library's (`csrc/host/step_batch.cc`).
         With `pad_to` (single decoded tokens only) the batch is filled up to that many sequences
         with rows that write nothing and whose results nobody reads, block tables get the given
         fixed width and every row's logits are produced: the shapes and addresses of such a
-        context depend on `pad_to` alone, so its kernels can be recorded once and replayed."""
-        layout, dev, starts, counts = self._fill_step(sequences, pad_to, table_width, staging or self._staging)
+        context depend on `pad_to` alone, so its kernels can be recorded once and replayed.
+        With `pad_rows` as well (any batch with at most one wanted place a sequence) the step has `pad_to`
+        sequences, `pad_rows` rows and `pad_to` wanted rows, the added ones without effect; what the mixers
+        planned from `facts` follows the layout in the same copy and is found in `plan_views`."""
+        extra = None
+        if facts is not None and facts.plans:
+            extra = np.concatenate([plan.words() for plan in facts.plans.values()])
+        layout, dev, starts, counts, used = self._fill_step(sequences, pad_to, table_width, staging or self._staging,
+                                                            pad_rows, extra)
         n, G = len(sequences), len(self.groups)
         T, B, R, decode = (int(v) for v in layout[:4])
+        plan_views = None
+        if facts is not None:
+            plan_views, at = {}, used
+            for key, plan in facts.plans.items():
+                words = plan.words().size
+                plan_views[key] = dev[at:at + words].view(-1, 4)
+                at += words
+            if not any(len(s.want) for s in sequences):
+                R = 0                        # nothing is wanted: the head is skipped
 
         def dview(offset, count, shape=None):
             t = dev[int(offset):int(offset) + count]
@@ -241,7 +279,7 @@ class ModelRunner:
             max_query_len=int(layout[13 + 3 * G]), max_context_len=int(layout[12 + 3 * G]),
             fresh=(starts == 0).tolist() + [True] * pads,
             decode_tiles=dview(layout[11], 4 * B, (B, 4)) if decode else None, real_sequences=real,
-            want_every_row=bool(decode) and R == T)
+            want_every_row=bool(decode) and R == T, facts=facts, plan_views=plan_views)
 
     def forward(self, sequences: Sequence[SequenceStep], observe=None) -> torch.Tensor | None:
         """Runs the batch; returns the logits [wanted, vocab] (float32, on the device) in the
@@ -255,6 +293,10 @@ class ModelRunner:
         self.steps += 1
         if observe is None and self._replayable(sequences):
             return self._forward_recorded(sequences)
+        if observe is None and self.record_mixed:
+            shapes = self._fixed_shapes(sequences)
+            if shapes is not None:
+                return self._forward_fixed(sequences, *shapes)
         ctx = self.build_context(sequences)
         ctx.observe = observe
         with torch.no_grad():
@@ -287,27 +329,86 @@ class ModelRunner:
             kernels.launch_count += record.launches
             return record.logits[:real]
         ctx = self.build_context(sequences, pad_to=bucket, table_width=width, staging=record.staging)
-        if record.graph is None:
-            ctx.max_context_len = context_class      # launches are planned for the class, not for this step
-            record.ctx = ctx
-            stream = torch.cuda.current_stream()
-            side = torch.cuda.Stream(device=self.device)
-            side.wait_stream(stream)
-            with torch.no_grad(), torch.cuda.stream(side):
-                self.model.forward(ctx, self.storage)          # first use of every kernel outside the recording
-            stream.wait_stream(side)
-            graph = torch.cuda.CUDAGraph()
-            counted = kernels.launch_count
-            with torch.no_grad(), torch.cuda.graph(graph, pool=self._graph_pool):
-                record.logits = self.model.forward(ctx, self.storage)
-            record.launches = kernels.launch_count - counted     # recorded, not run
-            kernels.launch_count = counted
-            if self._graph_pool is None:
-                self._graph_pool = graph.pool()
-            record.graph = graph
+        ctx.max_context_len = context_class      # launches are planned for the class, not for this step
+        self._record(record, ctx)
         record.graph.replay()
         kernels.launch_count += record.launches
         return record.logits[:real]
+
+    def _record(self, record: _Recorded, ctx: StepContext) -> None:
+        """Runs the context's step once outside a recording (first use of every kernel, scratch buffers at
+        their sizes), then records it."""
+        record.ctx = ctx
+        stream = torch.cuda.current_stream()
+        side = torch.cuda.Stream(device=self.device)
+        side.wait_stream(stream)
+        with torch.no_grad(), torch.cuda.stream(side):
+            self.model.forward(ctx, self.storage)
+        stream.wait_stream(side)
+        graph = torch.cuda.CUDAGraph()
+        counted = kernels.launch_count
+        with torch.no_grad(), torch.cuda.graph(graph, pool=self._graph_pool):
+            record.logits = self.model.forward(ctx, self.storage)
+        record.launches = kernels.launch_count - counted     # recorded, not run
+        kernels.launch_count = counted
+        if self._graph_pool is None:
+            self._graph_pool = graph.pool()
+        record.graph = graph
+
+    # ------------------------------------------------------------------ recorded steps with prompt portions
+    # A step that holds prompt portions launches as many kernels as a decode step, and for a small model the
+    # host needs longer to queue them than the device to run them.  Such a step is recorded too, with fixed
+    # shapes: rows padded to `fixed_rows`, sequences to a power of two (the added ones without rows), as many
+    # wanted rows as sequences, block tables at their full width.  What else decides the launches (how many
+    # attention tiles of which kind) the mixers state as the step's signature, planned on the host from the
+    # step's facts; their plans travel with the layout in the step's one copy to the device, to addresses that
+    # stay.  A key is recorded when it comes back (`record_after`), so one-off shapes cost nothing.
+    def _fixed_shapes(self, sequences):
+        n = len(sequences)
+        if n > self._largest_bucket:
+            return None
+        q_start, start_pos, longest, wanted = [0], [], 0, 0
+        for s in sequences:
+            count = len(s.tokens)
+            if count <= 0 or len(s.want) > 1:
+                return None
+            q_start.append(q_start[-1] + count)
+            start_pos.append(s.start_pos)
+            longest = max(longest, s.start_pos + count)
+            wanted += len(s.want)
+        if q_start[-1] > self.mixed_rows_max or longest > self.limits.max_seq_len:
+            return None
+        rows, bucket = fixed_rows(q_start[-1]), 1 << (n - 1).bit_length()
+        context_class = max(512, 1 << (longest - 1).bit_length())
+        facts = StepFacts(q_start, start_pos, context_class, padded_sequences=bucket, padded_tokens=rows)
+        key = (rows, bucket, context_class, wanted > 0, self.model.step_signature(facts))
+        if key not in self._records:
+            seen = self._seen[key] = self._seen.get(key, 0) + 1
+            if seen <= self.record_after or len(self._records) >= self.max_records:
+                return None
+        return key, facts, rows, bucket, context_class
+
+    def _forward_fixed(self, sequences, key, facts, rows, bucket, context_class):
+        self.recorded_steps += 1
+        wanted = sum(len(s.want) for s in sequences)
+        record = self._records.get(key)
+        if record is None:
+            record = self._records[key] = _Recorded(self.device)
+        width = -(-self.limits.max_seq_len // self.limits.page_size)
+        if record.graph is not None:
+            extra = np.concatenate([plan.words() for plan in facts.plans.values()]) if facts.plans else None
+            used = self._fill_step(sequences, bucket, width, record.staging, rows, extra)[4]
+            if used != record.plan_offset:
+                raise BackendError("a recorded step's layout moved")
+        else:
+            ctx = self.build_context(sequences, pad_to=bucket, table_width=width, staging=record.staging, pad_rows=rows,
+                                     facts=facts)
+            ctx.max_context_len = context_class
+            record.plan_offset = self.h2d_last_layout_words
+            self._record(record, ctx)
+        record.graph.replay()
+        kernels.launch_count += record.launches
+        return record.logits[:wanted] if wanted else None
 
     def step(self, sequences: Sequence[SequenceStep], observe=None) -> torch.Tensor | None:
         """`forward`, then wait for the device: when it returns, the cache holds the step's

@@ -25,6 +25,7 @@ class Model:
         # cache entry that each run of the order reads; runs that borrow a cache write nothing
         self.cache_entry = [e.cache_of if e.cache_of is not None else i for i, e in enumerate(spec.run_order)]
         self.writes_cache = [e.cache_of is None for e in spec.run_order]
+        self._cache_parts = [b.cache_part() for b in self.blocks if b.cache_part() is not None]
 
     def _need(self, entry, which: str):
         part = self.blocks[entry.layer].cache_part()
@@ -39,6 +40,10 @@ class Model:
     def replayable(self) -> bool:
         """Whether steps of single decoded tokens may be recorded: every part that keeps a cache allows it."""
         return all(getattr(b.cache_part(), "replayable", False) for b in self.blocks if b.cache_part() is not None)
+
+    def step_signature(self, facts) -> tuple:
+        """What the mixers say decides a step's launches beyond its shapes, layer by layer."""
+        return tuple(part.step_signature(facts) for part in self._cache_parts)
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

@@ -7,23 +7,51 @@ attention reads the cache through the request's block table; one projection brin
 heads back to the model width."""
 from __future__ import annotations
 
+from dataclasses import dataclass
+
+import numpy as np
 import torch
 
 from .. import kernels
 from ..errors import InvalidRequest
 from ..weights.spec import WeightSpec
-from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, Prenormed, observing
+from .base import MIXERS, NORMS, POSITION_ENCODINGS, KVNeed, Mixer, PartSpec, Prenormed, StepFacts, observing
 from .linear import few_rows, linear
 
 
-def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, window: int = 0, key_block: int = 128,
-                         sms: int = 1):
-    """Cuts the step's sequences into tiles for the tensor-core kernels: sequences with few
+@dataclass
+class TileLists:
+    """A step's attention tiles as the host planned them: `narrow` for the kernels for few rows, `wide` for the
+    others, entries (sequence, first row of the step, tokens, share word).  For a step with fixed shapes
+    `narrow_cap` and `wide_cap` are the rows of the two lists on the device (filled up with entries of no
+    tokens, which the kernels skip); 0 there: the list is empty and its kernel is not launched."""
+
+    narrow: list
+    wide: list
+    longest_narrow: int
+    shared: bool
+    narrow_cap: int = 0
+    wide_cap: int = 0
+
+    def signature(self) -> tuple:
+        return (self.narrow_cap, self.wide_cap, self.shared)
+
+    def words(self) -> np.ndarray:
+        """The lists as the int32 words of the device copy of a step with fixed shapes."""
+        out = np.zeros((self.narrow_cap + self.wide_cap, 4), dtype=np.int32)
+        if self.narrow:
+            out[:len(self.narrow)] = self.narrow
+        if self.wide:
+            out[self.narrow_cap:self.narrow_cap + len(self.wide)] = self.wide
+        return out.reshape(-1)
+
+
+def attention_tile_lists(facts: StepFacts, group: int, wide_rows: int, kv_heads: int = 1, window: int = 0,
+                         key_block: int = 128, sms: int = 1) -> TileLists:
+    """Cuts the step's sequences into tiles for the tensor-core kernels, on the host: sequences with few
     query rows (decoded tokens, short portions) go to the kernels for few rows in tiles of
     16 // group tokens, the others in tiles of wide_rows // group tokens, those with the most
-    keys first.  Returns (narrow tiles, wide tiles, longest context of a narrow tile, whether
-    wide tiles share their keys) with the tile lists on the device, or None for an empty list.
-    The plan is kept in the context for the other layers of the step.
+    keys first.  The lists are kept in `facts.plans` for the other layers of the step.
 
     The tcgen05 kernel for wide tiles takes two tiles of rows a CTA and one CTA an SM.  A short
     portion (a slice of a long prompt under the token budget) makes fewer CTAs than the GPU has
@@ -33,16 +61,13 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
     with one tile has no partner on the tensor cores, so this pays only while SMs would idle).
     `key_block` is the kernel's block of keys and `sms` the device's multiprocessors, as the kernel's
     library and the device state them."""
-    plans = ctx.__dict__.setdefault("_attention_plans", {})
     key = (group, wide_rows, kv_heads, window, key_block)
-    if key in plans:
-        return plans[key]
+    if key in facts.plans:
+        return facts.plans[key]
     narrow_tokens = kernels.MMA_ROWS_NARROW // group
     wide_tokens = wide_rows // group
-    if ctx.decode_tiles is not None and narrow_tokens >= 1:     # single tokens: the step's own tile list
-        plans[key] = (ctx.decode_tiles, None, ctx.max_context_len, False)
-        return plans[key]
-    lengths = [ctx.host_q_start[i + 1] - ctx.host_q_start[i] for i in range(ctx.num_sequences)]
+    real = len(facts.start_pos)
+    lengths = [facts.q_start[i + 1] - facts.q_start[i] for i in range(real)]
     tensor_core = wide_rows == kernels.PREFILL_TC_ROWS
     entries = sum(-(-n // wide_tokens) for n in lengths if n > narrow_tokens)
     spare = sms // max(entries * kv_heads, 1) if tensor_core else 1      # CTAs an entry may become
@@ -50,14 +75,14 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
     longest_narrow = 0
     shared = False
     for i, n in enumerate(lengths):
-        first = ctx.host_q_start[i]
+        first = facts.q_start[i]
         if narrow_tokens >= 1 and n <= narrow_tokens:
             narrow.append((i, first, n, 0))
-            longest_narrow = max(longest_narrow, ctx.host_start_pos[i] + n)
+            longest_narrow = max(longest_narrow, facts.start_pos[i] + n)
             continue
         for start in range(0, n, wide_tokens):
             tokens = min(wide_tokens, n - start)
-            begin = ctx.host_start_pos[i] + start                        # position of the entry's first token
+            begin = facts.start_pos[i] + start                           # position of the entry's first token
             first_key = max(0, begin - window + 1) if window else 0
             blocks = -(-(begin + tokens) // key_block) - first_key // key_block
             shares = min(spare, blocks // 4, 255) if spare >= 2 else 1
@@ -71,10 +96,42 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
                 wide.append((i, first + start, tokens, 0, begin))
     wide.sort(key=lambda t: -t[4])          # a tile late in a long request walks the most keys: start it first (stable:
     wide = [t[:4] for t in wide]            # the shares of an entry stay together and in their order)
+    lists = TileLists(narrow, wide, longest_narrow, shared)
+    if facts.padded_sequences:              # fixed shapes: the device lists have a length that many steps share
+        lists.narrow_cap = facts.padded_sequences if narrow else 0
+        lists.wide_cap = max(16, 1 << (len(wide) - 1).bit_length()) if wide else 0
+    facts.plans[key] = lists
+    return lists
+
+
+def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, window: int = 0, key_block: int = 128,
+                         sms: int = 1):
+    """The step's tile lists on the device: (narrow tiles, wide tiles, longest context of a narrow tile,
+    whether wide tiles share their keys), None for an empty list.  The plan is kept in the context for the
+    other layers of the step.  A step of single decoded tokens brings its own list; a step with fixed shapes
+    finds the lists where the step function copied them (`ctx.plan_views`), at addresses that stay."""
+    plans = ctx.__dict__.setdefault("_attention_plans", {})
+    key = (group, wide_rows, kv_heads, window, key_block)
+    if key in plans:
+        return plans[key]
+    narrow_tokens = kernels.MMA_ROWS_NARROW // group
+    if ctx.decode_tiles is not None and narrow_tokens >= 1:     # single tokens: the step's own tile list
+        plans[key] = (ctx.decode_tiles, None, ctx.max_context_len, False)
+        return plans[key]
+    facts = ctx.facts
+    if facts is None:
+        real = ctx.real_sequences or ctx.num_sequences
+        facts = StepFacts(ctx.host_q_start[:real + 1], ctx.host_start_pos[:real], ctx.max_context_len)
+    lists = attention_tile_lists(facts, group, wide_rows, kv_heads, window, key_block, sms)
+    if ctx.plan_views is not None:
+        both = ctx.plan_views[key]
+        plans[key] = (both[:lists.narrow_cap] if lists.narrow_cap else None, both[lists.narrow_cap:] if lists.wide_cap else None,
+                      ctx.max_context_len, lists.shared)
+        return plans[key]
     device = ctx.positions.device
-    both = torch.tensor(narrow + wide, dtype=torch.int32).view(-1, 4).pin_memory().to(device, non_blocking=True)
-    plans[key] = (both[:len(narrow)] if narrow else None, both[len(narrow):] if wide else None,
-                  min(longest_narrow, ctx.max_context_len), shared)
+    both = torch.tensor(lists.narrow + lists.wide, dtype=torch.int32).view(-1, 4).pin_memory().to(device, non_blocking=True)
+    plans[key] = (both[:len(lists.narrow)] if lists.narrow else None, both[len(lists.narrow):] if lists.wide else None,
+                  min(lists.longest_narrow, ctx.max_context_len), lists.shared)
     return plans[key]
 
 
@@ -95,6 +152,15 @@ def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident
     return max(1, power)
 
 
+def tile_plan_arguments(d: int, group: int, page_size: int, nkv: int, window: int, device) -> tuple:
+    """What the planner is asked for an attention of these sizes (bfloat16, head size a multiple of 16): rows of
+    a wide tile and the block of keys as the kernel that will run states them."""
+    sms = kernels.sm_count(device)
+    if kernels.attention_prefill_tc_supported(d, group, page_size):
+        return (group, kernels.PREFILL_TC_ROWS, nkv, window, kernels.attention_prefill_tc_key_block(d), sms)
+    return (group, kernels.MMA_ROWS_WIDE, nkv, window, 128, sms)
+
+
 def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) -> None:
     """Attention of this step's queries over their requests' cached keys and values.  bfloat16
     with a head size that is a multiple of 16 runs on the tensor cores: decoded tokens and short
@@ -110,11 +176,7 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
     page_size = cache.k.shape[2]
     sms = kernels.sm_count(q.device)
     tensor_core_rows = kernels.attention_prefill_tc_supported(d, group, page_size)
-    if tensor_core_rows:
-        narrow, wide, longest, shared = plan_attention_tiles(ctx, group, kernels.PREFILL_TC_ROWS, nkv, window,
-                                                             kernels.attention_prefill_tc_key_block(d), sms)
-    else:
-        narrow, wide, longest, shared = plan_attention_tiles(ctx, group, kernels.MMA_ROWS_WIDE, nkv, window, sms=sms)
+    narrow, wide, longest, shared = plan_attention_tiles(ctx, *tile_plan_arguments(d, group, page_size, nkv, window, q.device))
     if narrow is not None:
         splits = choose_splits(narrow.shape[0], nkv, longest, sms)
         if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
@@ -180,6 +242,15 @@ class GroupedQueryAttention(Mixer):
         if rotation is not None:          # the kernels' launchers say what they rotate; anything else is refused here, at load
             kernels.check_rotation(self.d, rotation.rotary_dim, rotation.pairing, rotation.magnitude)
         self.inv_freq = rotation.inv_freq if rotation is not None else None
+
+    def step_signature(self, facts: StepFacts):
+        """Which launches a step with these facts makes, beyond what its shapes say: the lengths of its tile lists
+        and whether entries share their keys (None: no list is planned, one kernel takes every row)."""
+        group = self.nq // self.nkv
+        if self.runtime.dtype is not torch.bfloat16 or not kernels.attention_mma_supported(self.d, group):
+            return None
+        arguments = tile_plan_arguments(self.d, group, self.runtime.page_size, self.nkv, self.window, self.o.device)
+        return attention_tile_lists(facts, *arguments).signature()
 
     def forward(self, h, ctx, cache, write_cache=True, into=None):
         tokens = h.shape[0]

@@ -21,6 +21,8 @@ Interfaces (all tensors on the device; `ctx` is an `engine.context.StepContext`)
   PositionEncoding.rotations(ctx) -> table | None  optional: (cos, sin) of the step's tokens, made once a step
   Mixer.forward(h, ctx, cache, write_cache) -> y   h, y [T, width]; `cache` is the entry of
       `CacheStorage` that this run of the layer reads (and writes when `write_cache`)
+  Mixer.step_signature(facts) -> hashable | None  optional: what, beyond the shapes, decides a step's launches
+      (`facts` is a `StepFacts`); steps with fixed shapes are recorded once per signature
   FeedForward.forward(h, ctx) -> y
   Block.forward(stream, pending, ctx, cache, write_cache) -> pending
       `stream` is the float32 residual stream [T, width], updated in place; `pending` is a
@@ -85,6 +87,22 @@ class Rotation:
     rotary_dim: int
     pairing: str = "split_half"
     magnitude: float = 1.0
+
+
+@dataclass
+class StepFacts:
+    """What the host knows about a step before anything of it is on the device: the rows of every real
+    sequence and where each starts in its request.  A part plans its launches from these (an attention cuts
+    the sequences into tiles) and may be asked beforehand which launches a step will make
+    (`step_signature`): a step whose shapes are fixed is recorded once per signature and replayed.
+    `plans` keeps what was planned, by the planner's own key, for the layers that share it."""
+
+    q_start: list[int]                 # [real sequences + 1] first row of each real sequence
+    start_pos: list[int]               # [real sequences] position of its first token of this step
+    longest_context: int               # tokens of the longest sequence after the step, or the class it falls in
+    padded_sequences: int = 0          # sequences of a step with fixed shapes (the real ones come first), else 0
+    padded_tokens: int = 0             # its rows
+    plans: dict = field(default_factory=dict)
 
 
 @dataclass
@@ -207,6 +225,11 @@ class Mixer(Part):
     takes_prenormed = False       # `forward` takes a `Prenormed` as `h`
 
     def cache_need(self) -> KVNeed | None:
+        return None
+
+    def step_signature(self, facts: "StepFacts"):
+        """What, beyond the shapes of a step, decides which kernels this mixer launches for it and with which
+        grids (hashable; None: nothing).  A replayable mixer plans from `facts` only what this covers."""
         return None
 
     def state_need(self) -> StateNeed | None:

@@ -107,10 +107,96 @@ def test_recorded_decode_steps_equal_queued_ones(model_folders, name, dtype):
             T.check_rows(got, torch.stack([want[r][heads[r] + k] for r in reqs]), dtype, f"decode step {k} (recorded={record})")
             rows.append(got)
         if record:
-            assert len(runner._records) == 1 and next(iter(runner._records))[0] == 4
+            decode_records = [key for key in runner._records if len(key) == 2]
+            assert len(decode_records) == 1 and decode_records[0][0] == 4
         results.append(torch.stack(rows))
     if dtype == "float32":
         assert torch.equal(results[0], results[1])
+
+
+def mixed_schedule(lengths, decoded, budget, caps):
+    """Steps of a small continuous batch, as the scheduler would cut them: every request whose prompt is in
+    decodes one token a step, the others bring portions of their prompts (at most `caps[k]` tokens in step k)
+    under a budget of tokens a step.  Entries: (request index, first position, tokens, wanted place or None)."""
+    done = [0] * len(lengths)
+    steps, k = [], 0
+    while any(d < n + decoded for d, n in zip(done, lengths)):
+        left, step = budget, []
+        for i, n in enumerate(lengths):
+            if n <= done[i] < n + decoded and left > 0:
+                step.append((i, done[i], 1, 0))
+                left -= 1
+        for i, n in enumerate(lengths):
+            if done[i] < n and left > 0:
+                take = min(n - done[i], left, caps[k % len(caps)])
+                step.append((i, done[i], take, take - 1 if done[i] + take == n else None))
+                left -= take
+        for i, _, take, _ in step:
+            done[i] += take
+        steps.append(step)
+        k += 1
+    return steps
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+@pytest.mark.parametrize("name", ["A", "B", "D"])
+def test_recorded_steps_with_prompt_portions_equal_queued_ones(model_folders, name, dtype):
+    """Steps that hold portions of prompts beside decoded tokens are padded to fixed shapes, recorded once per
+    shape and replayed.  Every wanted row equals the plain implementation's, and in float32 the rows of a runner
+    that queues every kernel bit for bit; shapes come back, so recordings are replayed with other contents, in
+    other pages and with other tile lists."""
+    vocab = TINY[name][0]["vocab_size"]
+    lengths = [90, 70, 50, 33]
+    reqs = list(T.requests_for(vocab, [n + 12 for n in lengths], seed=31).values())
+    want = [plain(model_folders[name], tokens) for tokens in reqs]
+    steps = mixed_schedule(lengths, 12, 40, [13, 24, 17, 20, 9])
+    results = []
+    for record in (True, False):
+        runner = runner_for(model_folders[name], name, dtype, pages=128)
+        assert runner.record_mixed
+        runner.record_mixed, runner.record_after = record, 0
+        for i in range(len(reqs)):
+            runner.cache.open(i + 1)
+        rows = []
+        for k, step in enumerate(steps):
+            batch = []
+            for i, first, take, place in step:
+                runner.cache.extend(i + 1, first + take)
+                batch.append(SequenceStep(i + 1, reqs[i][first:first + take], first, [] if place is None else [place]))
+            got = runner.step(batch)
+            wanted = [(i, first + place) for i, first, _, place in step if place is not None]
+            assert (got is None) == (not wanted)
+            if wanted:
+                got = got.double().cpu()
+                T.check_rows(got, torch.stack([want[i][p] for i, p in wanted]), dtype, f"step {k} (recorded={record})")
+                rows.append(got)
+        if record:
+            fixed = [key for key in runner._records if len(key) == 5]
+            mixed_steps = sum(1 for step in steps if any(take > 1 for _, _, take, _ in step))
+            assert len(fixed) >= 3 and mixed_steps > len(fixed)               # recordings were replayed
+            assert runner.recorded_steps == len(steps)
+        results.append(torch.cat(rows))
+    if dtype == "float32":
+        assert torch.equal(results[0], results[1])
+
+
+def test_generation_through_recorded_steps_with_portions(model_folders):
+    """The entry point with a small token budget: its mixed steps are recorded (every shape at its first use)
+    and the tokens are the ones that a runner without recordings generates."""
+    folder = model_folders["D"]
+    prompts = [[(3 * i + k) % 500 + 4 for i in range(n)] for k, n in enumerate([70, 45, 100, 12, 64, 33])]
+    out = []
+    for record in (True, False):
+        limits = RuntimeConfig(max_seq_len=256, page_size=16, prefill_budget=48, max_running=4, record_mixed_steps=record)
+        engine = EngineHandle.load(folder, 0, config=limits, dtype="float32", num_pages=80)
+        engine.runner.record_after = 0
+        results = engine.generate_many(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
+        out.append([r.token_ids for r in results])
+        if record:
+            assert any(len(key) == 5 for key in engine.runner._records)
+        assert engine.runner.cache.free_pages() == 80
+        engine.shutdown()
+    assert out[0] == out[1]
 
 
 sharpen = T.sharpen

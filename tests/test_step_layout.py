@@ -81,3 +81,52 @@ def test_the_bound_covers_mixed_steps_and_too_small_a_buffer_is_reported():
     small = fn(cache.handle, 3, requests.ctypes.data, starts.ctypes.data, counts.ctypes.data, tokens.ctypes.data,
                want_counts.ctypes.data, want.ctypes.data, 0, 0, 64, 1000, buf.ctypes.data, 16, layout.ctypes.data)
     assert small == -7 and layout[0] == used
+
+
+def test_a_step_padded_to_fixed_shapes_keeps_its_layout_and_its_added_rows_write_nothing():
+    """A mixed step padded to fixed rows and sequences: the layout depends on the padded sizes alone, the added
+    sequences have no rows, the added rows write nothing, and the wanted rows are the real ones, then row 0."""
+    page, width = 4, 16
+    cache = CacheManager([CacheGroup("full", 0, 64)], page, 8)
+    lib = host_api()
+    fn = lib.mrs_step_build_padded
+    fn.restype = ctypes.c_int64
+    fn.argtypes = [ctypes.c_void_p, ctypes.c_int] + [ctypes.c_void_p] * 6 + [
+        ctypes.c_int, ctypes.c_int, ctypes.c_int, ctypes.c_int64, ctypes.c_int64, ctypes.c_void_p, ctypes.c_int64,
+        ctypes.c_void_p]
+
+    def build(counts, want_counts, want, pad_to, pad_rows):
+        n = len(counts)
+        counts = np.array(counts, dtype=np.int32)
+        requests = np.arange(1, n + 1, dtype=np.int64)
+        starts = np.zeros(n, dtype=np.int64)
+        tokens = np.arange(1, int(counts.sum()) + 1, dtype=np.int32)
+        want_counts = np.array(want_counts, dtype=np.int32)
+        want = np.array(want, dtype=np.int32)
+        layout = np.zeros(17, dtype=np.int64)
+        bound = step_layout_bound(pad_rows, pad_to, width, 1)
+        buf = np.full(bound, 77, dtype=np.int32)
+        used = fn(cache.handle, n, requests.ctypes.data, starts.ctypes.data, counts.ctypes.data, tokens.ctypes.data,
+                  want_counts.ctypes.data, want.ctypes.data, pad_to, pad_rows, width, 64, 1000, buf.ctypes.data, bound,
+                  layout.ctypes.data)
+        return int(used), layout, buf
+
+    for r, n in enumerate((7, 1, 13)):
+        cache.open(r + 1)
+        cache.extend(r + 1, n)
+    used, layout, buf = build([7, 1, 13], [0, 1, 1], [0, 12], 4, 32)
+    assert used > 0, lib.mrs_step_last_error()
+    T, B, R, decode = (int(v) for v in layout[:4])
+    assert (T, B, R, decode) == (32, 4, 4, 0)
+    assert list(buf[layout[7]:layout[7] + 5]) == [0, 7, 8, 21, 21]              # the added sequence has no rows
+    assert list(buf[layout[10]:layout[10] + 4]) == [7, 20, 0, 0]                # real wanted rows, then row 0
+    slots = buf[layout[14]:layout[14] + T]
+    assert (slots[:21] >= 0).all() and (slots[21:] == -1).all()                 # added rows write nothing
+    assert (buf[layout[6] + 21:layout[6] + T] == B - 1).all() and (buf[layout[5] + 21:layout[5] + T] == 0).all()
+    assert (buf[layout[12] + 3 * width:layout[12] + 4 * width] == 0).all()      # the added sequence reads page 0
+    # another step of the same padded sizes: the same offsets and the same need
+    used2, layout2, _ = build([2, 1], [1, 1], [1, 0], 4, 32)
+    assert used2 == used and list(layout2[:12]) == list(layout[:12])
+    # refusals: two wanted places in a sequence, fewer rows than the step has
+    assert build([7, 1], [2, 0], [0, 1], 4, 32)[0] == -6
+    assert build([7, 1, 13], [0, 0, 0], [], 4, 16)[0] == -6

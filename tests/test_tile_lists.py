@@ -1,0 +1,65 @@
+"""The host's plan of a step's attention tiles (`parts/attention.py: attention_tile_lists`): every row of every
+sequence in exactly one tile (or in every share of one), few rows in narrow tiles, the caps of a step with
+fixed shapes."""
+import random
+
+import pytest
+
+from mini_rsglang_b200 import kernels
+from mini_rsglang_b200.parts.attention import attention_tile_lists
+from mini_rsglang_b200.parts.base import StepFacts
+
+
+def facts_of(lengths, starts, padded=(0, 0)):
+    q_start = [0]
+    for n in lengths:
+        q_start.append(q_start[-1] + n)
+    return StepFacts(q_start, list(starts), max(s + n for s, n in zip(starts, lengths)), padded[0], padded[1])
+
+
+@pytest.mark.parametrize("group,wide_rows,sms", [(4, kernels.PREFILL_TC_ROWS, 148), (2, kernels.PREFILL_TC_ROWS, 148),
+                                                 (1, 64, 1), (8, kernels.PREFILL_TC_ROWS, 16)])
+def test_every_row_lies_in_one_tile(group, wide_rows, sms):
+    rng = random.Random(group * 1000 + sms)
+    for _ in range(50):
+        n = rng.randint(1, 9)
+        lengths = [rng.choice([1, 1, 2, 3, 17, 64, 200, 513]) for _ in range(n)]
+        starts = [rng.choice([0, 0, 5, 700, 4000]) for _ in range(n)]
+        facts = facts_of(lengths, starts)
+        lists = attention_tile_lists(facts, group, wide_rows, 8, 0, 128, sms)
+        assert attention_tile_lists(facts, group, wide_rows, 8, 0, 128, sms) is lists        # kept for the other layers
+        covered = [0] * facts.q_start[-1]
+        narrow_tokens = kernels.MMA_ROWS_NARROW // group
+        for seq, first, tokens, share in lists.narrow:
+            assert share == 0 and 0 < tokens <= narrow_tokens and tokens == lengths[seq]
+            for r in range(first, first + tokens):
+                covered[r] += 1
+        by_share = {}
+        for seq, first, tokens, share in lists.wide:
+            assert 0 < tokens <= wide_rows // group
+            assert facts.q_start[seq] <= first and first + tokens <= facts.q_start[seq + 1]
+            count = share >> 8
+            if count:
+                by_share.setdefault((seq, first, tokens, count), []).append(share & 0xFF)
+            else:
+                for r in range(first, first + tokens):
+                    covered[r] += 1
+        for (seq, first, tokens, count), indices in by_share.items():
+            assert indices == list(range(count)) and lists.shared                           # all shares, in order
+            for r in range(first, first + tokens):
+                covered[r] += 1
+        assert covered == [1] * len(covered)
+
+
+def test_fixed_shapes_give_caps_that_hold_the_lists_and_words_in_their_places():
+    facts = facts_of([1, 1, 200, 40], [900, 30, 0, 512], padded=(8, 256))
+    lists = attention_tile_lists(facts, 4, kernels.PREFILL_TC_ROWS, 8, 0, 128, 148)
+    assert lists.narrow_cap == 8 and lists.wide_cap >= max(16, len(lists.wide))
+    assert lists.signature() == (lists.narrow_cap, lists.wide_cap, lists.shared)
+    words = lists.words().reshape(-1, 4)
+    assert words.shape[0] == lists.narrow_cap + lists.wide_cap
+    assert [tuple(w) for w in words[:len(lists.narrow)]] == lists.narrow
+    assert (words[len(lists.narrow):lists.narrow_cap] == 0).all()                           # entries without tokens
+    assert [tuple(w) for w in words[lists.narrow_cap:lists.narrow_cap + len(lists.wide)]] == lists.wide
+    only_wide = attention_tile_lists(facts_of([300], [0], padded=(1, 320)), 4, kernels.PREFILL_TC_ROWS, 8, 0, 128, 148)
+    assert only_wide.narrow_cap == 0 and only_wide.wide_cap >= 16
