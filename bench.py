@@ -121,8 +121,9 @@ def continuous_run(args, torch, shape_name: str, cfg: dict, peak: dict) -> dict:
     """The serving workload of the 0.6B configuration: `--requests` requests (64) whose prompt lengths are drawn
     uniformly from 16 to 2,048 (seeded), `--output-tokens` generated tokens each (64), all submitted at once to
     `EngineHandle`; prompts are cut into portions under a budget of 512 tokens a step and run beside the decoded
-    tokens of the requests that are further on.  A first, smaller wave runs untimed so that every kernel has been
-    built and every batch size has been recorded once."""
+    tokens of the requests that are further on.  A first wave of the same lengths (other tokens) runs untimed so
+    that every kernel has been built and every step shape has been recorded once: the timed wave is the steady
+    state of a server that has seen its traffic before."""
     import random
 
     from mini_rsglang_b200 import RuntimeConfig, SamplingParams
@@ -145,7 +146,7 @@ def continuous_run(args, torch, shape_name: str, cfg: dict, peak: dict) -> dict:
     def prompts(ns):
         return [[rng.randrange(cfg["vocab_size"]) for _ in range(n)] for n in ns]
 
-    engine.generate_many(prompts(lengths[:max(8, requests // 4)] + [16] * max_running), params)     # warm-up wave, untimed
+    engine.generate_many(prompts(lengths), params)     # warm-up wave of the same lengths, untimed: every step shape is recorded
     work = prompts(lengths)
     torch.cuda.synchronize()
     steps0, recorded0, h2d0 = runner.steps, runner.recorded_steps, runner.h2d_bytes

@@ -152,9 +152,9 @@ class ModelRunner:
         self._largest_bucket = min(256, 1 << (limits.max_running - 1).bit_length())
         self._records: dict[tuple, _Recorded] = {}
         self._graph_pool = None
-        # steps with prompt portions: recorded with fixed shapes once a key has been seen `record_after` times
+        # steps with prompt portions: recorded with fixed shapes once a key has been seen more than `record_after` times
         self.record_mixed = self.record_decode and limits.record_mixed_steps
-        self.record_after = 1
+        self.record_after = 0
         self.max_records = 96
         self.mixed_rows_max = 1024
         self._seen: dict[tuple, int] = {}
@@ -293,7 +293,7 @@ class ModelRunner:
         self.steps += 1
         if observe is None and self._replayable(sequences):
             return self._forward_recorded(sequences)
-        if observe is None and self.record_mixed:
+        if observe is None and self.record_decode and self.record_mixed:
             shapes = self._fixed_shapes(sequences)
             if shapes is not None:
                 return self._forward_fixed(sequences, *shapes)
@@ -362,7 +362,7 @@ class ModelRunner:
     # wanted rows as sequences, block tables at their full width.  What else decides the launches (how many
     # attention tiles of which kind) the mixers state as the step's signature, planned on the host from the
     # step's facts; their plans travel with the layout in the step's one copy to the device, to addresses that
-    # stay.  A key is recorded when it comes back (`record_after`), so one-off shapes cost nothing.
+    # stay.  A recording costs about two queued steps; at most `max_records` are made.
     def _fixed_shapes(self, sequences):
         n = len(sequences)
         if n > self._largest_bucket:

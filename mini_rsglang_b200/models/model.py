@@ -42,8 +42,16 @@ class Model:
         return all(getattr(b.cache_part(), "replayable", False) for b in self.blocks if b.cache_part() is not None)
 
     def step_signature(self, facts) -> tuple:
-        """What the mixers say decides a step's launches beyond its shapes, layer by layer."""
-        return tuple(part.step_signature(facts) for part in self._cache_parts)
+        """What the mixers say decides a step's launches beyond its shapes: every layer's answer, a run of equal
+        answers once with its length."""
+        out = []
+        for part in self._cache_parts:
+            signature = part.step_signature(facts)
+            if out and out[-1][0] == signature:
+                out[-1][1] += 1
+            else:
+                out.append([signature, 1])
+        return tuple((signature, count) for signature, count in out)
 
     def weight_bytes(self) -> int:
         seen, total = set(), 0

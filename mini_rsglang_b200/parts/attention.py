@@ -213,6 +213,7 @@ class GroupedQueryAttention(Mixer):
             if norm is not None and norm.width != self.d:
                 raise InvalidRequest("a head norm must have the head's width")
         self.qkv = self.o = self.inv_freq = None
+        self._plan_arguments = None        # what the tile planner is asked for this attention, found at first use
 
     def weight_specs(self):
         specs = [WeightSpec(self.name("q_proj.weight"), (self.nq * self.d, self.width)),
@@ -246,11 +247,16 @@ class GroupedQueryAttention(Mixer):
     def step_signature(self, facts: StepFacts):
         """Which launches a step with these facts makes, beyond what its shapes say: the lengths of its tile lists
         and whether entries share their keys (None: no list is planned, one kernel takes every row)."""
-        group = self.nq // self.nkv
-        if self.runtime.dtype is not torch.bfloat16 or not kernels.attention_mma_supported(self.d, group):
+        if self._plan_arguments is None:
+            group = self.nq // self.nkv
+            if self.runtime.dtype is not torch.bfloat16 or not kernels.attention_mma_supported(self.d, group):
+                self._plan_arguments = ()
+            else:
+                self._plan_arguments = tile_plan_arguments(self.d, group, self.runtime.page_size, self.nkv, self.window,
+                                                           self.o.device)
+        if not self._plan_arguments:
             return None
-        arguments = tile_plan_arguments(self.d, group, self.runtime.page_size, self.nkv, self.window, self.o.device)
-        return attention_tile_lists(facts, *arguments).signature()
+        return attention_tile_lists(facts, *self._plan_arguments).signature()
 
     def forward(self, h, ctx, cache, write_cache=True, into=None):
         tokens = h.shape[0]

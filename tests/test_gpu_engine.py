@@ -564,7 +564,7 @@ def test_recorded_decode_steps_across_classes_of_context_length(model_folders, d
             k += 1
         assert at["r1"] > 1024 and at["r2"] > 512
         if record:
-            keys = sorted(runner._records)
+            keys = sorted(key for key in runner._records if len(key) == 2)      # the decode steps' recordings
             assert len(keys) >= 5, keys
             assert {c for _, c in keys} == {512, 1024, 2048} and {b for b, _ in keys} == {1, 2, 4}
             assert runner._records[keys[0]].ctx.block_tables[0].shape[1] == 128
@@ -632,7 +632,7 @@ def test_real_vocabulary_and_a_recorded_step_beyond_2048_tokens(dtype):
         got.append(logits.double().cpu())
     got = torch.cat(got)
     T.check_rows(got, want, dtype, "real vocabulary")
-    assert sorted(runner._records) == [(1, 2048), (1, 4096)]
+    assert sorted(key for key in runner._records if len(key) == 2) == [(1, 2048), (1, 4096)]
     for row, choice in zip(want[1:], choices):
         best = P.greedy(row)
         allowed = 2e-5 * max(1.0, row.abs().max().item()) if dtype == "float32" else 0.02 * row.abs().max().item()
