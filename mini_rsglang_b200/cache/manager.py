@@ -26,7 +26,16 @@ def host_api() -> ctypes.CDLL:
     table = {
         "mrs_last_error": (ctypes.c_char_p, []),
         "mrs_cache_create": (c_vp, [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), p_i64, c_int, c_int]),
+        "mrs_cache_create_sharing": (c_vp, [c_int, ctypes.POINTER(c_int), ctypes.POINTER(c_int), p_i64, c_int, c_int]),
         "mrs_cache_destroy": (None, [c_vp]),
+        "mrs_cache_open_prompt": (c_int, [c_vp, c_i64, c_vp, c_i64, c_i64, c_i64, p_i64]),
+        "mrs_cache_publish": (c_int, [c_vp, c_i64, c_vp, c_i64]),
+        "mrs_cache_clear_idle": (c_i64, [c_vp]),
+        "mrs_cache_shares_prefixes": (c_int, [c_vp]),
+        "mrs_cache_cached_pages": (c_i64, [c_vp]),
+        "mrs_cache_evictable_pages": (c_i64, [c_vp]),
+        "mrs_sched_drain_cached": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_vp, c_int]),
+        "mrs_sched_cached_tokens": (c_i64, [c_vp]),
         "mrs_cache_open": (c_int, [c_vp, c_i64, c_i64, c_i64]),
         "mrs_cache_extend": (c_int, [c_vp, c_i64, c_i64]),
         "mrs_cache_trim": (c_int, [c_vp, c_i64, c_i64]),
@@ -83,9 +92,13 @@ class CacheManager:
     `open` takes a state slot and, with `reserve_tokens`, a promise of the pages a request of
     that length needs at worst; `extend` makes the pages for the next tokens; `trim` gives back
     what a window has passed; `close` gives back everything.  `check` verifies that no page is
-    lost, held twice or freed twice."""
+    lost, held twice or freed twice.
 
-    def __init__(self, groups: list[CacheGroup], page_size: int, max_slots: int):
+    With `prefix_cache` requests share the full pages of equal first tokens (`open_prompt`, `publish`;
+    the reference's `--prefix-cache`, crates/cache/src/lib.rs:15-240): pages that only the tree of prefixes
+    holds are not free but count as room, and are evicted, least recently used first, when a pool runs short."""
+
+    def __init__(self, groups: list[CacheGroup], page_size: int, max_slots: int, prefix_cache: bool = False):
         if not groups:
             raise InvalidRequest("a cache needs at least one group")
         self.lib = host_api()
@@ -96,7 +109,11 @@ class CacheManager:
         kinds = (ctypes.c_int * n)(*[1 if g.kind == "window" else 0 for g in groups])
         windows = (ctypes.c_int * n)(*[int(g.window) for g in groups])
         pages = (ctypes.c_int64 * n)(*[int(g.num_pages) for g in groups])
-        self.handle = self.lib.mrs_cache_create(n, kinds, windows, pages, self.page_size, self.max_slots)
+        if prefix_cache and any(g.kind != "full" for g in groups):
+            raise InvalidRequest("prefix sharing needs layers that keep all their keys: a window of keys cannot be shared")
+        create = self.lib.mrs_cache_create_sharing if prefix_cache else self.lib.mrs_cache_create
+        self.handle = create(n, kinds, windows, pages, self.page_size, self.max_slots)
+        self.prefix_cache = bool(prefix_cache)
         if not self.handle:
             raise InvalidRequest(f"cache manager: {last_error(self.lib)}")
         self._scratch = np.empty(max(int(g.num_pages) for g in groups) + 1, dtype=np.int32)
@@ -130,6 +147,39 @@ class CacheManager:
         if slot < 0:
             self._raise(slot, f"open request {request}")
         return slot
+
+    def open_prompt(self, request: int, prompt, reserve_tokens: int, max_step: int = 1) -> tuple[int, int]:
+        """Opens a request with its prompt: (state slot, prompt tokens found in shared pages).  The request's
+        length starts behind the shared tokens; they are not computed again."""
+        tokens = np.ascontiguousarray(prompt, dtype=np.int32)
+        shared = ctypes.c_int64(0)
+        slot = self.lib.mrs_cache_open_prompt(self.handle, request, tokens.ctypes.data, tokens.size, reserve_tokens,
+                                              max_step, ctypes.byref(shared))
+        if slot < 0:
+            self._raise(slot, f"open request {request}")
+        return slot, int(shared.value)
+
+    def publish(self, request: int, tokens, computed: int) -> None:
+        """The first `computed` tokens of the request are in its pages: their full pages are shared from now on."""
+        tokens = np.ascontiguousarray(tokens, dtype=np.int32)
+        if computed > tokens.size:
+            raise InvalidRequest("publish: more tokens computed than given")
+        code = self.lib.mrs_cache_publish(self.handle, request, tokens.ctypes.data, computed)
+        if code < 0:
+            self._raise(code, f"publish request {request}")
+
+    def clear_idle_cache(self) -> int:
+        """Evicts every page that only the tree of prefixes holds; returns how many."""
+        n = int(self.lib.mrs_cache_clear_idle(self.handle))
+        if n < 0:
+            self._raise(n, "clear the idle cache")
+        return n
+
+    def cached_pages(self) -> int:
+        return int(self.lib.mrs_cache_cached_pages(self.handle))
+
+    def evictable_pages(self) -> int:
+        return int(self.lib.mrs_cache_evictable_pages(self.handle))
 
     def extend(self, request: int, new_length: int) -> None:
         code = self.lib.mrs_cache_extend(self.handle, request, new_length)

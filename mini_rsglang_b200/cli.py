@@ -40,7 +40,7 @@ def build_parser() -> argparse.ArgumentParser:
     p.add_argument("--max-running", type=int, default=32)
     p.add_argument("--max-waiting", type=int, default=256)
     p.add_argument("--no-prefix-cache", action="store_true",
-                   help="accepted for compatibility: prefix sharing is not built, so it is always off")
+                   help="do not share the cache pages of equal first tokens between requests")
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     p.add_argument("--num-pages", type=int, default=None, help="size of the page pool (overrides --kv-mib)")
     sub = p.add_subparsers(dest="command", required=True)
@@ -75,7 +75,8 @@ def build_parser() -> argparse.ArgumentParser:
 
 def runtime_config(args) -> RuntimeConfig:
     return RuntimeConfig(max_seq_len=args.max_seq_len, page_size=args.page_size, prefill_budget=args.prefill_budget,
-                         max_running=args.max_running, max_waiting=args.max_waiting, prefix_cache=False)
+                         max_running=args.max_running, max_waiting=args.max_waiting,
+                         prefix_cache=not args.no_prefix_cache)
 
 
 def event_json(event) -> str:
@@ -138,17 +139,20 @@ def command_bench(args) -> int:
     from .engine import load_test
     from .engine.handle import EngineHandle
 
-    if args.cache_mode != "cold":
-        raise InvalidRequest("only --cache-mode cold: this engine shares nothing between requests (no prefix cache)")
     if args.kv_mib <= 0:
         raise InvalidRequest("kv_mib must be positive")
-    engine = EngineHandle.load(args.model, args.device, args.kv_mib * 1024 * 1024, runtime_config(args),
-                               dtype=args.dtype, num_pages=args.num_pages)
-    try:
-        result = load_test.run(engine, args.input_tokens, args.output_tokens, args.requests, args.concurrency, args.seed)
-    finally:
-        engine.shutdown()
-    report = json.dumps({"backend": "b200-tcgen05-tma", "devices": [args.device], "runs": [result]}, indent=2)
+    runs = []
+    for warm in {"cold": (False,), "hot": (True,), "both": (False, True)}[args.cache_mode]:
+        limits = runtime_config(args)
+        limits.prefix_cache = warm          # a cold run shares nothing, a hot one reads a prompt that is in the cache
+        engine = EngineHandle.load(args.model, args.device, args.kv_mib * 1024 * 1024, limits, dtype=args.dtype,
+                                   num_pages=args.num_pages)
+        try:
+            runs.append(load_test.run(engine, args.input_tokens, args.output_tokens, args.requests, args.concurrency,
+                                      args.seed, warm=warm))
+        finally:
+            engine.shutdown()
+    report = json.dumps({"backend": "b200-tcgen05-tma", "devices": [args.device], "runs": runs}, indent=2)
     if args.output:
         with open(args.output, "w") as f:
             f.write(report)

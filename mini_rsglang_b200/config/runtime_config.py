@@ -14,7 +14,8 @@ class RuntimeConfig:
     prefill_budget: int = 512    # tokens of one step (decoded tokens and prompt portions)
     max_running: int = 32        # requests that hold cache pages at the same time
     max_waiting: int = 256       # requests queued before admission
-    prefix_cache: bool = False   # accepted for the reference's flag; sharing is not built
+    prefix_cache: bool = False   # requests share the full pages of equal first tokens (the reference's default is on;
+                                 # here the entry point leaves it off unless asked, the command line turns it on)
     record_mixed_steps: bool = True   # steps with prompt portions are recorded with fixed shapes and replayed
 
     def validate(self) -> None:

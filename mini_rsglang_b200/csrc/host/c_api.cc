@@ -28,22 +28,52 @@ static int guarded(F f) {
 API const char* mrs_last_error() { return g_error.c_str(); }
 
 // ----------------------------------------------------------------------------- cache manager
-API void* mrs_cache_create(int n_groups, const int* kinds, const int* windows, const int64_t* num_pages,
-                           int page_size, int max_slots) {
+static void* cache_create(int n_groups, const int* kinds, const int* windows, const int64_t* num_pages, int page_size,
+                          int max_slots, bool prefix_cache) {
     try {
         std::vector<mrs::GroupSpec> groups;
         for (int g = 0; g < n_groups; ++g)
             groups.push_back({kinds[g] == 1 ? mrs::GroupKind::Window : mrs::GroupKind::Full, windows[g], num_pages[g]});
-        return new mrs::CacheManager(std::move(groups), page_size, max_slots);
+        return new mrs::CacheManager(std::move(groups), page_size, max_slots, prefix_cache);
     } catch (const std::exception& e) {
         g_error = e.what();
         return nullptr;
     }
 }
+API void* mrs_cache_create(int n_groups, const int* kinds, const int* windows, const int64_t* num_pages,
+                           int page_size, int max_slots) {
+    return cache_create(n_groups, kinds, windows, num_pages, page_size, max_slots, false);
+}
+// The same with prefix sharing between requests (every group must keep all keys).
+API void* mrs_cache_create_sharing(int n_groups, const int* kinds, const int* windows, const int64_t* num_pages,
+                                   int page_size, int max_slots) {
+    return cache_create(n_groups, kinds, windows, num_pages, page_size, max_slots, true);
+}
 API void mrs_cache_destroy(void* c) { delete static_cast<mrs::CacheManager*>(c); }
 API int mrs_cache_open(void* c, int64_t request, int64_t reserve_tokens, int64_t max_step) {
     return guarded([&] { return static_cast<mrs::CacheManager*>(c)->open(request, reserve_tokens, max_step); });
 }
+// Opens a request whose prompt is known; with prefix sharing `shared_tokens` gets the tokens found in shared pages.
+API int mrs_cache_open_prompt(void* c, int64_t request, const int32_t* prompt, int64_t prompt_len, int64_t reserve_tokens,
+                              int64_t max_step, int64_t* shared_tokens) {
+    return guarded([&] {
+        return static_cast<mrs::CacheManager*>(c)->open_prompt(request, prompt, prompt_len, reserve_tokens, max_step, shared_tokens);
+    });
+}
+API int mrs_cache_publish(void* c, int64_t request, const int32_t* tokens, int64_t computed) {
+    return guarded([&] { return static_cast<mrs::CacheManager*>(c)->publish(request, tokens, computed); });
+}
+API int64_t mrs_cache_clear_idle(void* c) {
+    try {
+        return static_cast<mrs::CacheManager*>(c)->clear_idle_cache();
+    } catch (const std::exception& e) {
+        g_error = e.what();
+        return kException;
+    }
+}
+API int mrs_cache_shares_prefixes(void* c) { return static_cast<mrs::CacheManager*>(c)->prefix_cache() ? 1 : 0; }
+API int64_t mrs_cache_cached_pages(void* c) { return static_cast<mrs::CacheManager*>(c)->cached_pages(); }
+API int64_t mrs_cache_evictable_pages(void* c) { return static_cast<mrs::CacheManager*>(c)->evictable_pages(); }
 API int mrs_cache_extend(void* c, int64_t request, int64_t new_length) {
     return guarded([&] { return static_cast<mrs::CacheManager*>(c)->extend(request, new_length); });
 }
@@ -172,8 +202,8 @@ API int mrs_sched_fail(void* s, int reason) {
     });
 }
 // Requests that ended since the last call; at most cap are written and returned, the rest stay for the next call.
-API int mrs_sched_drain(void* s, int64_t* requests, int32_t* reasons, int64_t* prompt_tokens,
-                        int64_t* completion_tokens, int cap) {
+static int drain(void* s, int64_t* requests, int32_t* reasons, int64_t* prompt_tokens, int64_t* completion_tokens,
+                 int64_t* cached_tokens, int cap) {
     return guarded([&]() -> int {
         const auto pending = static_cast<mrs::Scheduler*>(s)->drain_finished((size_t)std::max(cap, 0));
         const int n = (int)pending.size();
@@ -182,10 +212,21 @@ API int mrs_sched_drain(void* s, int64_t* requests, int32_t* reasons, int64_t* p
             reasons[i] = (int)pending[(size_t)i].reason;
             prompt_tokens[i] = pending[(size_t)i].prompt_tokens;
             completion_tokens[i] = pending[(size_t)i].completion_tokens;
+            if (cached_tokens) cached_tokens[i] = pending[(size_t)i].cached_tokens;
         }
         return n;
     });
 }
+API int mrs_sched_drain(void* s, int64_t* requests, int32_t* reasons, int64_t* prompt_tokens,
+                        int64_t* completion_tokens, int cap) {
+    return drain(s, requests, reasons, prompt_tokens, completion_tokens, nullptr, cap);
+}
+// The same with the prompt tokens that each request found in shared pages.
+API int mrs_sched_drain_cached(void* s, int64_t* requests, int32_t* reasons, int64_t* prompt_tokens,
+                               int64_t* completion_tokens, int64_t* cached_tokens, int cap) {
+    return drain(s, requests, reasons, prompt_tokens, completion_tokens, cached_tokens, cap);
+}
+API int64_t mrs_sched_cached_tokens(void* s) { return static_cast<mrs::Scheduler*>(s)->counters().cached_tokens; }
 API void mrs_sched_counters(void* s, int64_t* out9) {
     const mrs::Counters& c = static_cast<mrs::Scheduler*>(s)->counters();
     const int64_t values[9] = {c.submitted, c.completed, c.cancelled, c.failed, c.prompt_tokens,

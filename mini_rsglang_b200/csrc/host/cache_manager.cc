@@ -20,6 +20,12 @@ int32_t PagePool::allocate() {
     return p;
 }
 
+void PagePool::retain(int32_t page) {
+    if (page < 0 || (size_t)page >= refs_.size() || refs_[(size_t)page] <= 0)
+        throw std::logic_error("retain of a page that nobody holds");
+    refs_[(size_t)page] += 1;
+}
+
 void PagePool::release(int32_t page) {
     if (page < 0 || (size_t)page >= refs_.size() || refs_[(size_t)page] <= 0)
         throw std::logic_error("double page release");
@@ -28,7 +34,7 @@ void PagePool::release(int32_t page) {
 
 static int64_t ceil_div(int64_t a, int64_t b) { return (a + b - 1) / b; }
 
-CacheManager::CacheManager(std::vector<GroupSpec> groups, int page_size, int max_slots)
+CacheManager::CacheManager(std::vector<GroupSpec> groups, int page_size, int max_slots, bool prefix_cache)
     : groups_(std::move(groups)), page_size_(page_size), max_slots_(max_slots) {
     if (groups_.empty() || page_size <= 0 || max_slots <= 0) throw std::invalid_argument("empty cache geometry");
     for (const auto& g : groups_) {
@@ -38,7 +44,23 @@ CacheManager::CacheManager(std::vector<GroupSpec> groups, int page_size, int max
     }
     reserved_.assign(groups_.size(), 0);
     for (int s = max_slots - 1; s >= 0; --s) free_slots_.push_back(s);
+    if (prefix_cache) {
+        for (const auto& g : groups_)
+            if (g.kind != GroupKind::Full) throw std::invalid_argument("prefix sharing needs groups that keep all keys");
+        tree_ = std::make_unique<PrefixTree>(page_size, (int)groups_.size());
+    }
 }
+
+// Evicts up to `nodes` pages that only the tree holds (one page a group each) and gives them back.
+int64_t CacheManager::evict(int64_t nodes) {
+    if (!tree_ || nodes <= 0) return 0;
+    std::vector<std::pair<int, int32_t>> released;
+    const int64_t gone = tree_->evict(nodes, &released);
+    for (const auto& [g, page] : released) pools_[(size_t)g].release(page);
+    return gone;
+}
+
+int64_t CacheManager::clear_idle_cache() { return evict(INT64_MAX); }
 
 // The first logical page that a query at `next_position` (or any later one) can still read.
 int64_t CacheManager::first_needed_page(int g, int64_t next_position) const {
@@ -77,7 +99,7 @@ int CacheManager::open(int64_t request, int64_t reserve_tokens, int64_t max_step
             if (need[g] > pools_[g].total()) return kTooLarge;
         }
         for (size_t g = 0; g < groups_.size(); ++g)
-            if (pools_[g].free_count() < reserved_[g] + need[g]) return kNoRoom;
+            if (pools_[g].free_count() + evictable_pages() < reserved_[g] + need[g]) return kNoRoom;
     }
     if (free_slots_.empty()) return kNoSlot;
     Lease lease;
@@ -96,6 +118,63 @@ int CacheManager::open(int64_t request, int64_t reserve_tokens, int64_t max_step
     return slot;
 }
 
+int CacheManager::open_prompt(int64_t request, const int32_t* prompt, int64_t prompt_len, int64_t reserve_tokens,
+                              int64_t max_step, int64_t* shared_tokens) {
+    if (shared_tokens) *shared_tokens = 0;
+    if (!tree_) return open(request, reserve_tokens, max_step);
+    if (leases_.count(request)) return kDuplicate;
+    if (reserve_tokens < prompt_len || prompt_len <= 0 || !prompt) return kInvalid;
+    const int64_t all = ceil_div(reserve_tokens, page_size_);
+    for (size_t g = 0; g < groups_.size(); ++g)
+        if (all > pools_[g].total()) return kTooLarge;
+    if (free_slots_.empty()) return kNoSlot;
+    std::vector<std::vector<int32_t>> found;
+    const int node = tree_->lookup(prompt, prompt_len - 1, &found);
+    tree_->pin(node);                       // what this request reads must not count as room
+    const int64_t shared = (int64_t)found[0].size();
+    for (size_t g = 0; g < groups_.size(); ++g)
+        if (pools_[g].free_count() + evictable_pages() < reserved_[g] + (all - shared)) {
+            tree_->unpin(node);
+            return kNoRoom;
+        }
+    Lease lease;
+    lease.request = request;
+    lease.slot = free_slots_.back();
+    free_slots_.pop_back();
+    lease.tables = std::move(found);
+    lease.first_live.assign(groups_.size(), 0);
+    lease.held.assign(groups_.size(), shared);
+    lease.reserved.assign(groups_.size(), all - shared);
+    lease.promise.assign(groups_.size(), all);
+    lease.promised_pages = all;
+    lease.node = node;
+    lease.shared_tokens = shared * page_size_;
+    lease.length = lease.shared_tokens;
+    for (size_t g = 0; g < groups_.size(); ++g) {
+        for (int32_t page : lease.tables[g]) pools_[g].retain(page);
+        reserved_[g] += all - shared;
+    }
+    if (shared_tokens) *shared_tokens = lease.shared_tokens;
+    const int slot = lease.slot;
+    leases_.emplace(request, std::move(lease));
+    return slot;
+}
+
+int CacheManager::publish(int64_t request, const int32_t* tokens, int64_t computed) {
+    if (!tree_) return kOk;
+    auto it = leases_.find(request);
+    if (it == leases_.end()) return kUnknown;
+    Lease& lease = it->second;
+    if (computed > lease.length || computed < 0 || !tokens) return kInvalid;
+    std::vector<std::pair<int, int32_t>> retained;
+    const int node = tree_->insert(tokens, computed, lease.tables, &retained);
+    for (const auto& [g, page] : retained) pools_[(size_t)g].retain(page);
+    tree_->pin(node);                       // the new path first, so that no node of both paths is ever unpinned
+    tree_->unpin(lease.node);
+    lease.node = node;
+    return kOk;
+}
+
 int CacheManager::extend(int64_t request, int64_t new_length) {
     auto it = leases_.find(request);
     if (it == leases_.end()) return kUnknown;
@@ -103,11 +182,14 @@ int CacheManager::extend(int64_t request, int64_t new_length) {
     if (new_length < lease.length) return kInvalid;
     const int64_t pages = ceil_div(new_length, page_size_);
     // First see whether every group can give what is asked: a refusal changes nothing.
+    int64_t short_of = 0;              // pages that the pools lack and the prefix tree may give back
     for (size_t g = 0; g < groups_.size(); ++g) {
         const int64_t take = std::max<int64_t>(0, pages - (int64_t)lease.tables[g].size());
         const int64_t promised_to_others = reserved_[g] - lease.reserved[g];
-        if (pools_[g].free_count() - promised_to_others < take) return kNoRoom;
+        if (pools_[g].free_count() + evictable_pages() - promised_to_others < take) return kNoRoom;
+        short_of = std::max(short_of, take - pools_[g].free_count());
     }
+    evict(short_of);
     for (size_t g = 0; g < groups_.size(); ++g) {
         auto& table = lease.tables[g];
         while ((int64_t)table.size() < pages) {
@@ -157,6 +239,7 @@ int CacheManager::close(int64_t request) {
             if (page >= 0) pools_[g].release(page);
         reserved_[g] -= lease.reserved[g];
     }
+    if (tree_) tree_->unpin(lease.node);
     free_slots_.push_back(lease.slot);
     leases_.erase(it);
     return kOk;
@@ -172,6 +255,18 @@ std::string CacheManager::check() const {
     for (size_t g = 0; g < groups_.size(); ++g) {
         const auto& pool = pools_[g];
         std::vector<int32_t> expected((size_t)pool.total(), 0);
+        std::vector<char> in_tree((size_t)pool.total(), 0);
+        if (tree_) {
+            std::vector<std::pair<int, int32_t>> resident;
+            tree_->resident(&resident);
+            for (const auto& [group, page] : resident) {
+                if (group != (int)g) continue;
+                if (page < 0 || page >= pool.total()) { bad << "group " << g << ": the prefix tree holds page " << page << " outside the pool; "; continue; }
+                if (in_tree[(size_t)page]) bad << "group " << g << ": the prefix tree holds page " << page << " twice; ";
+                in_tree[(size_t)page] = 1;
+                expected[(size_t)page] += 1;
+            }
+        }
         int64_t promised = 0;
         for (const auto& [id, lease] : leases_) {
             promised += lease.reserved[g];
@@ -188,7 +283,7 @@ std::string CacheManager::check() const {
             }
         }
         if (promised != reserved_[g]) bad << "group " << g << ": promises " << reserved_[g] << " != sum over requests " << promised << "; ";
-        if (reserved_[g] > pool.free_count()) bad << "group " << g << ": more pages promised than free; ";
+        if (reserved_[g] > pool.free_count() + evictable_pages()) bad << "group " << g << ": more pages promised than free; ";
         std::vector<char> in_free((size_t)pool.total(), 0);
         for (int32_t page : pool.free_list()) {
             if (page < 0 || page >= pool.total()) { bad << "group " << g << ": free list holds page " << page << "; "; continue; }
@@ -198,7 +293,7 @@ std::string CacheManager::check() const {
         for (int64_t page = 0; page < pool.total(); ++page) {
             const int32_t refs = pool.refs()[(size_t)page];
             if (refs != expected[(size_t)page]) bad << "group " << g << ": page " << page << " has " << refs << " holders on record, " << expected[(size_t)page] << " in the tables; ";
-            if (expected[(size_t)page] > 1) bad << "group " << g << ": page " << page << " held twice; ";
+            if (expected[(size_t)page] > 1 && !in_tree[(size_t)page]) bad << "group " << g << ": page " << page << " held twice; ";
             if ((refs == 0) != (in_free[(size_t)page] != 0)) bad << "group " << g << ": page " << page << (refs == 0 ? " lost (neither held nor free); " : " both held and free; ");
         }
     }
@@ -213,6 +308,13 @@ std::string CacheManager::check() const {
     }
     for (int s = 0; s < max_slots_; ++s)
         if (!slot_used[(size_t)s]) bad << "slot " << s << " lost; ";
+    if (tree_) {
+        bad << tree_->check();
+        for (const auto& [id, lease] : leases_) {
+            if (!tree_->pinned(lease.node) && lease.node != 0) bad << "request " << id << " reads a prefix that is not pinned; ";
+            if ((int64_t)tree_->depth(lease.node) * page_size_ < lease.shared_tokens) bad << "request " << id << " pins less than it shares; ";
+        }
+    }
     return bad.str();
 }
 

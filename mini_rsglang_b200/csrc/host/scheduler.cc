@@ -52,7 +52,7 @@ bool Scheduler::cancel(int64_t request) {
 
 void Scheduler::finish(size_t index, Finish reason) {
     Running& r = running_[index];
-    finished_.push_back({r.input.id, reason, r.prompt_len, r.generated});
+    finished_.push_back({r.input.id, reason, r.prompt_len, r.generated, r.cached});
     switch (reason) {
         case Finish::Stop: case Finish::Length: counters_.completed += 1; break;
         case Finish::Cancelled: counters_.cancelled += 1; break;
@@ -66,9 +66,13 @@ void Scheduler::admit() {
     while ((int)running_.size() < max_running_ && !waiting_.empty()) {
         const Submission& front = waiting_.front();
         const int64_t length = (int64_t)front.tokens.size() + front.max_tokens;
-        const int slot = cache_->open(front.id, length, prefill_budget_);
+        int64_t shared = 0;
+        const int slot = cache_->open_prompt(front.id, front.tokens.data(), (int64_t)front.tokens.size(), length,
+                                             prefill_budget_, &shared);
         if (slot < 0) break;   // the head of the queue waits, and so do those behind it
         Running r;
+        r.computed = r.cached = shared;
+        counters_.cached_tokens += shared;
         r.input = std::move(waiting_.front());
         waiting_.pop_front();
         r.tokens = r.input.tokens;
@@ -142,8 +146,11 @@ void Scheduler::commit(const std::vector<int32_t>& sampled) {
     size_t next = 0;
     for (size_t j = 0; j < plan_.size(); ++j) {
         Running& r = running_[plan_index_[j]];
+        const bool prompt_was_open = r.computed < r.prompt_len;
         r.computed = plan_[j].start_pos + plan_[j].count;
         cache_->trim(r.input.id, r.computed);
+        if (prompt_was_open && r.computed >= r.prompt_len)      // the prompt is in the cache: others may read its pages
+            cache_->publish(r.input.id, r.tokens.data(), r.prompt_len);
         if (!plan_[j].sample) continue;
         const int32_t token = sampled[next++];
         r.tokens.push_back(token);

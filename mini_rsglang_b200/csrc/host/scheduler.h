@@ -13,6 +13,11 @@
 // max_tokens) can be promised to it, so a running request never lacks a page; a request that
 // does not fit now waits at the head of the queue and holds back those behind it; one that can
 // never fit is refused when it is submitted.  Nothing is preempted, swapped or recomputed.
+//
+// With prefix sharing in the cache manager a request is admitted with its prompt: what the tree has of the
+// prompt's first pages is not computed again (`computed` starts behind them; the last prompt token is always
+// computed), and when a request's prompt is in the cache its full pages are published for those that follow
+// (reference: acquire / publish, crates/runtime/src/scheduler.rs:174, 283).
 #pragma once
 #include <cstdint>
 #include <deque>
@@ -39,6 +44,7 @@ struct Running {
     int64_t prompt_len = 0;
     int64_t computed = 0;          // tokens whose keys and values are in the cache
     int64_t generated = 0;
+    int64_t cached = 0;            // prompt tokens found in shared pages at admission
     int slot = -1;
     bool cancel = false;
 };
@@ -56,11 +62,12 @@ struct Finished {
     Finish reason;
     int64_t prompt_tokens;
     int64_t completion_tokens;
+    int64_t cached_tokens = 0;
 };
 
 struct Counters {
     int64_t submitted = 0, completed = 0, cancelled = 0, failed = 0;
-    int64_t prompt_tokens = 0, generated_tokens = 0;
+    int64_t prompt_tokens = 0, generated_tokens = 0, cached_tokens = 0;
     int64_t prefill_batches = 0, decode_batches = 0, mixed_batches = 0;
 };
 

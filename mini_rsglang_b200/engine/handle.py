@@ -70,6 +70,7 @@ class GenerationResult:
     finish_reason: str
     prompt_tokens: int
     completion_tokens: int
+    cached_tokens: int = 0      # prompt tokens read from pages that an earlier request left (prefix sharing)
 
 
 class GenerationStream:
@@ -187,7 +188,7 @@ class EngineHandle:
                         stream.terminal = True
                         results[event.request_id] = GenerationResult(
                             event.request_id, tokens[event.request_id], event.reason, event.prompt_tokens,
-                            event.completion_tokens)
+                            event.completion_tokens, event.cached_tokens)
                     elif isinstance(event, Error):
                         raise BackendError(event.message)
 
@@ -211,7 +212,8 @@ class EngineHandle:
             self.params.pop(done.request_id, None)
             self.generated.pop(done.request_id, None)
             if stream is not None:
-                stream.events.append(Finished(done.request_id, done.reason, done.prompt_tokens, done.completion_tokens))
+                stream.events.append(Finished(done.request_id, done.reason, done.prompt_tokens, done.completion_tokens,
+                                              done.cached_tokens))
 
     def run_step(self) -> bool:
         """Plans, runs and commits one step.  False when there was nothing to run."""
@@ -260,12 +262,14 @@ class EngineHandle:
         out.update(waiting=self.scheduler.waiting(), running=self.scheduler.running(),
                    free_pages=sum(by_group), free_pages_by_group=by_group,
                    total_pages=sum(cache.total_pages(g) for g in range(len(self.runner.groups))),
-                   cached_pages=0, cached_tokens=0,
+                   cached_pages=cache.cached_pages() * len(self.runner.groups),
                    peak_memory_bytes=torch.cuda.max_memory_allocated(self.runner.device), healthy=self.healthy)
         return out
 
     def clear_cache(self) -> None:
-        """Nothing is cached between requests (no prefix sharing), so nothing to clear."""
+        """Gives back every page that only the tree of shared prefixes holds (reference: `clear_idle_cache`,
+        crates/cache/src/lib.rs:376-380).  Nothing to do without prefix sharing."""
+        self.runner.cache.clear_idle_cache()
 
     def shutdown(self) -> None:
         if self.healthy:

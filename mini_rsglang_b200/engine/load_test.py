@@ -1,8 +1,10 @@
 """A closed-loop load test of the engine: a fixed number of requests, a fixed number of them
 in flight, fixed prompt and output lengths (reference: `mini-rsglang bench`,
 crates/server/src/bench.rs:16-170).  The reference tokenises a repeated sentence; without a
-tokenizer the prompts here are seeded uniform random token ids of the same length, every
-request's different so that nothing could be shared between them."""
+tokenizer the prompts here are seeded uniform random token ids of the same length.  Cold
+(`warm=False`): every request's prompt is different and the engine shares nothing.  Warm: as in
+the reference every request brings the same prompt to an engine that shares prefixes, after one
+request of one token that leaves the prompt's pages behind (bench.rs:41-49)."""
 from __future__ import annotations
 
 import math
@@ -59,17 +61,26 @@ def _wave(engine: EngineHandle, prompts: list[list[int]], output_tokens: int, co
 
 
 def run(engine: EngineHandle, input_tokens: int, output_tokens: int, requests: int, concurrency: int,
-        seed: int = 0, warmup_waves: int = 2) -> dict:
+        seed: int = 0, warmup_waves: int = 2, warm: bool = False) -> dict:
     if min(input_tokens, output_tokens, requests, concurrency) <= 0 or concurrency > engine.config.max_running:
         raise InvalidRequest("positive benchmark sizes required; concurrency must be <= max_running")
     rng = random.Random(seed)
     vocab = engine.info["vocab_size"]
 
+    shared_prompt = [rng.randrange(vocab) for _ in range(input_tokens)]
+
     def prompts(n):
+        if warm:
+            return [list(shared_prompt) for _ in range(n)]
         return [[rng.randrange(vocab) for _ in range(input_tokens)] for _ in range(n)]
 
+    if warm:
+        if not engine.config.prefix_cache:
+            raise InvalidRequest("a warm run needs an engine that shares prefixes")
+        engine.generate_many([shared_prompt], SamplingParams(max_tokens=1, ignore_eos=True))
     for _ in range(warmup_waves):          # the measured batch and token shapes, before the clock starts
         _wave(engine, prompts(concurrency), output_tokens, concurrency)
+    before = engine.metrics()
     started = time.perf_counter()
     first, gaps, latency = _wave(engine, prompts(requests), output_tokens, concurrency)
     elapsed = time.perf_counter() - started
@@ -78,9 +89,9 @@ def run(engine: EngineHandle, input_tokens: int, output_tokens: int, requests: i
         return {"p50": percentile(values, 0.5) * 1000.0, "p95": percentile(values, 0.95) * 1000.0}
 
     after = engine.metrics()
-    return {"warmup_waves": warmup_waves, "cache_mode": "disabled", "model": engine.info["model_id"],
+    return {"warmup_waves": warmup_waves, "cache_mode": "warm_prefix" if warm else "disabled", "model": engine.info["model_id"],
             "input_tokens": input_tokens, "output_tokens": output_tokens, "requests": requests, "concurrency": concurrency,
             "elapsed_s": elapsed, "output_tokens_per_s": requests * output_tokens / elapsed,
             "requests_per_s": requests / elapsed, "ttft_ms": spread(first), "itl_ms": spread(gaps),
             "latency_ms": spread(latency), "raw_ttft_s": first, "raw_itl_s": gaps, "raw_latency_s": latency,
-            "cached_tokens": 0, "peak_memory_bytes": after["peak_memory_bytes"], "metrics": after}
+            "cached_tokens": after["cached_tokens"] - before["cached_tokens"], "peak_memory_bytes": after["peak_memory_bytes"], "metrics": after}

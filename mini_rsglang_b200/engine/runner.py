@@ -134,7 +134,10 @@ class ModelRunner:
                 raise InvalidRequest("invalid KV memory budget")
             groups.append(CacheGroup(kind, window, pages))
         self.groups = groups
-        self.cache = CacheManager(groups, limits.page_size, limits.max_running)
+        if limits.prefix_cache and (any(g.kind != "full" for g in groups) or any(need is not None for need in state_needs)):
+            raise InvalidRequest("prefix sharing needs a model whose layers keep all their keys and no state of their "
+                                 "own per request: a window of keys or a recurrent state cannot be shared")
+        self.cache = CacheManager(groups, limits.page_size, limits.max_running, prefix_cache=limits.prefix_cache)
         self.storage = CacheStorage(kv_needs, state_needs, groups, group_of, limits.max_running, runtime)
         self._staging = _Staging(self.device)
         lib = host_api()

@@ -31,6 +31,7 @@ class FinishedRequest:
     reason: str
     prompt_tokens: int
     completion_tokens: int
+    cached_tokens: int = 0       # prompt tokens that were found in shared pages and not computed again
 
 
 class Scheduler:
@@ -56,7 +57,7 @@ class Scheduler:
         self._sample = np.empty(cap, dtype=np.int32)
         self._tokens = np.empty(max(limits.prefill_budget, 1), dtype=np.int32)
         self._done = (np.empty(64, dtype=np.int64), np.empty(64, dtype=np.int32), np.empty(64, dtype=np.int64),
-                      np.empty(64, dtype=np.int64))          # buffers of `drain`, which runs twice a step
+                      np.empty(64, dtype=np.int64), np.empty(64, dtype=np.int64))     # buffers of `drain`, which runs twice a step
 
     def __del__(self):
         handle, self.handle = getattr(self, "handle", None), None
@@ -129,13 +130,14 @@ class Scheduler:
     def drain(self) -> list[FinishedRequest]:
         """Requests that ended since the last call, in the order they ended."""
         out = []
-        req, reason, prompt, done = self._done
+        req, reason, prompt, done, cached = self._done
         cap = req.size
         while True:
-            n = self.lib.mrs_sched_drain(self.handle, req.ctypes.data, reason.ctypes.data, prompt.ctypes.data,
-                                         done.ctypes.data, cap)
+            n = self.lib.mrs_sched_drain_cached(self.handle, req.ctypes.data, reason.ctypes.data, prompt.ctypes.data,
+                                                done.ctypes.data, cached.ctypes.data, cap)
             for i in range(max(n, 0)):
-                out.append(FinishedRequest(int(req[i]), FINISH_REASONS[int(reason[i])], int(prompt[i]), int(done[i])))
+                out.append(FinishedRequest(int(req[i]), FINISH_REASONS[int(reason[i])], int(prompt[i]), int(done[i]),
+                                           int(cached[i])))
             if n < cap:
                 return out
 
@@ -144,4 +146,6 @@ class Scheduler:
         self.lib.mrs_sched_counters(self.handle, values.ctypes.data)
         names = ("submitted", "completed", "cancelled", "failed", "prompt_tokens", "generated_tokens",
                  "prefill_batches", "decode_batches", "mixed_batches")
-        return dict(zip(names, (int(v) for v in values)))
+        out = dict(zip(names, (int(v) for v in values)))
+        out["cached_tokens"] = int(self.lib.mrs_sched_cached_tokens(self.handle))
+        return out

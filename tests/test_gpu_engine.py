@@ -378,7 +378,77 @@ def test_command_line_load_test_reports_fixed_lengths(model_folders, tmp_path):
     refused = subprocess.run(cmd[:-2] + ["--concurrency", "9"], capture_output=True, text=True, timeout=300)
     assert refused.returncode != 0 and "concurrency must be <= max_running" in refused.stderr
     hot = subprocess.run(cmd[:-2] + ["--cache-mode", "hot"], capture_output=True, text=True, timeout=300)
-    assert hot.returncode != 0 and "no prefix cache" in hot.stderr
+    assert hot.returncode == 0, hot.stderr
+    run = json.loads(hot.stdout[hot.stdout.index("{"):])["runs"][0]
+    # every request brings the prompt that is in the cache: 32 of its 37 tokens lie in full pages and are not computed
+    assert run["cache_mode"] == "warm_prefix" and run["cached_tokens"] == 7 * 32
+    assert len(run["raw_latency_s"]) == 7 and run["metrics"]["cached_pages"] >= 2
+
+
+@pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
+def test_requests_that_share_their_first_tokens_read_them_from_the_cache(model_folders, dtype):
+    """Prefix sharing through the entry point: prompts with common first pages, one after the other and side by
+    side.  What a request reads from an earlier request's pages gives the tokens that computing it again gives
+    (equal in float32, where the cutting changes no bit), the counts of cached tokens are the full pages before
+    the last prompt token, and when the idle cache is cleared every page is free again."""
+    name = "D"
+    folder = model_folders[name]
+    cfg, weights = P.PlainConfig.load(folder), P.load_plain_weights(folder)
+    vocab = TINY[name][0]["vocab_size"]
+    common = [(5 * i + 3) % vocab for i in range(50)]
+    prompts = [common + [7, 8, 9], common[:40] + [1, 2], common + [7, 8, 9], [9] * 20, common[:17], common + [7, 8, 9, 10]]
+    out = {}
+    for share in (True, False):
+        limits = RuntimeConfig(max_seq_len=256, page_size=16, prefill_budget=24, max_running=2, prefix_cache=share)
+        engine = EngineHandle.load(folder, 0, config=limits, dtype=dtype, num_pages=40)
+        first = engine.generate_many(prompts[:1], SamplingParams(max_tokens=5, ignore_eos=True))
+        rest = engine.generate_many(prompts[1:], SamplingParams(max_tokens=5, ignore_eos=True))
+        results = first + rest
+        out[share] = [r.token_ids for r in results]
+        if share:
+            # full pages of 16 before the last prompt token that an earlier request had published
+            assert [r.cached_tokens for r in results] == [0, 32, 48, 0, 16, 48]
+            metrics = engine.metrics()
+            assert metrics["cached_tokens"] == 144 and metrics["cached_pages"] > 0
+            assert engine.runner.cache.free_pages() < 40
+            engine.runner.cache.check_integrity()
+            engine.clear_cache()
+        else:
+            assert all(r.cached_tokens == 0 for r in results)
+        assert engine.runner.cache.free_pages() == 40
+        engine.runner.cache.check_integrity()
+        engine.shutdown()
+    if dtype == "float32":
+        assert out[True] == out[False]
+    for prompt, generated in zip(prompts, out[True]):       # and the shared run's choices are the plain implementation's
+        tokens = list(prompt)
+        for token in generated:
+            logits = P.logits_of_sequence(cfg, weights, tokens)[-1]
+            best = P.greedy(logits)
+            allowed = 2e-5 if dtype == "float32" else 0.02 * logits.abs().max().item()
+            assert token == best or (logits[best] - logits[token]).item() <= allowed
+            tokens.append(token)
+
+
+def test_prefix_sharing_is_refused_for_a_model_that_cannot_share(model_folders):
+    """A window of keys or a state of its own per request cannot be shared: asking for it fails at load."""
+    from mini_rsglang_b200 import InvalidRequest
+    import dataclasses
+    from mini_rsglang_b200.models.registry import load_config, model_spec_for
+    from mini_rsglang_b200.parts.base import PartSpec
+    folder = model_folders["A"]
+    config = load_config(folder)
+    spec = model_spec_for(config)
+    mixer = spec.layers[0].parts["mixer"]
+    windowed = PartSpec(mixer.kind, {**mixer.params, "window": 8})
+    spec.layers[0] = dataclasses.replace(spec.layers[0], parts={**spec.layers[0].parts, "mixer": windowed})
+    limits = RuntimeConfig(max_seq_len=64, page_size=4, max_running=2, prefix_cache=True)
+    from mini_rsglang_b200.parts.base import Runtime
+    from mini_rsglang_b200.weights import load_weights
+    runtime = Runtime(torch.device("cuda:0"), torch.float32, 4)
+    tensors = load_weights(folder, spec.weight_specs(), runtime.dtype, runtime.device, spec.ignorable_weights)
+    with pytest.raises(InvalidRequest, match="prefix sharing"):
+        ModelRunner(config, tensors, runtime, limits, num_pages=16, spec=spec)
 
 
 def test_portions_of_a_long_prompt_share_their_keys(model_folders, monkeypatch):
