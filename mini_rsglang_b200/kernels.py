@@ -8,6 +8,7 @@ from __future__ import annotations
 
 import ctypes
 import math
+import os
 
 import torch
 
@@ -563,7 +564,7 @@ GEMM_TC_MAX_ROWS = 128          # what the kernel takes
 # against 6.79 ms).  Alone, a product of 16 to 128 rows takes the library the same 9 us (N = K = 4,096) while this
 # kernel goes from 11 to 33 us: its epilogue (a thread a weight row, looping over the rows) and the partial sums of
 # the ranges of K grow with the rows.
-GEMM_TC_BEST_ROWS = 8
+GEMM_TC_BEST_ROWS = int(os.environ.get("MRS_GEMM_TC_BEST_ROWS", "8"))      # the variable: for measuring other crossovers
 
 
 def gemm_tc_library() -> ctypes.CDLL:
