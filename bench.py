@@ -117,6 +117,29 @@ def model_numbers(cfg: dict, layers: int) -> dict:
             "attn_flops_per_pair": 4 * nq * d * layers}
 
 
+def kernel_shares(torch, run) -> None:
+    """Runs `run` under torch.profiler and prints, kernel by kernel, launches, the sum and the mean of their
+    durations and the share of the sum (kernels that start under their predecessor overlap it, so the sum is more
+    than the wall clock: compare shares)."""
+    import collections
+
+    from torch.profiler import ProfilerActivity, profile
+
+    with profile(activities=[ProfilerActivity.CUDA]) as prof:
+        run()
+        torch.cuda.synchronize()
+    table = collections.defaultdict(lambda: [0, 0.0])
+    for event in prof.events():
+        if event.device_type.name == "CUDA":
+            entry = table[event.name[:100]]
+            entry[0] += 1
+            entry[1] += event.device_time
+    total = sum(t for _, t in table.values()) or 1.0
+    print(f"kernels: {total / 1e3:.1f} ms in {sum(n for n, _ in table.values())} launches", file=sys.stderr)
+    for name, (n, t) in sorted(table.items(), key=lambda kv: -kv[1][1])[:24]:
+        print(f"{t / 1e3:9.2f} ms {100 * t / total:5.1f}% {n:7d} launches {t / n:8.1f} us  {name}", file=sys.stderr)
+
+
 def continuous_run(args, torch, shape_name: str, cfg: dict, peak: dict) -> dict:
     """The serving workload of the 0.6B configuration: `--requests` requests (64) whose prompt lengths are drawn
     uniformly from 16 to 2,048 (seeded), `--output-tokens` generated tokens each (64), all submitted at once to
@@ -161,6 +184,8 @@ def continuous_run(args, torch, shape_name: str, cfg: dict, peak: dict) -> dict:
     generated = sum(r.completion_tokens for r in results)
     prompt_tokens = sum(lengths)
     assert all(r.finish_reason == "length" and r.completion_tokens == out_tokens for r in results)
+    if args.kernel_shares:
+        kernel_shares(torch, lambda: engine.generate_many(prompts(lengths), params))
     engine.shutdown()
     total = prompt_tokens + generated
     return {
@@ -198,6 +223,9 @@ def main() -> int:
     parser.add_argument("--output-tokens", type=int, default=64, help="--continuous: generated tokens a request")
     parser.add_argument("--prefill-budget", type=int, default=512, help="--continuous: tokens a step")
     parser.add_argument("--max-running", type=int, default=64, help="--continuous: requests in flight at most")
+    parser.add_argument("--kernel-shares", action="store_true",
+                        help="--continuous: after the timed wave, one more wave under torch.profiler; its kernels' shares of the "
+                             "device's time go to standard error (not a timing)")
     args = parser.parse_args()
 
     if args.impl == "reference":
