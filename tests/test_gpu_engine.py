@@ -151,10 +151,12 @@ def test_recorded_steps_with_prompt_portions_equal_queued_ones(model_folders, na
     want = [plain(model_folders[name], tokens) for tokens in reqs]
     steps = mixed_schedule(lengths, 12, 40, [13, 24, 17, 20, 9])
     results = []
-    for record in (True, False):
+    for record in (True, False, "few"):
         runner = runner_for(model_folders[name], name, dtype, pages=128)
         assert runner.record_mixed
-        runner.record_mixed, runner.record_after = record, 0
+        runner.record_mixed, runner.record_after = bool(record), 0
+        if record == "few":                  # room for two recordings: every other shape is queued kernel by kernel
+            runner.max_records = 2
         for i in range(len(reqs)):
             runner.cache.open(i + 1)
         rows = []
@@ -170,14 +172,16 @@ def test_recorded_steps_with_prompt_portions_equal_queued_ones(model_folders, na
                 got = got.double().cpu()
                 T.check_rows(got, torch.stack([want[i][p] for i, p in wanted]), dtype, f"step {k} (recorded={record})")
                 rows.append(got)
-        if record:
+        if record == "few":
+            assert 1 <= len([key for key in runner._records if len(key) == 5]) <= 2 and runner.recorded_steps < len(steps)
+        elif record:
             fixed = [key for key in runner._records if len(key) == 5]
             mixed_steps = sum(1 for step in steps if any(take > 1 for _, _, take, _ in step))
             assert len(fixed) >= 3 and mixed_steps > len(fixed)               # recordings were replayed
             assert runner.recorded_steps == len(steps)
         results.append(torch.cat(rows))
     if dtype == "float32":
-        assert torch.equal(results[0], results[1])
+        assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
 
 
 def test_generation_through_recorded_steps_with_portions(model_folders):
@@ -470,6 +474,36 @@ def test_portions_of_a_long_prompt_share_their_keys(model_folders, monkeypatch):
     shared = [tiles for tiles, shares in calls if shares]
     assert shared and all((t[3] >> 8) >= 2 for tiles in shared for t in tiles if t[3])
     assert any(not shares and all(t[2] <= 64 for t in tiles) for tiles, shares in calls)      # one tile: 128 rows / 2 heads of a group
+
+
+def test_recorded_portions_of_long_prompts_share_their_keys_and_reuse_their_recording(model_folders):
+    """Portions of 256 tokens of two long prompts, one wanted place at most a step: the steps are recorded with fixed
+    shapes, entries that share their keys among them (the merge kernel is part of those recordings), and the second
+    prompt replays what the first recorded, with other tile lists in other pages.  The wanted rows equal the plain
+    implementation's, decoded tokens beside the last portions included."""
+    folder = model_folders["D"]
+    runner = runner_for(folder, "D", "bfloat16", pages=240, max_seq_len=2048)
+    reqs = T.requests_for(TINY["D"][0]["vocab_size"], [1540, 1541], seed=47)
+    for i, tokens in enumerate(reqs.values()):
+        want = plain(folder, tokens)
+        runner.cache.open(i + 1)
+        records = len(runner._records)
+        at = 0
+        for n in [256] * 6:
+            runner.cache.extend(i + 1, at + n)
+            last = at + n == 1536
+            got = runner.step([SequenceStep(i + 1, tokens[at:at + n], at, [n - 1] if last else [])])
+            at += n
+            assert (got is None) == (not last)
+        T.check_rows(got.double().cpu(), want[1535:1536], "bfloat16", f"request {i}: the last portion's last row")
+        for p in range(1536, len(tokens)):
+            runner.cache.extend(i + 1, p + 1)
+            got = runner.step([SequenceStep(i + 1, [tokens[p]], p, [0])])
+            T.check_rows(got.double().cpu(), want[p:p + 1], "bfloat16", f"request {i}: decoded token at {p}")
+        if i == 1:
+            assert len(runner._records) == records              # nothing new was recorded for the second prompt
+    fixed = [key for key in runner._records if len(key) == 5]
+    assert any(signature[0][2] for key in fixed for signature in key[4] if signature[0]), fixed      # entries that share keys
 
 
 def test_gate_up_product_for_many_rows_carries_the_activation(model_folders, monkeypatch):
