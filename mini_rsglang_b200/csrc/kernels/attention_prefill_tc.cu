@@ -4,7 +4,9 @@
 //
 // A CTA works on two tiles of 128 query rows of one key/value head: a tile is 128 / group
 // consecutive tokens of one request times the group's query heads, so a key is read once for all
-// the heads that share it, and the second tile holds the tokens that follow the first.  The keys
+// the heads that share it, and the second tile holds the tokens that follow the first.  A group
+// that does not divide 128 (5 query heads a key/value head: 25 tokens, 125 rows) leaves the tile's
+// last rows empty: they are zeroed once, masked everywhere and never stored.  The keys
 // are walked in blocks of 128:
 //   warp 0      fetches the query tiles and, page by page through the request's block table, the
 //               keys and values of every block with bulk tensor copies (TMA, 128-byte swizzle)
@@ -119,6 +121,15 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
         blocks = b1 - b0;
     }
 
+    const int used_rows = tokens_per_tile * group;             // rows of a tile that a copy of queries fills
+    if (used_rows < BM) {
+        // the rows behind them belong to no token: zeros, so that nothing they yield is anything but finite
+        for (int idx = threadIdx.x; idx < TILES * HALVES * (BM - used_rows) * 8; idx += THREADS) {
+            const int chunk = idx & 7, line = (idx >> 3) % (BM - used_rows), part = (idx >> 3) / (BM - used_rows);
+            *reinterpret_cast<uint4*>(q_smem + part * Q_HALF_BYTES + (used_rows + line) * 128 + chunk * 16) = make_uint4(0, 0, 0, 0);
+        }
+        fence_async_shared();
+    }
     if (threadIdx.x == 0) {
         mbar_init(&bars->q_full, 1);
         for (int s = 0; s < STAGES; ++s) {
@@ -155,7 +166,7 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
             tma_prefetch_descriptor(&k_map);
             tma_prefetch_descriptor(&v_map);
             // rows past the last token arrive as zeros or as other tokens' queries, and are never stored
-            mbar_arrive_expect_tx(&bars->q_full, TILES * Q_TILE_BYTES);
+            mbar_arrive_expect_tx(&bars->q_full, TILES * HALVES * used_rows * 128);
             for (int i = 0; i < TILES; ++i)
                 for (int h = 0; h < HALVES; ++h)
                     tma_load_3d(q_smem + i * Q_TILE_BYTES + h * Q_HALF_BYTES, &q_map, &bars->q_full, h * 64, kv_head * group,
@@ -434,9 +445,9 @@ MRS_EXPORT int mrs_attention_prefill_tc_kv_map(const void* cache, long long page
                                     CU_TENSOR_MAP_SWIZZLE_128B);
 }
 
-// Tensor map of the step's queries [tokens, nq, D] for copies of 64 columns of (128 / group tokens) x (group heads).
+// Tensor map of the step's queries [tokens, nq, D] for copies of 64 columns of (128 / group tokens, rounded down) x (group heads).
 MRS_EXPORT int mrs_attention_prefill_tc_q_map(const void* q, long long tokens, int nq, int group, void* map_out) {
-    if (tokens <= 0 || nq <= 0 || group <= 0 || BM % group || nq % group) return MRS_BAD_ARGUMENT;
+    if (tokens <= 0 || nq <= 0 || group <= 0 || group > BM || nq % group) return MRS_BAD_ARGUMENT;
     const uint64_t dims[3] = {(uint64_t)D, (uint64_t)nq, (uint64_t)tokens};
     const uint64_t strides[2] = {(uint64_t)D * 2, (uint64_t)nq * D * 2};
     const uint32_t box[3] = {64, (uint32_t)group, (uint32_t)(BM / group)};
@@ -448,7 +459,7 @@ MRS_EXPORT long long mrs_attention_prefill_tc_partial_floats(int num_tiles, int 
     return (long long)num_tiles * nkv * TILES * BM * PARTIAL_STRIDE;
 }
 
-// Work entries of up to 256 / group consecutive tokens of one request each: (sequence, first token, tokens, share).
+// Work entries of up to 2 x (128 / group, rounded down) consecutive tokens of one request each: (sequence, first token, tokens, share).
 // share = 0: the entry walks all its keys.  share = index | count << 8 (count 2..255, the `count` entries of one
 // portion one after the other): every entry walks one share of the key blocks; `partials`
 // (mrs_attention_prefill_tc_partial_floats) carries their sums and `with_shares` must be set, so that the merge runs.
@@ -459,7 +470,7 @@ MRS_EXPORT int mrs_attention_prefill_tc(const void* q_map, const void* k_map, co
     if (num_tiles <= 0) return 0;
     if (with_shares && (!partials || num_tiles > 65535)) return MRS_BAD_ARGUMENT;
     const int shift = page_shift_of(page_size);
-    if (shift < 0 || page_size < 8 || nkv <= 0 || nq % nkv || BM % (nq / nkv)) return MRS_BAD_ARGUMENT;
+    if (shift < 0 || page_size < 8 || nkv <= 0 || nq % nkv || nq / nkv > BM) return MRS_BAD_ARGUMENT;
     static bool configured = false;
     if (!configured) {
         cudaError_t e = cudaFuncSetAttribute(attention_prefill_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES);
@@ -484,7 +495,7 @@ MRS_EXPORT int mrs_attention_prefill_tc_take_error(unsigned int* word) { return 
 MRS_EXPORT int mrs_attention_prefill_tc_mirror_errors(unsigned int* host_word) { return mrs_set_error_mirror(host_word); }
 
 MRS_EXPORT const char* mrs_attention_prefill_tc_error_string(int code) {
-    if (code == MRS_BAD_ARGUMENT) return "arguments outside what the kernel supports (page size below 8 or no power of two, a group of query heads that does not divide 128)";
+    if (code == MRS_BAD_ARGUMENT) return "arguments outside what the kernel supports (page size below 8 or no power of two, more than 128 query heads a key/value head)";
     if (code == MRS_TENSOR_MAP_FAILED) return "the driver refused the tensor map (address, sizes or strides)";
     return cudaGetErrorString((cudaError_t)code);
 }

@@ -476,10 +476,11 @@ _prefill_libs: dict[int, ctypes.CDLL] = {}
 _prefill_kv_maps: dict[tuple, tuple] = {}
 _prefill_q_map: dict[torch.device, tuple] = {}
 PREFILL_TC_ROWS = 256          # two tiles of 128 query rows a CTA
+PREFILL_TC_TILES = 2           # a tile holds 128 // group tokens (a group that does not divide 128 leaves rows empty)
 
 
 def attention_prefill_tc_supported(d: int, group: int, page_size: int) -> bool:
-    return d in (64, 128) and 128 % group == 0 and page_size >= 8
+    return d in (64, 128) and 1 <= group <= PREFILL_TC_ROWS // PREFILL_TC_TILES and page_size >= 8
 
 
 def attention_prefill_tc_key_block(d: int) -> int:
@@ -794,8 +795,49 @@ _many_rows_lib = None
 _many_rows_maps: dict[tuple, tuple] = {}
 # Measured against the library's product followed by `silu_mul` (8B shape, K 4096, N 24576): 290 against 299 us at
 # 2,048 rows, 418 against 429 us at 3,072, 550 against 646 us at 4,096; below 2,048 rows the library's pair is ahead
-# (1,536: 221 against 217 us; 512: 90 against 83 us: the 128 x 256 tiles fill the SMs' last round badly).
-GEMM_GATED_ROWS_MIN = 2048
+# (1,536: 221 against 217 us; 512: 90 against 83 us: the 128 x 256 tiles fill the SMs' last round badly).  At other
+# shapes the order differs (prefill of 2,048 tokens: 14B shape, K 5120, N 34816: 58.2 ms with this kernel against
+# 57.7 ms; 0.6B shape, K 1024, N 6144: 4.9 against 4.4 ms), so from GEMM_GATED_ROWS_MIN rows on the two are timed
+# once per (N, K, thousand of rows) on the first such product and the faster one is kept (`gemm_gated_rows_wins`).
+GEMM_GATED_ROWS_MIN = int(os.environ.get("MRS_GEMM_GATED_ROWS_MIN", "2048"))      # the variable: for measuring other crossovers
+GEMM_GATED_MEASURE = "MRS_GEMM_GATED_ROWS_MIN" not in os.environ                  # False: the kernel from that many rows on
+_gated_rows_choice: dict[tuple, bool] = {}
+
+
+def gemm_gated_rows_wins(x: torch.Tensor, weight: torch.Tensor) -> bool:
+    """Whether the tcgen05 gate/up product with the activation in it is the faster way for these sizes on this
+    device: at least GEMM_GATED_ROWS_MIN rows, and ahead of the library's product followed by `silu_mul` when the
+    two were timed (three runs each after one, CUDA events, on buffers of their own; never while a step is being
+    recorded: such steps have fewer rows anyway)."""
+    rows = x.shape[0]
+    if rows < GEMM_GATED_ROWS_MIN or not gemm_gated_rows_supported(x, weight):
+        return False
+    if not GEMM_GATED_MEASURE or torch.cuda.is_current_stream_capturing():
+        return True
+    n, k = weight.shape
+    key = (x.device, n, k, min(-(-rows // 1024), 16))
+    if key not in _gated_rows_choice:
+        act = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=x.device)
+
+        def own():
+            gemm_gated_rows(x, weight, act)
+
+        def library():
+            silu_mul(torch.mm(x, weight.t()), act, 64)
+
+        times = []
+        for run in (own, library):
+            run()
+            start, end = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            start.record()
+            for _ in range(3):
+                run()
+            end.record()
+            end.synchronize()
+            times.append(start.elapsed_time(end))
+        _gated_rows_choice[key] = times[0] <= times[1]
+    return _gated_rows_choice[key]
+
 
 def gemm_many_rows_library() -> ctypes.CDLL:
     global _many_rows_lib

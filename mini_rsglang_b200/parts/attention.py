@@ -65,10 +65,11 @@ def attention_tile_lists(facts: StepFacts, group: int, wide_rows: int, kv_heads:
     if key in facts.plans:
         return facts.plans[key]
     narrow_tokens = kernels.MMA_ROWS_NARROW // group
-    wide_tokens = wide_rows // group
+    tensor_core = wide_rows == kernels.PREFILL_TC_ROWS
+    tiles = kernels.PREFILL_TC_TILES if tensor_core else 1            # tiles of an entry; a tile holds whole tokens
+    wide_tokens = tiles * (wide_rows // tiles // group)
     real = len(facts.start_pos)
     lengths = [facts.q_start[i + 1] - facts.q_start[i] for i in range(real)]
-    tensor_core = wide_rows == kernels.PREFILL_TC_ROWS
     entries = sum(-(-n // wide_tokens) for n in lengths if n > narrow_tokens)
     spare = sms // max(entries * kv_heads, 1) if tensor_core else 1      # CTAs an entry may become
     narrow, wide = [], []

@@ -55,8 +55,7 @@ class SwiGLU(FeedForward):
                 kernels.gemm_tc(h, self.gate_up, act, gated=True)
         else:
             h = plain(h)
-            if (self.block and not observing(ctx) and h.shape[0] >= kernels.GEMM_GATED_ROWS_MIN
-                    and kernels.gemm_gated_rows_supported(h, self.gate_up)):
+            if self.block == 64 and not observing(ctx) and kernels.gemm_gated_rows_wins(h, self.gate_up):
                 kernels.gemm_gated_rows(h, self.gate_up, act)      # many rows: the tcgen05 product with the activation in it
             else:
                 kernels.silu_mul(linear(h, self.gate_up), act, self.block)

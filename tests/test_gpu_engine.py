@@ -476,6 +476,24 @@ def test_portions_of_a_long_prompt_share_their_keys(model_folders, monkeypatch):
     assert any(not shares and all(t[2] <= 64 for t in tiles) for tiles, shares in calls)      # one tile: 128 rows / 2 heads of a group
 
 
+def test_the_gate_up_product_for_many_rows_is_chosen_by_a_measurement_kept_per_shape(monkeypatch):
+    """From the least number of rows on, the tcgen05 gate/up product and the library's product with `silu_mul`
+    are timed once for a shape and the faster one is kept; below it, and where the kernel cannot run, the library."""
+    from mini_rsglang_b200 import kernels
+
+    monkeypatch.setattr(kernels, "GEMM_GATED_ROWS_MIN", 256)
+    monkeypatch.setattr(kernels, "GEMM_GATED_MEASURE", True)
+    weight = (torch.randn(512, 256, device="cuda:0") / 16).to(torch.bfloat16)
+    x = torch.randn(300, 256, device="cuda:0").to(torch.bfloat16)
+    kernels._gated_rows_choice.clear()
+    first = kernels.gemm_gated_rows_wins(x, weight)
+    assert isinstance(first, bool) and len(kernels._gated_rows_choice) == 1
+    assert kernels.gemm_gated_rows_wins(x, weight) is first and len(kernels._gated_rows_choice) == 1      # kept
+    assert kernels.gemm_gated_rows_wins(x[:100], weight) is False                                            # too few rows
+    assert kernels.gemm_gated_rows_wins(x, weight[:200]) is False                                            # no whole blocks
+    kernels.check_device_errors()
+
+
 def test_recorded_portions_of_long_prompts_share_their_keys_and_reuse_their_recording(model_folders):
     """Portions of 256 tokens of two long prompts, one wanted place at most a step: the steps are recorded with fixed
     shapes, entries that share their keys among them (the merge kernel is part of those recordings), and the second
@@ -513,6 +531,7 @@ def test_gate_up_product_for_many_rows_carries_the_activation(model_folders, mon
     from mini_rsglang_b200 import kernels
 
     monkeypatch.setattr(kernels, "GEMM_GATED_ROWS_MIN", 64)
+    monkeypatch.setattr(kernels, "GEMM_GATED_MEASURE", False)      # the kernel, whatever the library would take here
     used = []
     real = kernels.gemm_gated_rows
     monkeypatch.setattr(kernels, "gemm_gated_rows", lambda *a, **k: (used.append("gemm_gated_rows"), real(*a, **k))[1])

@@ -244,7 +244,9 @@ class PagedCase:
 
     def run_mma(self, mode, splits=1):
         group = self.nq // self.nkv
-        per_tile = {"rows": 64, "tc": 256, "tc_shares": 256}.get(mode, 16) // group
+        per_tile = {"rows": 64}.get(mode, 16) // group
+        if mode in ("tc", "tc_shares"):          # two tiles of 128 rows, each a whole number of tokens
+            per_tile = 2 * (128 // group)
         tiles = []
         for i in range(len(self.spans)):
             first, n = self.q_start[i], self.q_start[i + 1] - self.q_start[i]
@@ -320,27 +322,28 @@ def test_attention_decode_tma(nq, nkv, d, page, splits):
     close(case.run_mma("tma", splits), case.plain(), torch.bfloat16, f"attention_decode_tma, {splits} splits")
 
 
-TC_SHAPES = [(8, 2, 128, 16), (12, 3, 64, 8), (4, 4, 64, 64), (16, 1, 128, 128), (2, 1, 128, 32), (32, 1, 64, 16)]
+TC_SHAPES = [(8, 2, 128, 16), (12, 3, 64, 8), (4, 4, 64, 64), (16, 1, 128, 128), (2, 1, 128, 32), (32, 1, 64, 16),
+             (10, 2, 128, 16), (3, 1, 64, 8), (14, 2, 128, 32), (48, 1, 64, 16)]      # groups of 5, 3, 7, 48: rows of a tile stay empty
 TC_SPANS = [(0, 1), (0, 70), (130, 3), (257, 1), (63, 66), (1, 2), (300, 200), (0, 513), (1000, 37)]
 
 
 @pytest.mark.parametrize("nq,nkv,d,page", TC_SHAPES)
 def test_attention_prefill_tc(nq, nkv, d, page):
-    """Head sizes 64 and 128, groups of 1 to 32 query heads, pages of 8 to 128 rows; portions of 1 to
-    513 tokens on contexts up to 1,037: several tiles a request, several blocks of keys a tile, blocks
-    that need no mask, the diagonal, and tiles that are not full."""
+    """Head sizes 64 and 128, groups of 1 to 48 query heads (among them groups that do not divide a tile's 128
+    rows), pages of 8 to 128 rows; portions of 1 to 513 tokens on contexts up to 1,037: several tiles a request,
+    several blocks of keys a tile, blocks that need no mask, the diagonal, and tiles that are not full."""
     assert kernels.attention_prefill_tc_supported(d, nq // nkv, page)
     case = PagedCase(torch.bfloat16, nq, nkv, d, page, TC_SPANS, seed=nq + d)
     close(case.run_mma("tc"), case.plain(), torch.bfloat16, "attention_prefill_tc")
 
 
 @pytest.mark.parametrize("shares", [2, 3, 7])
-@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (4, 4, 64, 8), (4, 1, 128, 32)])
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (4, 4, 64, 8), (4, 1, 128, 32), (10, 2, 128, 16)])
 def test_attention_prefill_tc_shares_of_the_keys(nq, nkv, d, page, shares):
     """Entries that walk one share of their key blocks each, merged by the second kernel: portions deep in a long
     context, a fresh prompt whose first entries have fewer blocks than shares (empty shares), a tile without
     a block in the last share, a ragged last entry."""
-    case = PagedCase(torch.bfloat16, nq, nkv, d, page, [(1000, 70), (0, 300), (130, 3 + 256 // (nq // nkv)), (2000, 40)], seed=shares)
+    case = PagedCase(torch.bfloat16, nq, nkv, d, page, [(1000, 70), (0, 300), (130, 3 + 2 * (128 // (nq // nkv))), (2000, 40)], seed=shares)
     close(case.run_mma("tc_shares", shares), case.plain(), torch.bfloat16, f"{shares} shares of the keys")
 
 

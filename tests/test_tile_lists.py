@@ -18,7 +18,8 @@ def facts_of(lengths, starts, padded=(0, 0)):
 
 
 @pytest.mark.parametrize("group,wide_rows,sms", [(4, kernels.PREFILL_TC_ROWS, 148), (2, kernels.PREFILL_TC_ROWS, 148),
-                                                 (1, 64, 1), (8, kernels.PREFILL_TC_ROWS, 16)])
+                                                 (1, 64, 1), (8, kernels.PREFILL_TC_ROWS, 16), (5, kernels.PREFILL_TC_ROWS, 148),
+                                                 (3, 64, 1)])
 def test_every_row_lies_in_one_tile(group, wide_rows, sms):
     rng = random.Random(group * 1000 + sms)
     for _ in range(50):
@@ -36,7 +37,8 @@ def test_every_row_lies_in_one_tile(group, wide_rows, sms):
                 covered[r] += 1
         by_share = {}
         for seq, first, tokens, share in lists.wide:
-            assert 0 < tokens <= wide_rows // group
+            per_tile = wide_rows // 2 // group if wide_rows == kernels.PREFILL_TC_ROWS else wide_rows // group
+            assert 0 < tokens <= (2 * per_tile if wide_rows == kernels.PREFILL_TC_ROWS else per_tile)
             assert facts.q_start[seq] <= first and first + tokens <= facts.q_start[seq + 1]
             count = share >> 8
             if count:
