@@ -262,7 +262,7 @@ def main() -> int:
     max_batch = max([batch] + point_batches)
     page = 16
     pages = max_batch * (-(-context // page)) + 2 * (-(-2048 // page)) + 8
-    limits = RuntimeConfig(max_seq_len=context, page_size=page, prefill_budget=2048, max_running=max_batch, max_waiting=256)
+    limits = RuntimeConfig(max_seq_len=max(context, 2048), page_size=page, prefill_budget=2048, max_running=max_batch, max_waiting=256)
     engine = EngineHandle.from_random(config, seed=1, dtype="bfloat16", config=limits, num_pages=pages)
     runner = engine.runner
     for entry in runner.storage.entries:      # cache contents do not change the timing; avoid all-zero keys anyway
