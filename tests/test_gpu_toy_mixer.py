@@ -409,12 +409,15 @@ def plain_window(folder, tokens, window_of_layer):
     return P.linear(ar, x, w["lm_head.weight"], round_out=False)
 
 
+@pytest.mark.parametrize("one_wanted", [False, True])
 @pytest.mark.parametrize("dtype,head_dim", [("float32", 32), ("bfloat16", 64), ("bfloat16", 32)])
-def test_window_layers_have_pages_of_their_own_and_give_them_back(tmp_path, dtype, head_dim):
+def test_window_layers_have_pages_of_their_own_and_give_them_back(tmp_path, dtype, head_dim, one_wanted):
     """A layer that sees a window of keys beside one that sees all: two page groups, the window group's
     pages go back to its pool while the request runs (its block table gets holes), the pool is far
     smaller than the request and is used again and again, and the logits equal the plain ones.  Head
-    size 64 runs the kernels fed by bulk tensor copies and the tcgen05 kernel with a window."""
+    size 64 runs the kernels fed by bulk tensor copies and the tcgen05 kernel with a window.  With one wanted place
+    a step the steps are recorded with fixed shapes: the two layers plan tile lists of their own (a window's first
+    key differs), both travel with the step's layout, and recordings are replayed over block tables with holes."""
     register_architecture("toy_window", WindowConfig, window_spec, replace=True)
     try:
         window, page = 24, 8
@@ -435,8 +438,9 @@ def test_window_layers_have_pages_of_their_own_and_give_them_back(tmp_path, dtyp
             n = min(sizes[step % len(sizes)], len(tokens) - fed)
             cache.extend(1, fed + n)
             least_free = min(least_free, cache.free_pages(0))
-            got = runner.step([SequenceStep(1, tokens[fed:fed + n], fed, [0, n - 1])]).double().cpu()
-            T.check_rows(got, want[[fed, fed + n - 1]], dtype, f"window model, {dtype}, head {head_dim}, step {step}")
+            places = [n - 1] if one_wanted else [0, n - 1]
+            got = runner.step([SequenceStep(1, tokens[fed:fed + n], fed, places)]).double().cpu()
+            T.check_rows(got, want[[fed + p for p in places]], dtype, f"window model, {dtype}, head {head_dim}, step {step}")
             fed += n
             cache.trim(1, fed)
             cache.check_integrity()
@@ -449,5 +453,12 @@ def test_window_layers_have_pages_of_their_own_and_give_them_back(tmp_path, dtyp
         assert cache.total_pages(0) - least_free <= -(-(window - 1 + 64) // page) + 1 < len(tokens) // page
         cache.close(1)
         cache.check_integrity()
+        fixed = [key for key in runner._records if len(key) == 5]
+        if one_wanted:
+            assert fixed and runner.recorded_steps == step
+            if dtype == "bfloat16":          # a plan a layer: the window's tile lists are not the full layer's
+                assert all(len(runner._records[key].ctx.plan_views) == 2 for key in fixed)
+        else:
+            assert not fixed
     finally:
         ARCHITECTURES.pop("toy_window", None)
