@@ -434,6 +434,46 @@ def test_requests_that_share_their_first_tokens_read_them_from_the_cache(model_f
             tokens.append(token)
 
 
+@pytest.mark.parametrize("seed", [11, 12, 13])
+def test_random_traffic_gives_the_same_tokens_with_and_without_recordings_and_sharing(model_folders, seed):
+    """Random prompts from a few families of common first tokens, random lengths and output lengths, a small token
+    budget and a page pool that holds only some of them at a time: in float32 an engine that records its steps and
+    shares prefixes generates, token for token, what one that queues every kernel and shares nothing generates;
+    nothing leaks, and the manager's books balance after every wave."""
+    import random
+    name = "B"
+    folder = model_folders[name]
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(seed)
+    families = [[rng.randrange(3, vocab) for _ in range(70)] for _ in range(3)]
+    waves = []
+    for _ in range(3):
+        prompts, params = [], []
+        for _ in range(rng.randrange(4, 9)):
+            family = rng.choice(families)
+            prompts.append(family[:rng.randrange(1, 70)] + [rng.randrange(3, vocab) for _ in range(rng.randrange(0, 9))])
+            params.append(SamplingParams(max_tokens=rng.randrange(1, 12), ignore_eos=rng.random() < 0.5,
+                                         temperature=rng.choice([0.0, 0.0, 0.8]), seed=rng.randrange(1 << 30)))
+        waves.append((prompts, params))
+    out = []
+    for fancy in (True, False):
+        limits = RuntimeConfig(max_seq_len=128, page_size=16, prefill_budget=32, max_running=4, prefix_cache=fancy, record_mixed_steps=fancy)
+        engine = EngineHandle.load(folder, 0, config=limits, dtype="float32", num_pages=24)
+        engine.runner.record_decode = fancy
+        tokens = []
+        for prompts, params in waves:
+            results = engine.generate_many(prompts, params)
+            tokens.append([(r.token_ids, r.finish_reason) for r in results])
+            engine.runner.cache.check_integrity()
+        if fancy:
+            assert engine.metrics()["cached_tokens"] > 0 and any(len(key) == 5 for key in engine.runner._records)
+            engine.clear_cache()
+        assert engine.runner.cache.free_pages() == 24
+        engine.shutdown()
+        out.append(tokens)
+    assert out[0] == out[1]
+
+
 def test_prefix_sharing_is_refused_for_a_model_that_cannot_share(model_folders):
     """A window of keys or a state of its own per request cannot be shared: asking for it fails at load."""
     from mini_rsglang_b200 import InvalidRequest
