@@ -58,6 +58,9 @@ void Scheduler::finish(size_t index, Finish reason) {
         case Finish::Cancelled: counters_.cancelled += 1; break;
         case Finish::Error: counters_.failed += 1; break;
     }
+    // a request that ended by itself leaves what it generated behind as well: a next turn that begins with
+    // this one's prompt and answer reads both (reference: terminal(), crates/runtime/src/scheduler.rs:94-96)
+    if (reason == Finish::Stop || reason == Finish::Length) cache_->publish(r.input.id, r.tokens.data(), r.computed);
     cache_->close(r.input.id);
     running_.erase(running_.begin() + (std::ptrdiff_t)index);
 }

@@ -16,8 +16,9 @@
 //
 // With prefix sharing in the cache manager a request is admitted with its prompt: what the tree has of the
 // prompt's first pages is not computed again (`computed` starts behind them; the last prompt token is always
-// computed), and when a request's prompt is in the cache its full pages are published for those that follow
-// (reference: acquire / publish, crates/runtime/src/scheduler.rs:174, 283).
+// computed), and when a request's prompt is in the cache its full pages are published for those that follow;
+// a request that ends by a stop token or by its length publishes what it generated too
+// (reference: acquire / publish, crates/runtime/src/scheduler.rs:94-96, 174, 283).
 #pragma once
 #include <cstdint>
 #include <deque>

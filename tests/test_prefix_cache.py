@@ -232,6 +232,27 @@ def test_a_repeated_prompt_is_not_computed_again():
     assert cache.free_pages() == 64 and s.idle()
 
 
+def test_a_next_turn_reads_the_prompt_and_the_answer_of_the_turn_before():
+    s, cache = make()
+    prompt = list(range(10, 20))                 # 10 tokens, pages of 4
+    s.submit(1, prompt, max_tokens=7)
+    _, finished = drive(s, cache)
+    assert finished[0].reason == "length" and finished[0].completion_tokens == 7
+    # the request held 10 + 7 tokens, of which the last was sampled and never computed: 16 tokens = 4 full pages stay
+    assert cache.cached_pages() == 4
+    turn = prompt + [42] * 7 + [50, 51, 52]
+    s.submit(2, turn, max_tokens=1)
+    shapes, finished = drive(s, cache)
+    assert finished[0].cached_tokens == 16 and shapes == [[(2, 16, 4, True)]]
+    s.submit(3, prompt, max_tokens=2)
+    s.plan()
+    s.cancel(3)                                  # a cancelled request publishes nothing beyond its prompt's pages
+    s.plan()
+    cache.check_integrity()
+    cache.clear_idle_cache()
+    assert cache.free_pages() == 64
+
+
 def test_requests_that_run_together_share_what_the_first_has_published():
     s, cache = make(budget=8, running=2)
     prompt = list(range(30, 47))                 # 17 tokens
