@@ -43,6 +43,9 @@ def build_parser() -> argparse.ArgumentParser:
                    help="do not share the cache pages of equal first tokens between requests")
     p.add_argument("--dtype", choices=["bfloat16", "float32"], default="bfloat16")
     p.add_argument("--num-pages", type=int, default=None, help="size of the page pool (overrides --kv-mib)")
+    p.add_argument("--random-weights", type=int, default=None, metavar="SEED",
+                   help="take only config.json from --model and draw the weights on the device from this seed "
+                        "(other tensors than `random-model` writes for the seed: those are drawn on the CPU)")
     sub = p.add_subparsers(dest="command", required=True)
 
     g = sub.add_parser("generate", help="generate from token ids")
@@ -79,6 +82,20 @@ def runtime_config(args) -> RuntimeConfig:
                          prefix_cache=not args.no_prefix_cache)
 
 
+def load_engine(args, limits: RuntimeConfig):
+    """The engine of the command line: weights from the model folder, or, with --random-weights, seeded random ones
+    for the folder's config.json, drawn on the device."""
+    from .engine.handle import EngineHandle
+
+    if args.random_weights is None:
+        return EngineHandle.load(args.model, args.device, args.kv_mib * 1024 * 1024, limits, dtype=args.dtype,
+                                 num_pages=args.num_pages)
+    from .models.registry import load_config
+
+    return EngineHandle.from_random(load_config(args.model), args.random_weights, args.device, args.kv_mib * 1024 * 1024,
+                                    limits, dtype=args.dtype, num_pages=args.num_pages)
+
+
 def event_json(event) -> str:
     """One event in the reference's JSON shape (serde's externally tagged enum)."""
     from .engine.handle import Error, Finished, Token
@@ -110,8 +127,7 @@ def command_generate(args) -> int:
     sampling.validate()
     if args.kv_mib <= 0:
         raise InvalidRequest("kv_mib must be positive")
-    engine = EngineHandle.load(args.model, args.device, args.kv_mib * 1024 * 1024, runtime_config(args),
-                               dtype=args.dtype, num_pages=args.num_pages)
+    engine = load_engine(args, runtime_config(args))
     streams = [engine.generate(GenerateRequest(TokenIds(p), sampling)) for p in prompts]
     completed = True
     for stream in streams:
@@ -145,8 +161,7 @@ def command_bench(args) -> int:
     for warm in {"cold": (False,), "hot": (True,), "both": (False, True)}[args.cache_mode]:
         limits = runtime_config(args)
         limits.prefix_cache = warm          # a cold run shares nothing, a hot one reads a prompt that is in the cache
-        engine = EngineHandle.load(args.model, args.device, args.kv_mib * 1024 * 1024, limits, dtype=args.dtype,
-                                   num_pages=args.num_pages)
+        engine = load_engine(args, limits)
         try:
             runs.append(load_test.run(engine, args.input_tokens, args.output_tokens, args.requests, args.concurrency,
                                       args.seed, warm=warm))

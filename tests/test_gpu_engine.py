@@ -360,6 +360,17 @@ def test_command_line_generates_what_the_entry_point_generates(model_folders, tm
     assert tokens == P.generate_greedy(cfg, weights, [3, 1, 4, 1, 5], 5)
     bad = subprocess.run(cmd[:-6] + ["--token-ids", "3,x", "--max-tokens", "5"], capture_output=True, text=True, timeout=300)
     assert bad.returncode != 0 and "comma-separated integers" in bad.stderr
+    # --random-weights SEED: only config.json is read; the same seed gives the same tokens
+    only_config = tmp_path / "only_config"
+    only_config.mkdir()
+    (only_config / "config.json").write_text(open(os.path.join(folder, "config.json")).read())
+    runs = []
+    for seed in ("5", "5"):
+        random_cmd = [cmd[0], cmd[1], "--model", str(only_config), "--random-weights", seed] + cmd[4:-1]
+        proc = subprocess.run(random_cmd, capture_output=True, text=True, timeout=300)
+        assert proc.returncode == 0, proc.stderr
+        runs.append(proc.stdout.strip().splitlines()[0])
+    assert runs[0] == runs[1] and len(runs[0].split(",")) == 5
 
 
 def test_command_line_load_test_reports_fixed_lengths(model_folders, tmp_path):
