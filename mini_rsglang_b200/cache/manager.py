@@ -61,6 +61,7 @@ def host_api() -> ctypes.CDLL:
         "mrs_sched_tokens": (c_int, [c_vp, c_i64, c_i64, c_i64, c_vp]),
         "mrs_sched_plan_tokens": (c_i64, [c_vp, c_vp, c_i64]),
         "mrs_sched_commit": (c_int, [c_vp, c_vp, c_int]),
+        "mrs_sched_resolve": (c_int, [c_vp, c_vp, c_vp, c_int]),
         "mrs_sched_fail": (c_int, [c_vp, c_int]),
         "mrs_sched_drain": (c_int, [c_vp, c_vp, c_vp, c_vp, c_vp, c_int]),
         "mrs_sched_counters": (None, [c_vp, c_vp]),

@@ -17,6 +17,7 @@ class RuntimeConfig:
     prefix_cache: bool = False   # requests share the full pages of equal first tokens (the reference's default is on;
                                  # here the entry point leaves it off unless asked, the command line turns it on)
     record_mixed_steps: bool = True   # steps with prompt portions are recorded with fixed shapes and replayed
+    overlap_steps: bool = True        # a step is queued before the tokens of the step before it have reached the host
 
     def validate(self) -> None:
         limits = (self.max_seq_len, self.page_size, self.prefill_budget, self.max_running,

@@ -195,6 +195,14 @@ API int mrs_sched_commit(void* s, const int32_t* sampled, int n) {
         return 0;
     });
 }
+// The values of tokens that were committed as unknown (-1): (request, token) pairs.
+API int mrs_sched_resolve(void* s, const int64_t* requests, const int32_t* tokens, int n) {
+    return guarded([&] {
+        static_cast<mrs::Scheduler*>(s)->resolve(std::vector<int64_t>(requests, requests + n),
+                                                 std::vector<int32_t>(tokens, tokens + n));
+        return 0;
+    });
+}
 API int mrs_sched_fail(void* s, int reason) {
     return guarded([&] {
         static_cast<mrs::Scheduler*>(s)->fail(static_cast<mrs::Finish>(reason));

@@ -93,7 +93,8 @@ const std::vector<PlannedSequence>& Scheduler::plan() {
         if (running_[i].cancel) finish(i, Finish::Cancelled);
     admit();
     bool any_prefill = false, any_decode = false;
-    for (const auto& r : running_) (r.computed < r.prompt_len ? any_prefill : any_decode) = true;
+    for (const auto& r : running_)
+        if (!r.length_reached) (r.computed < r.prompt_len ? any_prefill : any_decode) = true;
     if (!any_prefill && !any_decode) return plan_;
     bool take_prefill = true, take_decode = true;
     if (policy_ == Policy::Alternate) {
@@ -107,7 +108,7 @@ const std::vector<PlannedSequence>& Scheduler::plan() {
     if (take_decode) {
         for (size_t i = 0; i < running_.size() && budget > 0; ++i) {
             Running& r = running_[i];
-            if (r.computed < r.prompt_len) continue;
+            if (r.computed < r.prompt_len || r.length_reached) continue;
             if (cache_->extend(r.input.id, r.computed + 1) != kOk)
                 throw std::logic_error("a running request ran out of promised pages");
             plan_.push_back({r.input.id, r.slot, r.computed, 1, true});
@@ -141,14 +142,33 @@ const Running* Scheduler::find(int64_t request) const {
     return nullptr;
 }
 
+// Whether a request whose newest token is `token` ends with it, and why.
+bool Scheduler::ends_with(Running& r, int32_t token, Finish* reason) const {
+    if (r.cancel) *reason = Finish::Cancelled;
+    else if (!r.input.ignore_eos && std::find(eos_.begin(), eos_.end(), token) != eos_.end()) *reason = Finish::Stop;
+    else if (r.generated >= r.input.max_tokens) *reason = Finish::Length;
+    else return false;
+    return true;
+}
+
 void Scheduler::commit(const std::vector<int32_t>& sampled) {
     size_t expected = 0;
     for (const auto& p : plan_) expected += p.sample;
     if (sampled.size() != expected) throw std::invalid_argument("runner output IDs do not match sampled batch");
-    std::vector<std::pair<size_t, Finish>> ending;   // ascending by index: plan_index_ is ascending per kind
+    std::vector<std::pair<size_t, Finish>> ending;
     size_t next = 0;
     for (size_t j = 0; j < plan_.size(); ++j) {
-        Running& r = running_[plan_index_[j]];
+        // by its id: a request may have ended between plan() and commit() (resolve() of the step before)
+        size_t index = plan_index_[j];
+        if (index >= running_.size() || running_[index].input.id != plan_[j].request) {
+            for (index = 0; index < running_.size(); ++index)
+                if (running_[index].input.id == plan_[j].request) break;
+        }
+        if (index == running_.size()) {
+            next += plan_[j].sample;
+            continue;
+        }
+        Running& r = running_[index];
         const bool prompt_was_open = r.computed < r.prompt_len;
         r.computed = plan_[j].start_pos + plan_[j].count;
         cache_->trim(r.input.id, r.computed);
@@ -156,19 +176,40 @@ void Scheduler::commit(const std::vector<int32_t>& sampled) {
             cache_->publish(r.input.id, r.tokens.data(), r.prompt_len);
         if (!plan_[j].sample) continue;
         const int32_t token = sampled[next++];
+        if (r.unknown) throw std::logic_error("a second token of a request was committed before the first was resolved");
         r.tokens.push_back(token);
         r.generated += 1;
         counters_.generated_tokens += 1;
-        if (r.cancel) ending.push_back({plan_index_[j], Finish::Cancelled});
-        else if (!r.input.ignore_eos && std::find(eos_.begin(), eos_.end(), token) != eos_.end())
-            ending.push_back({plan_index_[j], Finish::Stop});
-        else if (r.generated >= r.input.max_tokens) ending.push_back({plan_index_[j], Finish::Length});
+        if (token == kUnknownToken) {
+            r.unknown = true;
+            r.length_reached = r.generated >= r.input.max_tokens;
+            continue;
+        }
+        Finish reason;
+        if (ends_with(r, token, &reason)) ending.push_back({index, reason});
     }
     std::sort(ending.begin(), ending.end(), [](const auto& a, const auto& b) { return a.first < b.first; });
     size_t removed = 0;
     for (auto& [index, reason] : ending) finish(index - removed++, reason);
     plan_.clear();
     plan_index_.clear();
+}
+
+void Scheduler::resolve(const std::vector<int64_t>& requests, const std::vector<int32_t>& tokens) {
+    if (requests.size() != tokens.size()) throw std::invalid_argument("resolve: as many tokens as requests");
+    for (size_t k = 0; k < requests.size(); ++k) {
+        size_t index = 0;
+        for (; index < running_.size(); ++index)
+            if (running_[index].input.id == requests[k]) break;
+        if (index == running_.size()) continue;                  // ended meanwhile
+        Running& r = running_[index];
+        if (!r.unknown) throw std::logic_error("resolve: the request has no unknown token");
+        if (tokens[k] < 0 || tokens[k] >= vocab_size_) throw std::invalid_argument("resolve: token outside the vocabulary");
+        r.tokens.back() = tokens[k];
+        r.unknown = false;
+        Finish reason;
+        if (ends_with(r, tokens[k], &reason)) finish(index, reason);
+    }
 }
 
 void Scheduler::fail(Finish reason) {

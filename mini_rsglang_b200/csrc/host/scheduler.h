@@ -48,7 +48,13 @@ struct Running {
     int64_t cached = 0;            // prompt tokens found in shared pages at admission
     int slot = -1;
     bool cancel = false;
+    bool unknown = false;          // its last token was committed before its value was known (kUnknownToken)
+    bool length_reached = false;   // ... and was its last by max_tokens: the request ends when the value arrives
 };
+
+// A sampled token whose value the caller does not know yet (the step that samples it is still running): commit()
+// takes it in a value's place, resolve() brings the value.
+constexpr int32_t kUnknownToken = -1;
 
 struct PlannedSequence {
     int64_t request;
@@ -93,7 +99,16 @@ public:
 
     // One token per planned sequence with sample == true, in plan order.
     // Throws std::invalid_argument when the count differs.
+    // A token may be kUnknownToken: the caller has queued the step and goes on before it has read what was
+    // sampled.  The request then counts as one token further (its next step decodes that token, which the
+    // caller takes from the device), but whether it ends is decided when resolve() brings the value: until
+    // then it is planned as if it went on, except that a request at its max_tokens is not planned again.  At
+    // most one token of a request is unknown at a time.  A request that has ended since the plan (by resolve()
+    // or a cancel) is passed over, its token dropped.
     void commit(const std::vector<int32_t>& sampled);
+    // The values of tokens committed as unknown: (request, token) in any order.  Each request is finished
+    // here if the token ends it (stop token, max_tokens reached, cancelled); a request that is gone is skipped.
+    void resolve(const std::vector<int64_t>& requests, const std::vector<int32_t>& tokens);
     // The step failed (or the engine shuts down): every request ends with `reason`, pages freed.
     void fail(Finish reason);
     // Requests that ended since the last call (by cancel, plan, commit or fail), in the order they ended.
@@ -103,6 +118,7 @@ public:
 
 private:
     void finish(size_t index, Finish reason);
+    bool ends_with(Running& r, int32_t token, Finish* reason) const;
     void admit();
     CacheManager* cache_;
     int64_t max_seq_len_, prefill_budget_;

@@ -4,6 +4,28 @@
 #include "common.cuh"
 
 // ---------------------------------------------------------------------------------------------
+// Tokens that the step before sampled and the host has not read yet: ids[rows[i]] = sampled[index[i]].
+// A step can then be queued before its predecessor's tokens have reached the host.  A value that is no
+// token (the sampler's mark of a row without finite logits, below zero) becomes token 0 here; the host
+// sees the mark itself when it reads the step before, and fails the step.
+// ---------------------------------------------------------------------------------------------
+__global__ void patch_tokens_kernel(int* __restrict__ ids, const int* __restrict__ rows, const int* __restrict__ index,
+                                    const int* __restrict__ sampled, int n, int vocab) {
+    pdl_launch_dependents();
+    pdl_wait();
+    const int i = blockIdx.x * blockDim.x + threadIdx.x;
+    if (i >= n) return;
+    const int token = sampled[index[i]];
+    ids[rows[i]] = token < 0 || token >= vocab ? 0 : token;
+}
+
+MRS_EXPORT int mrs_patch_tokens(int* ids, const int* rows, const int* index, const int* sampled, int n, int vocab, void* stream) {
+    if (n <= 0) return 0;
+    MRS_LAUNCH(patch_tokens_kernel, (n + 127) / 128, 128, 0, stream, ids, rows, index, sampled, n, vocab);
+    MRS_RETURN_LAUNCH_STATUS();
+}
+
+// ---------------------------------------------------------------------------------------------
 // Embedding: residual[t, :] = float(table[ids[t], :])      (reference: ops.cu:15-18)
 // ---------------------------------------------------------------------------------------------
 template <typename T>

@@ -26,7 +26,7 @@ from ..errors import BackendError, EngineError, EngineStopped
 from ..models.registry import load_config
 from ..sampling import Sampler, SamplingParams
 from .runner import ModelRunner, SequenceStep
-from .scheduler import Scheduler
+from .scheduler import UNKNOWN_TOKEN, Scheduler
 
 
 @dataclass
@@ -114,6 +114,16 @@ class GenerationStream:
         return event
 
 
+class _InFlight:
+    """A step that has been queued and whose sampled tokens the host has not read yet."""
+
+    def __init__(self, ids: list[int], tokens, done):
+        self.ids = ids                                  # requests that sample, in the step's order
+        self.place = {request_id: k for k, request_id in enumerate(ids)}
+        self.tokens = tokens                            # int32 [len(ids)] on the device, or None
+        self.done = done                                # recorded behind the step
+
+
 class EngineHandle:
     def __init__(self, runner: ModelRunner, eos_ids: list[int], policy: str = "mixed", model_id: str = ""):
         self.runner = runner
@@ -126,6 +136,7 @@ class EngineHandle:
         self.generated: dict[int, int] = {}
         self.next_id = 1
         self.healthy = True
+        self._in_flight: _InFlight | None = None
         self.info = {"model_id": model_id, "vocab_size": runner.config.vocab_size,
                      "num_pages": [g.num_pages for g in runner.groups], "dtype": str(runner.runtime.dtype)}
 
@@ -216,42 +227,94 @@ class EngineHandle:
                                               done.cached_tokens))
 
     def run_step(self) -> bool:
-        """Plans, runs and commits one step.  False when there was nothing to run."""
+        """Plans, runs and commits one step.  False when there was nothing to run.
+
+        With `overlap_steps` (the default) a step is queued before the tokens of the step before it have reached
+        the host: the scheduler is told of tokens whose values are still unknown, the next step takes them from
+        the device (`ModelRunner.forward(carried=...)`), and while it runs the host reads the step before,
+        streams its tokens and ends what they end.  Tokens and `Finished` events therefore arrive one step late,
+        and a request that a stop token ended has one more row computed in vain.  Cache pages given back while a
+        step still runs are safe to hand out: whatever uses them next is queued behind that step."""
         if not self.healthy:
             raise EngineStopped("engine stopped")
         plan = self.scheduler.plan()
         self._emit_finished()
         if not plan:
-            return False
-        batch = [SequenceStep(p.request_id, p.tokens, p.start_pos, [len(p.tokens) - 1] if p.sample else [])
-                 for p in plan]
-        sampled_ids = [p.request_id for p in plan if p.sample]
+            if self._in_flight is None:
+                return False
+            self._guarded(self._resolve_in_flight)          # the last step's tokens
+            return True
+        self._guarded(self._run_plan, plan)
+        return True
+
+    def _guarded(self, work, *args):
         try:
-            logits = self.runner.forward(batch)
-            if sampled_ids:
-                tokens = self.sampler.sample(logits, [self.params[i] for i in sampled_ids],
-                                             [self.generated[i] for i in sampled_ids])
-            else:
-                tokens = []
-                torch.cuda.current_stream().synchronize()
-            kernels.check_device_errors()
+            return work(*args)
         except (EngineError, RuntimeError) as e:
             # a failed step ends every request and gives every page back (scheduler.rs:332-359)
             self.healthy = False
+            self._in_flight = None
             message = f"{type(e).__name__}: {e}"
             for stream in list(self.streams.values()):
                 stream.events.append(Error(stream.request_id, message))
             self.scheduler.fail("error")
             self._emit_finished()
             raise BackendError(message) from e
-        self.scheduler.commit(tokens)
-        for request_id, token in zip(sampled_ids, tokens):
-            self.generated[request_id] += 1
+
+    def _run_plan(self, plan) -> None:
+        overlap = self.config.overlap_steps
+        before = self._in_flight
+        batch, rows, index, at = [], [], [], 0
+        for p in plan:
+            tokens = p.tokens
+            if len(tokens) == 1 and tokens[0] == UNKNOWN_TOKEN:       # sampled by the step that is still running
+                rows.append(at)
+                index.append(before.place[p.request_id])
+                tokens = [0]
+            batch.append(SequenceStep(p.request_id, tokens, p.start_pos, [len(tokens) - 1] if p.sample else []))
+            at += len(tokens)
+        sampled_ids = [p.request_id for p in plan if p.sample]
+        logits = self.runner.forward(batch, carried=(rows, index, before.tokens) if rows else None)
+        chosen = None
+        if sampled_ids:
+            chosen = self.sampler.launch(logits, [self.params[i] for i in sampled_ids],
+                                         [self.generated[i] for i in sampled_ids])
+        done = torch.cuda.Event()
+        done.record()
+        self._in_flight = _InFlight(sampled_ids, chosen, done)
+        if before is not None:
+            self._resolve(before)               # the host's share of the step before, while this one runs
+        if not overlap:
+            self._resolve_in_flight(commit=True)
+            return
+        self.scheduler.commit([UNKNOWN_TOKEN] * len(sampled_ids))
+        for request_id in sampled_ids:
+            if request_id in self.generated:    # (not ended by the step before, whose tokens have just arrived)
+                self.generated[request_id] += 1
+
+    def _resolve_in_flight(self, commit: bool = False) -> None:
+        step, self._in_flight = self._in_flight, None
+        self._resolve(step, commit)
+
+    def _resolve(self, step: "_InFlight", commit: bool = False) -> None:
+        """Waits for a queued step, reads what it sampled, tells the scheduler and the streams."""
+        if step.ids:
+            tokens = self.sampler.read(step.tokens)
+        else:
+            tokens = []
+            step.done.synchronize()
+        kernels.check_device_errors()
+        if commit:                              # in lockstep: the plan is still the scheduler's last
+            self.scheduler.commit(tokens)
+        else:
+            self.scheduler.resolve(step.ids, tokens)
+        for request_id, token in zip(step.ids, tokens):
+            if commit and request_id in self.generated:
+                self.generated[request_id] += 1
             stream = self.streams.get(request_id)
             if stream is not None:
                 stream.events.append(Token(request_id, token))
         self._emit_finished()
-        return True
 
     # ------------------------------------------------------------------ the rest of the reference's surface
     def metrics(self) -> dict:
@@ -274,5 +337,6 @@ class EngineHandle:
     def shutdown(self) -> None:
         if self.healthy:
             self.scheduler.fail("cancelled")
+            self._in_flight = None          # what a queued step samples belongs to nobody any more
             self._emit_finished()
             self.healthy = False

@@ -187,11 +187,14 @@ class ModelRunner:
 
     # ------------------------------------------------------------------ one step
     def _fill_step(self, sequences: Sequence[SequenceStep], pad_to: int | None, table_width: int | None,
-                   staging: "_Staging", pad_rows: int = 0, extra: np.ndarray | None = None):
+                   staging: "_Staging", pad_rows: int = 0, extra: np.ndarray | None = None, carried=None):
         """Checks the batch, lays its facts out in the staging buffer (the host library does both) and
         starts the copy to the device.  `extra`: int32 words that follow the layout in the same copy (the
-        mixers' plans of a step with fixed shapes).  Returns the layout, the device buffer, the first
-        positions, the token counts and the words that the layout took."""
+        mixers' plans of a step with fixed shapes).  `carried` = (rows, index, sampled): token ids that the
+        host does not know yet, because the step that sampled them is still running: after the copy, row
+        rows[i] of the step's ids gets sampled[index[i]] on the device (`sampled`: that step's int32 tokens).
+        Returns the layout, the device buffer, the first positions, the token counts and the words that the
+        layout took."""
         if not sequences:
             raise InvalidRequest("empty batch or KV pool")
         n = len(sequences)
@@ -212,14 +215,22 @@ class ModelRunner:
         widest = table_width or -(-self.limits.max_seq_len // self.limits.page_size)
         # a padded step has `pad_to` rows and sequences whatever the number of real ones: its need, and with it
         # the size of a recorded step's fixed buffers, depends on `pad_to` alone
+        if carried is not None:
+            rows, index, sampled = carried
+            if len(rows) != len(index) or len(rows) > n:
+                raise InvalidRequest("carried tokens: a row and an index each, at most one a sequence")
+            words = np.asarray(list(rows) + list(index), dtype=np.int32)
+        room = (0 if extra is None else int(extra.size)) + 2 * (pad_to or n)   # a buffer of fixed size has room for carried tokens
+        if carried is not None:
+            extra = words if extra is None else np.concatenate([extra, words])
         more = 0 if extra is None else int(extra.size)
         guess = step_layout_bound(pad_rows or pad_to or int(counts.sum()), pad_to or n, widest, G)
         for _ in range(2):
-            host, dev = staging.reserve(guess + more)
+            host, dev = staging.reserve(guess + room)
             used = self._step_build(self.cache.handle, n, requests.ctypes.data, starts.ctypes.data, counts.ctypes.data,
                                     tokens.ctypes.data, want_counts.ctypes.data, want.ctypes.data, int(pad_to or 0),
                                     int(pad_rows), int(table_width or 0), self.limits.max_seq_len, self.config.vocab_size,
-                                    host.data_ptr(), host.numel() - more, layout.ctypes.data)
+                                    host.data_ptr(), host.numel() - room, layout.ctypes.data)
             if used != -7:
                 break
             guess = int(layout[0])
@@ -232,11 +243,17 @@ class ModelRunner:
             host[used:used + more] = torch.from_numpy(extra)
         staging.upload(used + more)
         self.h2d_bytes += 4 * (used + more)
+        if carried is not None and len(rows):
+            at, count = used + more - 2 * len(rows), len(rows)
+            if max(rows) >= int(layout[0]) or min(rows) < 0:
+                raise InvalidRequest("carried tokens: a row outside the step")
+            kernels.patch_tokens(dev[int(layout[4]):int(layout[4]) + int(layout[0])], dev[at:at + count],
+                                 dev[at + count:at + 2 * count], sampled, self.config.vocab_size)
         return layout, dev, starts, counts, used
 
     def build_context(self, sequences: Sequence[SequenceStep], pad_to: int | None = None,
                       table_width: int | None = None, staging: _Staging | None = None, pad_rows: int = 0,
-                      facts: StepFacts | None = None) -> StepContext:
+                      facts: StepFacts | None = None, carried=None) -> StepContext:
         """Checks the batch and copies what the kernels need to know about it to the device in
         one transfer; the checking and the layout are the host library's (`csrc/host/step_batch.cc`).
         With `pad_to` (single decoded tokens only) the batch is filled up to that many sequences
@@ -250,7 +267,7 @@ class ModelRunner:
         if facts is not None and facts.plans:
             extra = np.concatenate([plan.words() for plan in facts.plans.values()])
         layout, dev, starts, counts, used = self._fill_step(sequences, pad_to, table_width, staging or self._staging,
-                                                            pad_rows, extra)
+                                                            pad_rows, extra, carried)
         n, G = len(sequences), len(self.groups)
         T, B, R, decode = (int(v) for v in layout[:4])
         plan_views = None
@@ -284,7 +301,7 @@ class ModelRunner:
             decode_tiles=dview(layout[11], 4 * B, (B, 4)) if decode else None, real_sequences=real,
             want_every_row=bool(decode) and R == T, facts=facts, plan_views=plan_views)
 
-    def forward(self, sequences: Sequence[SequenceStep], observe=None) -> torch.Tensor | None:
+    def forward(self, sequences: Sequence[SequenceStep], observe=None, carried=None) -> torch.Tensor | None:
         """Runs the batch; returns the logits [wanted, vocab] (float32, on the device) in the
         order of the sequences and of their `want`, or None when nothing is wanted.  The
         kernels are queued, not awaited.  The result is valid until the next call.
@@ -295,12 +312,12 @@ class ModelRunner:
         every one of those stages as a kernel of its own and is never replayed from a recording."""
         self.steps += 1
         if observe is None and self._replayable(sequences):
-            return self._forward_recorded(sequences)
+            return self._forward_recorded(sequences, carried)
         if observe is None and self.record_decode and self.record_mixed:
             shapes = self._fixed_shapes(sequences)
             if shapes is not None:
-                return self._forward_fixed(sequences, *shapes)
-        ctx = self.build_context(sequences)
+                return self._forward_fixed(sequences, *shapes, carried=carried)
+        ctx = self.build_context(sequences, carried=carried)
         ctx.observe = observe
         with torch.no_grad():
             return self.model.forward(ctx, self.storage)
@@ -315,7 +332,7 @@ class ModelRunner:
         return (self.record_decode and 0 < len(sequences) <= self._largest_bucket
                 and all(len(s.tokens) == 1 and len(s.want) == 1 for s in sequences))
 
-    def _forward_recorded(self, sequences) -> torch.Tensor:
+    def _forward_recorded(self, sequences, carried=None) -> torch.Tensor:
         self.recorded_steps += 1
         real = len(sequences)
         bucket = 1 << (real - 1).bit_length()
@@ -327,11 +344,11 @@ class ModelRunner:
             record = self._records[key] = _Recorded(self.device)
         width = -(-self.limits.max_seq_len // self.limits.page_size)
         if record.graph is not None:          # the recorded context's tensors stay where they are: only their contents change
-            self._fill_step(sequences, bucket, width, record.staging)
+            self._fill_step(sequences, bucket, width, record.staging, carried=carried)
             record.graph.replay()
             kernels.launch_count += record.launches
             return record.logits[:real]
-        ctx = self.build_context(sequences, pad_to=bucket, table_width=width, staging=record.staging)
+        ctx = self.build_context(sequences, pad_to=bucket, table_width=width, staging=record.staging, carried=carried)
         ctx.max_context_len = context_class      # launches are planned for the class, not for this step
         self._record(record, ctx)
         record.graph.replay()
@@ -391,7 +408,7 @@ class ModelRunner:
                 return None
         return key, facts, rows, bucket, context_class
 
-    def _forward_fixed(self, sequences, key, facts, rows, bucket, context_class):
+    def _forward_fixed(self, sequences, key, facts, rows, bucket, context_class, carried=None):
         self.recorded_steps += 1
         wanted = sum(len(s.want) for s in sequences)
         record = self._records.get(key)
@@ -400,12 +417,12 @@ class ModelRunner:
         width = -(-self.limits.max_seq_len // self.limits.page_size)
         if record.graph is not None:
             extra = np.concatenate([plan.words() for plan in facts.plans.values()]) if facts.plans else None
-            used = self._fill_step(sequences, bucket, width, record.staging, rows, extra)[4]
+            used = self._fill_step(sequences, bucket, width, record.staging, rows, extra, carried)[4]
             if used != record.plan_offset:
                 raise BackendError("a recorded step's layout moved")
         else:
             ctx = self.build_context(sequences, pad_to=bucket, table_width=width, staging=record.staging, pad_rows=rows,
-                                     facts=facts)
+                                     facts=facts, carried=carried)
             ctx.max_context_len = context_class
             record.plan_offset = self.h2d_last_layout_words
             self._record(record, ctx)

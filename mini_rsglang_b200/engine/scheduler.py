@@ -14,6 +14,7 @@ from ..errors import BackendError, CapacityError, InvalidRequest
 
 FINISH_REASONS = ("stop", "length", "cancelled", "error")
 POLICIES = {"mixed": 0, "alternate": 1}
+UNKNOWN_TOKEN = -1      # committed in place of a token whose step is still running; `resolve` brings the value
 
 
 @dataclass
@@ -119,8 +120,20 @@ class Scheduler:
         return out
 
     def commit(self, sampled: list[int]) -> None:
+        """One token per sampled sequence of the plan, in its order; `UNKNOWN_TOKEN` for a token whose step is still
+        running (its value follows with `resolve`, before the request's next token is committed)."""
         arr = np.asarray(sampled, dtype=np.int32)
         code = self.lib.mrs_sched_commit(self.handle, arr.ctypes.data, arr.size)
+        if code == EXCEPTION:
+            raise BackendError(last_error(self.lib))
+
+    def resolve(self, requests: list[int], tokens: list[int]) -> None:
+        """The values of tokens that were committed as `UNKNOWN_TOKEN`: the requests they end are finished here."""
+        ids = np.asarray(requests, dtype=np.int64)
+        values = np.asarray(tokens, dtype=np.int32)
+        if ids.size != values.size:
+            raise InvalidRequest("resolve: as many tokens as requests")
+        code = self.lib.mrs_sched_resolve(self.handle, ids.ctypes.data, values.ctypes.data, ids.size)
         if code == EXCEPTION:
             raise BackendError(last_error(self.lib))
 

@@ -19,6 +19,7 @@ _c_int, _c_vp, _c_float = ctypes.c_int, ctypes.c_void_p, ctypes.c_float
 
 _SIGNATURES = {
     "mrs_embed": [_c_int, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
+    "mrs_patch_tokens": [_c_vp, _c_vp, _c_vp, _c_vp, _c_int, _c_int, _c_vp],
     "mrs_add_rmsnorm": [_c_int, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_vp, _c_int, _c_int, _c_int, _c_vp],
     "mrs_rmsnorm": [_c_int, _c_vp, _c_vp, _c_float, _c_vp, _c_int, _c_int, _c_vp],
     "mrs_qk_norm_rope_store": [_c_int, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_vp, _c_float, _c_vp, _c_vp,
@@ -128,6 +129,20 @@ def embed(table: torch.Tensor, ids: torch.Tensor, residual: torch.Tensor) -> Non
         raise InvalidRequest("embed: width mismatch")
     _check(library().mrs_embed(_is_bf16(table.dtype), table.data_ptr(), ids.data_ptr(), residual.data_ptr(),
                                tokens, width, _stream()), "embed")
+
+
+def patch_tokens(ids: torch.Tensor, rows: torch.Tensor, index: torch.Tensor, sampled: torch.Tensor, vocab: int) -> None:
+    """ids[rows[i]] = sampled[index[i]]: the tokens that the step before sampled go into this step's ids on the
+    device, before the host has read them."""
+    global launch_count
+    n = rows.shape[0]
+    _need(ids, torch.int32, "token ids")
+    _need(rows, torch.int32, "rows", (n,))
+    _need(index, torch.int32, "index", (n,))
+    _need(sampled, torch.int32, "sampled tokens")
+    launch_count += 1
+    _check(library().mrs_patch_tokens(ids.data_ptr(), rows.data_ptr(), index.data_ptr(), sampled.data_ptr(), n, int(vocab),
+                                      _stream()), "patch_tokens")
 
 
 def add_rmsnorm(residual: torch.Tensor, delta: torch.Tensor | None, weight: torch.Tensor, eps: float,

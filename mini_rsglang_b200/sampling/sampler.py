@@ -33,6 +33,18 @@ class Sampler:
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], draw_index: Sequence[int]) -> list[int]:
         """One token per row of `logits` [rows, vocab] (float32, on the device)."""
+        return self.read(self.launch(logits, params, draw_index))
+
+    def read(self, out: torch.Tensor) -> list[int]:
+        """Waits for tokens that `launch` chose and brings them to the host."""
+        tokens = out.cpu().tolist()
+        if any(t < 0 for t in tokens):
+            raise BackendError("empty/nonfinite logits")
+        return tokens
+
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], draw_index: Sequence[int]) -> torch.Tensor:
+        """Queues the choice of one token per row of `logits`; returns them on the device (int32 [rows]; a row
+        without finite logits gives -1).  Nothing is waited for."""
         rows = logits.shape[0]
         assert rows == len(params) == len(draw_index)
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
@@ -49,7 +61,4 @@ class Sampler:
             draws = torch.tensor(list(draw_index), dtype=torch.int32)
             dev = self.device
             kernels.sample(logits, temperature.to(dev), top_k.to(dev), top_p.to(dev), seeds.to(dev), draws.to(dev), out)
-        tokens = out.cpu().tolist()
-        if any(t < 0 for t in tokens):
-            raise BackendError("empty/nonfinite logits")
-        return tokens
+        return out

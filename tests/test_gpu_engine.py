@@ -449,8 +449,9 @@ def test_requests_that_share_their_first_tokens_read_them_from_the_cache(model_f
 def test_random_traffic_gives_the_same_tokens_with_and_without_recordings_and_sharing(model_folders, seed):
     """Random prompts from a few families of common first tokens, random lengths and output lengths, a small token
     budget and a page pool that holds only some of them at a time: in float32 an engine that records its steps and
-    shares prefixes generates, token for token, what one that queues every kernel and shares nothing generates;
-    nothing leaks, and the manager's books balance after every wave."""
+    shares prefixes generates, token for token, what one that queues every kernel and shares nothing generates,
+    whether or not steps are queued before the tokens of the step before them are known (stop tokens among them:
+    half of the requests end on one); nothing leaks, and the manager's books balance after every wave."""
     import random
     name = "B"
     folder = model_folders[name]
@@ -467,8 +468,9 @@ def test_random_traffic_gives_the_same_tokens_with_and_without_recordings_and_sh
                                          temperature=rng.choice([0.0, 0.0, 0.8]), seed=rng.randrange(1 << 30)))
         waves.append((prompts, params))
     out = []
-    for fancy in (True, False):
-        limits = RuntimeConfig(max_seq_len=128, page_size=16, prefill_budget=32, max_running=4, prefix_cache=fancy, record_mixed_steps=fancy)
+    for fancy, overlap in ((True, True), (False, False), (True, False), (False, True)):
+        limits = RuntimeConfig(max_seq_len=128, page_size=16, prefill_budget=32, max_running=4,
+                               prefix_cache=fancy, record_mixed_steps=fancy, overlap_steps=overlap)
         engine = EngineHandle.load(folder, 0, config=limits, dtype="float32", num_pages=24)
         engine.runner.record_decode = fancy
         tokens = []
@@ -482,7 +484,7 @@ def test_random_traffic_gives_the_same_tokens_with_and_without_recordings_and_sh
         assert engine.runner.cache.free_pages() == 24
         engine.shutdown()
         out.append(tokens)
-    assert out[0] == out[1]
+    assert out[0] == out[1] == out[2] == out[3]
 
 
 def test_prefix_sharing_is_refused_for_a_model_that_cannot_share(model_folders):
@@ -611,7 +613,7 @@ def test_a_failed_step_ends_every_request_and_gives_every_page_back(model_folder
     assert engine.scheduler.running() == 2 and engine.scheduler.waiting() == 1      # two run, the third waits
     assert engine.runner.cache.free_pages() < 40
 
-    def broken(batch, observe=None):
+    def broken(batch, observe=None, carried=None):
         raise BackendError("injected: the device fell over")
 
     engine.runner.forward = broken
@@ -662,14 +664,15 @@ def test_a_wait_that_runs_out_fails_the_step_and_leaves_the_device_usable(model_
     assert engine.run_step() and engine.run_step()
     real = engine.runner.forward
 
-    def forward_with_a_stuck_wait(batch, observe=None):
-        logits = real(batch, observe)
+    def forward_with_a_stuck_wait(batch, observe=None, carried=None):
+        logits = real(batch, observe, carried)
         kernels.wait_probe(1 << 16)
         return logits
 
     engine.runner.forward = forward_with_a_stuck_wait
     with pytest.raises(BackendError, match="gave up waiting"):
-        engine.run_step()
+        engine.run_step()               # the step is queued; the host looks at the error words when it reads a step's
+        engine.run_step()               # tokens, which with overlapped steps is one call later
     events = list(stream.events)
     assert any(isinstance(e, Error) for e in events) and events[-1].reason == "error"
     assert engine.healthy is False and engine.metrics()["free_pages"] == 16

@@ -21,7 +21,7 @@ def test_host_tests_pass_under_asan_and_ubsan():
         env = native.sanitizer_environment()
     except BackendError as e:
         pytest.skip(str(e))
-    files = [os.path.join(ROOT, "tests", f) for f in ("test_cache_manager.py", "test_scheduler.py", "test_step_layout.py", "test_prefix_cache.py")]
+    files = [os.path.join(ROOT, "tests", f) for f in ("test_cache_manager.py", "test_scheduler.py", "test_step_layout.py", "test_prefix_cache.py", "test_scheduler_lookahead.py")]
     proc = subprocess.run([sys.executable, "-m", "pytest", "-x", "-q", "-p", "no:cacheprovider", *files],
                           env=env, capture_output=True, text=True, timeout=900, cwd=ROOT)
     tail = (proc.stdout + proc.stderr)[-3000:]
