@@ -117,10 +117,10 @@ class GenerationStream:
 class _InFlight:
     """A step that has been queued and whose sampled tokens the host has not read yet."""
 
-    def __init__(self, ids: list[int], tokens, done):
+    def __init__(self, ids: list[int], chosen, done):
         self.ids = ids                                  # requests that sample, in the step's order
         self.place = {request_id: k for k, request_id in enumerate(ids)}
-        self.tokens = tokens                            # int32 [len(ids)] on the device, or None
+        self.chosen = chosen                            # what the sampler launched (`sampling.sampler.Chosen`), or None
         self.done = done                                # recorded behind the step
 
 
@@ -274,7 +274,7 @@ class EngineHandle:
             batch.append(SequenceStep(p.request_id, tokens, p.start_pos, [len(tokens) - 1] if p.sample else []))
             at += len(tokens)
         sampled_ids = [p.request_id for p in plan if p.sample]
-        logits = self.runner.forward(batch, carried=(rows, index, before.tokens) if rows else None)
+        logits = self.runner.forward(batch, carried=(rows, index, before.chosen.tokens) if rows else None)
         chosen = None
         if sampled_ids:
             chosen = self.sampler.launch(logits, [self.params[i] for i in sampled_ids],
@@ -299,7 +299,7 @@ class EngineHandle:
     def _resolve(self, step: "_InFlight", commit: bool = False) -> None:
         """Waits for a queued step, reads what it sampled, tells the scheduler and the streams."""
         if step.ids:
-            tokens = self.sampler.read(step.tokens)
+            tokens = self.sampler.read(step.chosen)
         else:
             tokens = []
             step.done.synchronize()

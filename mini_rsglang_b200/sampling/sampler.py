@@ -27,24 +27,36 @@ def uniform_from_counter(seed: int, index: int) -> float:
     return (z >> 40) / 16777216.0
 
 
+class Chosen:
+    """Tokens that `Sampler.launch` chose: on the device (`tokens`, for a step that goes on before the host has
+    seen them) and on their way to pinned host memory (`host`, complete when `arrived` has happened)."""
+
+    def __init__(self, tokens: torch.Tensor, host: torch.Tensor, arrived: torch.cuda.Event):
+        self.tokens, self.host, self.arrived = tokens, host, arrived
+
+
 class Sampler:
     def __init__(self, device: torch.device):
         self.device = device
+        self._pinned: list[torch.Tensor] = []       # host buffers that take turns: two results may be outstanding
+        self._turn = 0
 
     def sample(self, logits: torch.Tensor, params: Sequence[SamplingParams], draw_index: Sequence[int]) -> list[int]:
         """One token per row of `logits` [rows, vocab] (float32, on the device)."""
         return self.read(self.launch(logits, params, draw_index))
 
-    def read(self, out: torch.Tensor) -> list[int]:
-        """Waits for tokens that `launch` chose and brings them to the host."""
-        tokens = out.cpu().tolist()
+    def read(self, chosen: Chosen) -> list[int]:
+        """Waits for tokens that `launch` chose and returns them."""
+        chosen.arrived.synchronize()
+        tokens = chosen.host.tolist()
         if any(t < 0 for t in tokens):
             raise BackendError("empty/nonfinite logits")
         return tokens
 
-    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], draw_index: Sequence[int]) -> torch.Tensor:
-        """Queues the choice of one token per row of `logits`; returns them on the device (int32 [rows]; a row
-        without finite logits gives -1).  Nothing is waited for."""
+    def launch(self, logits: torch.Tensor, params: Sequence[SamplingParams], draw_index: Sequence[int]) -> Chosen:
+        """Queues the choice of one token per row of `logits` (int32; a row without finite logits gives -1) and
+        their copy to the host, right behind it in the stream, so that work queued later does not hold the copy
+        up.  Nothing is waited for."""
         rows = logits.shape[0]
         assert rows == len(params) == len(draw_index)
         out = torch.empty(rows, dtype=torch.int32, device=self.device)
@@ -61,4 +73,13 @@ class Sampler:
             draws = torch.tensor(list(draw_index), dtype=torch.int32)
             dev = self.device
             kernels.sample(logits, temperature.to(dev), top_k.to(dev), top_p.to(dev), seeds.to(dev), draws.to(dev), out)
-        return out
+        while len(self._pinned) < 3:
+            self._pinned.append(torch.empty(max(256, rows), dtype=torch.int32, pin_memory=True))
+        self._turn = (self._turn + 1) % 3
+        if self._pinned[self._turn].numel() < rows:
+            self._pinned[self._turn] = torch.empty(2 * rows, dtype=torch.int32, pin_memory=True)
+        host = self._pinned[self._turn][:rows]
+        host.copy_(out, non_blocking=True)
+        arrived = torch.cuda.Event()
+        arrived.record()
+        return Chosen(out, host, arrived)
