@@ -184,6 +184,7 @@ def continuous_run(args, torch, shape_name: str, cfg: dict, peak: dict) -> dict:
     generated = sum(r.completion_tokens for r in results)
     prompt_tokens = sum(lengths)
     assert all(r.finish_reason == "length" and r.completion_tokens == out_tokens for r in results)
+    recorded, h2d = runner.recorded_steps - recorded0, runner.h2d_bytes - h2d0
     if args.kernel_shares:
         kernel_shares(torch, lambda: engine.generate_many(prompts(lengths), params))
     engine.shutdown()
@@ -195,8 +196,8 @@ def continuous_run(args, torch, shape_name: str, cfg: dict, peak: dict) -> dict:
         "dtype": "bf16", "data": "synthetic: seeded random weights, seeded prompt lengths, uniform random token ids",
         "prompt_tokens_per_s": round(prompt_tokens / elapsed, 1), "generated_tokens_per_s": round(generated / elapsed, 1),
         "prompt_tokens": prompt_tokens, "generated_tokens": generated, "elapsed_s": round(elapsed, 4),
-        "recorded_step_share": round((runner.recorded_steps - recorded0) / max(steps, 1), 4),
-        "h2d_bytes_per_step": (runner.h2d_bytes - h2d0) // max(steps, 1),
+        "recorded_step_share": round(recorded / max(steps, 1), 4),
+        "h2d_bytes_per_step": h2d // max(steps, 1),
         "config": {"model": shape_name, "layers": cfg["num_hidden_layers"], "layers_of_shape": cfg["num_hidden_layers"],
                    "hidden": cfg["hidden_size"], "q_heads": cfg["num_attention_heads"], "kv_heads": cfg["num_key_value_heads"],
                    "head_dim": cfg["head_dim"], "intermediate": cfg["intermediate_size"], "vocab": cfg["vocab_size"],
