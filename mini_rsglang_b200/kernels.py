@@ -326,16 +326,28 @@ def attention_mma_library(d: int) -> ctypes.CDLL:
 _retired: list[torch.Tensor] = []     # outgrown scratch buffers: recorded steps may still point at them
 
 
-def attention_scratch(device: torch.device, floats: int) -> torch.Tensor:
+def attention_scratch(device: torch.device, floats: int, lane: int = 0) -> torch.Tensor:
     """Scratch memory for split attention, kept and grown per device.  A buffer that is outgrown
-    is never freed: a step recorded earlier replays with its address."""
-    have = _scratch.get(device)
+    is never freed: a step recorded earlier replays with its address.  `lane`: the attention for few rows
+    (0) and the one for prompt portions (1) have buffers of their own, because a step that holds both runs
+    them side by side."""
+    have = _scratch.get((device, lane))
     if have is None or have.numel() < floats:
         if have is not None:
             _retired.append(have)
         have = torch.empty(max(2 * floats, 1 << 22), dtype=torch.float32, device=device)
-        _scratch[device] = have
+        _scratch[(device, lane)] = have
     return have
+
+
+_side_streams: dict[torch.device, torch.cuda.Stream] = {}
+
+
+def side_stream(device: torch.device) -> torch.cuda.Stream:
+    """A second stream of the device, for kernels of one step that do not depend on one another."""
+    if device not in _side_streams:
+        _side_streams[device] = torch.cuda.Stream(device=device)
+    return _side_streams[device]
 
 
 _counters: dict[torch.device, torch.Tensor] = {}
@@ -559,7 +571,7 @@ def attention_prefill_tc(q, k_cache, v_cache, positions, block_table, tiles, out
     if code != 0:
         fail(code, "tensor map of the queries")
     launch_count += 2 if shares else 1
-    partials = attention_scratch(q.device, lib.mrs_attention_prefill_tc_partial_floats(tiles.shape[0], nkv)) if shares else None
+    partials = attention_scratch(q.device, lib.mrs_attention_prefill_tc_partial_floats(tiles.shape[0], nkv), lane=1) if shares else None
     code = lib.mrs_attention_prefill_tc(q_map, maps[0], maps[1], positions.data_ptr(), block_table.data_ptr(),
                                         block_table.shape[1], tiles.data_ptr(), tiles.shape[0], out.data_ptr(), nq, nkv,
                                         k_cache.shape[2], float(scale if scale is not None else 1.0 / math.sqrt(d)),

@@ -7,6 +7,7 @@ attention reads the cache through the request's block table; one projection brin
 heads back to the model width."""
 from __future__ import annotations
 
+import os
 from dataclasses import dataclass
 
 import numpy as np
@@ -70,11 +71,8 @@ def attention_tile_lists(facts: StepFacts, group: int, wide_rows: int, kv_heads:
     wide_tokens = tiles * (wide_rows // tiles // group)
     real = len(facts.start_pos)
     lengths = [facts.q_start[i + 1] - facts.q_start[i] for i in range(real)]
-    entries = sum(-(-n // wide_tokens) for n in lengths if n > narrow_tokens)
-    spare = sms // max(entries * kv_heads, 1) if tensor_core else 1      # CTAs an entry may become
-    narrow, wide = [], []
+    narrow, found = [], []
     longest_narrow = 0
-    shared = False
     for i, n in enumerate(lengths):
         first = facts.q_start[i]
         if narrow_tokens >= 1 and n <= narrow_tokens:
@@ -86,15 +84,23 @@ def attention_tile_lists(facts: StepFacts, group: int, wide_rows: int, kv_heads:
             begin = facts.start_pos[i] + start                           # position of the entry's first token
             first_key = max(0, begin - window + 1) if window else 0
             blocks = -(-(begin + tokens) // key_block) - first_key // key_block
-            shares = min(spare, blocks // 4, 255) if spare >= 2 else 1
-            if shares >= 2:
-                shared = True
-                wide += [(i, first + start, tokens, s | shares << 8, begin) for s in range(shares)]
-            elif spare >= 2 and tokens > wide_tokens // 2 >= 1:
-                half = wide_tokens // 2
-                wide += [(i, first + start, half, 0, begin), (i, first + start + half, tokens - half, 0, begin + half)]
-            else:
-                wide.append((i, first + start, tokens, 0, begin))
+            found.append((i, first + start, tokens, begin, blocks))
+    # CTAs an entry may become.  Beside decoded tokens the kernel for few rows runs at the same time and wants SMs
+    # of its own: the wide entries then share WIDE_SHARE_BESIDE_NARROW of them.
+    room = int(sms * WIDE_SHARE_BESIDE_NARROW) if narrow else sms
+    spare = room // max(len(found) * kv_heads, 1) if tensor_core else 1
+    wide = []
+    shared = False
+    for i, first, tokens, begin, blocks in found:
+        shares = min(spare, blocks // 4, 255) if spare >= 2 else 1
+        if shares >= 2:
+            shared = True
+            wide += [(i, first, tokens, s | shares << 8, begin) for s in range(shares)]
+        elif spare >= 2 and tokens > wide_tokens // 2 >= 1:
+            half = wide_tokens // 2
+            wide += [(i, first, half, 0, begin), (i, first + half, tokens - half, 0, begin + half)]
+        else:
+            wide.append((i, first, tokens, 0, begin))
     wide.sort(key=lambda t: -t[4])          # a tile late in a long request walks the most keys: start it first (stable:
     wide = [t[:4] for t in wide]            # the shares of an entry stay together and in their order)
     lists = TileLists(narrow, wide, longest_narrow, shared)
@@ -178,17 +184,42 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
     sms = kernels.sm_count(q.device)
     tensor_core_rows = kernels.attention_prefill_tc_supported(d, group, page_size)
     narrow, wide, longest, shared = plan_attention_tiles(ctx, *tile_plan_arguments(d, group, page_size, nkv, window, q.device))
-    if narrow is not None:
+    def few_rows():
         splits = choose_splits(narrow.shape[0], nkv, longest, sms)
         if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
             kernels.attention_decode_tma(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
         else:
             kernels.attention_mma_keys(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
-    if wide is not None:
+
+    def many_rows():
         if tensor_core_rows:
             kernels.attention_prefill_tc(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window, shares=shared)
         else:
             kernels.attention_mma_rows(q, cache.k, cache.v, ctx.positions, table, wide, out, nq, nkv, d, window)
+
+    if narrow is not None and wide is not None and SIDE_BY_SIDE:
+        # Decoded tokens beside prompt portions: the two kernels touch other rows of q and out, and they want
+        # other things of the GPU (the first streams keys at the memory's speed from few resident warps, the
+        # second computes in a few CTAs that fill their SMs), so they run side by side on two streams, which a
+        # recorded step keeps as two branches.
+        main, side = torch.cuda.current_stream(), kernels.side_stream(q.device)
+        side.wait_stream(main)
+        with torch.cuda.stream(side):
+            few_rows()
+        many_rows()
+        main.wait_stream(side)
+        return
+    if narrow is not None:
+        few_rows()
+    if wide is not None:
+        many_rows()
+
+
+SIDE_BY_SIDE = os.environ.get("MRS_ATTENTION_SIDE_BY_SIDE", "1") == "1"      # the variable: for measuring
+# Continuous batching, 64 requests of 16 to 2,048 prompt tokens and 64 generated ones, portions under 512 tokens a
+# step: 0.6B shape 143.7k tokens/s one kernel after the other, 159.9k side by side, 162.4k with the wide entries cut
+# for a quarter of the SMs only (the same with no cutting at all); 8B shape 45.6k, 47.0k, 47.3k.
+WIDE_SHARE_BESIDE_NARROW = float(os.environ.get("MRS_WIDE_SHARE", "0.25"))
 
 
 @MIXERS.register("gqa_attention")
