@@ -48,3 +48,4 @@ class StepContext:
     # step, and for every plan that `facts.plans` holds the device copy of its words, at an address that stays.
     facts: StepFacts | None = None
     plan_views: dict | None = None
+    layout_words: int = 0              # int32 words of the step's layout in its staging buffer (the plans follow them)

@@ -155,16 +155,13 @@ class ModelRunner:
         self._largest_bucket = min(256, 1 << (limits.max_running - 1).bit_length())
         self._records: dict[tuple, _Recorded] = {}
         self._graph_pool = None
-        # steps with prompt portions: recorded with fixed shapes once a key has been seen more than `record_after` times
+        # steps with prompt portions: recorded with fixed shapes at their key's first use
         self.record_mixed = self.record_decode and limits.record_mixed_steps
-        self.record_after = 0
         self.max_records = 96
         self.mixed_rows_max = 1024
-        self._seen: dict[tuple, int] = {}
         self.steps = 0
         self.recorded_steps = 0     # steps that were replayed from a recording
         self.h2d_bytes = 0      # bytes of batch metadata copied to the device so far
-        self.h2d_last_layout_words = 0
 
     # ------------------------------------------------------------------ construction
     @classmethod
@@ -238,7 +235,6 @@ class ModelRunner:
             message = self._step_error().decode("utf-8", "replace")
             raise (BackendError if used == -100 else InvalidRequest)(message)
         used = int(used)
-        self.h2d_last_layout_words = used
         if more:
             host[used:used + more] = torch.from_numpy(extra)
         staging.upload(used + more)
@@ -299,7 +295,7 @@ class ModelRunner:
             max_query_len=int(layout[13 + 3 * G]), max_context_len=int(layout[12 + 3 * G]),
             fresh=(starts == 0).tolist() + [True] * pads,
             decode_tiles=dview(layout[11], 4 * B, (B, 4)) if decode else None, real_sequences=real,
-            want_every_row=bool(decode) and R == T, facts=facts, plan_views=plan_views)
+            want_every_row=bool(decode) and R == T, facts=facts, plan_views=plan_views, layout_words=used)
 
     def forward(self, sequences: Sequence[SequenceStep], observe=None, carried=None) -> torch.Tensor | None:
         """Runs the batch; returns the logits [wanted, vocab] (float32, on the device) in the
@@ -402,10 +398,8 @@ class ModelRunner:
         context_class = max(512, 1 << (longest - 1).bit_length())
         facts = StepFacts(q_start, start_pos, context_class, padded_sequences=bucket, padded_tokens=rows)
         key = (rows, bucket, context_class, wanted > 0, self.model.step_signature(facts))
-        if key not in self._records:
-            seen = self._seen[key] = self._seen.get(key, 0) + 1
-            if seen <= self.record_after or len(self._records) >= self.max_records:
-                return None
+        if key not in self._records and len(self._records) >= self.max_records:
+            return None
         return key, facts, rows, bucket, context_class
 
     def _forward_fixed(self, sequences, key, facts, rows, bucket, context_class, carried=None):
@@ -424,7 +418,7 @@ class ModelRunner:
             ctx = self.build_context(sequences, pad_to=bucket, table_width=width, staging=record.staging, pad_rows=rows,
                                      facts=facts, carried=carried)
             ctx.max_context_len = context_class
-            record.plan_offset = self.h2d_last_layout_words
+            record.plan_offset = ctx.layout_words
             self._record(record, ctx)
         record.graph.replay()
         kernels.launch_count += record.launches

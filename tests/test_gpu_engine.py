@@ -154,7 +154,7 @@ def test_recorded_steps_with_prompt_portions_equal_queued_ones(model_folders, na
     for record in (True, False, "few"):
         runner = runner_for(model_folders[name], name, dtype, pages=128)
         assert runner.record_mixed
-        runner.record_mixed, runner.record_after = bool(record), 0
+        runner.record_mixed = bool(record)
         if record == "few":                  # room for two recordings: every other shape is queued kernel by kernel
             runner.max_records = 2
         for i in range(len(reqs)):
@@ -193,7 +193,6 @@ def test_generation_through_recorded_steps_with_portions(model_folders):
     for record in (True, False):
         limits = RuntimeConfig(max_seq_len=256, page_size=16, prefill_budget=48, max_running=4, record_mixed_steps=record)
         engine = EngineHandle.load(folder, 0, config=limits, dtype="float32", num_pages=80)
-        engine.runner.record_after = 0
         results = engine.generate_many(prompts, SamplingParams(max_tokens=10, ignore_eos=True))
         out.append([r.token_ids for r in results])
         if record:
