@@ -839,10 +839,12 @@ def gemm_gated_rows_wins(x: torch.Tensor, weight: torch.Tensor) -> bool:
     rows = x.shape[0]
     if rows < GEMM_GATED_ROWS_MIN or not gemm_gated_rows_supported(x, weight):
         return False
-    if not GEMM_GATED_MEASURE or torch.cuda.is_current_stream_capturing():
+    if not GEMM_GATED_MEASURE:
         return True
     n, k = weight.shape
-    key = (x.device, n, k, min(-(-rows // 1024), 16))
+    key = (x.device, n, k, 1 << (rows - 1).bit_length() if rows <= 1024 else 1024 * min(-(-rows // 1024), 16))
+    if torch.cuda.is_current_stream_capturing():         # a step being recorded ran once just before: the choice is made
+        return _gated_rows_choice.get(key, False)
     if key not in _gated_rows_choice:
         act = torch.empty((rows, n // 2), dtype=torch.bfloat16, device=x.device)
 
