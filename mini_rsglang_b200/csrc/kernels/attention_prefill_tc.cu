@@ -67,6 +67,28 @@ __device__ __forceinline__ float fast_exp2(float x) {
     return y;
 }
 
+// The softmax threads are bound by the instructions they issue, so two of sm_100's wider ones are used: the
+// maximum of three numbers, and arithmetic on two floats at once (a pair of registers taken as one operand).
+__device__ __forceinline__ float max3(float a, float b, float c) {
+    float d;
+    asm("max.f32 %0, %1, %2, %3;" : "=f"(d) : "f"(a), "f"(b), "f"(c));
+    return d;
+}
+__device__ __forceinline__ float2 fma2(float2 a, float2 b, float2 c) {
+    float2 d;
+    asm("{\n .reg .b64 ra, rb, rc, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n mov.b64 rc, {%6, %7};\n"
+        " fma.rn.f32x2 rd, ra, rb, rc;\n mov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y), "f"(c.x), "f"(c.y));
+    return d;
+}
+__device__ __forceinline__ float2 add2(float2 a, float2 b) {
+    float2 d;
+    asm("{\n .reg .b64 ra, rb, rd;\n mov.b64 ra, {%2, %3};\n mov.b64 rb, {%4, %5};\n"
+        " add.rn.f32x2 rd, ra, rb;\n mov.b64 {%0, %1}, rd;\n}"
+        : "=f"(d.x), "=f"(d.y) : "f"(a.x), "f"(a.y), "f"(b.x), "f"(b.y));
+    return d;
+}
+
 struct Barriers {
     uint64_t q_full, k_full[STAGES], k_empty[STAGES], v_full[STAGES], v_empty[STAGES];
     uint64_t s_full[TILES], p_ready[TILES], pv_done[TILES];
@@ -292,7 +314,10 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
                 }
             } else {
 #pragma unroll
-                for (int c = 0; c < BN; ++c) part_max[c & 3] = fmaxf(part_max[c & 3], x[c]);
+                for (int c = 0; c < BN; c += 8) {
+#pragma unroll
+                    for (int k = 0; k < 4; ++k) part_max[k] = max3(part_max[k], x[c + k], x[c + 4 + k]);
+                }
             }
             // the scale is positive, so the maximum of the scaled scores is the scaled maximum
             const float block_max = fmaxf(fmaxf(part_max[0], part_max[1]), fmaxf(part_max[2], part_max[3])) * scale_log2;
@@ -315,20 +340,23 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
                 }
             }
             // probabilities, 32 scores at a time; their 16 words of bfloat16 pairs go where the scores lay
-            float part_sum[4] = {0.0f, 0.0f, 0.0f, 0.0f};
+            float2 part_sum[4] = {make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f), make_float2(0.0f, 0.0f)};
+            const float2 scale2 = make_float2(scale_log2, scale_log2), minus_base = make_float2(-base, -base);
 #pragma unroll
             for (int c0 = 0; c0 < BN; c0 += 32) {
                 uint32_t packed[16];
 #pragma unroll
                 for (int c = 0; c < 32; c += 2) {
-                    const float p0 = fast_exp2(fmaf(x[c0 + c], scale_log2, -base)), p1 = fast_exp2(fmaf(x[c0 + c + 1], scale_log2, -base));
-                    part_sum[(c >> 1) & 3] += p0 + p1;
-                    __nv_bfloat162 pair = __floats2bfloat162_rn(p0, p1);
+                    const float2 t = fma2(make_float2(x[c0 + c], x[c0 + c + 1]), scale2, minus_base);
+                    const float2 p = make_float2(fast_exp2(t.x), fast_exp2(t.y));
+                    part_sum[(c >> 1) & 3] = add2(part_sum[(c >> 1) & 3], p);
+                    __nv_bfloat162 pair = __floats2bfloat162_rn(p.x, p.y);
                     packed[c / 2] = *reinterpret_cast<uint32_t*>(&pair);
                 }
                 tmem_store_16_words(s_tmem + c0 / 2, packed);
             }
-            sum = sum * alpha + ((part_sum[0] + part_sum[1]) + (part_sum[2] + part_sum[3]));
+            sum = sum * alpha + (((part_sum[0].x + part_sum[0].y) + (part_sum[1].x + part_sum[1].y)) +
+                                 ((part_sum[2].x + part_sum[2].y) + (part_sum[3].x + part_sum[3].y)));
             tmem_store_wait();
             tcgen05_fence_before_sync();
             __syncwarp();
