@@ -184,6 +184,37 @@ def test_recorded_steps_with_prompt_portions_equal_queued_ones(model_folders, na
         assert torch.equal(results[0], results[1]) and torch.equal(results[0], results[2])
 
 
+def test_the_two_attention_kernels_of_a_mixed_step_side_by_side_give_what_they_give_one_after_the_other(model_folders, monkeypatch):
+    """Decoded tokens beside prompt portions: the attention for few rows runs on a second stream beside the one for
+    prompt portions.  The logits are, bit for bit, those of the two kernels run one after the other, queued and
+    recorded."""
+    from mini_rsglang_b200.parts import attention
+    name, dtype = "D", "bfloat16"
+    vocab = TINY[name][0]["vocab_size"]
+    lengths = [150, 90, 40]
+    reqs = list(T.requests_for(vocab, [n + 6 for n in lengths], seed=53).values())
+    steps = mixed_schedule(lengths, 6, 64, [40, 33, 50])
+    results = []
+    for side_by_side, record in ((True, True), (False, True), (True, False), (False, False)):
+        monkeypatch.setattr(attention, "SIDE_BY_SIDE", side_by_side)
+        runner = runner_for(model_folders[name], name, dtype, pages=128)
+        runner.record_mixed = runner.record_decode = record
+        for i in range(len(reqs)):
+            runner.cache.open(i + 1)
+        rows = []
+        for step in steps:
+            batch = []
+            for i, first, take, place in step:
+                runner.cache.extend(i + 1, first + take)
+                batch.append(SequenceStep(i + 1, reqs[i][first:first + take], first, [] if place is None else [place]))
+            got = runner.step(batch)
+            if got is not None:
+                rows.append(got.cpu())
+        results.append(torch.cat(rows))
+    assert any(len(step) > 1 and any(take > 1 for _, _, take, _ in step) and any(take == 1 for _, _, take, _ in step) for step in steps)
+    assert torch.equal(results[0], results[1]) and torch.equal(results[2], results[3])
+
+
 def test_generation_through_recorded_steps_with_portions(model_folders):
     """The entry point with a small token budget: its mixed steps are recorded (every shape at its first use)
     and the tokens are the ones that a runner without recordings generates."""

@@ -34,6 +34,27 @@ def test_embed(dtype):
     assert torch.equal(out, table.float()[ids.long()])
 
 
+def test_patch_tokens_fills_ids_from_what_another_step_sampled():
+    """ids[rows[i]] = sampled[index[i]]; a value that is no token (the sampler's mark of a bad row, or beyond the
+    vocabulary) becomes token 0; the other ids stay."""
+    ids = torch.arange(100, 140, dtype=torch.int32, device=DEV)
+    rows = torch.tensor([3, 0, 39, 17, 20], dtype=torch.int32, device=DEV)
+    index = torch.tensor([2, 2, 0, 4, 1], dtype=torch.int32, device=DEV)
+    sampled = torch.tensor([7, -1, 299, 5, 300], dtype=torch.int32, device=DEV)
+    kernels.patch_tokens(ids, rows, index, sampled, 300)
+    want = list(range(100, 140))
+    want[3], want[0], want[39], want[17], want[20] = 299, 299, 7, 0, 0
+    assert ids.tolist() == want
+    big_rows = torch.randperm(5000, device=DEV)[:3000].to(torch.int32)
+    big_index = torch.randint(0, 64, (3000,), device=DEV, dtype=torch.int32)
+    big_sampled = torch.randint(0, 1000, (64,), device=DEV, dtype=torch.int32)
+    big = torch.full((5000,), -5, dtype=torch.int32, device=DEV)
+    kernels.patch_tokens(big, big_rows, big_index, big_sampled, 1000)
+    expect = torch.full((5000,), -5, dtype=torch.int32, device=DEV)
+    expect[big_rows.long()] = big_sampled[big_index.long()]
+    assert torch.equal(big, expect)
+
+
 @pytest.mark.parametrize("dtype", DTYPES)
 @pytest.mark.parametrize("width", [72, 75, 1000, 4096, 5120, 16384, 16388])
 def test_add_rmsnorm(dtype, width):
