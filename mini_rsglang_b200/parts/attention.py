@@ -143,20 +143,35 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
 
 
 def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident: int = 2) -> int:
-    """CTAs per tile in the kernels for few rows.  Measured on a B200 (context 4,096, 8 key/value
-    heads): one round of CTAs beats several (every CTA pays for its start and for the merge), and
-    more CTAs than fill the GPU's slots (`resident` per SM) only add merges.  So: the fewest splits
-    that fill about 85% of the slots, at most 16 (a single request: 10.9 us with 16, 13.7 us with 32),
-    every split with at least two 64-key blocks, rounded up to a power of two."""
+    """CTAs per tile in the kernels for few rows: a power of two (2, 4, 8 or 16 shares run as one thread-block
+    cluster and merge through distributed shared memory), every share with at least two 64-key blocks, all CTAs
+    resident at once (`resident` per SM), at most 8 shares (16 for a single request with a long context).
+
+    Measured on a B200 with 8 key/value heads of 128, contexts of 4,096 and 16,384, 1 to 16 requests, the kernel
+    alone and in decode steps.  With few keys in all (up to about 75 MB a layer) the kernel is bound by its start and
+    its merge, and the fewest shares that give every SM a CTA are best (4 requests at 4,096: a decode step takes
+    3.89 ms with 4 shares, 4.13 ms with 8); with more keys it is bound by memory and wants two CTAs an SM (8
+    requests: 4.23 ms with 4 shares, 4.49 ms with 2).  More CTAs than slots, or clusters of 16 for more than one
+    request, cost 9 to 12 us a layer (2 requests at 4,096: 13.7 us with 8 shares, 24.4 us with 16; 6 requests:
+    22.2 us with 4, 30.8 us with 8; 12 requests: 36.3 us with 2, 45.5 us with 4; a decode step at batch 2 went from
+    4.04 to 3.66 ms when the count stopped being rounded up past the slots)."""
     blocks = -(-longest_context // 64)
     slots = sms * resident
-    want = -(-(85 * slots) // (100 * max(tiles * nkv, 1)))
-    most = max(1, min(16, blocks // 2))
-    # a power of two: 2, 4, 8 or 16 shares run as one thread-block cluster and merge through distributed shared memory
-    power = 1 << max(want - 1, 0).bit_length()
-    while power > most:
-        power //= 2
-    return max(1, power)
+    pairs = max(tiles * nkv, 1)
+    most = max(1, min(8, blocks // 2))
+    if pairs * 16 <= slots // 2 and blocks // 16 >= 16:
+        most = 16
+    splits = 1
+    if pairs * blocks <= FEW_KEYS_BLOCKS:           # few keys: stop as soon as (nearly) every SM has a CTA
+        while splits * 2 <= most and pairs * splits < (85 * sms) // 100 and pairs * splits * 2 <= slots:
+            splits *= 2
+    else:                                           # many keys: as many resident CTAs as there are slots
+        while splits * 2 <= most and pairs * splits * 2 <= slots:
+            splits *= 2
+    return splits
+
+
+FEW_KEYS_BLOCKS = 2300      # 64-key blocks over all (tile, key/value head) pairs: about 75 MB of keys and values at heads of 128
 
 
 def tile_plan_arguments(d: int, group: int, page_size: int, nkv: int, window: int, device) -> tuple:
