@@ -24,13 +24,23 @@ constexpr int BLOCK_K = 64;          // one 128-byte swizzled row of bfloat16
 constexpr int UMMA_K = 16;
 constexpr int THREADS = 192;         // warp 0: copies, warp 1: MMA, warps 2..5: accumulator to memory
 constexpr int W_TILE_BYTES = TILE_N * BLOCK_K * 2;
+#ifndef MRS_GEMM_TC_BLOCKS
+#define MRS_GEMM_TC_BLOCKS 2
+#endif
+#ifndef MRS_GEMM_TC_RING
+#define MRS_GEMM_TC_RING 8
+#endif
 
 template <int MPAD> struct Shape {
     static constexpr int X_TILE_BYTES = MPAD * BLOCK_K * 2;
-    static constexpr int STAGE_BYTES = W_TILE_BYTES + X_TILE_BYTES;
+    static constexpr int BLOCK_BYTES = W_TILE_BYTES + X_TILE_BYTES;          // a block of K: its weight tile, then its rows of x
+    // blocks of K in a stage: one barrier round and one commit for all of them (a commit holds the issuing lane
+    // until the MMAs before it have drained, some 400 clocks whatever their number)
+    static constexpr int BLOCKS = MRS_GEMM_TC_BLOCKS;
+    static constexpr int STAGE_BYTES = BLOCKS * BLOCK_BYTES;
     // measured in the engine (decode step at batch 8, rings of 5, 6, 7, 8, 9, 10, 11 stages of 16 rows):
     // 4.51, 4.35, 4.27, 4.27, 4.32, 4.38, 4.42 ms
-    static constexpr int STAGES = MPAD <= 32 ? 8 : (MPAD <= 64 ? 6 : 5);
+    static constexpr int STAGES = (MPAD <= 32 ? MRS_GEMM_TC_RING : (MPAD <= 64 ? 6 : 5)) / BLOCKS;
     static constexpr int TMEM_COLUMNS = 2 * MPAD < 32 ? 32 : 2 * MPAD;
     static constexpr size_t SMEM_BYTES = 1024 + (size_t)STAGES * STAGE_BYTES + (2 * STAGES + 4) * sizeof(uint64_t) + 16 +
                                          (size_t)MPAD * (MPAD <= 32 ? 128 : 64) * sizeof(float) + 4 * MPAD * sizeof(float) +
@@ -118,64 +128,98 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
 
     if (warp == 0) {
         // ------------------------------------------------------------------ copies
-        if (lane == 0) {
+        // The whole warp walks the loop and one elected lane issues: addresses and coordinates are then the same in
+        // every lane, and an issue costs a fraction of what it costs a lone lane in divergent code.
+        const bool leader = elect_one();
+        if (leader) {
             tma_prefetch_descriptor(&w_map);
             tma_prefetch_descriptor(&x_map);
-            // The weights do not depend on the kernel before this one: the first ring of weight tiles is
-            // asked for at once, and only the activations wait for that kernel to finish.
-            int it = 0;
-            int first_kb[S::STAGES];
-            bool waited = false;
-            for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
-                const int tile = unit / splits, split = unit % splits;
-                const int kb0 = (int)((long long)split * k_blocks / splits), kb1 = (int)((long long)(split + 1) * k_blocks / splits);
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % S::STAGES;
-                    if (it == S::STAGES && !waited) {      // the ring is full of weights: now the activations
-                        pdl_wait();
-                        waited = true;
-                        for (int j = 0; j < S::STAGES; ++j)
-                            tma_load_2d(smem + j * S::STAGE_BYTES + W_TILE_BYTES, &x_map, &full[j], first_kb[j] * BLOCK_K, 0);
-                    }
-                    if (waited) mbar_wait(&empty[s], ((it / S::STAGES) & 1) ^ 1);
-                    mbar_arrive_expect_tx(&full[s], S::STAGE_BYTES);
-                    unsigned char* stage = smem + s * S::STAGE_BYTES;
-                    tma_load_2d(stage, &w_map, &full[s], kb * BLOCK_K, tile * TILE_N);
-                    if (waited) tma_load_2d(stage + W_TILE_BYTES, &x_map, &full[s], kb * BLOCK_K, 0);
-                    else first_kb[it] = kb;
+        }
+        // The weights do not depend on the kernel before this one: the first ring of weight tiles is
+        // asked for at once, and only the activations wait for that kernel to finish.
+        int it = 0;
+        int first_kb[S::STAGES], first_blocks[S::STAGES];
+        bool waited = false;
+        // the rows of x of a stage's blocks
+        auto fetch_x = [&](int s, int kb, int blocks) {
+            if (leader)
+#pragma unroll
+                for (int b = 0; b < S::BLOCKS; ++b)
+                    if (b < blocks)
+                        tma_load_2d(smem + s * S::STAGE_BYTES + b * S::BLOCK_BYTES + W_TILE_BYTES, &x_map, &full[s], (kb + b) * BLOCK_K, 0);
+        };
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
+            const int tile = unit / splits, split = unit % splits;
+            const int kb0 = (int)((long long)split * k_blocks / splits), kb1 = (int)((long long)(split + 1) * k_blocks / splits);
+            for (int kb = kb0; kb < kb1; kb += S::BLOCKS, ++it) {
+                const int s = it % S::STAGES;
+                const int blocks = min(S::BLOCKS, kb1 - kb);
+                if (it == S::STAGES && !waited) {      // the ring is full of weights: now the activations
+                    pdl_wait();
+                    waited = true;
+#pragma unroll
+                    for (int j = 0; j < S::STAGES; ++j) fetch_x(j, first_kb[j], first_blocks[j]);
                 }
+                if (waited) mbar_wait(&empty[s], ((it / S::STAGES) & 1) ^ 1);
+                if (leader) {
+                    mbar_arrive_expect_tx(&full[s], blocks * S::BLOCK_BYTES);
+#pragma unroll
+                    for (int b = 0; b < S::BLOCKS; ++b)
+                        if (b < blocks) tma_load_2d(smem + s * S::STAGE_BYTES + b * S::BLOCK_BYTES, &w_map, &full[s], (kb + b) * BLOCK_K, tile * TILE_N);
+                }
+                if (waited) fetch_x(s, kb, blocks);
+                else {
+#pragma unroll
+                    for (int j = 0; j < S::STAGES; ++j)
+                        if (j == it) first_kb[j] = kb, first_blocks[j] = blocks;
+                }
+                __syncwarp();
             }
-            if (!waited) {                                  // fewer blocks than stages
-                pdl_wait();
-                for (int j = 0; j < it; ++j)
-                    tma_load_2d(smem + j * S::STAGE_BYTES + W_TILE_BYTES, &x_map, &full[j], first_kb[j] * BLOCK_K, 0);
-            }
+        }
+        if (!waited) {                                  // fewer steps than stages
+            pdl_wait();
+#pragma unroll
+            for (int j = 0; j < S::STAGES; ++j)
+                if (j < it) fetch_x(j, first_kb[j], first_blocks[j]);
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16_f32(TILE_N, MPAD);
-            int it = 0, round = 0;
-            for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++round) {
-                const int split = unit % splits;
-                const int kb0 = (int)((long long)split * k_blocks / splits), kb1 = (int)((long long)(split + 1) * k_blocks / splits);
-                const int buffer = round & 1;
-                mbar_wait(&acc_empty[buffer], ((round >> 1) & 1) ^ 1);
+        const bool leader = elect_one();
+        constexpr uint32_t idesc = umma_idesc_bf16_f32(TILE_N, MPAD);
+        int it = 0, round = 0;
+        for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++round) {
+            const int split = unit % splits;
+            const int kb0 = (int)((long long)split * k_blocks / splits), kb1 = (int)((long long)(split + 1) * k_blocks / splits);
+            const int buffer = round & 1;
+            mbar_wait(&acc_empty[buffer], ((round >> 1) & 1) ^ 1);
+            tcgen05_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buffer * MPAD;
+            for (int kb = kb0; kb < kb1; kb += S::BLOCKS, ++it) {
+                const int s = it % S::STAGES;
+                const int blocks = min(S::BLOCKS, kb1 - kb);
+                mbar_wait(&full[s], (it / S::STAGES) & 1);
                 tcgen05_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buffer * MPAD;
-                for (int kb = kb0; kb < kb1; ++kb, ++it) {
-                    const int s = it % S::STAGES;
-                    mbar_wait(&full[s], (it / S::STAGES) & 1);
-                    tcgen05_fence_after_sync();
-                    const uint32_t w_addr = smem_u32(smem + s * S::STAGE_BYTES), x_addr = w_addr + W_TILE_BYTES;
+                if (leader) {
 #pragma unroll
-                    for (int k = 0; k < BLOCK_K / UMMA_K; ++k)
-                        umma_bf16(d_tmem, umma_smem_desc_sw128(w_addr + k * UMMA_K * 2), umma_smem_desc_sw128(x_addr + k * UMMA_K * 2),
-                                  idesc, kb > kb0 || k > 0);
+                    for (int b = 0; b < S::BLOCKS; ++b)
+                        if (b < blocks) {
+                            const uint64_t w_desc = umma_smem_desc_sw128(smem_u32(smem + s * S::STAGE_BYTES + b * S::BLOCK_BYTES));
+                            const uint64_t x_desc = umma_smem_desc_sw128(smem_u32(smem + s * S::STAGE_BYTES + b * S::BLOCK_BYTES + W_TILE_BYTES));
+                            if (kb > kb0 || b > 0) {
+#pragma unroll
+                                for (int k = 0; k < BLOCK_K / UMMA_K; ++k) umma_bf16_more(d_tmem, w_desc + 2 * k, x_desc + 2 * k, idesc);
+                            } else {
+                                umma_bf16_first(d_tmem, w_desc, x_desc, idesc);
+#pragma unroll
+                                for (int k = 1; k < BLOCK_K / UMMA_K; ++k) umma_bf16_more(d_tmem, w_desc + 2 * k, x_desc + 2 * k, idesc);
+                            }
+                        }
                     umma_commit(&empty[s]);          // the stage is free once these MMAs have read it
                 }
-                umma_commit(&acc_full[buffer]);
+                __syncwarp();
             }
+            if (leader) umma_commit(&acc_full[buffer]);
+            __syncwarp();
         }
     } else {
         // ------------------------------------------------------------------ accumulator -> memory
