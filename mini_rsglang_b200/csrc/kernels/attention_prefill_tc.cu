@@ -227,19 +227,28 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
         }
     } else if (warp == 1) {
         // ------------------------------------------------------------------ MMA
-        if (lane == 0 && blocks > 0) {                       // (a share of the keys can be empty)
+        // The whole warp walks the loop and one elected lane issues: descriptors and addresses are then the same
+        // in every lane, and an MMA costs its issuer some 40 clocks instead of 100 in divergent code.
+        if (blocks > 0) {                                    // (a share of the keys can be empty)
+            const bool leader = elect_one();
             constexpr uint32_t idesc_s = umma_idesc_bf16_f32(BM, BN);
             constexpr uint32_t idesc_o = umma_idesc_bf16_f32(BM, D, true);
             const uint32_t q_addr = smem_u32(q_smem);
             // scores of block j of tile i (the keys of block j are in their stage)
             auto issue_scores = [&](int i, int j) {
                 const uint32_t k_addr = smem_u32(k_smem + (j % STAGES) * KV_TILE_BYTES);
+                if (leader) {
+                    const uint32_t s_tmem = tmem_base + i * S_COLUMNS;
 #pragma unroll
-                for (int k = 0; k < D / 16; ++k)
-                    umma_bf16(tmem_base + i * S_COLUMNS,
-                              umma_smem_desc_sw128(q_addr + i * Q_TILE_BYTES + (k / 4) * Q_HALF_BYTES + (k % 4) * 32),
-                              umma_smem_desc_sw128(k_addr + (k / 4) * KV_HALF_BYTES + (k % 4) * 32), idesc_s, k > 0);
-                umma_commit(&bars->s_full[i]);
+                    for (int k = 0; k < D / 16; ++k) {
+                        const uint64_t q_desc = umma_smem_desc_sw128(q_addr + i * Q_TILE_BYTES + (k / 4) * Q_HALF_BYTES + (k % 4) * 32);
+                        const uint64_t k_desc = umma_smem_desc_sw128(k_addr + (k / 4) * KV_HALF_BYTES + (k % 4) * 32);
+                        if (k == 0) umma_bf16_first(s_tmem, q_desc, k_desc, idesc_s);
+                        else umma_bf16_more(s_tmem, q_desc, k_desc, idesc_s);
+                    }
+                    umma_commit(&bars->s_full[i]);
+                }
+                __syncwarp();
             };
             mbar_wait(&bars->q_full, 0);
             mbar_wait(&bars->k_full[0], 0);
@@ -247,7 +256,8 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
 #pragma unroll
             for (int i = 0; i < TILES; ++i)
                 if (tile_blocks[i] > 0) issue_scores(i, 0);
-            umma_commit(&bars->k_empty[0]);
+            if (leader) umma_commit(&bars->k_empty[0]);
+            __syncwarp();
             // The tiles take turns: P.V of a tile's block, then at once the scores of its next block (the
             // probabilities lie where the scores lay, and MMAs run in the order they are issued).
             for (int j = 0; j < blocks; ++j) {
@@ -260,20 +270,30 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
                     if (!waited_v) mbar_wait(&bars->v_full[s], (j / STAGES) & 1), waited_v = true;
                     tcgen05_fence_after_sync();
                     const uint32_t v_addr = smem_u32(v_smem + s * KV_TILE_BYTES);
+                    if (leader) {
+                        const uint32_t o_tmem = tmem_base + O_COLUMN + i * D, p_tmem = tmem_base + i * S_COLUMNS;
 #pragma unroll
-                    for (int k = 0; k < BN / 16; ++k)
-                        umma_bf16_a_tmem(tmem_base + O_COLUMN + i * D, tmem_base + i * S_COLUMNS + k * 8,
-                                         umma_smem_desc_sw128_mn(v_addr + k * 2048, KV_HALF_BYTES), idesc_o, j > 0 || k > 0);
+                        for (int k = 0; k < BN / 16; ++k) {
+                            const uint64_t v_desc = umma_smem_desc_sw128_mn(v_addr + k * 2048, KV_HALF_BYTES);
+                            if (k == 0 && j == 0) umma_bf16_a_tmem(o_tmem, p_tmem, v_desc, idesc_o, false);
+                            else umma_bf16_a_tmem(o_tmem, p_tmem + k * 8, v_desc, idesc_o, true);
+                        }
+                    }
+                    __syncwarp();
                     if (j + 1 < tile_blocks[i]) {
                         if (!waited_k) mbar_wait(&bars->k_full[(j + 1) % STAGES], ((j + 1) / STAGES) & 1), waited_k = true;
                         tcgen05_fence_after_sync();
                         issue_scores(i, j + 1);
                     } else {
-                        umma_commit(&bars->pv_done[i]);          // the tile's last block: its accumulator is final
+                        if (leader) umma_commit(&bars->pv_done[i]);          // the tile's last block: its accumulator is final
+                        __syncwarp();
                     }
                 }
-                umma_commit(&bars->v_empty[s]);
-                if (waited_k) umma_commit(&bars->k_empty[(j + 1) % STAGES]);
+                if (leader) {
+                    umma_commit(&bars->v_empty[s]);
+                    if (waited_k) umma_commit(&bars->k_empty[(j + 1) % STAGES]);
+                }
+                __syncwarp();
             }
         }
     } else {

@@ -65,46 +65,61 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_many_rows_kernel(
     pdl_launch_dependents();
     pdl_wait();
 
+    // In the copy and MMA warps the whole warp walks the loop and one elected lane issues: addresses and descriptors
+    // are then the same in every lane, which makes an issue cheap.
     if (warp == 0) {
-        if (lane == 0) {
+        const bool leader = elect_one();
+        if (leader) {
             tma_prefetch_descriptor(&x_map);
             tma_prefetch_descriptor(&w_map);
-            int it = 0;
-            bool alive = true;
-            for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
-                const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    if (!(alive = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1))) break;
+        }
+        int it = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x) {
+            const int m0 = (tile % m_tiles) * BM, n0 = (tile / m_tiles) * BN;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!(alive = mbar_wait(&empty[s], ((it / STAGES) & 1) ^ 1))) break;
+                unsigned char* stage = smem + s * STAGE_BYTES;
+                if (leader) {
                     mbar_arrive_expect_tx(&full[s], STAGE_BYTES);
-                    unsigned char* stage = smem + s * STAGE_BYTES;
                     tma_load_2d(stage, &x_map, &full[s], kb * BK, m0);
                     tma_load_2d(stage + A_BYTES, &w_map, &full[s], kb * BK, n0);
                 }
+                __syncwarp();
             }
         }
     } else if (warp == 1) {
-        if (lane == 0) {
-            constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
-            int it = 0, round = 0;
-            for (int tile = blockIdx.x; tile < tiles; tile += gridDim.x, ++round) {
-                const int buffer = round & 1;
-                if (!mbar_wait(&acc_empty[buffer], ((round >> 1) & 1) ^ 1)) break;
+        const bool leader = elect_one();
+        constexpr uint32_t idesc = umma_idesc_bf16_f32(BM, BN);
+        int it = 0, round = 0;
+        bool alive = true;
+        for (int tile = blockIdx.x; tile < tiles && alive; tile += gridDim.x, ++round) {
+            const int buffer = round & 1;
+            if (!(alive = mbar_wait(&acc_empty[buffer], ((round >> 1) & 1) ^ 1))) break;
+            tcgen05_fence_after_sync();
+            const uint32_t d_tmem = tmem_base + buffer * BN;
+            for (int kb = 0; kb < k_blocks; ++kb, ++it) {
+                const int s = it % STAGES;
+                if (!(alive = mbar_wait(&full[s], (it / STAGES) & 1))) break;
                 tcgen05_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + buffer * BN;
-                for (int kb = 0; kb < k_blocks; ++kb, ++it) {
-                    const int s = it % STAGES;
-                    if (!mbar_wait(&full[s], (it / STAGES) & 1)) break;
-                    tcgen05_fence_after_sync();
-                    const uint32_t a_addr = smem_u32(smem + s * STAGE_BYTES), b_addr = a_addr + A_BYTES;
+                const uint64_t a_desc = umma_smem_desc_sw128(smem_u32(smem + s * STAGE_BYTES));
+                const uint64_t b_desc = umma_smem_desc_sw128(smem_u32(smem + s * STAGE_BYTES + A_BYTES));
+                if (leader) {
+                    if (kb > 0) {
 #pragma unroll
-                    for (int k = 0; k < BK / UMMA_K; ++k)
-                        umma_bf16(d_tmem, umma_smem_desc_sw128(a_addr + k * UMMA_K * 2), umma_smem_desc_sw128(b_addr + k * UMMA_K * 2),
-                                  idesc, kb > 0 || k > 0);
+                        for (int k = 0; k < BK / UMMA_K; ++k) umma_bf16_more(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc);
+                    } else {
+                        umma_bf16_first(d_tmem, a_desc, b_desc, idesc);
+#pragma unroll
+                        for (int k = 1; k < BK / UMMA_K; ++k) umma_bf16_more(d_tmem, a_desc + 2 * k, b_desc + 2 * k, idesc);
+                    }
                     umma_commit(&empty[s]);
                 }
-                umma_commit(&acc_full[buffer]);
+                __syncwarp();
             }
+            if (leader) umma_commit(&acc_full[buffer]);
+            __syncwarp();
         }
     } else {
         const int quarter = warp & 3;

@@ -466,8 +466,11 @@ MRS_EXPORT int mrs_gemm_tc_map(const void* base, long long rows, long long cols,
 
 // Ranges of K for a weight matrix [N, K] on a GPU with `sms` SMs, by a count of the time an SM
 // spends: rounds of units x (64-column blocks of a unit + a unit's fixed cost + the cost of
-// leaving and adding partial sums when there are several ranges).  It depends on N, K and the
-// GPU alone, never on the rows of the product.
+// leaving and adding partial sums when there are several ranges), the costs in blocks' worth of
+// time.  It depends on N, K and the GPU alone, never on the rows of the product.  The costs 4 and 8
+// were measured in decode steps (with 2 and 2 the gate/up product of the 8B shape took 3 ranges
+// instead of 2: batch 8 4.155 against 4.104 ms a step, batch 16 5.129 against 4.997 ms; 14B shape
+// at batch 16 8.83 against 8.61 ms; 1 and 1, 3 and 4, 6 and 12, 4 and 16, 8 and 8 all slower).
 MRS_EXPORT int mrs_gemm_tc_splits(int N, int K, int sms) {
     const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K, n_tiles = (N + TILE_N - 1) / TILE_N;
     int limit = k_blocks / 4;
@@ -476,7 +479,7 @@ MRS_EXPORT int mrs_gemm_tc_splits(int N, int K, int sms) {
     long long best_cost = -1;
     for (int s = 1; s <= limit; ++s) {
         const long long rounds = ((long long)n_tiles * s + sms - 1) / sms;
-        const long long cost = rounds * ((k_blocks + s - 1) / s + 2 + (s > 1 ? 2 : 0));
+        const long long cost = rounds * ((k_blocks + s - 1) / s + 4 + (s > 1 ? 8 : 0));
         if (best_cost < 0 || cost < best_cost) best = s, best_cost = cost;
     }
     return best;

@@ -587,12 +587,11 @@ _gemm_lib = None
 _weight_maps: dict[tuple, tuple] = {}
 _gemm_state: dict[torch.device, dict] = {}
 GEMM_TC_MAX_ROWS = 128          # what the kernel takes
-# Measured in the engine (decode steps of the 8B shape, context 4,096, with the norms riding on the products): 9% faster
-# than the library's products at batch 8, the same at 16 (5.21 against 5.14 to 5.29 ms a step), 20% slower at 32 (8.14
-# against 6.79 ms).  Alone, a product of 16 to 128 rows takes the library the same 9 us (N = K = 4,096) while this
-# kernel goes from 11 to 33 us: its epilogue (a thread a weight row, looping over the rows) and the partial sums of
-# the ranges of K grow with the rows.
-GEMM_TC_BEST_ROWS = int(os.environ.get("MRS_GEMM_TC_BEST_ROWS", "8"))      # the variable: for measuring other crossovers
+# Measured in the engine (decode steps at a context of 4,096, with the norms riding on the products), this kernel against
+# the library's products: batch 8 9% faster; batch 16 5.13 against 5.22 ms a step at the 8B shape, 8.83 against 8.94 ms
+# at the 14B shape (context 8,192), 2.36 against 2.46 ms at the 0.6B shape; batch 32 8.15 against 6.65 ms.  Its epilogue
+# (a thread a weight row, looping over the rows) and the partial sums of the ranges of K grow with the rows.
+GEMM_TC_BEST_ROWS = int(os.environ.get("MRS_GEMM_TC_BEST_ROWS", "16"))      # the variable: for measuring other crossovers
 
 
 def gemm_tc_library() -> ctypes.CDLL:
