@@ -542,6 +542,29 @@ MRS_EXPORT int mrs_attention_decode_tma(const void* k_map, const void* v_map, co
     MRS_RETURN_LAUNCH_STATUS();
 }
 
+// Thread-block clusters of `splits` CTAs of this kernel that the GPU holds at once (0: no such cluster): what a
+// plan may count on when it wants every share of every tile resident together.  Asked of the driver once a size.
+MRS_EXPORT int mrs_attention_decode_tma_resident_clusters(int splits) {
+    static int known[17] = {};
+    if (splits < 2 || splits > 16 || (splits & (splits - 1))) return 0;
+    if (known[splits] == 0) {
+        known[splits] = -1;
+        if (cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, (int)SMEM_BYTES) == cudaSuccess &&
+            (splits <= 8 || cudaFuncSetAttribute(attention_decode_kernel, cudaFuncAttributeNonPortableClusterSizeAllowed, 1) == cudaSuccess)) {
+            cudaLaunchConfig_t probe = {};
+            probe.gridDim = dim3(64, 1, splits), probe.blockDim = dim3(THREADS), probe.dynamicSmemBytes = SMEM_BYTES;
+            cudaLaunchAttribute shape;
+            shape.id = cudaLaunchAttributeClusterDimension;
+            shape.val.clusterDim.x = 1, shape.val.clusterDim.y = 1, shape.val.clusterDim.z = splits;
+            probe.attrs = &shape, probe.numAttrs = 1;
+            int clusters = 0;
+            if (cudaOccupancyMaxActiveClusters(&clusters, attention_decode_kernel, &probe) == cudaSuccess && clusters > 0) known[splits] = clusters;
+        }
+        (void)cudaGetLastError();
+    }
+    return known[splits] > 0 ? known[splits] : 0;
+}
+
 // Reads and clears this library's error word (waits for the device).  0: no kernel gave up a wait.
 MRS_EXPORT int mrs_attention_decode_tma_take_error(unsigned int* word) { return mrs_take_error_word(word); }
 // Mirrors the error word into a word of pinned host memory from now on.

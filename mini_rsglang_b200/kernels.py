@@ -438,6 +438,8 @@ def attention_decode_tma_library(d: int) -> ctypes.CDLL:
         lib.mrs_attention_decode_tma.restype = _c_int
         lib.mrs_attention_decode_tma_scratch_floats.argtypes = [_c_int, _c_int, _c_int]
         lib.mrs_attention_decode_tma_scratch_floats.restype = ctypes.c_longlong
+        lib.mrs_attention_decode_tma_resident_clusters.argtypes = [_c_int]
+        lib.mrs_attention_decode_tma_resident_clusters.restype = _c_int
         lib.mrs_attention_decode_tma_take_error.argtypes = [ctypes.POINTER(ctypes.c_uint)]
         lib.mrs_attention_decode_tma_take_error.restype = _c_int
         lib.mrs_attention_decode_tma_error_string.argtypes = [_c_int]
@@ -445,6 +447,20 @@ def attention_decode_tma_library(d: int) -> ctypes.CDLL:
         _decode_libs[d] = lib
         _register_error_word(f"attention_decode_tma (head size {d})", lib, "mrs_attention_decode_tma")
     return _decode_libs[d]
+
+
+_resident_clusters: dict[tuple, int] = {}
+
+
+def attention_decode_tma_resident_clusters(d: int, splits: int, device) -> int:
+    """Thread-block clusters of `splits` CTAs of the decode attention (head size d) that the GPU holds at once, as
+    the driver states it (B200, head size 128: 148, 71, 33 and 14 clusters of 2, 4, 8 and 16); 0 where no such
+    cluster runs."""
+    key = (d, splits, torch.device(device).index or 0)
+    if key not in _resident_clusters:
+        with torch.cuda.device(device):
+            _resident_clusters[key] = int(attention_decode_tma_library(d).mrs_attention_decode_tma_resident_clusters(splits))
+    return _resident_clusters[key]
 
 
 def _aligned_block(size: int, alignment: int):

@@ -142,10 +142,12 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
     return plans[key]
 
 
-def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident: int = 2) -> int:
-    """CTAs per tile in the kernels for few rows: a power of two (2, 4, 8 or 16 shares run as one thread-block
+def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident: int = 2, clusters=None) -> int:
+    """CTAs per tile in the kernels for few rows.  Powers of two (2, 4, 8 or 16 shares run as one thread-block
     cluster and merge through distributed shared memory), every share with at least two 64-key blocks, all CTAs
-    resident at once (`resident` per SM), at most 8 shares (16 for a single request with a long context).
+    resident at once (`resident` per SM), at most 8 shares (16 for a single request with a long context); one
+    share fewer (7, which meet through memory) where the clusters of 8 would take nearly all that the GPU holds
+    at once.  `clusters(size)`: how many clusters of that size the GPU holds at once (None: not asked).
 
     Measured on a B200 with 8 key/value heads of 128, contexts of 4,096 and 16,384, 1 to 16 requests, the kernel
     alone and in decode steps.  With few keys in all (up to about 75 MB a layer) the kernel is bound by its start and
@@ -154,7 +156,13 @@ def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident
     requests: 4.23 ms with 4 shares, 4.49 ms with 2).  More CTAs than slots, or clusters of 16 for more than one
     request, cost 9 to 12 us a layer (2 requests at 4,096: 13.7 us with 8 shares, 24.4 us with 16; 6 requests:
     22.2 us with 4, 30.8 us with 8; 12 requests: 36.3 us with 2, 45.5 us with 4; a decode step at batch 2 went from
-    4.04 to 3.66 ms when the count stopped being rounded up past the slots)."""
+    4.04 to 3.66 ms when the count stopped being rounded up past the slots).  The GPU holds 33 clusters of 8; with 4
+    requests 8 shares are 32 of them, and inside a decode step (not alone) they come to stand late, between the
+    products before and after: 12 layers at a context of 16,384 take 1.970 ms a step with 8 shares, 1.709 ms with 7,
+    1.742 with 6, 1.849 with 4; at 4,096 1.483, 1.376, 1.395 and 1.399 ms.  With 3 requests in the same recording
+    7 shares cost 2% (1.642 against 1.599 ms)."""
+    if os.environ.get("MRS_DECODE_SPLITS"):           # the variable: for measuring other counts
+        return int(os.environ["MRS_DECODE_SPLITS"])
     blocks = -(-longest_context // 64)
     slots = sms * resident
     pairs = max(tiles * nkv, 1)
@@ -168,6 +176,10 @@ def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident
     else:                                           # many keys: as many resident CTAs as there are slots
         while splits * 2 <= most and pairs * splits * 2 <= slots:
             splits *= 2
+    if clusters is not None and splits >= 8:
+        room = clusters(splits)
+        if room and pairs * 5 > room * 4:           # more than four fifths of the clusters that fit at once
+            splits -= 1
     return splits
 
 
@@ -200,10 +212,12 @@ def paged_attention(q, cache, ctx, out, nq: int, nkv: int, d: int, window: int) 
     tensor_core_rows = kernels.attention_prefill_tc_supported(d, group, page_size)
     narrow, wide, longest, shared = plan_attention_tiles(ctx, *tile_plan_arguments(d, group, page_size, nkv, window, q.device))
     def few_rows():
-        splits = choose_splits(narrow.shape[0], nkv, longest, sms)
         if kernels.attention_decode_tma_supported(d, group, cache.k.shape[2]):
+            splits = choose_splits(narrow.shape[0], nkv, longest, sms,
+                                   clusters=lambda size: kernels.attention_decode_tma_resident_clusters(d, size, q.device))
             kernels.attention_decode_tma(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
         else:
+            splits = choose_splits(narrow.shape[0], nkv, longest, sms)
             kernels.attention_mma_keys(q, cache.k, cache.v, ctx.positions, table, narrow, out, nq, nkv, d, window, splits)
 
     def many_rows():

@@ -65,3 +65,26 @@ def test_fixed_shapes_give_caps_that_hold_the_lists_and_words_in_their_places():
     assert [tuple(w) for w in words[lists.narrow_cap:lists.narrow_cap + len(lists.wide)]] == lists.wide
     only_wide = attention_tile_lists(facts_of([300], [0], padded=(1, 320)), 4, kernels.PREFILL_TC_ROWS, 8, 0, 128, 148)
     assert only_wide.narrow_cap == 0 and only_wide.wide_cap >= 16
+
+
+def test_shares_of_the_keys_fit_the_gpu():
+    """The split rule of the kernels for few rows: every share has two blocks of keys at least, all CTAs are
+    resident at once, and clusters of 8 are not taken where they would need nearly all that the GPU holds."""
+    from mini_rsglang_b200.parts.attention import choose_splits
+    room = {2: 148, 4: 71, 8: 33, 16: 14}.get          # what a B200 states for the decode attention at heads of 128
+    sms = 148
+    for context in (64, 200, 1024, 4096, 8192, 16384, 65536):
+        for tiles in (1, 2, 3, 4, 6, 8, 16, 32, 64, 128):
+            for nkv in (1, 2, 8):
+                plain = choose_splits(tiles, nkv, context, sms)
+                fitted = choose_splits(tiles, nkv, context, sms, clusters=room)
+                for splits in (plain, fitted):
+                    assert 1 <= splits <= 16
+                    assert splits == 1 or splits * 2 <= max(2, -(-context // 64))
+                    assert splits == 1 or tiles * nkv * splits <= 2 * sms
+                assert fitted in (plain, plain - 1)
+                if fitted != plain:
+                    assert plain >= 8 and tiles * nkv * 5 > room(plain) * 4
+    assert choose_splits(4, 8, 8192, sms) == 8 and choose_splits(4, 8, 8192, sms, clusters=room) == 7
+    assert choose_splits(2, 8, 8192, sms, clusters=room) == 8           # 16 clusters of 33: they fit
+    assert choose_splits(1, 8, 32768, sms, clusters=room) == 16
