@@ -145,9 +145,9 @@ def plan_attention_tiles(ctx, group: int, wide_rows: int, kv_heads: int = 1, win
 def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident: int = 2, clusters=None) -> int:
     """CTAs per tile in the kernels for few rows.  Powers of two (2, 4, 8 or 16 shares run as one thread-block
     cluster and merge through distributed shared memory), every share with at least two 64-key blocks, all CTAs
-    resident at once (`resident` per SM), at most 8 shares (16 for a single request with a long context); one
-    share fewer (7, which meet through memory) where the clusters of 8 would take nearly all that the GPU holds
-    at once.  `clusters(size)`: how many clusters of that size the GPU holds at once (None: not asked).
+    resident at once (`resident` per SM), at most 8 shares (16 for a single request with a long context); with
+    many keys and few requests any count that fills seven eighths of the slots; one share fewer (which then meet
+    through memory) where clusters of 8 or 16 would take nearly all that the GPU holds at once.  `clusters(size)`: how many clusters of that size the GPU holds at once (None: not asked).
 
     Measured on a B200 with 8 key/value heads of 128, contexts of 4,096 and 16,384, 1 to 16 requests, the kernel
     alone and in decode steps.  With few keys in all (up to about 75 MB a layer) the kernel is bound by its start and
@@ -160,7 +160,10 @@ def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident
     requests 8 shares are 32 of them, and inside a decode step (not alone) they come to stand late, between the
     products before and after: 12 layers at a context of 16,384 take 1.970 ms a step with 8 shares, 1.709 ms with 7,
     1.742 with 6, 1.849 with 4; at 4,096 1.483, 1.376, 1.395 and 1.399 ms.  With 3 requests in the same recording
-    7 shares cost 2% (1.642 against 1.599 ms)."""
+    7 shares cost 2% (1.642 against 1.599 ms).  One or two requests with long contexts want more shares than a
+    cluster has, so many that seven eighths of the slots are taken (counts that are no cluster meet through memory,
+    which the long walks pay for): 12 layers at a context of 36,000, one request 1.608 ms a step with 16 shares,
+    1.524 with 32; two requests 1.914 ms with 8 shares, 1.757 with 18 (16, as clusters of 16: 2.062)."""
     if os.environ.get("MRS_DECODE_SPLITS"):           # the variable: for measuring other counts
         return int(os.environ["MRS_DECODE_SPLITS"])
     blocks = -(-longest_context // 64)
@@ -176,6 +179,9 @@ def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident
     else:                                           # many keys: as many resident CTAs as there are slots
         while splits * 2 <= most and pairs * splits * 2 <= slots:
             splits *= 2
+        filling = min(blocks // 2, (slots * 7 // 8) // pairs, 64)
+        if filling >= 8:                            # few requests with long contexts: any count that fills the GPU
+            splits = filling
     if clusters is not None and splits >= 8:
         room = clusters(splits)
         if room and pairs * 5 > room * 4:           # more than four fifths of the clusters that fit at once

@@ -79,12 +79,14 @@ def test_shares_of_the_keys_fit_the_gpu():
                 plain = choose_splits(tiles, nkv, context, sms)
                 fitted = choose_splits(tiles, nkv, context, sms, clusters=room)
                 for splits in (plain, fitted):
-                    assert 1 <= splits <= 16
+                    assert 1 <= splits <= 64
                     assert splits == 1 or splits * 2 <= max(2, -(-context // 64))
                     assert splits == 1 or tiles * nkv * splits <= 2 * sms
                 assert fitted in (plain, plain - 1)
                 if fitted != plain:
-                    assert plain >= 8 and tiles * nkv * 5 > room(plain) * 4
+                    assert plain in (8, 16) and tiles * nkv * 5 > room(plain) * 4
     assert choose_splits(4, 8, 8192, sms) == 8 and choose_splits(4, 8, 8192, sms, clusters=room) == 7
     assert choose_splits(2, 8, 8192, sms, clusters=room) == 8           # 16 clusters of 33: they fit
-    assert choose_splits(1, 8, 32768, sms, clusters=room) == 16
+    assert choose_splits(1, 8, 16384, sms, clusters=room) == 16
+    assert choose_splits(1, 8, 32768, sms, clusters=room) == 32         # more than a cluster has: they meet through memory
+    assert choose_splits(2, 8, 32768, sms, clusters=room) == 15         # 16 clusters of 16 do not fit
