@@ -122,16 +122,21 @@ __global__ void __launch_bounds__(THREADS, 1) attention_prefill_kernel(
     const int key_begin = window > 0 ? max(0, first_pos - window + 1) : 0;
     int block_first = key_begin / BN;
     int blocks = 0;
+    // An entry may hold two tiles that are not neighbours: `gap` tokens of the request lie between them (other
+    // entries take those).  The plan pairs an early tile, whose walk is short, with a late one, so that the CTAs of a
+    // prompt take equally long; both read the same blocks of keys while the early one has any.
+    const int gap = (int)((unsigned)work.share >> 16);
+    int key_end = first_pos;
 #pragma unroll
     for (int i = 0; i < TILES; ++i) {
-        tile_first[i] = work.first_token + i * tokens_per_tile;
+        tile_first[i] = work.first_token + i * (tokens_per_tile + gap);
         tile_tokens[i] = max(0, min(tokens_per_tile, work.tokens - i * tokens_per_tile));
-        tile_first_pos[i] = first_pos + i * tokens_per_tile;
+        tile_first_pos[i] = first_pos + i * (tokens_per_tile + gap);
         const int last_pos = tile_first_pos[i] + tile_tokens[i] - 1;
         tile_blocks[i] = tile_tokens[i] > 0 ? (last_pos + BN) / BN - block_first : 0;
         blocks = max(blocks, tile_blocks[i]);
+        if (tile_tokens[i] > 0) key_end = last_pos + 1;
     }
-    const int key_end = first_pos + work.tokens;
     const int shares = (work.share >> 8) & 0xFF;
     if (shares > 1) {
         // this entry's share of the key blocks; a tile may have none of its blocks in it

@@ -91,6 +91,37 @@ def attention_tile_lists(facts: StepFacts, group: int, wide_rows: int, kv_heads:
     spare = room // max(len(found) * kv_heads, 1) if tensor_core else 1
     wide = []
     shared = False
+    if tensor_core and tiles == 2 and spare < 2 and len(found) * kv_heads <= room and not window and PAIR_FAR_TILES:
+        # One round of CTAs, more than half the SMs: what is left to gain is their balance.  The tiles of a portion
+        # walk 1, 2, 3, ... blocks of keys more than the first, and a CTA holds two tiles: the first with the last,
+        # the second with the last but one, and so on, so that every CTA has the same work; the early tile is done
+        # after a few blocks and the late one walks on alone.  The entry's fourth number carries the tokens between
+        # its tiles (<< 16).  Measured alone, neighbours against pairs: 2,048 tokens of 16 query heads (128 CTAs)
+        # 42.9 against 39.9 us, 512 tokens of 40 heads (88 CTAs) 19.9 against 18.8 us, 1,024 tokens of 32 heads
+        # (128 CTAs) 26.5 against 26.1 us.  With more CTAs than SMs the rounds balance themselves and the pairs lose,
+        # since a tile without a partner uses the tensor cores half (2,048 tokens of 32 heads, 256 CTAs: 49.6 against
+        # 64.5 us; 8,192 tokens: 494 against 683 us), so neighbours stay together there.
+        per_tile = wide_tokens // 2
+        for i, n in enumerate(lengths):
+            if narrow_tokens >= 1 and n <= narrow_tokens:
+                continue
+            count = -(-n // per_tile)
+            first, begin = facts.q_start[i], facts.start_pos[i]
+            if count < 4 or count * per_tile >= 1 << 15:
+                wide += [(i, f, t, 0, 2 * b) for (j, f, t, p, b) in found if j == i]
+                continue
+            for a in range(count // 2):
+                b = count - 1 - a
+                last = min(per_tile, n - b * per_tile)
+                blocks_a = -(-(begin + (a + 1) * per_tile) // key_block)
+                blocks_b = -(-(begin + b * per_tile + last) // key_block)
+                wide.append((i, first + a * per_tile, per_tile + last, ((b - a - 1) * per_tile) << 16, 1.2 * blocks_b + 0.8 * blocks_a))
+            if count % 2:
+                a = count // 2
+                wide.append((i, first + a * per_tile, per_tile, 0, 1.2 * -(-(begin + (a + 1) * per_tile) // key_block)))
+        wide.sort(key=lambda t: -t[4])          # by the time they take, in blocks of two tiles
+        wide = [t[:4] for t in wide]
+        found = []
     for i, first, tokens, begin, blocks in found:
         shares = min(spare, blocks // 4, 255) if spare >= 2 else 1
         if shares >= 2:
@@ -101,8 +132,9 @@ def attention_tile_lists(facts: StepFacts, group: int, wide_rows: int, kv_heads:
             wide += [(i, first, half, 0, begin), (i, first + half, tokens - half, 0, begin + half)]
         else:
             wide.append((i, first, tokens, 0, begin))
-    wide.sort(key=lambda t: -t[4])          # a tile late in a long request walks the most keys: start it first (stable:
-    wide = [t[:4] for t in wide]            # the shares of an entry stay together and in their order)
+    if found:
+        wide.sort(key=lambda t: -t[4])      # a tile late in a long request walks the most keys: start it first (stable:
+        wide = [t[:4] for t in wide]        # the shares of an entry stay together and in their order)
     lists = TileLists(narrow, wide, longest_narrow, shared)
     if facts.padded_sequences:              # fixed shapes: the device lists have a length that many steps share
         lists.narrow_cap = facts.padded_sequences if narrow else 0
@@ -255,6 +287,7 @@ SIDE_BY_SIDE = os.environ.get("MRS_ATTENTION_SIDE_BY_SIDE", "1") == "1"      # t
 # step: 0.6B shape 143.7k tokens/s one kernel after the other, 159.9k side by side, 162.4k with the wide entries cut
 # for a quarter of the SMs only (the same with no cutting at all); 8B shape 45.6k, 47.0k, 47.3k.
 WIDE_SHARE_BESIDE_NARROW = float(os.environ.get("MRS_WIDE_SHARE", "0.25"))
+PAIR_FAR_TILES = os.environ.get("MRS_PAIR_FAR_TILES", "1") == "1"      # the variable: for measuring
 
 
 @MIXERS.register("gqa_attention")

@@ -266,11 +266,20 @@ class PagedCase:
     def run_mma(self, mode, splits=1):
         group = self.nq // self.nkv
         per_tile = {"rows": 64}.get(mode, 16) // group
-        if mode in ("tc", "tc_shares"):          # two tiles of 128 rows, each a whole number of tokens
+        if mode in ("tc", "tc_shares", "tc_pairs"):          # two tiles of 128 rows, each a whole number of tokens
             per_tile = 2 * (128 // group)
         tiles = []
         for i in range(len(self.spans)):
             first, n = self.q_start[i], self.q_start[i + 1] - self.q_start[i]
+            if mode == "tc_pairs":               # the first tile of a request with its last, the second with the last but one, ...
+                one = 128 // group
+                count = -(-n // one)
+                for a in range(count // 2):
+                    b = count - 1 - a
+                    tiles.append((i, first + a * one, one + min(one, n - b * one), ((b - a - 1) * one) << 16))
+                if count % 2:
+                    tiles.append((i, first + (count // 2) * one, min(one, n - (count // 2) * one), 0))
+                continue
             for s in range(0, n, per_tile):
                 if mode == "tc_shares":          # `splits` entries that walk one share of the keys each
                     tiles += [(i, first + s, min(per_tile, n - s), share | splits << 8) for share in range(splits)]
@@ -282,7 +291,7 @@ class PagedCase:
                 self.dev(self.positions), self.dev(self.table), tiles, out, self.nq, self.nkv, self.d, self.window)
         if mode == "keys":
             kernels.attention_mma_keys(*args, splits=splits)
-        elif mode in ("tc", "tc_shares"):
+        elif mode in ("tc", "tc_shares", "tc_pairs"):
             kernels.attention_prefill_tc(*args, shares=mode == "tc_shares")
             torch.cuda.synchronize()
             kernels.check_device_errors()
@@ -366,6 +375,17 @@ def test_attention_prefill_tc_shares_of_the_keys(nq, nkv, d, page, shares):
     a block in the last share, a ragged last entry."""
     case = PagedCase(torch.bfloat16, nq, nkv, d, page, [(1000, 70), (0, 300), (130, 3 + 2 * (128 // (nq // nkv))), (2000, 40)], seed=shares)
     close(case.run_mma("tc_shares", shares), case.plain(), torch.bfloat16, f"{shares} shares of the keys")
+
+
+@pytest.mark.parametrize("nq,nkv,d,page", [(8, 2, 128, 16), (4, 4, 64, 8), (10, 2, 128, 16), (2, 1, 128, 32), (16, 8, 128, 16)])
+def test_attention_prefill_tc_tiles_that_are_no_neighbours(nq, nkv, d, page):
+    """Entries whose two tiles lie apart in their request (the first tile with the last, and so on inwards): a tile
+    that is done after one block beside one that walks a dozen, a last tile that is not full, an odd count whose
+    middle tile stands alone, requests of one and two tiles, and cached tokens before the portion."""
+    one = 128 // (nq // nkv)
+    case = PagedCase(torch.bfloat16, nq, nkv, d, page, [(0, 12 * one), (0, 7 * one + 3), (300, 5 * one - 1), (0, one), (64, 2 * one), (0, 3)], seed=nq)
+    close(case.run_mma("tc_pairs"), case.plain(), torch.bfloat16, "tiles that are no neighbours")
+    assert torch.equal(case.run_mma("tc_pairs"), case.run_mma("tc"))          # a row's walk is the same whoever shares its CTA
 
 
 def test_attention_prefill_tc_rescales_when_the_maximum_grows():

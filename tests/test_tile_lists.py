@@ -24,7 +24,7 @@ def test_every_row_lies_in_one_tile(group, wide_rows, sms):
     rng = random.Random(group * 1000 + sms)
     for _ in range(50):
         n = rng.randint(1, 9)
-        lengths = [rng.choice([1, 1, 2, 3, 17, 64, 200, 513]) for _ in range(n)]
+        lengths = [rng.choice([1, 1, 2, 3, 17, 64, 200, 513, 1500, 2048]) for _ in range(n)]
         starts = [rng.choice([0, 0, 5, 700, 4000]) for _ in range(n)]
         facts = facts_of(lengths, starts)
         lists = attention_tile_lists(facts, group, wide_rows, 8, 0, 128, sms)
@@ -40,9 +40,15 @@ def test_every_row_lies_in_one_tile(group, wide_rows, sms):
             per_tile = wide_rows // 2 // group if wide_rows == kernels.PREFILL_TC_ROWS else wide_rows // group
             assert 0 < tokens <= (2 * per_tile if wide_rows == kernels.PREFILL_TC_ROWS else per_tile)
             assert facts.q_start[seq] <= first and first + tokens <= facts.q_start[seq + 1]
-            count = share >> 8
+            count, gap = (share >> 8) & 0xFF, share >> 16
             if count:
+                assert gap == 0
                 by_share.setdefault((seq, first, tokens, count), []).append(share & 0xFF)
+            elif gap:                       # two tiles that are no neighbours: `gap` tokens of the request between them
+                assert wide_rows == kernels.PREFILL_TC_ROWS and tokens > per_tile
+                assert first + per_tile + gap + tokens - per_tile <= facts.q_start[seq + 1]
+                for r in list(range(first, first + per_tile)) + list(range(first + per_tile + gap, first + gap + tokens)):
+                    covered[r] += 1
             else:
                 for r in range(first, first + tokens):
                     covered[r] += 1
@@ -90,3 +96,27 @@ def test_shares_of_the_keys_fit_the_gpu():
     assert choose_splits(1, 8, 16384, sms, clusters=room) == 16
     assert choose_splits(1, 8, 32768, sms, clusters=room) == 32         # more than a cluster has: they meet through memory
     assert choose_splits(2, 8, 32768, sms, clusters=room) == 15         # 16 clusters of 16 do not fit
+
+
+def test_one_round_of_entries_pairs_early_tiles_with_late_ones():
+    """With one round of CTAs (more than half the SMs, not more than all) the tiles of a portion are paired first with
+    last: every entry then walks about as many blocks of keys as any other."""
+    tokens = 1024
+    facts = facts_of([tokens], [0])
+    lists = attention_tile_lists(facts, 4, kernels.PREFILL_TC_ROWS, 8, 0, 128, 148)
+    per_tile = kernels.PREFILL_TC_ROWS // 2 // 4
+    assert len(lists.wide) == tokens // per_tile // 2 and not lists.shared and not lists.narrow
+    work = []
+    for seq, first, count, share in lists.wide:
+        gap = share >> 16
+        assert share & 0xFFFF == 0 and count == 2 * per_tile
+        a, b = first // per_tile, (first + per_tile + gap) // per_tile
+        assert a + b == tokens // per_tile - 1                     # first with last, second with last but one, ...
+        work.append(-(-(a + 1) * per_tile // 128) + -(-(b + 1) * per_tile // 128))
+    assert max(work) - min(work) <= 1
+
+    def gaps(lengths, starts, window=0):
+        return [share >> 16 for _, _, _, share in attention_tile_lists(facts_of(lengths, starts), 4, kernels.PREFILL_TC_ROWS, 8, window, 128, 148).wide]
+    assert not any(gaps([2048], [0]))               # more CTAs than SMs: the rounds balance themselves
+    assert not any(gaps([1024], [0], window=256))   # with a window every tile walks the same few blocks
+    assert not any(gaps([256], [4096]))             # few CTAs: shares of the keys instead
