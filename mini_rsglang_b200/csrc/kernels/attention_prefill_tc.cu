@@ -4,14 +4,17 @@
 //
 // A CTA works on two tiles of 128 query rows of one key/value head: a tile is 128 / group
 // consecutive tokens of one request times the group's query heads, so a key is read once for all
-// the heads that share it, and the second tile holds the tokens that follow the first.  A group
+// the heads that share it, and the second tile holds the tokens that follow the first, or, when
+// the entry says so (its fourth number >> 16: tokens between the tiles), tokens further on in the
+// same request: a late tile, whose walk is long, beside an early one, whose walk is short.  A group
 // that does not divide 128 (5 query heads a key/value head: 25 tokens, 125 rows) leaves the tile's
 // last rows empty: they are zeroed once, masked everywhere and never stored.  The keys
 // are walked in blocks of 128:
 //   warp 0      fetches the query tiles and, page by page through the request's block table, the
 //               keys and values of every block with bulk tensor copies (TMA, 128-byte swizzle)
 //               into two-stage rings; every lane owns one page of a block;
-//   warp 1      one thread issues the MMAs: S = Q.K^T of each tile into the tile's score buffer in
+//   warp 1      walks its loop whole, one elected lane issues the MMAs (an issue is cheap when every
+//               lane holds the same addresses): S = Q.K^T of each tile into the tile's score buffer in
 //               tensor memory, then O += P.V with P read from tensor memory (it overwrites the
 //               scores it came from) and V taken as it lies in the cache (rows of keys, the MN-major
 //               operand form);

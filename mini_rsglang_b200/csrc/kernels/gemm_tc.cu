@@ -5,8 +5,10 @@
 // weight streamer: the roles of the operands are swapped (128 weight rows are the M of the MMA,
 // the tokens its N, padded to 16/32/64/128), a producer warp fetches 128 x 64 weight tiles and
 // the matching slice of x with bulk tensor copies (TMA, 128-byte swizzle) into a ring of
-// shared-memory stages, one thread issues tcgen05.mma on the stages into an accumulator in
-// tensor memory, and four warps read finished accumulators back and store them transposed.
+// shared-memory stages of two such blocks of K, a second warp issues tcgen05.mma on the stages
+// into an accumulator in tensor memory (both warps walk their loops whole and one elected lane
+// issues; a stage costs one barrier round and one tcgen05.commit), and four warps read finished
+// accumulators back and store them transposed.
 // CTAs are persistent: each walks its share of the work units (a unit = 128 weight rows x a
 // range of K), with two accumulators in tensor memory, so copies and MMAs of the next unit run
 // while the last one is stored.

@@ -562,7 +562,9 @@ def attention_prefill_tc(q, k_cache, v_cache, positions, block_table, tiles, out
                          window: int = 0, scale: float | None = None, shares: bool = False) -> None:
     """Work entries of up to 256 // (nq // nkv) tokens of one request each, on the tcgen05 tensor cores.  The
     fourth number of an entry is 0, or index | count << 8 when `count` entries (one after the other in the list)
-    walk one share of the keys each; `shares` says that the list has such entries, whose sums a second kernel merges."""
+    walk one share of the keys each (`shares` says that the list has such entries, whose sums a second kernel
+    merges), or gap << 16 when the entry's second tile of 128 // (nq // nkv) tokens starts `gap` tokens behind
+    the end of its first (the entry's token count is that of both tiles)."""
     global launch_count
     _attention_mma_checks(q, k_cache, v_cache, positions, block_table, tiles, out, nq, nkv, d)
     lib = attention_prefill_tc_library(d)
