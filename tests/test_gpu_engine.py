@@ -732,6 +732,39 @@ def test_dropping_a_stream_or_leaving_its_block_cancels_the_request(model_folder
     engine.shutdown()
 
 
+@pytest.mark.parametrize("name,dtype", [("B", "float32"), ("D", "bfloat16")])
+def test_a_whole_prompt_of_more_than_a_thousand_tokens_is_one_recorded_step(model_folders, name, dtype):
+    """Steps of up to 2,048 rows are recorded: a prompt of 1,400 tokens as one step, then a second prompt of the same
+    rounded length through the same recording, each beside a decoded token of a third request.  The last rows equal
+    the plain implementation's and, in float32, those of a runner that queues every kernel, bit for bit."""
+    vocab = TINY[name][0]["vocab_size"]
+    reqs = list(T.requests_for(vocab, [1400, 1380, 40], seed=77).values())
+    want = [plain(model_folders[name], tokens) for tokens in reqs]
+    rows = {}
+    for record in (True, False):
+        runner = runner_for(model_folders[name], name, dtype, pages=3 * 1500 // TINY[name][1] + 8, max_seq_len=1536)
+        assert runner.mixed_rows_max >= 1408
+        runner.record_mixed = record
+        for i in range(3):
+            runner.cache.open(i + 1)
+        runner.cache.extend(3, 38)
+        runner.step([SequenceStep(3, reqs[2][:38], 0, [])])
+        got = []
+        for k, i in enumerate((0, 1)):
+            n = len(reqs[i])
+            runner.cache.extend(i + 1, n)
+            runner.cache.extend(3, 39 + k)
+            out = runner.step([SequenceStep(3, [reqs[2][38 + k]], 38 + k, [0]), SequenceStep(i + 1, reqs[i], 0, [n - 1])]).double().cpu()
+            T.check_rows(out, torch.stack([want[2][38 + k], want[i][n - 1]]), dtype, f"prompt {i} (recorded={record})")
+            got.append(out)
+        if record:
+            fixed = [key for key in runner._records if len(key) == 5 and key[0] >= 1408]
+            assert len(fixed) == 1 and runner.recorded_steps >= 2           # both long steps through one recording
+        rows[record] = torch.cat(got)
+    if dtype == "float32":
+        assert torch.equal(rows[True], rows[False])
+
+
 @pytest.mark.parametrize("dtype", ["float32", "bfloat16"])
 def test_recorded_decode_steps_across_classes_of_context_length(model_folders, dtype):
     """Three requests decode from 480, 700 and 20 tokens of context until the first has passed 1,024: steps are
