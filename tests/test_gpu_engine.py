@@ -319,6 +319,33 @@ def test_greedy_generation_through_the_entry_point(model_folders, name, dtype):
     engine.shutdown()
 
 
+@pytest.mark.parametrize("name", ["B", "D"])
+def test_float32_tokens_do_not_depend_on_pages_budget_or_concurrency(model_folders, name):
+    """The same prompts through engines with other page sizes, token budgets, numbers of requests in flight, with and
+    without shared prefixes, recordings and overlapped steps: in float32 every engine generates the same tokens,
+    since a row's arithmetic does not depend on how the tokens were cut or where in the cache they lie."""
+    import random
+    folder = model_folders[name]
+    vocab = TINY[name][0]["vocab_size"]
+    rng = random.Random(8)
+    family = [rng.randrange(vocab) for _ in range(200)]
+    prompts = [[rng.randrange(vocab) for _ in range(n)] for n in (1, 2, 17, 100, 260)] + [family[:150], family[:190] + [3, 4], family[:64]]
+    outputs = []
+    settings = [dict(page_size=16, prefill_budget=512, max_running=32), dict(page_size=8, prefill_budget=9, max_running=2),
+                dict(page_size=4, prefill_budget=64, max_running=3, prefix_cache=True),
+                dict(page_size=32, prefill_budget=2048, max_running=8, record_mixed_steps=False),
+                dict(page_size=64, prefill_budget=100, max_running=5, overlap_steps=False, prefix_cache=True),
+                dict(page_size=128, prefill_budget=300, max_running=4)]
+    for setting in settings:
+        limits = RuntimeConfig(max_seq_len=512, max_waiting=64, **setting)
+        engine = EngineHandle.load(folder, 0, config=limits, dtype="float32", num_pages=40 * 512 // setting["page_size"])
+        results = engine.generate_many(prompts, SamplingParams(max_tokens=12, ignore_eos=True))
+        outputs.append([r.token_ids for r in results])
+        engine.shutdown()
+    for setting, output in zip(settings[1:], outputs[1:]):
+        assert output == outputs[0], f"other tokens with {setting}"
+
+
 def test_streams_events_stop_reason_and_seeded_sampling(model_folders):
     folder = model_folders["B"]
     limits = RuntimeConfig(max_seq_len=128, page_size=16, prefill_budget=8, max_running=4)
