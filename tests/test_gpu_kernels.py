@@ -456,10 +456,12 @@ def test_one_far_key_among_hundreds(runner):
         close(got, case.plain(), dtype, f"{runner} vs plain, far key at {far}")
 
 
-@pytest.mark.parametrize("runner", ["simt16", "tma1", "tma16", "tc"])
+@pytest.mark.parametrize("runner", ["simt16", "tma1", "tma16", "tma7", "tma15", "tma32", "tc"])
 def test_one_far_key_among_tens_of_thousands(runner):
     """The same at a context of 40,000 tokens with heads of 128 (block tables of 2,500 pages, scattered): a decoded
-    token and a portion of a prompt find one key at the start, in the middle and near the end."""
+    token and a portion of a prompt find one key at the start, in the middle and near the end.  The shares of the
+    keys as one cluster (16) and as counts that are no cluster and meet through memory (7, 15, 32: what the plan
+    takes for few requests with long contexts)."""
     dtype = torch.bfloat16
     nq, nkv, d, page = 8, 2, 128, 16
     case = PagedCase(dtype, nq, nkv, d, page, [(39990, 1), (39000, 70)], seed=9)
@@ -474,8 +476,10 @@ def test_one_far_key_among_tens_of_thousands(runner):
             for lp in range(-(-(c + n) // page)):
                 rows = slice(lp * page, min(c + n, (lp + 1) * page))
                 case.kc[case.table[i, lp], :, :rows.stop - rows.start] = case.ks[i][rows].transpose(0, 1)
-        got = {"simt16": case.run_simt, "tma1": lambda: case.run_mma("tma", 1), "tma16": lambda: case.run_mma("tma", 16),
-               "tc": lambda: case.run_mma("tc")}[runner]()
+        if runner.startswith("tma"):
+            got = case.run_mma("tma", int(runner[3:]))
+        else:
+            got = {"simt16": case.run_simt, "tc": lambda: case.run_mma("tc")}[runner]()
         want_rows = torch.cat([case.vs[0][far].reshape(1, -1)] + [case.vs[1][far].reshape(1, -1)] * 70).double()
         want = want_rows.view(71, nkv, 1, d).expand(71, nkv, nq // nkv, d).reshape(71, nq * d)
         close(got, want, dtype, f"{runner}, far key at {far} of 40,000")
