@@ -50,6 +50,34 @@ template <int MPAD> struct Shape {
                                          MPAD * sizeof(float);                                           // the rows' norm factors
 };
 
+// How K is cut, as one number: ranges a tile (low 8 bits) for the first `tiles_first` tiles (bits 16 and up), and,
+// where bits 8-15 are not zero, that many ranges for the tiles behind them: the tiles of a last round of units
+// that would fill the GPU partly take more ranges, so that they fill it, and the round is shorter.
+struct Ranges {
+    int first, rest, tiles_first;
+};
+__host__ __device__ __forceinline__ Ranges ranges_of(int packed, int n_tiles) {
+    Ranges r;
+    r.first = packed & 0xFF;
+    r.rest = (packed >> 8) & 0xFF;
+    r.tiles_first = r.rest ? (packed >> 16) : n_tiles;
+    if (r.tiles_first > n_tiles) r.tiles_first = n_tiles;
+    return r;
+}
+__host__ __device__ __forceinline__ int units_of(const Ranges& r, int n_tiles) {
+    return r.tiles_first * r.first + (n_tiles - r.tiles_first) * r.rest;
+}
+// A unit's tile, its range of K and the ranges of that tile.
+__device__ __forceinline__ void unit_place(const Ranges& r, int unit, int& tile, int& split, int& splits) {
+    const int units_first = r.tiles_first * r.first;
+    if (unit < units_first) {
+        tile = unit / r.first, split = unit % r.first, splits = r.first;
+    } else {
+        const int u = unit - units_first;
+        tile = r.tiles_first + u / r.rest, split = u % r.rest, splits = r.rest;
+    }
+}
+
 __device__ __forceinline__ void epilogue_sync() { asm volatile("bar.sync 2, 128;" ::: "memory"); }
 
 enum { EPI_PLAIN = 0, EPI_GATED = 1, EPI_HEADS = 2, EPI_RESIDUAL = 3 };
@@ -105,7 +133,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
     const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
     const int n_tiles = (N + TILE_N - 1) / TILE_N;
-    const int units = n_tiles * splits;
+    const Ranges ranges = ranges_of(splits, n_tiles);
+    const int units = units_of(ranges, n_tiles);
 
     if (threadIdx.x == 0) {
         for (int s = 0; s < S::STAGES; ++s) {
@@ -151,8 +180,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
                         tma_load_2d(smem + s * S::STAGE_BYTES + b * S::BLOCK_BYTES + W_TILE_BYTES, &x_map, &full[s], (kb + b) * BLOCK_K, 0);
         };
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x) {
-            const int tile = unit / splits, split = unit % splits;
-            const int kb0 = (int)((long long)split * k_blocks / splits), kb1 = (int)((long long)(split + 1) * k_blocks / splits);
+            int tile, split, of;
+            unit_place(ranges, unit, tile, split, of);
+            const int kb0 = (int)((long long)split * k_blocks / of), kb1 = (int)((long long)(split + 1) * k_blocks / of);
             for (int kb = kb0; kb < kb1; kb += S::BLOCKS, ++it) {
                 const int s = it % S::STAGES;
                 const int blocks = min(S::BLOCKS, kb1 - kb);
@@ -190,8 +220,9 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
         constexpr uint32_t idesc = umma_idesc_bf16_f32(TILE_N, MPAD);
         int it = 0, round = 0;
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++round) {
-            const int split = unit % splits;
-            const int kb0 = (int)((long long)split * k_blocks / splits), kb1 = (int)((long long)(split + 1) * k_blocks / splits);
+            int tile, split, of;
+            unit_place(ranges, unit, tile, split, of);
+            const int kb0 = (int)((long long)split * k_blocks / of), kb1 = (int)((long long)(split + 1) * k_blocks / of);
             const int buffer = round & 1;
             mbar_wait(&acc_empty[buffer], ((round >> 1) & 1) ^ 1);
             tcgen05_fence_after_sync();
@@ -259,7 +290,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
         }
         int round = 0;
         for (int unit = blockIdx.x; unit < units; unit += gridDim.x, ++round) {
-            const int tile = unit / splits;
+            int tile, split, of;
+            unit_place(ranges, unit, tile, split, of);
             const int buffer = round & 1;
             // the stream's old values and the next norm's weight of this thread's column: asked for early,
             // needed only by the CTA that finishes the tile
@@ -283,8 +315,8 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
             if (lane == 0) mbar_arrive(&acc_empty[buffer]);      // the MMA warp may overwrite this accumulator
 
             const int n = tile * TILE_N + row;
-            bool finished = splits == 1;                  // does this CTA hold the tile's final sums?
-            if (splits > 1) {
+            bool finished = of == 1;                      // does this CTA hold the tile's final sums?
+            if (of > 1) {
                 // partial sums of this range of K, then: the CTA that finishes the tile last adds all ranges in order
                 constexpr int V = MPAD / 4;                                   // float4s of a padded row
                 constexpr int RANGES_AT_ONCE = MPAD == 16 ? 4 : (MPAD == 32 ? 2 : 1);
@@ -297,23 +329,23 @@ __global__ void __launch_bounds__(THREADS, 1) gemm_small_m_kernel(
                 epilogue_sync();
                 if (epi_thread == 0) {
                     const int arrived = atomicAdd(&counters[tile], 1);
-                    is_last = arrived == splits - 1;
+                    is_last = arrived == of - 1;
                     if (is_last) counters[tile] = 0;           // ready for the next launch
                 }
                 epilogue_sync();
                 finished = is_last;
                 if (finished) {
                     __threadfence();
-                    const float4* first = reinterpret_cast<const float4*>(partials) + ((size_t)tile * splits * TILE_N + row) * m4;
+                    const float4* first = reinterpret_cast<const float4*>(partials) + ((size_t)(unit - split) * TILE_N + row) * m4;
 #pragma unroll
                     for (int m = 0; m < MPAD; ++m) acc[m] = 0.0f;
-                    for (int s0 = 0; s0 < splits; s0 += RANGES_AT_ONCE) {
+                    for (int s0 = 0; s0 < of; s0 += RANGES_AT_ONCE) {
                         float4 v[RANGES_AT_ONCE][V];                      // all loads of a pass are in flight together
 #pragma unroll
                         for (int u = 0; u < RANGES_AT_ONCE; ++u)
 #pragma unroll
                             for (int j = 0; j < V; ++j)
-                                v[u][j] = (s0 + u < splits && j < m4) ? __ldcg(first + (size_t)(s0 + u) * TILE_N * m4 + j)
+                                v[u][j] = (s0 + u < of && j < m4) ? __ldcg(first + (size_t)(s0 + u) * TILE_N * m4 + j)
                                                                       : make_float4(0.0f, 0.0f, 0.0f, 0.0f);
 #pragma unroll
                         for (int u = 0; u < RANGES_AT_ONCE; ++u)
@@ -484,12 +516,31 @@ MRS_EXPORT int mrs_gemm_tc_splits(int N, int K, int sms) {
         const long long cost = rounds * ((k_blocks + s - 1) / s + 4 + (s > 1 ? 8 : 0));
         if (best_cost < 0 || cost < best_cost) best = s, best_cost = cost;
     }
+    // A last round of units that fills the GPU partly (after at least one full round): its tiles take as many ranges
+    // as fill it, and the round is that much shorter.  The gate/up product of the 8B shape (192 tiles, 2 ranges: 2.6
+    // rounds) gives its last 44 tiles 3 ranges; the head product (1,187 tiles, 8.02 rounds) its last 3 tiles 16.
+    const long long units = (long long)n_tiles * best;
+    const int rest_units = (int)(units % sms);
+    if (units > sms && rest_units > 0 && rest_units % best == 0 && n_tiles < (1 << 15)) {
+        const int rest_tiles = rest_units / best;
+        int more = sms / rest_tiles;
+        more = more > limit ? limit : more;
+        if (more > best) return best | more << 8 | (n_tiles - rest_tiles) << 16;
+    }
     return best;
 }
 
 // Floats of `partials` and ints of `counters` (zeroed once by the caller) that a product needs.
 MRS_EXPORT long long mrs_gemm_tc_partial_floats(int M, int N, int splits) {
-    return splits <= 1 ? 0 : (long long)((N + TILE_N - 1) / TILE_N) * splits * TILE_N * ((M + 3) / 4 * 4);
+    const int n_tiles = (N + TILE_N - 1) / TILE_N;
+    const Ranges r = ranges_of(splits, n_tiles);
+    return r.first <= 1 && r.rest <= 1 ? 0 : (long long)units_of(r, n_tiles) * TILE_N * ((M + 3) / 4 * 4);
+}
+// Whether a count of ranges (or a plan of two counts, as mrs_gemm_tc_splits gives it) suits K.
+static bool ranges_fit(int splits, int N, int K) {
+    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
+    const Ranges r = ranges_of(splits, (N + TILE_N - 1) / TILE_N);
+    return splits > 0 && r.first >= 1 && r.first <= k_blocks && r.rest <= k_blocks && r.tiles_first >= 0;
 }
 MRS_EXPORT int mrs_gemm_tc_counters(int N) { return (N + TILE_N - 1) / TILE_N; }
 
@@ -508,10 +559,9 @@ MRS_EXPORT int mrs_gemm_tc_small_m(const void* w_map, const void* x_map, void* o
     if (link_in) link = *reinterpret_cast<const NormLink*>(link_in);
     if (link.in_square_sums && (link.in_parts <= 0 || link.in_stride < M)) return MRS_BAD_ARGUMENT;
     if (link.stream && (gated || out_is_f32 || mpad > 32 || !link.next_weight || !link.out_square_sums)) return MRS_BAD_ARGUMENT;
-    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
-    if (K <= 0 || K % 8 || M > mpad || splits < 1 || splits > k_blocks || ctas < 1) return MRS_BAD_ARGUMENT;
+    if (K <= 0 || K % 8 || M > mpad || !ranges_fit(splits, N, K) || ctas < 1) return MRS_BAD_ARGUMENT;
     if (splits > 1 && (!partials || !counters)) return MRS_BAD_ARGUMENT;
-    const int units = ((N + TILE_N - 1) / TILE_N) * splits;
+    const int units = units_of(ranges_of(splits, (N + TILE_N - 1) / TILE_N), (N + TILE_N - 1) / TILE_N);
     if (ctas > units) ctas = units;
     const CUtensorMap* wm = reinterpret_cast<const CUtensorMap*>(w_map);
     const CUtensorMap* xm = reinterpret_cast<const CUtensorMap*>(x_map);
@@ -555,12 +605,11 @@ MRS_EXPORT int mrs_gemm_tc_qkv_heads(const void* w_map, const void* x_map, void*
     link.stream = nullptr;
     if (link.in_square_sums && (link.in_parts <= 0 || link.in_stride < M)) return MRS_BAD_ARGUMENT;
     const int N = (nq + 2 * nkv) * TILE_N;
-    const int k_blocks = (K + BLOCK_K - 1) / BLOCK_K;
-    if (K <= 0 || K % 8 || M > mpad || mpad > 32 || splits < 1 || splits > k_blocks || ctas < 1 || nq <= 0 || nkv <= 0 ||
+    if (K <= 0 || K % 8 || M > mpad || mpad > 32 || !ranges_fit(splits, N, K) || ctas < 1 || nq <= 0 || nkv <= 0 ||
         page_size <= 0 || !q_out || !positions || (slots && (!k_cache || !v_cache)))
         return MRS_BAD_ARGUMENT;
     if (splits > 1 && (!partials || !counters)) return MRS_BAD_ARGUMENT;
-    const int units = (N / TILE_N) * splits;
+    const int units = units_of(ranges_of(splits, N / TILE_N), N / TILE_N);
     if (ctas > units) ctas = units;
     HeadEpilogue heads{(bf16*)q_out, (bf16*)k_cache, (bf16*)v_cache, positions, slots, q_norm, k_norm, inv_freq, eps, nq, nkv, page_size};
     const CUtensorMap* wm = reinterpret_cast<const CUtensorMap*>(w_map);

@@ -618,6 +618,47 @@ def test_gemm_tc_adds_to_the_stream_and_prepares_the_next_norm(m, n, k):
     assert ((got - exact).abs() / exact).max().item() < 1e-5, "sums of squares"
 
 
+@pytest.mark.parametrize("m", [1, 8, 16, 30])
+def test_gemm_tc_more_ranges_for_the_tiles_of_the_last_round(m):
+    """A plan of two counts of ranges (the first tiles 2, the tiles behind them 4 or 3), as the library plans a last
+    round of units that would fill the GPU partly: plain, gated and adding to the stream, all equal to the same
+    product with one count; and the plans of the shapes it was made for."""
+    lib = kernels.gemm_tc_library()
+    assert lib.mrs_gemm_tc_splits(24576, 4096, 148) == 2 | 3 << 8 | 148 << 16           # gate/up of the 8B shape: 44 tiles in the last round
+    assert lib.mrs_gemm_tc_splits(151936, 4096, 148) == 1 | 16 << 8 | 1184 << 16        # the head: 3 tiles
+    assert lib.mrs_gemm_tc_splits(4096, 4096, 148) == 4 and lib.mrs_gemm_tc_splits(6144, 4096, 148) == 3
+    n, k = 20 * 128 + 72, 1024
+    g = torch.Generator().manual_seed(m)
+    x = torch.randn(m, k, generator=g).to(torch.bfloat16).to(DEV)
+    w = (torch.randn(n, k, generator=g) / k ** 0.5).to(torch.bfloat16).to(DEV)
+    want = x.double().cpu() @ w.double().cpu().T
+    for plan in (2 | 4 << 8 | 12 << 16, 1 | 3 << 8 | 20 << 16, 3 | 2 << 8 | 1 << 16):
+        out = torch.full((m, n), float("nan"), dtype=torch.float32, device=DEV)
+        kernels.gemm_tc(x, w, out, splits=plan)
+        close(out, want, torch.float32, f"plan {plan:#x}")
+        stream = (3 * torch.randn(m, n, generator=g)).to(DEV)
+        before = stream.clone()
+        folded = torch.full((m, n), float("nan"), dtype=torch.bfloat16, device=DEV)
+        sums = kernels.gemm_tc(x, w, folded, splits=plan, residual=(stream, torch.ones(n, device=DEV)))
+        error = (stream.double().cpu() - before.double().cpu() - want).abs()
+        assert (error <= 2.0 ** -8 * want.abs() + 1e-5).all(), f"stream with plan {plan:#x}: {error.max().item():.3e}"
+        exact = (stream.double() ** 2).sum(1).cpu()
+        assert ((sums[:, :m].sum(0).cpu().double() - exact).abs() / exact).max().item() < 1e-5
+    inner = 20 * 64
+    mixed = (torch.randn(2 * inner, k, generator=g) / k ** 0.5 * 2).to(torch.bfloat16).to(DEV)
+    outs = []
+    for plan in (2 | 4 << 8 | 12 << 16, 2):
+        out = torch.full((m, inner), float("nan"), dtype=torch.bfloat16, device=DEV)
+        kernels.gemm_tc(x, mixed, out, gated=True, splits=plan)
+        outs.append(out)
+    both = x.double().cpu() @ mixed.double().cpu().T
+    gd, ud = both.view(m, -1, 2, 64)[:, :, 0].reshape(m, inner), both.view(m, -1, 2, 64)[:, :, 1].reshape(m, inner)
+    close(outs[0], gd / (1 + torch.exp(-gd)) * ud, torch.bfloat16, "gated with two counts of ranges")
+    assert torch.equal(outs[0][:, :12 * 64], outs[1][:, :12 * 64])      # the tiles with 2 ranges: the same bits either way
+    torch.cuda.synchronize()
+    kernels.check_device_errors()
+
+
 @pytest.mark.parametrize("m,n,k,out_dtype", [(1, 256, 136, torch.float32), (8, 151936 // 8, 4096, torch.float32),
                                             (7, 520, 1024, torch.bfloat16), (40, 384, 512, torch.bfloat16)])
 def test_gemm_tc_finishes_a_norm(m, n, k, out_dtype):
