@@ -179,7 +179,8 @@ def choose_splits(tiles: int, nkv: int, longest_context: int, sms: int, resident
     cluster and merge through distributed shared memory), every share with at least two 64-key blocks, all CTAs
     resident at once (`resident` per SM), at most 8 shares (16 for a single request with a long context); with
     many keys and few requests any count that fills seven eighths of the slots; one share fewer (which then meet
-    through memory) where clusters of 8 or 16 would take nearly all that the GPU holds at once.  `clusters(size)`: how many clusters of that size the GPU holds at once (None: not asked).
+    through memory) where clusters of 8 or 16 would take nearly all that the GPU holds at once.  `clusters(size)`:
+    how many clusters of that size the GPU holds at once (None: not asked).
 
     Measured on a B200 with 8 key/value heads of 128, contexts of 4,096 and 16,384, 1 to 16 requests, the kernel
     alone and in decode steps.  With few keys in all (up to about 75 MB a layer) the kernel is bound by its start and
